@@ -1,0 +1,580 @@
+"""Benchmark of the BatchNorm / Adam / BiasAdd+activation path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the workload over one batch of synthetic input:
+
+  workload resnet50_bn_train_bf16_b256 (N >= 1)
+      FusedBatchNormV3 (training) over ResNet-50's 53 BatchNorm layers, then
+      FusedBatchNormGradV3 over the same layers in reverse order; bf16 NHWC
+      activations at batch 256 per GPU, fp32 statistics.  With N > 1 every
+      layer is a cross-replica BatchNorm: the per-channel sums are all-reduced
+      with NCCL between the statistics pass and the element-wise pass (weak
+      scaling: the per-GPU batch is fixed).
+
+Rank 0 prints ONE JSON line.  `value` is Gelem/s over all GPUs with inputs
+resident in HBM (every layer has its own x and dy, 10.8 GB per GPU, so no input
+is re-read from L2 between launches); `e2e` is the same metric through the
+public op API with pinned host buffers, copies inside the timed region;
+`roofline` describes the dominant kernel, `ops` every op of the path
+(Adam, BiasAdd chains and the single-layer BatchNorm configurations) at N = 1;
+`cpu_baseline` is the CPU oracle timed on this machine's host cores.
+
+`--impl reference` times the CPU restatement of the reference path (the
+reference's own kernels need its vendor toolchain and TensorFlow, neither of
+which can be installed here) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# (count, H, W, C) of ResNet-50's 53 BatchNorm layers at 224x224 input.
+RESNET50_BN = [(1, 112, 112, 64), (6, 56, 56, 64), (4, 56, 56, 256), (8, 28, 28, 128),
+               (5, 28, 28, 512), (12, 14, 14, 256), (7, 14, 14, 1024), (6, 7, 7, 512),
+               (4, 7, 7, 2048)]
+BATCH = 256
+EPS = 1e-3
+WORKLOAD = "resnet50_bn_train_bf16_b256"
+METRIC = "bn_fwd_grad_throughput"
+UNIT = "Gelem/s"
+
+
+def layer_list():
+    out = []
+    for count, h, w, c in RESNET50_BN:
+        out += [(h, w, c)] * count
+    return out
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------ clock sampler --
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [s.strip() for s in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out["sm_mhz"] = float(np.median(sm))
+            out["sm_max_mhz"] = float(max(mx))
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ------------------------------------------------------------------ ours ----
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus %d needs torchrun with %d ranks" % (args.gpus, args.gpus))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import tensorflow_musa_extension_b200 as pkg
+    from tensorflow_musa_extension_b200 import raw_ops
+    from tensorflow_musa_extension_b200.cross_replica import SyncBatchNorm
+
+    pkg.load_plugin()
+    lib = raw_ops._lib()
+    layers = layer_list()
+    st = torch.cuda.current_stream()
+
+    # ---- device-resident inputs: one x and one dy per layer, outputs shared
+    # per shape.  bf16 values drawn once on the device (x ~ N(0,1),
+    # dy ~ N(0, 1e-2)), seed 4 + rank.
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4 + rank)
+    xs, dys, scales, offsets = [], [], [], []
+    out_y, out_dx = {}, {}
+    for (h, w, c) in layers:
+        rows = BATCH * h * w
+        x = torch.empty(rows, c, device=dev, dtype=torch.bfloat16)
+        x.normal_(0, 1, generator=gen)
+        dy = torch.empty(rows, c, device=dev, dtype=torch.bfloat16)
+        dy.normal_(0, 1e-2, generator=gen)
+        xs.append(x)
+        dys.append(dy)
+        scales.append(torch.empty(c, device=dev).uniform_(0.5, 1.5, generator=gen))
+        offsets.append(torch.empty(c, device=dev).normal_(0, 0.1, generator=gen))
+        if (rows, c) not in out_y:
+            out_y[(rows, c)] = torch.empty_like(x)
+            out_dx[(rows, c)] = torch.empty_like(x)
+    n_layers = len(layers)
+    elems_per_pass = sum(x.numel() for x in xs)
+    elems_per_step = 2 * elems_per_pass          # forward + gradient
+    sum_s = sum(x.numel() * 2 for x in xs)       # bytes of all x
+    algo_bytes_step = 5 * sum_s                  # 2*S forward + 3*S gradient
+
+    bns = [SyncBatchNorm(c, eps=EPS, dtype=torch.bfloat16, device=dev,
+                         max_rows=BATCH * h * w, group=(dist.group.WORLD if world > 1 else None))
+           for (h, w, c) in layers]
+
+    def step():
+        for i in range(n_layers):
+            bns[i].forward(xs[i], scales[i], offsets[i], out_y[tuple(xs[i].shape)])
+        for i in reversed(range(n_layers)):
+            bns[i].backward(dys[i], xs[i], scales[i], out_dx[tuple(xs[i].shape)])
+
+    launches_per_step = sum(b.launches_per_step for b in bns)
+
+    # Warm up eagerly, then capture the step in a CUDA graph (the launchers
+    # neither allocate nor synchronise, so a step is a pure launch sequence).
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        try:
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+                with torch.cuda.graph(g, stream=side):
+                    step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = g
+        except Exception as e:  # capture unsupported: time eager launches
+            if rank == 0:
+                print("graph capture failed, timing eager launches: %r" % (e,),
+                      file=sys.stderr)
+            graph = None
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run_step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = world * elems_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: pinned host buffers through the public op API
+    e2e = measure_e2e(torch, dist, raw_ops, layers, world, rank, dev, args)
+
+    result = None
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        result = {
+            "metric": METRIC, "value": round(value, 3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers": n_layers, "batch_per_gpu": BATCH,
+                       "layout": "NHWC", "stats_dtype": "f32",
+                       "elements_per_step_per_gpu": elems_per_step,
+                       "algorithmic_bytes_per_step_per_gpu": algo_bytes_step,
+                       "sync": "nccl all-reduce of 2*C fp32 per layer and pass"
+                               if world > 1 else "none (1 GPU)",
+                       "l2": "every layer has its own x and dy (10.8 GB per GPU), "
+                             "so inputs exceed L2 between reuses",
+                       "launch": "cuda graph replay" if graph is not None else "eager"},
+            "step_algorithmic_gbs_per_gpu": round(algo_bytes_step / (ms_per_step * 1e-3) / 1e9, 1),
+            "step_frac_of_peak": round(algo_bytes_step / (ms_per_step * 1e-3) / 1e9 / peak, 4),
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "e2e": e2e,
+        }
+    if world == 1:
+        ops, roof = measure_ops(torch, lib, raw_ops, dev, args)
+        result["roofline"] = roof
+        result["ops"] = ops
+        result["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_seconds)
+    else:
+        if rank == 0:
+            result["roofline"] = None
+            result["cpu_baseline"] = None
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def measure_e2e(torch, dist, raw_ops, layers, world, rank, dev, args):
+    """The same step through the public ops with HOST buffers: every layer's x
+    and dy start in pinned host memory and y / dx (and the statistics) are read
+    back, all inside the timed region."""
+    shapes = sorted({(BATCH * h * w, c) for (h, w, c) in layers})
+    gen = torch.Generator()
+    gen.manual_seed(40 + rank)
+    host = {}
+    for rows, c in shapes:
+        # One pinned x / dy per shape; values as in the device-resident run.
+        x = torch.empty(rows, c, dtype=torch.bfloat16).normal_(0, 1, generator=gen).pin_memory()
+        dy = torch.empty(rows, c, dtype=torch.bfloat16).normal_(0, 1e-2, generator=gen).pin_memory()
+        host[(rows, c)] = (x, dy)
+    par = {c: (torch.empty(c).uniform_(0.5, 1.5, generator=gen).pin_memory(),
+               torch.empty(c).normal_(0, 0.1, generator=gen).pin_memory())
+           for c in sorted({c for (_, _, c) in layers})}
+    empty = torch.empty(0)
+    from tensorflow_musa_extension_b200 import cross_replica as cr
+    group = dist.group.WORLD if world > 1 else None
+
+    def step():
+        saved = []
+        for (h, w, c) in layers:
+            x, _ = host[(BATCH * h * w, c)]
+            s, o = par[c]
+            if world > 1:
+                out = cr.sync_batch_norm_forward(x, s, o, EPS, group)
+            else:
+                out = raw_ops.FusedBatchNormV3(x, s, o, empty, empty, epsilon=EPS)
+            saved.append((out[3], out[4]))
+        for (h, w, c), (mean, var) in zip(reversed(layers), reversed(saved)):
+            x, dy = host[(BATCH * h * w, c)]
+            s, _ = par[c]
+            if world > 1:
+                cr.sync_batch_norm_backward(dy, x, s, mean, var, EPS, group)
+            else:
+                raw_ops.FusedBatchNormGradV3(dy, x, s, mean, var, None, epsilon=EPS)
+
+    elems = 2 * sum(BATCH * h * w * c for (h, w, c) in layers)
+    h2d = sum(BATCH * h * w * c * 2 for (h, w, c) in layers) * 3  # x (fwd), dy + x (grad)
+    d2h = sum(BATCH * h * w * c * 2 for (h, w, c) in layers) * 2  # y, dx
+    steps = max(1, min(args.steps, args.e2e_steps))
+    step()  # warm up: pinned-pool and allocator growth
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([dt], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    return {"value": round(world * elems * steps / dt / 1e9, 3), "unit": UNIT,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
+            "ms_per_step": round(dt / steps * 1e3, 2),
+            "api": ("raw_ops.FusedBatchNormV3 / FusedBatchNormGradV3" if world == 1 else "cross_replica.sync_batch_norm_forward / _backward") + " on pinned host tensors"}
+
+
+def time_launch(torch, fn, iters, flush=None):
+    """Median device time of fn() in ms (CUDA events on the current stream);
+    `flush` runs before every timed launch, outside the events."""
+    for _ in range(3):
+        if flush is not None:
+            flush()
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b))
+    return float(np.median(times))
+
+
+def measure_ops(torch, lib, raw_ops, dev, args):
+    """Per-op device timings at N = 1 for every configuration of the path, each
+    with its algorithmic bytes, and the roofline entry of the dominant kernel
+    of the headline workload.  L2 is flushed (a 512 MB write) before every
+    timed launch of the configurations whose inputs fit in L2."""
+    peak, peak_kind = measured_peak()
+    st = torch.cuda.current_stream().cuda_stream
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def flush():
+        flush_buf.fill_(1)
+
+    iters = 20
+    ops = {}
+
+    def entry(name, ms, algo_bytes, elems, note):
+        gbs = algo_bytes / (ms * 1e-3) / 1e9
+        ops[name] = {"ms": round(ms, 4), "algorithmic_bytes": algo_bytes,
+                     "achieved_gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                     "gelem_per_s": round(elems / (ms * 1e-3) / 1e9, 2), "note": note}
+
+    # Adam, config 4: fp32 N = 25,557,032 (715.6 MB per step: beyond L2).
+    n = 25_557_032
+    var = torch.randn(n, device=dev) * 0.05
+    m = torch.randn(n, device=dev) * 1e-4
+    v = torch.rand(n, device=dev) * 1e-6
+    g = torch.randn(n, device=dev) * 1e-3
+    alpha = 1e-3 * np.sqrt(1 - 0.999 ** 10) / (1 - 0.9 ** 10)
+    ms = time_launch(torch, lambda: lib.LaunchResourceApplyAdamFloat(
+        var.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), 0.9, 0.999, 1e-7,
+        alpha, n, st), iters)
+    entry("adam_f32_25.6M", ms, 28 * n, n, "inputs exceed L2")
+    del var, m, v, g
+
+    # BiasAdd chains, config 3: fp16 [65536, 1024] (268 MB per launch).
+    x = torch.randn(65536, 1024, device=dev, dtype=torch.float16)
+    b = (torch.randn(1024, device=dev) * 0.1).half()
+    y = torch.empty_like(x)
+    for name, act in (("bias_relu_f16", 1), ("bias_swish_f16", 2)):
+        ms = time_launch(torch, lambda: lib.LaunchBiasAct_F16(
+            x.data_ptr(), b.data_ptr(), y.data_ptr(), 65536, 1024, 1, act, st), iters)
+        entry(name, ms, 4 * x.numel(), x.numel(), "inputs exceed L2")
+    del x, y
+
+    # BatchNorm single layers: config 1 (fp32) and config 2 (fp16, bf16).
+    for name, shape, dt, sfx in (("cfg1_f32", (32 * 56 * 56, 64), torch.float32, "F32"),
+                                 ("cfg2_f16", (256 * 28 * 28, 256), torch.float16, "F16"),
+                                 ("cfg2_bf16", (256 * 28 * 28, 256), torch.bfloat16, "BF16")):
+        rows, c = shape
+        x = (torch.randn(rows, c, device=dev) * 3 + 1).to(dt)
+        dy = (torch.randn(rows, c, device=dev) * 1e-2).to(dt)
+        y = torch.empty_like(x)
+        sc = torch.rand(c, device=dev) + 0.5
+        of = torch.randn(c, device=dev) * 0.1
+        stats = [torch.empty(c, device=dev) for _ in range(6)]
+        need = lib.BnWorkspaceBytes(rows, c, 1)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        fwd = getattr(lib, "LaunchBnFwdTrain_" + sfx)
+        bwd = getattr(lib, "LaunchBnGrad_" + sfx)
+        s_bytes = x.numel() * x.element_size()
+        ms = time_launch(torch, lambda: fwd(
+            x.data_ptr(), sc.data_ptr(), of.data_ptr(), None, None, y.data_ptr(),
+            stats[0].data_ptr(), stats[1].data_ptr(), stats[2].data_ptr(),
+            stats[3].data_ptr(), rows, c, 1, EPS, 1.0, ws.data_ptr(), need, st),
+            iters, flush)
+        entry("bn_fwd_" + name, ms, 2 * s_bytes, x.numel(), "L2 flushed before each launch")
+        ms = time_launch(torch, lambda: bwd(
+            dy.data_ptr(), x.data_ptr(), sc.data_ptr(), stats[2].data_ptr(),
+            stats[3].data_ptr(), y.data_ptr(), stats[4].data_ptr(), stats[5].data_ptr(),
+            rows, c, 1, EPS, True, ws.data_ptr(), need, st), iters, flush)
+        entry("bn_grad_" + name, ms, 3 * s_bytes, x.numel(), "L2 flushed before each launch")
+        del x, dy, y
+
+    # Dominant kernel of the headline workload: the gradient element-wise pass
+    # (reads dy and x, writes dx: 3 * S per launch), timed alone on the largest
+    # ResNet-50 layer, [256, 56, 56, 256] bf16 (S = 411 MB).
+    rows, c = BATCH * 56 * 56, 256
+    x = torch.randn(rows, c, device=dev).to(torch.bfloat16)
+    dy = (torch.randn(rows, c, device=dev) * 1e-2).to(torch.bfloat16)
+    dx = torch.empty_like(x)
+    sc = torch.rand(c, device=dev) + 0.5
+    mean = torch.zeros(c, device=dev)
+    varc = torch.ones(c, device=dev)
+    sums = torch.zeros(2 * c, device=dev)
+    ds, do = torch.empty(c, device=dev), torch.empty(c, device=dev)
+    s_bytes = x.numel() * 2
+    ms = time_launch(torch, lambda: lib.LaunchBnGradApplyFromSums(
+        2, dy.data_ptr(), x.data_ptr(), sc.data_ptr(), mean.data_ptr(), varc.data_ptr(),
+        sums.data_ptr(), float(rows), dx.data_ptr(), None, None, rows, c, 1, EPS, st), iters)
+    achieved = 3 * s_bytes / (ms * 1e-3) / 1e9
+    roof = {"bound": "hbm", "kernel": "BnApplyLastKernel<bf16, grad>",
+            "case": "[256,56,56,256] bf16, 3*S = %d bytes per launch" % (3 * s_bytes),
+            "achieved": round(achieved, 1), "peak": peak, "peak_kind": peak_kind,
+            "unit": "GB/s", "frac": round(achieved / peak, 4), "ms": round(ms, 4),
+            "traffic": None}
+    tr = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tr):
+        try:
+            roof["traffic"] = json.load(open(tr)).get("bn_grad_apply_bf16_256x56x56x256")
+        except Exception:
+            pass
+    return ops, roof
+
+
+# ------------------------------------------------------------- CPU arms -----
+
+def _bf16_normal(rng, shape, std):
+    import ml_dtypes
+    return (rng.standard_normal(shape, dtype=np.float32) * std).astype(ml_dtypes.bfloat16)
+
+
+def cpu_workload(batch, seed=4):
+    from oracle import c_ref
+    rng = np.random.default_rng(seed)
+    data = {}
+    for (_, h, w, c) in RESNET50_BN:
+        rows = batch * h * w
+        data[(h, w, c)] = (_bf16_normal(rng, (rows, c), 1.0), _bf16_normal(rng, (rows, c), 1e-2),
+                           rng.uniform(0.5, 1.5, c).astype(np.float32),
+                           rng.normal(0, 0.1, c).astype(np.float32))
+    layers = layer_list()
+
+    def step():
+        saved = []
+        for key in layers:
+            x, _, s, o = data[key]
+            out = c_ref.bn_fwd_train(x, s, o, EPS)
+            saved.append((out[3], out[4]))
+        for key, (mean, var) in zip(reversed(layers), reversed(saved)):
+            x, dy, s, _ = data[key]
+            c_ref.bn_grad(dy, x, s, mean, var, EPS)
+
+    elems = 2 * sum(batch * h * w * c for (h, w, c) in layers)
+    return step, elems, c_ref.num_threads()
+
+
+def cpu_baseline(budget_s=15.0):
+    """The CPU oracle (C, all host threads) on a bounded sample of the workload:
+    the same 53 layers forward + gradient at batch 8 per layer."""
+    batch = 8
+    step, elems, cores = cpu_workload(batch)
+    step()
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        step()
+        n += 1
+        if time.perf_counter() - t0 > budget_s or n >= 20:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": round(elems * n / dt / 1e9, 4), "unit": UNIT, "cores": cores,
+            "kind": "port",
+            "sample": "same 53 layers fwd+grad at batch %d instead of %d, %d passes" % (batch, BATCH, n)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    batch = 8
+    step, elems, cores = cpu_workload(batch)
+    for _ in range(max(1, min(args.warmup, 3))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    ms = dt / args.steps * 1e3
+    val = round(elems * args.steps / dt / 1e9, 4)
+    sample = "same 53 layers fwd+grad at batch %d per layer instead of %d" % (batch, BATCH)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": 53, "batch_per_gpu": BATCH,
+                   "layout": "NHWC", "stats_dtype": "f32"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "CPU restatement of the reference path (oracle/cpu_ref.c): the reference's "
+                "own kernels need the MUSA toolchain, muDNN and TensorFlow 2.6.1, none of "
+                "which can be installed here",
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches")
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

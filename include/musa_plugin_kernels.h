@@ -1,0 +1,279 @@
+/* C ABI of libmusa_plugin_kernels.so: the device-code launcher layer of the
+ * `tensorflow_musa` plugin, rebuilt as hand-written CUDA for NVIDIA B200
+ * (sm_100a).
+ *
+ * The reference plugin keeps its device code behind `extern "C" Launch*()`
+ * functions that the C++ OpKernels call from `Compute()`; this header declares
+ * the same layer for the memory-bound training path (FusedBatchNorm forward and
+ * gradient, ApplyAdam, BiasAdd + activation).  Each declaration cites the
+ * reference interface it replaces, as `path:line` inside the reference project.
+ *
+ * Conventions shared by every launcher (they are the reference's):
+ *   - pointers are borrowed DEVICE pointers, valid until the stream work ends;
+ *   - host scalars are passed by value; nothing is read back from the device;
+ *   - a launcher enqueues work on `stream` and returns without synchronising;
+ *   - a launcher allocates nothing and keeps no global state; scratch memory is
+ *     passed in by the caller (TF: `OpKernelContext::allocate_temp`) after a
+ *     `*WorkspaceBytes()` query;
+ *   - a launcher is re-entrant (TF calls Compute() from several threads);
+ *   - empty inputs (`n <= 0`) return at once.
+ * The Adam launchers keep the reference's `void` return (the caller polls
+ * `cudaGetLastError()`, as musa_applyadam_op.cc:258-261 does).  The launchers
+ * that are new here return an int: 0 on success, a positive `cudaError_t` from
+ * the launch, or a negative MUSA_KERNELS_E* code for an argument the launcher
+ * refuses.  No launcher falls back to the host.
+ */
+#ifndef MUSA_PLUGIN_KERNELS_H_
+#define MUSA_PLUGIN_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque CUDA stream handle (`cudaStream_t`); declared here so that a C caller
+ * does not need the CUDA headers.  The reference type is `musaStream_t`. */
+#ifndef __DRIVER_TYPES_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+#define MUSA_KERNELS_OK 0
+#define MUSA_KERNELS_EINVAL (-1)      /* null pointer / negative size          */
+#define MUSA_KERNELS_EWORKSPACE (-2)  /* workspace missing or too small        */
+#define MUSA_KERNELS_EUNSUPPORTED (-3)/* dtype / activation code not known     */
+#define MUSA_KERNELS_ETOOLARGE (-4)   /* size beyond what the entry point holds */
+
+/* Library identity; lets a loader check that it found the sm_100a build. */
+const char* MusaKernelsVersion(void);
+/* Compute capability the device code was compiled for (100 => sm_100a). */
+int MusaKernelsTargetArch(void);
+
+/* ------------------------------------------------------------------ Adam -- */
+
+/* fp32 var/m/v/grad, one streaming pass: m = b1*m + (1-b1)*g;
+ * v = b2*v + (1-b2)*g*g; var -= alpha*m/(sqrt(v)+eps), `alpha` being the
+ * bias-corrected learning rate that the op computes on the host in fp64.
+ * Replaces tensorflow::musa::LaunchResourceApplyAdamFloat
+ * (musa_ext/kernels/training/musa_apply_sparse_adam_kernel.mu:159-169; declared
+ * for the op at musa_ext/kernels/training/musa_applyadam_op.cc:34-37; the
+ * reference gives this one C++ linkage, the argument list is unchanged). */
+void LaunchResourceApplyAdamFloat(float* var, float* m, float* v,
+                                  const float* grad, float beta1, float beta2,
+                                  float epsilon, float alpha, int64_t total,
+                                  cudaStream_t stream);
+
+/* var/m/v/grad all bf16 (or all fp16): widen, fp32 arithmetic, round to
+ * nearest even on store.  `use_nesterov` swaps the numerator for
+ * b1*m + (1-b1)*g.  Replaces LaunchApplyAdamSameType_{BFloat16,Half}
+ * (musa_ext/kernels/training/musa_applyadam_bf16_kernel.mu:133-156; declared
+ * for the op at musa_ext/kernels/training/musa_applyadam_op.cc:20-29). */
+void LaunchApplyAdamSameType_BFloat16(void* var, void* m, void* v,
+                                      const void* grad, float lr_t, float beta1,
+                                      float beta2, float epsilon, int64_t n,
+                                      bool use_nesterov, cudaStream_t stream);
+void LaunchApplyAdamSameType_Half(void* var, void* m, void* v, const void* grad,
+                                  float lr_t, float beta1, float beta2,
+                                  float epsilon, int64_t n, bool use_nesterov,
+                                  cudaStream_t stream);
+
+/* fp32 var/m/v with a grad of fp32, fp16 or bf16 (op
+ * MusaResourceApplyAdamMixed).  Replaces LaunchApplyAdamMixed_{Float,Half,
+ * BFloat16} (musa_ext/kernels/training/musa_applyadam_mixed_kernel.mu:108-137;
+ * declared at musa_ext/kernels/training/musa_applyadam_mixed_op.cc:49-62). */
+void LaunchApplyAdamMixed_Float(float* var, float* m, float* v,
+                                const void* grad, float lr_t, float beta1,
+                                float beta2, float epsilon, int64_t n,
+                                bool use_nesterov, cudaStream_t stream);
+void LaunchApplyAdamMixed_Half(float* var, float* m, float* v, const void* grad,
+                               float lr_t, float beta1, float beta2,
+                               float epsilon, int64_t n, bool use_nesterov,
+                               cudaStream_t stream);
+void LaunchApplyAdamMixed_BFloat16(float* var, float* m, float* v,
+                                   const void* grad, float lr_t, float beta1,
+                                   float beta2, float epsilon, int64_t n,
+                                   bool use_nesterov, cudaStream_t stream);
+
+/* ------------------------------------------------ BiasAdd + activation -- */
+
+/* Activation codes of LaunchBiasAct_*. */
+#define MUSA_ACT_IDENTITY 0 /* y = x + b                  (BiasAdd)           */
+#define MUSA_ACT_RELU 1     /* y = max(x + b, 0)          (Relu(BiasAdd))     */
+#define MUSA_ACT_SWISH 2    /* y = x * sigmoid(x + b)     (Mul(x,Sigmoid(..)))*/
+#define MUSA_ACT_SIGMOID 3  /* y = sigmoid(x + b)         (Sigmoid(BiasAdd))  */
+
+/* One read of x and one write of y for the whole chain.  x and y are viewed
+ * as [outer, channels, inner] with the bias indexed by the middle axis:
+ * NHWC / 2-D inputs pass inner = 1, NCHW passes outer = N, inner = H*W.
+ * `bias == NULL` applies the activation alone (the Relu and Sigmoid ops).
+ * 16-bit types compute in fp32 and round once on store.
+ * Replaces the muDNN Binary ADD with a stride-0 bias view
+ * (musa_ext/kernels/nn/musa_biasadd_op.cc:46-57), the muDNN Unary RELU and
+ * SIGMOID passes (musa_ext/kernels/nn/musa_relu_op.cc:33-36,
+ * musa_ext/kernels/nn/musa_sigmoid_op.cc:29-33) and the unused
+ * LaunchBiasAddReluKernel<T> (musa_ext/kernels/fusion/musa_linear_relu_kernel.mu:
+ * 69-77). */
+int LaunchBiasAct_F32(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream);
+int LaunchBiasAct_F16(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream);
+int LaunchBiasAct_BF16(const void* x, const void* bias, void* y, int64_t outer,
+                       int64_t channels, int64_t inner, int act,
+                       cudaStream_t stream);
+/* BiasAdd for the other registered dtypes (musa_ext/kernels/nn/musa_biasadd_op.cc:75-80:
+ * double, int32, int64); identity and relu only. */
+int LaunchBiasAct_F64(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream);
+int LaunchBiasAct_I32(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream);
+int LaunchBiasAct_I64(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream);
+
+/* ------------------------------------------------------ FusedBatchNorm -- */
+
+/* Tensor geometry: x, y, dy, dx are [outer, channels, inner], the statistics
+ * run over outer*inner values per channel.  NHWC: outer = N*H*W, inner = 1.
+ * NCHW: outer = N, inner = H*W.  scale/offset/mean/variance are fp32
+ * [channels] for every x dtype. */
+
+/* Bytes of scratch that the BatchNorm launchers below need for this geometry
+ * (the per-CTA partial sums of the two-level reduction).  The same figure
+ * serves forward and gradient.  16-byte aligned memory is expected. */
+size_t BnWorkspaceBytes(int64_t outer, int64_t channels, int64_t inner);
+
+/* Training-mode forward.  Outputs follow TensorFlow's CPU kernel:
+ *   y = (x - mean) * rsqrt(var + eps) * scale + offset, mean/var of the batch;
+ *   batch_mean = mean, batch_var = var * R/(R-1) (Bessel; R = outer*inner, not
+ *   applied when R == 1), blended with est_mean/est_var by exp_avg_factor when
+ *   that is not 1 (est_* may be NULL when it is 1);
+ *   saved_mean = mean, saved_var = population variance.
+ * Replaces muDNN BatchNorm::RunComposite plus the copies and the Bessel
+ * fix-up after it (musa_ext/kernels/nn/musa_fused_batchnorm_op.cc:106-171). */
+int LaunchBnFwdTrain_F32(const void* x, const float* scale, const float* offset,
+                         const float* est_mean, const float* est_var, void* y,
+                         float* batch_mean, float* batch_var, float* saved_mean,
+                         float* saved_var, int64_t outer, int64_t channels,
+                         int64_t inner, float epsilon, float exp_avg_factor,
+                         void* workspace, size_t workspace_bytes,
+                         cudaStream_t stream);
+int LaunchBnFwdTrain_F16(const void* x, const float* scale, const float* offset,
+                         const float* est_mean, const float* est_var, void* y,
+                         float* batch_mean, float* batch_var, float* saved_mean,
+                         float* saved_var, int64_t outer, int64_t channels,
+                         int64_t inner, float epsilon, float exp_avg_factor,
+                         void* workspace, size_t workspace_bytes,
+                         cudaStream_t stream);
+int LaunchBnFwdTrain_BF16(const void* x, const float* scale,
+                          const float* offset, const float* est_mean,
+                          const float* est_var, void* y, float* batch_mean,
+                          float* batch_var, float* saved_mean, float* saved_var,
+                          int64_t outer, int64_t channels, int64_t inner,
+                          float epsilon, float exp_avg_factor, void* workspace,
+                          size_t workspace_bytes, cudaStream_t stream);
+
+/* Inference-mode forward: y from the given mean/variance, one pass.
+ * Replaces muDNN BatchNorm::RunPure
+ * (musa_ext/kernels/nn/musa_fused_batchnorm_op.cc:172-178). */
+int LaunchBnFwdInfer_F32(const void* x, const float* scale, const float* offset,
+                         const float* est_mean, const float* est_var, void* y,
+                         int64_t outer, int64_t channels, int64_t inner,
+                         float epsilon, cudaStream_t stream);
+int LaunchBnFwdInfer_F16(const void* x, const float* scale, const float* offset,
+                         const float* est_mean, const float* est_var, void* y,
+                         int64_t outer, int64_t channels, int64_t inner,
+                         float epsilon, cudaStream_t stream);
+int LaunchBnFwdInfer_BF16(const void* x, const float* scale,
+                          const float* offset, const float* est_mean,
+                          const float* est_var, void* y, int64_t outer,
+                          int64_t channels, int64_t inner, float epsilon,
+                          cudaStream_t stream);
+
+/* Gradient.  `mean` and `variance` are reserve_space_1/2 of the forward op:
+ * the batch mean and the POPULATION variance (not an inverse std-dev).
+ *   doffset = sum(dy); dscale = sum(dy * (x - mean)) * rsqrt(var + eps);
+ *   training : dx = scale*inv * (dy - doffset/R - (x-mean)*inv*dscale/R)
+ *   inference: dx = dy * scale * inv.
+ * Every output element is written, so stale output memory cannot leak.
+ * Replaces LaunchVarianceToInvStd plus muDNN BatchNorm::RunBwd and the memsets
+ * before them (musa_ext/kernels/nn/musa_fused_batchnorm_op.cc:233-291). */
+int LaunchBnGrad_F32(const void* dy, const void* x, const float* scale,
+                     const float* mean, const float* variance, void* dx,
+                     float* dscale, float* doffset, int64_t outer,
+                     int64_t channels, int64_t inner, float epsilon,
+                     bool is_training, void* workspace, size_t workspace_bytes,
+                     cudaStream_t stream);
+int LaunchBnGrad_F16(const void* dy, const void* x, const float* scale,
+                     const float* mean, const float* variance, void* dx,
+                     float* dscale, float* doffset, int64_t outer,
+                     int64_t channels, int64_t inner, float epsilon,
+                     bool is_training, void* workspace, size_t workspace_bytes,
+                     cudaStream_t stream);
+int LaunchBnGrad_BF16(const void* dy, const void* x, const float* scale,
+                      const float* mean, const float* variance, void* dx,
+                      float* dscale, float* doffset, int64_t outer,
+                      int64_t channels, int64_t inner, float epsilon,
+                      bool is_training, void* workspace, size_t workspace_bytes,
+                      cudaStream_t stream);
+
+/* The two BatchNorm fix-up launchers of the reference, kept for callers that
+ * still hold muDNN-convention statistics: data[i] *= factor, and
+ * inv_std[i] = rsqrt(variance[i] + epsilon).  Replace LaunchBesselCorrection
+ * and LaunchVarianceToInvStd
+ * (musa_ext/kernels/nn/musa_fused_batchnorm_kernel.mu:38-56). */
+void LaunchBesselCorrection(float* data, float factor, int count,
+                            cudaStream_t stream);
+void LaunchVarianceToInvStd(const float* variance, float* inv_std,
+                            float epsilon, int count, cudaStream_t stream);
+
+/* ---- Cross-replica (SyncBN) halves: the same kernels, split where the
+ * all-reduce of the per-channel sums goes.  `dtype`: 0 fp32, 1 fp16, 2 bf16.
+ * The reference has no collective backend
+ * (musa_ext/mu/collective/musa_collective_runtime.cc:58-63 returns
+ * Unimplemented); these are what a cross-replica BatchNorm built on the same
+ * op pair calls either side of an NCCL all-reduce. */
+#define MUSA_DT_F32 0
+#define MUSA_DT_F16 1
+#define MUSA_DT_BF16 2
+
+/* sums[0:C] = sum(x), sums[C:2C] = sum(x*x) over this replica's rows. */
+int LaunchBnStatsSums(int dtype, const void* x, float* sums, int64_t outer,
+                      int64_t channels, int64_t inner, void* workspace,
+                      size_t workspace_bytes, cudaStream_t stream);
+/* From all-reduced sums over `total_count` values per channel to the four
+ * statistic outputs of the forward op. */
+int LaunchBnFinalizeFromSums(const float* sums, double total_count,
+                             const float* est_mean, const float* est_var,
+                             float* batch_mean, float* batch_var,
+                             float* saved_mean, float* saved_var,
+                             int64_t channels, float exp_avg_factor,
+                             cudaStream_t stream);
+/* y = (x - mean) * rsqrt(var + eps) * scale + offset (same as inference). */
+int LaunchBnApply(int dtype, const void* x, const float* scale,
+                  const float* offset, const float* mean, const float* variance,
+                  void* y, int64_t outer, int64_t channels, int64_t inner,
+                  float epsilon, cudaStream_t stream);
+/* sums[0:C] = sum(dy), sums[C:2C] = sum(dy * (x - mean)) over local rows. */
+int LaunchBnGradStatsSums(int dtype, const void* dy, const void* x,
+                          const float* mean, float* sums, int64_t outer,
+                          int64_t channels, int64_t inner, void* workspace,
+                          size_t workspace_bytes, cudaStream_t stream);
+/* dx, dscale, doffset from all-reduced sums over `total_count` values. */
+int LaunchBnGradApplyFromSums(int dtype, const void* dy, const void* x,
+                              const float* scale, const float* mean,
+                              const float* variance, const float* sums,
+                              double total_count, void* dx, float* dscale,
+                              float* doffset, int64_t outer, int64_t channels,
+                              int64_t inner, float epsilon,
+                              cudaStream_t stream);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* MUSA_PLUGIN_KERNELS_H_ */

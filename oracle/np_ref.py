@@ -1,0 +1,241 @@
+"""CPU oracle (NumPy) for the BatchNorm / ApplyAdam / BiasAdd+activation path.
+
+TEST INFRASTRUCTURE ONLY.  This module restates, on the CPU, the results that
+TensorFlow's CPU kernels give for the ops of this path, following the
+conventions that the reference plugin documents and tests against.  It is
+imported by the tests, by the smoke check and by the CPU-baseline leg of the
+benchmark; the product (the CUDA library and its Python front end) never
+imports it.
+
+Pinning status.  The stated target oracle is TensorFlow 2.6.1's CPU kernels.
+TensorFlow is not installable next to this code (no wheel for the interpreter,
+no network), and the reference's own arithmetic for BatchNorm / BiasAdd / Relu /
+Sigmoid sits in a closed vendor library, so:
+  * ApplyAdam is pinned to the reference's own NumPy restatement of the update
+    rule (test/ops/musa_resource_sparse_apply_adam_op_test.py:35-69), run from
+    the reference file by tests/golden/make_golden.py, and to the in-repo
+    device kernels it mirrors line by line;
+  * Relu / Sigmoid / BiasAdd are pinned to the literal cases of the reference
+    tests (test/ops/relu_op_test.py:58-96, test/ops/sigmoid_op_test.py:58-93,
+    test/ops/biasadd_op_test.py:74-116) whose answers are closed-form;
+  * FusedBatchNorm forward/gradient: PARITY UNPINNED against TensorFlow itself.
+    The restatement follows the output conventions the reference documents
+    (musa_ext/kernels/nn/musa_fused_batchnorm_op.cc:126-170, 265-277) and is
+    cross-checked against an independent implementation (PyTorch's CPU
+    batch_norm and its autograd) in tests/golden/make_golden.py.
+
+Every function accumulates in float64 and rounds once to the output dtype,
+except where the op's own arithmetic type matters (Adam: float32 throughout;
+16-bit element-wise chains: one rounding per un-fused op).
+"""
+import numpy as np
+
+try:  # bfloat16 as a NumPy dtype
+    import ml_dtypes
+
+    bfloat16 = np.dtype(ml_dtypes.bfloat16)
+except Exception:  # pragma: no cover - ml_dtypes ships with the image
+    bfloat16 = None
+
+
+# --------------------------------------------------------------------------
+# FusedBatchNorm{,V2,V3}
+# --------------------------------------------------------------------------
+
+def _channel_axis(ndim, data_format):
+    if data_format == "NHWC":
+        return ndim - 1
+    if data_format == "NCHW":
+        return 1
+    raise ValueError("data_format must be NHWC or NCHW, got %r" % (data_format,))
+
+
+def fused_batch_norm(x, scale, offset, mean=None, variance=None, epsilon=1e-3,
+                     exponential_avg_factor=1.0, data_format="NHWC",
+                     is_training=True):
+    """FusedBatchNormV3 forward.
+
+    Returns (y, batch_mean, batch_var, reserve_space_1, reserve_space_2,
+    reserve_space_3) with the conventions of
+    musa_ext/kernels/nn/musa_fused_batchnorm_op.cc:
+      :141-150  batch_var is the Bessel-corrected (1/(R-1)) variance,
+      :158-170  reserve_space_2 is the population (1/R) variance and the
+                correction is skipped when there is one value per channel,
+      :59-62    reserve_space_3 is a zero-filled 0-D tensor,
+      :173-178  inference uses the given mean/variance.
+    With exponential_avg_factor != 1 the first two statistics outputs are
+    blended with the incoming running values, as TensorFlow's CPU kernel does.
+    """
+    x = np.asarray(x)
+    out_dtype = x.dtype
+    ax = _channel_axis(x.ndim, data_format)
+    red = tuple(i for i in range(x.ndim) if i != ax)
+    shape = [1] * x.ndim
+    shape[ax] = x.shape[ax]
+    x64 = x.astype(np.float64)
+    scale64 = np.asarray(scale, np.float64).reshape(shape)
+    offset64 = np.asarray(offset, np.float64).reshape(shape)
+    eps = float(np.float32(epsilon))
+    if is_training:
+        count = x64.size // max(x.shape[ax], 1)
+        mu = x64.mean(axis=red)
+        var = ((x64 - mu.reshape(shape)) ** 2).mean(axis=red)
+        unbiased = var * (count / (count - 1.0)) if count > 1 else var
+        f = float(np.float32(exponential_avg_factor))
+        if f == 1.0:
+            bm, bv = mu, unbiased
+        else:
+            bm = (1.0 - f) * np.asarray(mean, np.float64) + f * mu
+            bv = (1.0 - f) * np.asarray(variance, np.float64) + f * unbiased
+        # The normalisation uses the float32 statistics that the op emits.
+        mu32 = mu.astype(np.float32).astype(np.float64)
+        var32 = var.astype(np.float32).astype(np.float64)
+        inv = 1.0 / np.sqrt(var32 + eps)
+        y = (x64 - mu32.reshape(shape)) * (inv.reshape(shape) * scale64) + offset64
+        return (y.astype(out_dtype), bm.astype(np.float32), bv.astype(np.float32),
+                mu.astype(np.float32), var.astype(np.float32),
+                np.zeros((), np.float32))
+    mu = np.asarray(mean, np.float64)
+    var = np.asarray(variance, np.float64)
+    inv = 1.0 / np.sqrt(var + eps)
+    y = (x64 - mu.reshape(shape)) * (inv.reshape(shape) * scale64) + offset64
+    return (y.astype(out_dtype), mu.astype(np.float32), var.astype(np.float32),
+            mu.astype(np.float32), var.astype(np.float32), np.zeros((), np.float32))
+
+
+def fused_batch_norm_grad(y_backprop, x, scale, reserve_space_1, reserve_space_2,
+                          epsilon=1e-3, data_format="NHWC", is_training=True):
+    """FusedBatchNormGradV3.
+
+    reserve_space_1 is the batch mean and reserve_space_2 the POPULATION
+    variance; the op converts the latter with rsqrt(var + eps)
+    (musa_ext/kernels/nn/musa_fused_batchnorm_op.cc:265-277,
+    musa_ext/kernels/nn/musa_fused_batchnorm_kernel.mu:23-29).
+    Returns (dx, dscale, doffset, out3, out4); the last two are the zero-filled
+    [C] placeholders that the reference emits (:220-242).
+    """
+    dy = np.asarray(y_backprop)
+    x = np.asarray(x)
+    ax = _channel_axis(x.ndim, data_format)
+    red = tuple(i for i in range(x.ndim) if i != ax)
+    shape = [1] * x.ndim
+    shape[ax] = x.shape[ax]
+    c = x.shape[ax]
+    count = x.size // max(c, 1)
+    dy64 = dy.astype(np.float64)
+    x64 = x.astype(np.float64)
+    mu = np.asarray(reserve_space_1, np.float64).reshape(shape)
+    var = np.asarray(reserve_space_2, np.float64).reshape(shape)
+    s = np.asarray(scale, np.float64).reshape(shape)
+    inv = 1.0 / np.sqrt(var + float(np.float32(epsilon)))
+    xc = x64 - mu
+    doffset = dy64.sum(axis=red)
+    dscale = (dy64 * xc).sum(axis=red) * inv.reshape(-1)
+    if is_training:
+        dx = s * inv * (dy64 - doffset.reshape(shape) / count
+                        - xc * inv * dscale.reshape(shape) / count)
+    else:
+        dx = dy64 * s * inv
+    zeros = np.zeros((c,), np.float32)
+    return (dx.astype(x.dtype), dscale.astype(np.float32),
+            doffset.astype(np.float32), zeros, zeros.copy())
+
+
+# --------------------------------------------------------------------------
+# ApplyAdam / ResourceApplyAdam / MusaResourceApplyAdamMixed
+# --------------------------------------------------------------------------
+
+def adam_alpha(lr, beta1_power, beta2_power):
+    """Bias-corrected step size, computed in float64 then narrowed, including
+    the reference-only first-step guard
+    (musa_ext/kernels/training/musa_applyadam_op.cc:236-246)."""
+    one_minus = 1.0 - float(beta1_power)
+    if abs(one_minus) < 1e-10:
+        return np.float32(lr)
+    return np.float32(float(lr) * np.sqrt(1.0 - float(beta2_power)) / one_minus)
+
+
+def apply_adam(var, m, v, beta1_power, beta2_power, lr, beta1, beta2, epsilon,
+               grad, use_nesterov=False):
+    """One Adam step.  State arrays of float32, float16 or bfloat16; grad of
+    any of those.  float32 arithmetic in the order of the device kernels
+    (musa_ext/kernels/training/musa_apply_sparse_adam_kernel.mu:150-156,
+    musa_ext/kernels/training/musa_applyadam_bf16_kernel.mu:92-111), one
+    round-to-nearest-even on store.  Returns new (var, m, v); inputs are not
+    modified."""
+    dt = np.asarray(var).dtype
+    f32 = np.float32
+    alpha = adam_alpha(f32(lr), f32(beta1_power), f32(beta2_power))
+    b1, b2, eps = f32(beta1), f32(beta2), f32(epsilon)
+    omb1, omb2 = f32(1.0) - b1, f32(1.0) - b2
+    g = np.asarray(grad).astype(f32)
+    m32 = np.asarray(m).astype(f32)
+    v32 = np.asarray(v).astype(f32)
+    var32 = np.asarray(var).astype(f32)
+    m_new = b1 * m32 + omb1 * g
+    v_new = b2 * v32 + omb2 * g * g
+    numer = (b1 * m_new + omb1 * g) if use_nesterov else m_new
+    var_new = var32 - alpha * numer / (np.sqrt(v_new) + eps)
+    return var_new.astype(dt), m_new.astype(dt), v_new.astype(dt)
+
+
+# --------------------------------------------------------------------------
+# BiasAdd, Relu, Sigmoid and the fused chains
+# --------------------------------------------------------------------------
+
+def _compute_dtype(dt):
+    # TensorFlow's CPU functors for half/bfloat16 widen to float per op.
+    if dt == np.float16 or (bfloat16 is not None and dt == bfloat16):
+        return np.float32
+    return dt
+
+
+def bias_add(x, bias, data_format="NHWC"):
+    """BiasAdd: bias along the last axis (NHWC / 2-D) or axis 1 (NCHW)
+    (musa_ext/kernels/nn/musa_biasadd_op.cc:33-57); the add is done in the
+    tensor's own type."""
+    x = np.asarray(x)
+    bias = np.asarray(bias)
+    ax = 1 if data_format == "NCHW" else x.ndim - 1
+    if x.size and bias.size and bias.shape[0] != x.shape[ax]:
+        raise ValueError("Dimension mismatch in BiasAdd")
+    if x.size == 0 or bias.size == 0:
+        return np.empty(x.shape, x.dtype)
+    shape = [1] * x.ndim
+    shape[ax] = x.shape[ax]
+    ct = _compute_dtype(x.dtype)
+    return (x.astype(ct) + bias.astype(ct).reshape(shape)).astype(x.dtype)
+
+
+def relu(x):
+    """Relu: max(x, 0) (musa_ext/kernels/nn/musa_relu_op.cc:19-57)."""
+    x = np.asarray(x)
+    return np.maximum(x, np.zeros((), x.dtype)).astype(x.dtype)
+
+
+def sigmoid(x):
+    """Sigmoid: 1 / (1 + exp(-x)) (musa_ext/kernels/nn/musa_sigmoid_op.cc:18-35);
+    float64 evaluation, one rounding."""
+    x = np.asarray(x)
+    x64 = x.astype(np.float64)
+    with np.errstate(over="ignore"):
+        return (1.0 / (1.0 + np.exp(-x64))).astype(x.dtype)
+
+
+def bias_add_relu(x, bias, data_format="NHWC"):
+    """The un-fused chain Relu(BiasAdd(x, b))."""
+    return relu(bias_add(x, bias, data_format))
+
+
+def bias_add_swish(x, bias, data_format="NHWC"):
+    """The un-fused chain Mul(x, Sigmoid(BiasAdd(x, b))), each op rounding to
+    the tensor's type as separate TensorFlow ops do."""
+    x = np.asarray(x)
+    ct = _compute_dtype(x.dtype)
+    s = sigmoid(bias_add(x, bias, data_format))
+    return (x.astype(ct) * s.astype(ct)).astype(x.dtype)
+
+
+def bias_add_sigmoid(x, bias, data_format="NHWC"):
+    """The un-fused chain Sigmoid(BiasAdd(x, b))."""
+    return sigmoid(bias_add(x, bias, data_format))

@@ -1,0 +1,83 @@
+"""ctypes prototypes of every entry point declared in
+include/musa_plugin_kernels.h.  `bind()` attaches argtypes/restype to a loaded
+library and fails loudly if a symbol is missing."""
+import ctypes
+
+c_i64 = ctypes.c_int64
+c_f32 = ctypes.c_float
+c_f64 = ctypes.c_double
+c_vp = ctypes.c_void_p
+c_int = ctypes.c_int
+c_bool = ctypes.c_bool
+c_size = ctypes.c_size_t
+
+_ADAM_SAME = [c_vp, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_i64, c_bool, c_vp]
+_BIAS_ACT = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_vp]
+_BN_TRAIN = [c_vp] * 10 + [c_i64, c_i64, c_i64, c_f32, c_f32, c_vp, c_size, c_vp]
+_BN_INFER = [c_vp] * 6 + [c_i64, c_i64, c_i64, c_f32, c_vp]
+_BN_GRAD = [c_vp] * 8 + [c_i64, c_i64, c_i64, c_f32, c_bool, c_vp, c_size, c_vp]
+
+# name -> (restype, argtypes)
+PROTOTYPES = {
+    "MusaKernelsVersion": (ctypes.c_char_p, []),
+    "MusaKernelsTargetArch": (c_int, []),
+    "LaunchResourceApplyAdamFloat":
+        (None, [c_vp, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_i64, c_vp]),
+    "LaunchApplyAdamSameType_BFloat16": (None, _ADAM_SAME),
+    "LaunchApplyAdamSameType_Half": (None, _ADAM_SAME),
+    "LaunchApplyAdamMixed_Float": (None, _ADAM_SAME),
+    "LaunchApplyAdamMixed_Half": (None, _ADAM_SAME),
+    "LaunchApplyAdamMixed_BFloat16": (None, _ADAM_SAME),
+    "LaunchBiasAct_F32": (c_int, _BIAS_ACT),
+    "LaunchBiasAct_F16": (c_int, _BIAS_ACT),
+    "LaunchBiasAct_BF16": (c_int, _BIAS_ACT),
+    "LaunchBiasAct_F64": (c_int, _BIAS_ACT),
+    "LaunchBiasAct_I32": (c_int, _BIAS_ACT),
+    "LaunchBiasAct_I64": (c_int, _BIAS_ACT),
+    "BnWorkspaceBytes": (c_size, [c_i64, c_i64, c_i64]),
+    "LaunchBnFwdTrain_F32": (c_int, _BN_TRAIN),
+    "LaunchBnFwdTrain_F16": (c_int, _BN_TRAIN),
+    "LaunchBnFwdTrain_BF16": (c_int, _BN_TRAIN),
+    "LaunchBnFwdInfer_F32": (c_int, _BN_INFER),
+    "LaunchBnFwdInfer_F16": (c_int, _BN_INFER),
+    "LaunchBnFwdInfer_BF16": (c_int, _BN_INFER),
+    "LaunchBnGrad_F32": (c_int, _BN_GRAD),
+    "LaunchBnGrad_F16": (c_int, _BN_GRAD),
+    "LaunchBnGrad_BF16": (c_int, _BN_GRAD),
+    "LaunchBesselCorrection": (None, [c_vp, c_f32, c_int, c_vp]),
+    "LaunchVarianceToInvStd": (None, [c_vp, c_vp, c_f32, c_int, c_vp]),
+    "LaunchBnStatsSums":
+        (c_int, [c_int, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]),
+    "LaunchBnFinalizeFromSums":
+        (c_int, [c_vp, c_f64] + [c_vp] * 6 + [c_i64, c_f32, c_vp]),
+    "LaunchBnApply":
+        (c_int, [c_int] + [c_vp] * 6 + [c_i64, c_i64, c_i64, c_f32, c_vp]),
+    "LaunchBnGradStatsSums":
+        (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]),
+    "LaunchBnGradApplyFromSums":
+        (c_int, [c_int] + [c_vp] * 6 + [c_f64] + [c_vp] * 3
+         + [c_i64, c_i64, c_i64, c_f32, c_vp]),
+}
+
+# Hooks outside the reference boundary (launch-shape sweeps).
+EXTRA_PROTOTYPES = {
+    "MusaKernelsSetTuning": (c_int, [c_int, c_int]),
+    "MusaKernelsGetTuning": (c_int, [c_int]),
+}
+
+ERROR_NAMES = {
+    -1: "invalid argument (null pointer or negative size)",
+    -2: "workspace missing, misaligned or too small",
+    -3: "unsupported dtype or activation code",
+    -4: "size beyond what the entry point holds",
+}
+
+
+def bind(lib):
+    """Attach prototypes; AttributeError names the first missing symbol."""
+    for table in (PROTOTYPES, EXTRA_PROTOTYPES):
+        for name, (restype, argtypes) in table.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+    return lib

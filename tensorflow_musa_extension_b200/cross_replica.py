@@ -1,0 +1,293 @@
+"""Multi-GPU forms of the path, one process per GPU over torch.distributed.
+
+* Cross-replica BatchNorm (SyncBN): the batch is sharded over the replicas;
+  each pass exchanges 2*C fp32 per-channel sums with ONE all-reduce placed
+  between the statistics kernel and the element-wise kernel:
+      forward : [sum x, sum x^2]            -> mean, variance over all replicas
+      gradient: [sum dy, sum dy*(x - mean)] -> dscale, doffset, dx
+  The Bessel factor of batch_variance uses the global count.
+* Range-sharded Adam: every replica holds the whole `var` but only its
+  contiguous range of m, v (and reads only that range of grad); after the
+  update the ranges of `var` are all-gathered in place.
+
+The reference has no collective backend (its
+musa_ext/mu/collective/musa_collective_runtime.cc:58-63 returns Unimplemented)
+and leaves data parallelism to tf.distribute; these classes are what a
+MirroredStrategy-style replica calls instead, built on the same launchers as
+the single-GPU ops.  The collectives are NCCL on GPUs; the same code runs on
+the gloo backend for host-side tests when it is given `kernels=` stand-ins.
+"""
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import raw_ops
+from .errors import InvalidArgumentError
+
+_DT_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def shard_range(n, world, rank):
+    """Contiguous range [lo, hi) of an n-element vector owned by `rank`:
+    ceil(n / world) elements per rank, the last ranks possibly short or empty."""
+    per = -(-n // world)
+    lo = min(n, rank * per)
+    hi = min(n, lo + per)
+    return lo, hi
+
+
+def _world(group):
+    if group is None or not dist.is_initialized():
+        return 1
+    return dist.get_world_size(group)
+
+
+class _DeviceKernels:
+    """The C launchers behind the four SyncBN stages."""
+
+    def __init__(self):
+        self.lib = raw_ops._lib()
+
+    @staticmethod
+    def _st():
+        return torch.cuda.current_stream().cuda_stream
+
+    def workspace_bytes(self, rows, c):
+        return self.lib.BnWorkspaceBytes(rows, c, 1)
+
+    def stats_sums(self, x, sums, ws):
+        rows, c = x.shape
+        raw_ops._check(self.lib.LaunchBnStatsSums(
+            _DT_CODE[x.dtype], x.data_ptr(), sums.data_ptr(), rows, c, 1,
+            ws.data_ptr(), ws.numel(), self._st()), "LaunchBnStatsSums")
+
+    def finalize(self, sums, count, stats, c):
+        raw_ops._check(self.lib.LaunchBnFinalizeFromSums(
+            sums.data_ptr(), float(count), None, None, stats[0].data_ptr(),
+            stats[1].data_ptr(), stats[2].data_ptr(), stats[3].data_ptr(), c, 1.0,
+            self._st()), "LaunchBnFinalizeFromSums")
+
+    def apply(self, x, scale, offset, mean, var, y, eps):
+        rows, c = x.shape
+        raw_ops._check(self.lib.LaunchBnApply(
+            _DT_CODE[x.dtype], x.data_ptr(), scale.data_ptr(), offset.data_ptr(),
+            mean.data_ptr(), var.data_ptr(), y.data_ptr(), rows, c, 1, eps, self._st()),
+            "LaunchBnApply")
+
+    def grad_stats_sums(self, dy, x, mean, sums, ws):
+        rows, c = x.shape
+        raw_ops._check(self.lib.LaunchBnGradStatsSums(
+            _DT_CODE[x.dtype], dy.data_ptr(), x.data_ptr(), mean.data_ptr(),
+            sums.data_ptr(), rows, c, 1, ws.data_ptr(), ws.numel(), self._st()),
+            "LaunchBnGradStatsSums")
+
+    def grad_apply(self, dy, x, scale, mean, var, sums, count, dx, dscale, doffset, eps):
+        rows, c = x.shape
+        raw_ops._check(self.lib.LaunchBnGradApplyFromSums(
+            _DT_CODE[x.dtype], dy.data_ptr(), x.data_ptr(), scale.data_ptr(),
+            mean.data_ptr(), var.data_ptr(), sums.data_ptr(), float(count), dx.data_ptr(),
+            dscale.data_ptr(), doffset.data_ptr(), rows, c, 1, eps, self._st()),
+            "LaunchBnGradApplyFromSums")
+
+    def fwd_local(self, x, scale, offset, y, stats, ws, eps):
+        rows, c = x.shape
+        fn = getattr(self.lib, "LaunchBnFwdTrain_" + raw_ops._SUFFIX[x.dtype])
+        raw_ops._check(fn(x.data_ptr(), scale.data_ptr(), offset.data_ptr(), None, None,
+                          y.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(),
+                          stats[2].data_ptr(), stats[3].data_ptr(), rows, c, 1, eps, 1.0,
+                          ws.data_ptr(), ws.numel(), self._st()), "LaunchBnFwdTrain")
+
+    def grad_local(self, dy, x, scale, mean, var, dx, dscale, doffset, ws, eps):
+        rows, c = x.shape
+        fn = getattr(self.lib, "LaunchBnGrad_" + raw_ops._SUFFIX[x.dtype])
+        raw_ops._check(fn(dy.data_ptr(), x.data_ptr(), scale.data_ptr(), mean.data_ptr(),
+                          var.data_ptr(), dx.data_ptr(), dscale.data_ptr(),
+                          doffset.data_ptr(), rows, c, 1, eps, True, ws.data_ptr(),
+                          ws.numel(), self._st()), "LaunchBnGrad")
+
+
+class SyncBatchNorm:
+    """One BatchNorm layer of a replica: channels-last [rows, C] activations,
+    preallocated statistics and workspace, no allocation per call.
+
+    forward()  fills y and self.batch_mean / batch_var / saved_mean / saved_var
+    backward() fills dx and self.dscale / self.doffset
+    `group=None` (or a world of 1) runs the plain single-GPU launchers.
+    `rows` may differ between replicas (a ragged last batch): the global count
+    travels with the sums.
+    """
+
+    def __init__(self, channels, eps=1e-3, dtype=torch.bfloat16, device="cuda",
+                 max_rows=0, group=None, kernels=None):
+        self.c = int(channels)
+        self.eps = float(eps)
+        self.group = group
+        self.world = _world(group)
+        self.k = kernels if kernels is not None else _DeviceKernels()
+        dev = torch.device(device)
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.batch_mean = torch.empty(self.c, **f32)
+        self.batch_var = torch.empty(self.c, **f32)
+        self.saved_mean = torch.empty(self.c, **f32)
+        self.saved_var = torch.empty(self.c, **f32)
+        self.dscale = torch.empty(self.c, **f32)
+        self.doffset = torch.empty(self.c, **f32)
+        # [sum, sumsq | count]: the row count rides in the same all-reduce.
+        self.sums = torch.zeros(2 * self.c + 1, **f32)
+        self.gsums = torch.zeros(2 * self.c, **f32)
+        nbytes = max(16, int(self.k.workspace_bytes(max(int(max_rows), 1), self.c)))
+        self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self._ws_rows = int(max_rows)
+        self.global_count = None
+        self.launches_per_step = 6 if self.world == 1 else 8
+
+    def _stats(self):
+        return (self.batch_mean, self.batch_var, self.saved_mean, self.saved_var)
+
+    def _check(self, x):
+        if x.dim() != 2 or x.shape[1] != self.c:
+            raise InvalidArgumentError(
+                "SyncBatchNorm: expected [rows, %d], got %s" % (self.c, tuple(x.shape)))
+        if x.shape[0] > self._ws_rows:
+            nbytes = max(16, int(self.k.workspace_bytes(x.shape[0], self.c)))
+            if nbytes > self.ws.numel():
+                self.ws = torch.empty(nbytes, dtype=torch.uint8, device=self.ws.device)
+            self._ws_rows = x.shape[0]
+
+    def forward(self, x, scale, offset, y):
+        self._check(x)
+        rows = x.shape[0]
+        if self.world == 1:
+            self.k.fwd_local(x, scale, offset, y, self._stats(), self.ws, self.eps)
+            self.global_count = float(rows)
+            return y
+        self.k.stats_sums(x, self.sums, self.ws)
+        self.sums[2 * self.c:].fill_(float(rows))
+        dist.all_reduce(self.sums, op=dist.ReduceOp.SUM, group=self.group)
+        # Static shapes: the global count is rows * world unless a replica is
+        # ragged; read it on the host only in that case.
+        self.global_count = float(rows) * self.world if self._uniform_rows else \
+            float(self.sums[2 * self.c].item())
+        self.k.finalize(self.sums, self.global_count, self._stats(), self.c)
+        self.k.apply(x, scale, offset, self.saved_mean, self.saved_var, y, self.eps)
+        return y
+
+    _uniform_rows = True
+
+    def set_ragged(self, ragged=True):
+        """Replicas may hold different row counts: fetch the all-reduced count
+        (one host sync per pass)."""
+        self._uniform_rows = not ragged
+
+    def backward(self, dy, x, scale, dx):
+        self._check(x)
+        rows = x.shape[0]
+        if self.world == 1:
+            self.k.grad_local(dy, x, scale, self.saved_mean, self.saved_var, dx,
+                              self.dscale, self.doffset, self.ws, self.eps)
+            return dx
+        self.k.grad_stats_sums(dy, x, self.saved_mean, self.gsums, self.ws)
+        dist.all_reduce(self.gsums, op=dist.ReduceOp.SUM, group=self.group)
+        count = self.global_count if self.global_count is not None else float(rows) * self.world
+        self.k.grad_apply(dy, x, scale, self.saved_mean, self.saved_var, self.gsums, count,
+                          dx, self.dscale, self.doffset, self.eps)
+        return dx
+
+
+def sync_batch_norm_forward(x, scale, offset, epsilon=1e-3, group=None):
+    """Cross-replica FusedBatchNormV3 (training) on a [rows, C] or NHWC tensor
+    that may live on the host; returns the op's six outputs in the input's
+    form.  The host path is the end-to-end form: H2D, kernels + all-reduce,
+    D2H."""
+    hf = raw_ops._HostForm()
+    xd = hf.to_device(x).contiguous()
+    sd = hf.to_device(scale, torch.float32)
+    od = hf.to_device(offset, torch.float32)
+    c = xd.shape[-1]
+    x2 = xd.reshape(-1, c)
+    bn = SyncBatchNorm(c, epsilon, xd.dtype, xd.device, x2.shape[0], group)
+    y = torch.empty_like(x2)
+    bn.forward(x2, sd, od, y)
+    r3 = torch.zeros((), dtype=torch.float32, device=xd.device)
+    outs = (y.reshape(xd.shape), bn.batch_mean, bn.batch_var, bn.saved_mean,
+            bn.saved_var, r3)
+    return raw_ops.FusedBatchNormV3Output(*hf.back_many(outs))
+
+
+def sync_batch_norm_backward(dy, x, scale, mean, variance, epsilon=1e-3, group=None):
+    """Cross-replica FusedBatchNormGradV3 (training); `mean` / `variance` are
+    the global reserve_space_1 / reserve_space_2 of the forward."""
+    hf = raw_ops._HostForm()
+    dyd = hf.to_device(dy).contiguous()
+    xd = hf.to_device(x).contiguous()
+    sd = hf.to_device(scale, torch.float32)
+    c = xd.shape[-1]
+    x2 = xd.reshape(-1, c)
+    bn = SyncBatchNorm(c, epsilon, xd.dtype, xd.device, x2.shape[0], group)
+    bn.saved_mean.copy_(hf.to_device(mean, torch.float32))
+    bn.saved_var.copy_(hf.to_device(variance, torch.float32))
+    dx = torch.empty_like(x2)
+    bn.backward(dyd.reshape(-1, c), x2, sd, dx)
+    z = torch.zeros(c, dtype=torch.float32, device=xd.device)
+    outs = (dx.reshape(xd.shape), bn.dscale, bn.doffset, z, z.clone())
+    return raw_ops.FusedBatchNormGradV3Output(*hf.back_many(outs))
+
+
+class ShardedAdam:
+    """ResourceApplyAdam over one flat parameter vector, sharded by contiguous
+    range.  Each replica keeps the whole `var`, its range of m and v, and
+    updates var[lo:hi] from grad[lo:hi]; `step()` then all-gathers the updated
+    ranges into every replica's `var`, in place.
+
+    The all-gather needs equal ranges; the vector is handled as
+    ceil(n / world) * world elements, the padding living in a private tail.
+    """
+
+    def __init__(self, var, group=None, beta1=0.9, beta2=0.999, epsilon=1e-7,
+                 chunks=1, update_fn=None):
+        if var.dim() != 1 or not var.is_contiguous():
+            raise InvalidArgumentError("ShardedAdam: var must be a flat contiguous vector")
+        self.group = group
+        self.world = _world(group)
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.n = var.numel()
+        self.per = -(-self.n // self.world)
+        self.lo, self.hi = shard_range(self.n, self.world, self.rank)
+        self.var = var
+        pad = self.per * self.world - self.n
+        # Padded mirror only when n is not a multiple of the world size.
+        self._padded = None
+        if self.world > 1 and pad:
+            self._padded = torch.zeros(self.per * self.world, dtype=var.dtype,
+                                       device=var.device)
+        self.m = torch.zeros(self.hi - self.lo, dtype=var.dtype, device=var.device)
+        self.v = torch.zeros(self.hi - self.lo, dtype=var.dtype, device=var.device)
+        self.beta1, self.beta2, self.epsilon = beta1, beta2, epsilon
+        self.chunks = max(1, int(chunks))
+        self._update = update_fn if update_fn is not None else self._device_update
+
+    @staticmethod
+    def _device_update(var, m, v, grad, b1p, b2p, lr, b1, b2, eps):
+        raw_ops.ResourceApplyAdam(var, m, v, b1p, b2p, lr, b1, b2, eps, grad)
+
+    def step(self, grad, lr, beta1_power, beta2_power):
+        """`grad` is the full gradient vector or this replica's range of it."""
+        if grad.numel() == self.n:
+            grad = grad[self.lo:self.hi]
+        elif grad.numel() != self.hi - self.lo:
+            raise InvalidArgumentError(
+                "ShardedAdam: grad has %d elements, expected %d or %d"
+                % (grad.numel(), self.n, self.hi - self.lo))
+        if self.hi > self.lo:
+            self._update(self.var[self.lo:self.hi], self.m, self.v, grad, beta1_power,
+                         beta2_power, lr, self.beta1, self.beta2, self.epsilon)
+        if self.world == 1:
+            return self.var
+        if self._padded is None:
+            dist.all_gather_into_tensor(self.var, self.var[self.lo:self.hi], group=self.group)
+        else:
+            shard = self._padded[self.rank * self.per:(self.rank + 1) * self.per]
+            shard[:self.hi - self.lo].copy_(self.var[self.lo:self.hi])
+            dist.all_gather_into_tensor(self._padded, shard, group=self.group)
+            self.var.copy_(self._padded[:self.n])
+        return self.var

@@ -1,0 +1,236 @@
+// ApplyAdam for sm_100a: one streaming pass that reads var, m, v, grad and
+// writes var, m, v with 128-bit accesses (28 B/element in fp32).
+//
+// Arithmetic follows the reference kernels exactly: fp32 math, IEEE sqrt and
+// divide, (1-beta) taken on the host
+// (musa_ext/kernels/training/musa_apply_sparse_adam_kernel.mu:140-157,
+//  musa_ext/kernels/training/musa_applyadam_bf16_kernel.mu:82-112,
+//  musa_ext/kernels/training/musa_applyadam_mixed_kernel.mu:55-86).
+#include "common.cuh"
+#include "tuning.h"
+#include "../../include/musa_plugin_kernels.h"
+
+namespace musa_b200 {
+namespace {
+
+struct AdamParams {
+  float lr_t;  // bias-corrected step size ("alpha" in the fp32 launcher)
+  float beta1;
+  float one_minus_b1;
+  float beta2;
+  float one_minus_b2;
+  float epsilon;
+};
+
+template <bool kNesterov>
+__device__ __forceinline__ void AdamStep(float& var, float& m, float& v,
+                                         float g, const AdamParams& p) {
+  const float m_new = p.beta1 * m + p.one_minus_b1 * g;
+  const float v_new = p.beta2 * v + p.one_minus_b2 * g * g;
+  const float numer =
+      kNesterov ? (p.beta1 * m_new + p.one_minus_b1 * g) : m_new;
+  m = m_new;
+  v = v_new;
+  var = var - p.lr_t * numer / (sqrtf(v_new) + p.epsilon);
+}
+
+// Each thread owns kUnroll packs of kEpt elements per tile; a tile is
+// blockDim.x * kUnroll consecutive packs, so that every load instruction of a
+// warp covers 32 consecutive packs.  All loads of a tile are issued before the
+// first use to keep 4 * kUnroll requests per thread in flight.
+template <typename StateT, typename GradT, int kEpt, int kUnroll,
+          bool kNesterov>
+__global__ void __launch_bounds__(256)
+    AdamKernel(StateT* __restrict__ var, StateT* __restrict__ m,
+               StateT* __restrict__ v, const GradT* __restrict__ grad,
+               AdamParams p, int64_t n) {
+  using SPack = Pack<StateT, kEpt>;
+  using GPack = Pack<GradT, kEpt>;
+  const int64_t n_packs = n / kEpt;
+  const int64_t tile = static_cast<int64_t>(blockDim.x) * kUnroll;
+  const int64_t n_tiles = (n_packs + tile - 1) / tile;
+
+  SPack* var_p = reinterpret_cast<SPack*>(var);
+  SPack* m_p = reinterpret_cast<SPack*>(m);
+  SPack* v_p = reinterpret_cast<SPack*>(v);
+  const GPack* g_p = reinterpret_cast<const GPack*>(grad);
+
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int64_t base = t * tile + threadIdx.x;
+    SPack pv[kUnroll], pm[kUnroll], pvv[kUnroll];
+    GPack pg[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+      if (i < n_packs) {
+        pg[u] = LoadStream(g_p + i);
+        pm[u] = LoadStream(m_p + i);
+        pvv[u] = LoadStream(v_p + i);
+        pv[u] = LoadStream(var_p + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+      if (i < n_packs) {
+#pragma unroll
+        for (int e = 0; e < kEpt; ++e) {
+          float fvar = ToF32(pv[u].v[e]);
+          float fm = ToF32(pm[u].v[e]);
+          float fv = ToF32(pvv[u].v[e]);
+          AdamStep<kNesterov>(fvar, fm, fv, ToF32(pg[u].v[e]), p);
+          pv[u].v[e] = FromF32<StateT>(fvar);
+          pm[u].v[e] = FromF32<StateT>(fm);
+          pvv[u].v[e] = FromF32<StateT>(fv);
+        }
+        StoreStream(m_p + i, pm[u]);
+        StoreStream(v_p + i, pvv[u]);
+        StoreStream(var_p + i, pv[u]);
+      }
+    }
+  }
+
+  // Ragged tail (n not a multiple of the pack width): one thread per element.
+  if (kEpt > 1 && blockIdx.x == 0) {
+    const int64_t i = n_packs * kEpt + threadIdx.x;
+    if (threadIdx.x < kEpt && i < n) {
+      float fvar = ToF32(var[i]);
+      float fm = ToF32(m[i]);
+      float fv = ToF32(v[i]);
+      AdamStep<kNesterov>(fvar, fm, fv, ToF32(grad[i]), p);
+      var[i] = FromF32<StateT>(fvar);
+      m[i] = FromF32<StateT>(fm);
+      v[i] = FromF32<StateT>(fv);
+    }
+  }
+}
+
+template <typename StateT, typename GradT, int kEpt, int kUnroll>
+void LaunchWithNesterov(StateT* var, StateT* m, StateT* v, const GradT* grad,
+                        const AdamParams& p, int64_t n, bool nesterov,
+                        cudaStream_t stream) {
+  const int threads = 256;
+  const int64_t n_packs = n / kEpt;
+  const int64_t tile = static_cast<int64_t>(threads) * kUnroll;
+  int64_t tiles = CeilDiv(n_packs, tile);
+  if (tiles < 1) tiles = 1;
+  // Tuning value 0: one tile per CTA.  k > 0: a persistent grid of k CTAs per
+  // SM that strides over the tiles.
+  const int per_sm = GetTuning(kTuneAdamCtasPerSm);
+  int64_t blocks = tiles;
+  if (per_sm > 0) {
+    const int64_t cap = static_cast<int64_t>(SmCount()) * per_sm;
+    if (blocks > cap) blocks = cap;
+  }
+  if (blocks > 0x7fffffffLL) blocks = 0x7fffffffLL;
+  if (nesterov) {
+    AdamKernel<StateT, GradT, kEpt, kUnroll, true>
+        <<<static_cast<unsigned>(blocks), threads, 0, stream>>>(var, m, v, grad,
+                                                               p, n);
+  } else {
+    AdamKernel<StateT, GradT, kEpt, kUnroll, false>
+        <<<static_cast<unsigned>(blocks), threads, 0, stream>>>(var, m, v, grad,
+                                                               p, n);
+  }
+}
+
+// Picks the 128-bit path when every pointer allows it, else element-wise
+// accesses (TF's BFC allocator hands out 64-byte aligned buffers, so the
+// vector path is the normal one; sliced or offset tensors take the other).
+template <typename StateT, typename GradT>
+void LaunchAdam(StateT* var, StateT* m, StateT* v, const GradT* grad,
+                float lr_t, float beta1, float beta2, float epsilon, int64_t n,
+                bool nesterov, cudaStream_t stream) {
+  if (n <= 0) return;
+  AdamParams p;
+  p.lr_t = lr_t;
+  p.beta1 = beta1;
+  p.one_minus_b1 = 1.0f - beta1;
+  p.beta2 = beta2;
+  p.one_minus_b2 = 1.0f - beta2;
+  p.epsilon = epsilon;
+  // State packs are 16 bytes; the grad pack has the same element count.
+  constexpr int kEpt = VecWidth<StateT>::value;
+  constexpr size_t kGradPackBytes = sizeof(GradT) * kEpt;
+  const bool vec_ok =
+      Aligned16(var) && Aligned16(m) && Aligned16(v) &&
+      (reinterpret_cast<uintptr_t>(grad) % kGradPackBytes) == 0;
+  if (vec_ok) {
+    if (GetTuning(kTuneAdamUnroll) == 1) {
+      LaunchWithNesterov<StateT, GradT, kEpt, 1>(var, m, v, grad, p, n,
+                                                 nesterov, stream);
+    } else if (GetTuning(kTuneAdamUnroll) == 4) {
+      LaunchWithNesterov<StateT, GradT, kEpt, 4>(var, m, v, grad, p, n,
+                                                 nesterov, stream);
+    } else {
+      LaunchWithNesterov<StateT, GradT, kEpt, 2>(var, m, v, grad, p, n,
+                                                 nesterov, stream);
+    }
+  } else {
+    LaunchWithNesterov<StateT, GradT, 1, 4>(var, m, v, grad, p, n, nesterov,
+                                            stream);
+  }
+}
+
+}  // namespace
+}  // namespace musa_b200
+
+using namespace musa_b200;
+
+extern "C" {
+
+void LaunchResourceApplyAdamFloat(float* var, float* m, float* v,
+                                  const float* grad, float beta1, float beta2,
+                                  float epsilon, float alpha, int64_t total,
+                                  cudaStream_t stream) {
+  LaunchAdam<float, float>(var, m, v, grad, alpha, beta1, beta2, epsilon, total,
+                           /*nesterov=*/false, stream);
+}
+
+void LaunchApplyAdamSameType_BFloat16(void* var, void* m, void* v,
+                                      const void* grad, float lr_t, float beta1,
+                                      float beta2, float epsilon, int64_t n,
+                                      bool use_nesterov, cudaStream_t stream) {
+  LaunchAdam<__nv_bfloat16, __nv_bfloat16>(
+      static_cast<__nv_bfloat16*>(var), static_cast<__nv_bfloat16*>(m),
+      static_cast<__nv_bfloat16*>(v), static_cast<const __nv_bfloat16*>(grad),
+      lr_t, beta1, beta2, epsilon, n, use_nesterov, stream);
+}
+
+void LaunchApplyAdamSameType_Half(void* var, void* m, void* v, const void* grad,
+                                  float lr_t, float beta1, float beta2,
+                                  float epsilon, int64_t n, bool use_nesterov,
+                                  cudaStream_t stream) {
+  LaunchAdam<__half, __half>(static_cast<__half*>(var), static_cast<__half*>(m),
+                             static_cast<__half*>(v),
+                             static_cast<const __half*>(grad), lr_t, beta1,
+                             beta2, epsilon, n, use_nesterov, stream);
+}
+
+void LaunchApplyAdamMixed_Float(float* var, float* m, float* v,
+                                const void* grad, float lr_t, float beta1,
+                                float beta2, float epsilon, int64_t n,
+                                bool use_nesterov, cudaStream_t stream) {
+  LaunchAdam<float, float>(var, m, v, static_cast<const float*>(grad), lr_t,
+                           beta1, beta2, epsilon, n, use_nesterov, stream);
+}
+
+void LaunchApplyAdamMixed_Half(float* var, float* m, float* v, const void* grad,
+                               float lr_t, float beta1, float beta2,
+                               float epsilon, int64_t n, bool use_nesterov,
+                               cudaStream_t stream) {
+  LaunchAdam<float, __half>(var, m, v, static_cast<const __half*>(grad), lr_t,
+                            beta1, beta2, epsilon, n, use_nesterov, stream);
+}
+
+void LaunchApplyAdamMixed_BFloat16(float* var, float* m, float* v,
+                                   const void* grad, float lr_t, float beta1,
+                                   float beta2, float epsilon, int64_t n,
+                                   bool use_nesterov, cudaStream_t stream) {
+  LaunchAdam<float, __nv_bfloat16>(var, m, v,
+                                   static_cast<const __nv_bfloat16*>(grad),
+                                   lr_t, beta1, beta2, epsilon, n, use_nesterov,
+                                   stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,1056 @@
+// FusedBatchNorm forward / gradient for sm_100a.
+//
+// Data layout.  x, y, dy, dx are [outer, channels, inner]; NHWC is
+// (outer = N*H*W, inner = 1), NCHW is (outer = N, inner = H*W).  Statistics
+// are fp32 [channels] for every x dtype.
+//
+// Structure.  Both directions are "two per-channel sums over all rows, then an
+// element-wise pass":
+//   forward : S1 = sum(x - K), S2 = sum((x - K)^2)      (K: per-channel shift)
+//   gradient: S1 = sum(dy),    S2 = sum(dy * (x - mean))
+// Level 1 (stats kernel): each thread owns one 128-bit channel pack and walks
+// rows, keeping 2 * kVec fp32 partials in registers; a CTA folds its row
+// lanes through shared memory and writes one partial row [2, C] to the
+// workspace.  Level 2 (finalize kernel): 8 channels x 128 partial-lanes per
+// CTA, fp64 accumulation, then the per-channel outputs.  The apply kernel
+// re-reads x (and dy) with the default L2 policy, walking the rows in the
+// opposite order of the stats kernel so that it meets the most recently read
+// lines first, and streams y / dx out with evict-first stores.
+//
+// The forward sums are taken about a per-channel shift K (the channel's first
+// element) so that the variance does not cancel when |mean| >> std; the
+// gradient sums are centred on the batch mean by construction.
+//
+// Output conventions follow the op this replaces
+// (musa_ext/kernels/nn/musa_fused_batchnorm_op.cc:126-170: batch_var is
+// Bessel-corrected, saved_var is the population variance, no correction when
+// there is one value per channel; :265-277: the gradient receives a variance
+// and turns it into 1/sqrt(var + eps)).
+#include "common.cuh"
+#include "tuning.h"
+#include "../../include/musa_plugin_kernels.h"
+
+namespace musa_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+// Upper bound of fp32 partials in the workspace (level-1 output).
+constexpr int64_t kMaxPartialFloats = 1 << 20;
+constexpr int64_t kMaxSplits = 4096;
+
+// ------------------------------------------------------------- planning --
+
+inline int Pow2Ceil(int64_t v) {
+  int p = 1;
+  while (p < v && p < kThreads) p <<= 1;
+  return p;
+}
+
+// Largest number of row splits the workspace has to hold for `rows` rows of
+// `channels` channels, whatever vector width or grid the launch picks.
+inline int64_t MaxSplits(int64_t rows, int64_t channels) {
+  int64_t by_ws = kMaxPartialFloats / (2 * channels);
+  if (by_ws < 1) by_ws = 1;
+  int64_t s = rows < 1 ? 1 : rows;
+  if (s > kMaxSplits) s = kMaxSplits;
+  if (s > by_ws) s = by_ws;
+  return s;
+}
+
+struct Plan {
+  int tx, ty;      // thread block = tx channel packs x ty row lanes
+  int gx;          // column blocks
+  int gy;          // row splits (= partial rows written by the stats kernel)
+  int64_t rows_per_cta;
+};
+
+// Channels-last plan.  `cv` = channel packs per row.
+inline Plan PlanLast(int64_t rows, int64_t channels, int64_t cv, int unroll,
+                     bool cap_by_workspace) {
+  Plan p;
+  p.tx = Pow2Ceil(cv);
+  p.ty = kThreads / p.tx;
+  p.gx = static_cast<int>(CeilDiv(cv, p.tx));
+  int per_sm = GetTuning(kTuneBnCtasPerSm);
+  if (per_sm < 1) per_sm = 8;
+  int64_t target = static_cast<int64_t>(SmCount()) * per_sm / p.gx;
+  if (target < 1) target = 1;
+  // Do not split below one unrolled sweep of the row lanes.
+  int64_t max_useful = CeilDiv(rows, static_cast<int64_t>(p.ty) * unroll);
+  if (max_useful < 1) max_useful = 1;
+  int64_t gy = target < max_useful ? target : max_useful;
+  if (cap_by_workspace) {
+    const int64_t cap = MaxSplits(rows, channels);
+    if (gy > cap) gy = cap;
+  }
+  if (gy > 65535) gy = 65535;
+  p.rows_per_cta = CeilDiv(rows, gy);
+  // Keep CTA row ranges a multiple of ty so that lanes stay aligned.
+  p.rows_per_cta = CeilDiv(p.rows_per_cta, p.ty) * p.ty;
+  p.gy = static_cast<int>(CeilDiv(rows, p.rows_per_cta));
+  if (p.gy < 1) p.gy = 1;
+  return p;
+}
+
+// ------------------------------------------------------------ level 1 ----
+
+enum Mode { kFwd = 0, kGrad = 1 };
+
+// Channels-last stats.  Grid (gx, gy), block (tx, ty).
+template <typename T, int kVec, int kUnroll, int kMode>
+__global__ void __launch_bounds__(kThreads)
+    BnStatsLastKernel(const T* __restrict__ x, const T* __restrict__ dy,
+                      const float* __restrict__ mean,
+                      float* __restrict__ partial, int64_t rows, int64_t cv,
+                      int64_t channels, int64_t rows_per_cta, bool keep) {
+  using P = Pack<T, kVec>;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int TX = blockDim.x, TY = blockDim.y;
+  const int64_t col = static_cast<int64_t>(blockIdx.x) * TX + tx;
+  const bool active = col < cv;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_cta;
+  int64_t r1 = r0 + rows_per_cta;
+  if (r1 > rows) r1 = rows;
+
+  float shift[kVec];
+  float s1[kVec], s2[kVec];
+#pragma unroll
+  for (int e = 0; e < kVec; ++e) {
+    s1[e] = 0.0f;
+    s2[e] = 0.0f;
+    shift[e] = 0.0f;
+  }
+
+  if (active) {
+    if constexpr (kMode == kFwd) {
+      const P first = LoadKeep(reinterpret_cast<const P*>(x) + col);
+#pragma unroll
+      for (int e = 0; e < kVec; ++e) shift[e] = ToF32(first.v[e]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < kVec; ++e) shift[e] = mean[col * kVec + e];
+    }
+    const P* xp = reinterpret_cast<const P*>(x) + col;
+    const P* dp = reinterpret_cast<const P*>(dy) + col;
+    int64_t r = r0 + ty;
+    const int64_t step = static_cast<int64_t>(TY) * kUnroll;
+    // Full sweeps: kUnroll independent loads per stream in flight.
+    for (; r + static_cast<int64_t>(kUnroll - 1) * TY < r1; r += step) {
+      P px[kUnroll];
+      P pd[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t off = (r + static_cast<int64_t>(u) * TY) * cv;
+        px[u] = keep ? LoadKeep(xp + off) : LoadStream(xp + off);
+        if constexpr (kMode == kGrad) {
+          pd[u] = keep ? LoadKeep(dp + off) : LoadStream(dp + off);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) {
+          const float d = ToF32(px[u].v[e]) - shift[e];
+          if constexpr (kMode == kFwd) {
+            s1[e] += d;
+            s2[e] = fmaf(d, d, s2[e]);
+          } else {
+            const float g = ToF32(pd[u].v[e]);
+            s1[e] += g;
+            s2[e] = fmaf(g, d, s2[e]);
+          }
+        }
+      }
+    }
+    for (; r < r1; r += TY) {
+      const int64_t off = r * cv;
+      const P px = keep ? LoadKeep(xp + off) : LoadStream(xp + off);
+      P pd;
+      if constexpr (kMode == kGrad) {
+        pd = keep ? LoadKeep(dp + off) : LoadStream(dp + off);
+      }
+#pragma unroll
+      for (int e = 0; e < kVec; ++e) {
+        const float d = ToF32(px.v[e]) - shift[e];
+        if constexpr (kMode == kFwd) {
+          s1[e] += d;
+          s2[e] = fmaf(d, d, s2[e]);
+        } else {
+          const float g = ToF32(pd.v[e]);
+          s1[e] += g;
+          s2[e] = fmaf(g, d, s2[e]);
+        }
+      }
+    }
+  }
+
+  // Fold the ty row lanes.  red[(s * kVec + e)][ty][tx]
+  __shared__ float red[2 * kVec * kThreads];
+  if (TY > 1) {
+#pragma unroll
+    for (int e = 0; e < kVec; ++e) {
+      red[((0 * kVec + e) * TY + ty) * TX + tx] = s1[e];
+      red[((1 * kVec + e) * TY + ty) * TX + tx] = s2[e];
+    }
+    __syncthreads();
+    const int tid = ty * TX + tx;
+    const int n_out = 2 * kVec * TX;
+    for (int o = tid; o < n_out; o += kThreads) {
+      const int otx = o % TX;
+      const int se = o / TX;  // s * kVec + e
+      float acc = 0.0f;
+      for (int j = 0; j < TY; ++j) acc += red[(se * TY + j) * TX + otx];
+      const int64_t ocol = static_cast<int64_t>(blockIdx.x) * TX + otx;
+      if (ocol < cv) {
+        const int s = se / kVec, e = se % kVec;
+        partial[(static_cast<int64_t>(blockIdx.y) * 2 + s) * channels +
+                ocol * kVec + e] = acc;
+      }
+    }
+  } else if (active) {
+#pragma unroll
+    for (int e = 0; e < kVec; ++e) {
+      partial[(static_cast<int64_t>(blockIdx.y) * 2 + 0) * channels +
+              col * kVec + e] = s1[e];
+      partial[(static_cast<int64_t>(blockIdx.y) * 2 + 1) * channels +
+              col * kVec + e] = s2[e];
+    }
+  }
+}
+
+// General layout stats ([outer, C, inner], inner > 1 or unaligned): grid
+// (C, gy); a CTA walks the planes (n, c) of its split with all 256 threads.
+template <typename T, int kVec, int kMode>
+__global__ void __launch_bounds__(kThreads)
+    BnStatsInnerKernel(const T* __restrict__ x, const T* __restrict__ dy,
+                       const float* __restrict__ mean,
+                       float* __restrict__ partial, int64_t outer,
+                       int64_t channels, int64_t inner, int64_t outer_per_cta) {
+  using P = Pack<T, kVec>;
+  const int64_t c = blockIdx.x;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * outer_per_cta;
+  int64_t n1 = n0 + outer_per_cta;
+  if (n1 > outer) n1 = outer;
+  const float shift =
+      kMode == kFwd ? ToF32(x[c * inner]) : mean[c];
+  const int64_t inner_packs = inner / kVec;
+  float s1 = 0.0f, s2 = 0.0f;
+  for (int64_t n = n0; n < n1; ++n) {
+    const int64_t base = (n * channels + c) * inner;
+    const P* xp = reinterpret_cast<const P*>(x + base);
+    const P* dp = reinterpret_cast<const P*>(dy + base);
+    for (int64_t i = threadIdx.x; i < inner_packs; i += kThreads) {
+      const P px = LoadKeep(xp + i);
+      P pd;
+      if constexpr (kMode == kGrad) pd = LoadKeep(dp + i);
+#pragma unroll
+      for (int e = 0; e < kVec; ++e) {
+        const float d = ToF32(px.v[e]) - shift;
+        if constexpr (kMode == kFwd) {
+          s1 += d;
+          s2 = fmaf(d, d, s2);
+        } else {
+          const float g = ToF32(pd.v[e]);
+          s1 += g;
+          s2 = fmaf(g, d, s2);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+  }
+  __shared__ float red[2][kThreads / 32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    red[0][warp] = s1;
+    red[1][warp] = s2;
+  }
+  __syncthreads();
+  if (threadIdx.x < 2) {
+    float acc = 0.0f;
+    for (int w = 0; w < kThreads / 32; ++w) acc += red[threadIdx.x][w];
+    partial[(static_cast<int64_t>(blockIdx.y) * 2 + threadIdx.x) * channels +
+            c] = acc;
+  }
+}
+
+// ------------------------------------------------------------ level 2 ----
+
+struct FinalizeArgs {
+  const float* partial;  // [splits, 2, C] level-1 output (or NULL with sums)
+  int splits;
+  int64_t channels;
+  double count;          // values per channel behind the sums (all replicas)
+  // forward
+  const void* x_first;   // tensor base: the shift K is re-read from it
+  int x_dtype;
+  int64_t shift_stride;  // elements between consecutive channels' K
+  const float* est_mean;
+  const float* est_var;
+  float* batch_mean;
+  float* batch_var;
+  float* saved_mean;
+  float* saved_var;
+  float exp_avg_factor;
+  // gradient
+  const float* variance;
+  float* dscale;
+  float* doffset;
+  float epsilon;
+  // both: totals for the apply pass / the all-reduce
+  float* sums;           // [2, C] or NULL
+};
+
+__device__ __forceinline__ float LoadAsF32(const void* base, int dtype,
+                                           int64_t i) {
+  if (dtype == MUSA_DT_F32) return static_cast<const float*>(base)[i];
+  if (dtype == MUSA_DT_F16) return __half2float(static_cast<const __half*>(base)[i]);
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]);
+}
+
+__device__ __forceinline__ void WriteFwdStats(const FinalizeArgs& a, int64_t c,
+                                              double mean, double var) {
+  if (var < 0.0) var = 0.0;
+  const double n = a.count;
+  const double unbiased = n > 1.0 ? var * (n / (n - 1.0)) : var;
+  if (a.saved_mean) a.saved_mean[c] = static_cast<float>(mean);
+  if (a.saved_var) a.saved_var[c] = static_cast<float>(var);
+  const double f = static_cast<double>(a.exp_avg_factor);
+  double bm = mean, bv = unbiased;
+  if (a.exp_avg_factor != 1.0f && a.est_mean != nullptr &&
+      a.est_var != nullptr) {
+    bm = (1.0 - f) * static_cast<double>(a.est_mean[c]) + f * mean;
+    bv = (1.0 - f) * static_cast<double>(a.est_var[c]) + f * unbiased;
+  }
+  if (a.batch_mean) a.batch_mean[c] = static_cast<float>(bm);
+  if (a.batch_var) a.batch_var[c] = static_cast<float>(bv);
+}
+
+// kOut: 0 forward statistics, 1 forward raw sums (sum x, sum x^2) for the
+// cross-replica all-reduce, 2 gradient (dscale, doffset and/or sums).
+// Block (8 channels, 128 partial lanes).
+template <int kOut>
+__global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
+  const int cx = threadIdx.x;  // 0..7
+  const int py = threadIdx.y;  // 0..127
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 8 + cx;
+  double t1 = 0.0, t2 = 0.0;
+  if (c < a.channels) {
+    for (int p = py; p < a.splits; p += 128) {
+      t1 += static_cast<double>(
+          a.partial[(static_cast<int64_t>(p) * 2 + 0) * a.channels + c]);
+      t2 += static_cast<double>(
+          a.partial[(static_cast<int64_t>(p) * 2 + 1) * a.channels + c]);
+    }
+  }
+  // A warp holds 4 partial lanes x 8 channels: fold lanes 8 and 16 apart.
+  t1 += __shfl_xor_sync(0xffffffffu, t1, 8);
+  t2 += __shfl_xor_sync(0xffffffffu, t2, 8);
+  t1 += __shfl_xor_sync(0xffffffffu, t1, 16);
+  t2 += __shfl_xor_sync(0xffffffffu, t2, 16);
+  __shared__ double red[2][32][8];
+  const int tid = py * 8 + cx;
+  const int warp = tid >> 5, lane = tid & 31;
+  if (lane < 8) {
+    red[0][warp][lane] = t1;
+    red[1][warp][lane] = t2;
+  }
+  __syncthreads();
+  if (tid < 8 && c < a.channels) {
+    double S1 = 0.0, S2 = 0.0;
+    for (int w = 0; w < 32; ++w) {
+      S1 += red[0][w][tid];
+      S2 += red[1][w][tid];
+    }
+    if constexpr (kOut == 0) {
+      const double K =
+          static_cast<double>(LoadAsF32(a.x_first, a.x_dtype, c * a.shift_stride));
+      const double md = S1 / a.count;
+      WriteFwdStats(a, c, K + md, S2 / a.count - md * md);
+    } else if constexpr (kOut == 1) {
+      const double K =
+          static_cast<double>(LoadAsF32(a.x_first, a.x_dtype, c * a.shift_stride));
+      // Local rows only: count is this replica's.
+      a.sums[c] = static_cast<float>(S1 + a.count * K);
+      a.sums[a.channels + c] =
+          static_cast<float>(S2 + 2.0 * K * S1 + a.count * K * K);
+    } else {
+      if (a.sums) {
+        a.sums[c] = static_cast<float>(S1);
+        a.sums[a.channels + c] = static_cast<float>(S2);
+      }
+      if (a.doffset) a.doffset[c] = static_cast<float>(S1);
+      if (a.dscale) {
+        const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
+        a.dscale[c] = static_cast<float>(S2) * inv;
+      }
+    }
+  }
+}
+
+// Per-channel epilogues when the sums already exist (after an all-reduce).
+__global__ void BnFinalizeFromSumsKernel(FinalizeArgs a, const float* sums) {
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c >= a.channels) return;
+  const double mean = static_cast<double>(sums[c]) / a.count;
+  const double var =
+      static_cast<double>(sums[a.channels + c]) / a.count - mean * mean;
+  WriteFwdStats(a, c, mean, var);
+}
+
+__global__ void BnGradScalesFromSumsKernel(const float* sums,
+                                           const float* variance, float epsilon,
+                                           float* dscale, float* doffset,
+                                           int64_t channels) {
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  doffset[c] = sums[c];
+  dscale[c] = sums[channels + c] * (1.0f / sqrtf(variance[c] + epsilon));
+}
+
+__global__ void ScaleKernel(float* data, float factor, int count) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) data[i] *= factor;
+}
+
+__global__ void InvStdKernel(const float* variance, float* inv_std,
+                             float epsilon, int count) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) inv_std[i] = 1.0f / sqrtf(variance[i] + epsilon);
+}
+
+// ---------------------------------------------------------- apply pass ----
+
+// Per-channel coefficients of the element-wise pass.
+//   forward : y  = (x - mean) * a + b          a = scale*inv, b = offset
+//   gradient: dx = a * (dy - c1 - (x - mean) * c2)
+//             training : a = scale*inv, c1 = S1/R, c2 = S2*inv*inv/R
+//             inference: a = scale*inv, c1 = c2 = 0
+struct ApplyArgs {
+  const float* scale;
+  const float* offset;    // forward only
+  const float* mean;
+  const float* variance;
+  const float* sums;      // gradient: [2, C] totals (NULL for inference grad)
+  float inv_count;        // gradient: 1 / R over all replicas
+  float epsilon;
+};
+
+template <typename T, int kVec, int kUnroll, int kMode>
+__global__ void __launch_bounds__(kThreads)
+    BnApplyLastKernel(const T* __restrict__ x, const T* __restrict__ dy,
+                      T* __restrict__ out, ApplyArgs a, int64_t rows,
+                      int64_t cv, int64_t channels, int64_t rows_per_cta,
+                      bool reverse) {
+  using P = Pack<T, kVec>;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int TX = blockDim.x, TY = blockDim.y;
+  const int64_t col = static_cast<int64_t>(blockIdx.x) * TX + tx;
+  if (col >= cv) return;
+  const int64_t chunk =
+      reverse ? (gridDim.y - 1 - blockIdx.y) : blockIdx.y;
+  const int64_t r0 = chunk * rows_per_cta;
+  int64_t r1 = r0 + rows_per_cta;
+  if (r1 > rows) r1 = rows;
+
+  float mean[kVec], ca[kVec], cb[kVec], cc[kVec];
+#pragma unroll
+  for (int e = 0; e < kVec; ++e) {
+    const int64_t c = col * kVec + e;
+    const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
+    mean[e] = a.mean[c];
+    ca[e] = a.scale[c] * inv;
+    if constexpr (kMode == kFwd) {
+      cb[e] = a.offset[c];
+      cc[e] = 0.0f;
+    } else {
+      if (a.sums != nullptr) {
+        cb[e] = a.sums[c] * a.inv_count;
+        cc[e] = a.sums[channels + c] * inv * inv * a.inv_count;
+      } else {
+        cb[e] = 0.0f;
+        cc[e] = 0.0f;
+      }
+    }
+  }
+
+  const P* xp = reinterpret_cast<const P*>(x) + col;
+  const P* dp = reinterpret_cast<const P*>(dy) + col;
+  P* op = reinterpret_cast<P*>(out) + col;
+  const int64_t n_rows = r1 - r0;
+  // Row lane ty visits local rows ty, ty + TY, ...; in reverse mode the local
+  // index is mirrored.
+  const int64_t step = static_cast<int64_t>(TY) * kUnroll;
+  for (int64_t l = ty; l < n_rows; l += step) {
+    P px[kUnroll];
+    P pd[kUnroll];
+    int64_t off[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t li = l + static_cast<int64_t>(u) * TY;
+      const bool ok = li < n_rows;
+      const int64_t r = reverse ? (r1 - 1 - li) : (r0 + li);
+      off[u] = ok ? r * cv : -1;
+      if (ok) {
+        px[u] = LoadKeep(xp + off[u]);
+        if constexpr (kMode == kGrad) pd[u] = LoadKeep(dp + off[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (off[u] >= 0) {
+        P o;
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) {
+          const float d = ToF32(px[u].v[e]) - mean[e];
+          float r;
+          if constexpr (kMode == kFwd) {
+            r = fmaf(d, ca[e], cb[e]);
+          } else {
+            const float g = ToF32(pd[u].v[e]);
+            r = ca[e] * (g - cb[e] - d * cc[e]);
+          }
+          o.v[e] = FromF32<T>(r);
+        }
+        StoreStream(op + off[u], o);
+      }
+    }
+  }
+}
+
+// General layout apply: packs never straddle a plane.
+template <typename T, int kVec, int kMode>
+__global__ void __launch_bounds__(kThreads)
+    BnApplyInnerKernel(const T* __restrict__ x, const T* __restrict__ dy,
+                       T* __restrict__ out, ApplyArgs a, int64_t n_packs,
+                       int64_t inner_packs, int64_t channels) {
+  using P = Pack<T, kVec>;
+  const P* xp = reinterpret_cast<const P*>(x);
+  const P* dp = reinterpret_cast<const P*>(dy);
+  P* op = reinterpret_cast<P*>(out);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+       i < n_packs; i += stride) {
+    const int64_t c = (i / inner_packs) % channels;
+    const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
+    const float mean = a.mean[c];
+    const float ca = a.scale[c] * inv;
+    float cb, cc = 0.0f;
+    if constexpr (kMode == kFwd) {
+      cb = a.offset[c];
+    } else {
+      cb = a.sums ? a.sums[c] * a.inv_count : 0.0f;
+      cc = a.sums ? a.sums[channels + c] * inv * inv * a.inv_count : 0.0f;
+    }
+    const P px = LoadKeep(xp + i);
+    P pd;
+    if constexpr (kMode == kGrad) pd = LoadKeep(dp + i);
+    P o;
+#pragma unroll
+    for (int e = 0; e < kVec; ++e) {
+      const float d = ToF32(px.v[e]) - mean;
+      float r;
+      if constexpr (kMode == kFwd) {
+        r = fmaf(d, ca, cb);
+      } else {
+        r = ca * (ToF32(pd.v[e]) - cb - d * cc);
+      }
+      o.v[e] = FromF32<T>(r);
+    }
+    StoreStream(op + i, o);
+  }
+}
+
+// ------------------------------------------------------------ host side --
+
+template <typename T>
+struct DtypeCode;
+template <>
+struct DtypeCode<float> {
+  static constexpr int value = MUSA_DT_F32;
+};
+template <>
+struct DtypeCode<__half> {
+  static constexpr int value = MUSA_DT_F16;
+};
+template <>
+struct DtypeCode<__nv_bfloat16> {
+  static constexpr int value = MUSA_DT_BF16;
+};
+
+struct Geom {
+  int64_t outer, channels, inner;
+  int64_t rows() const { return outer * inner; }  // values per channel
+};
+
+inline int CheckGeom(const Geom& g) {
+  if (g.outer < 0 || g.channels < 0 || g.inner < 0) return MUSA_KERNELS_EINVAL;
+  return MUSA_KERNELS_OK;
+}
+
+inline bool IsEmpty(const Geom& g) {
+  return g.outer == 0 || g.channels == 0 || g.inner == 0;
+}
+
+inline size_t WorkspaceBytes(const Geom& g) {
+  if (IsEmpty(g)) return 0;
+  const int64_t floats =
+      MaxSplits(g.outer, g.channels) * 2 * g.channels +
+      2 * g.channels;
+  return static_cast<size_t>(floats) * sizeof(float);
+}
+
+// Stats launch: fills partial[splits][2][C]; returns splits (<0: error).
+template <typename T, int kMode>
+int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
+                const Geom& g, cudaStream_t stream) {
+  constexpr int kVec = VecWidth<T>::value;
+  constexpr int kUnroll = 4;
+  const bool keep = GetTuning(kTuneBnStatsKeep) != 0;
+  const bool aligned = Aligned16(x) && (kMode == kFwd || Aligned16(dy));
+  if (g.inner == 1) {
+    if (g.channels % kVec == 0 && aligned) {
+      const int64_t cv = g.channels / kVec;
+      const Plan p = PlanLast(g.outer, g.channels, cv, kUnroll, true);
+      BnStatsLastKernel<T, kVec, kUnroll, kMode>
+          <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
+              x, dy, mean, partial, g.outer, cv, g.channels, p.rows_per_cta,
+              keep);
+      return p.gy;
+    }
+    const Plan p = PlanLast(g.outer, g.channels, g.channels, kUnroll, true);
+    BnStatsLastKernel<T, 1, kUnroll, kMode>
+        <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
+            x, dy, mean, partial, g.outer, g.channels, g.channels,
+            p.rows_per_cta, keep);
+    return p.gy;
+  }
+  // [outer, C, inner]: one grid column per channel.
+  int64_t target = static_cast<int64_t>(SmCount()) * 8 / g.channels;
+  if (target < 1) target = 1;
+  int64_t gy = target < g.outer ? target : g.outer;
+  const int64_t cap = MaxSplits(g.outer, g.channels);
+  if (gy > cap) gy = cap;
+  if (gy > 65535) gy = 65535;
+  const int64_t per = CeilDiv(g.outer, gy);
+  gy = CeilDiv(g.outer, per);
+  if (g.channels > 0x7fffffffLL) return MUSA_KERNELS_ETOOLARGE;
+  const dim3 grid(static_cast<unsigned>(g.channels), static_cast<unsigned>(gy));
+  if (g.inner % kVec == 0 && aligned) {
+    BnStatsInnerKernel<T, kVec, kMode><<<grid, kThreads, 0, stream>>>(
+        x, dy, mean, partial, g.outer, g.channels, g.inner, per);
+  } else {
+    BnStatsInnerKernel<T, 1, kMode><<<grid, kThreads, 0, stream>>>(
+        x, dy, mean, partial, g.outer, g.channels, g.inner, per);
+  }
+  return static_cast<int>(gy);
+}
+
+template <int kOut>
+void LaunchFinalize(const FinalizeArgs& a, cudaStream_t stream) {
+  const int grid = static_cast<int>(CeilDiv(a.channels, 8));
+  BnFinalizeKernel<kOut><<<grid, dim3(8, 128), 0, stream>>>(a);
+}
+
+template <typename T, int kMode>
+void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
+                 const Geom& g, cudaStream_t stream) {
+  constexpr int kVec = VecWidth<T>::value;
+  constexpr int kUnroll = 4;
+  const bool reverse = GetTuning(kTuneBnApplyReverse) != 0;
+  const bool aligned =
+      Aligned16(x) && Aligned16(out) && (kMode == kFwd || Aligned16(dy));
+  if (g.inner == 1) {
+    if (g.channels % kVec == 0 && aligned) {
+      const int64_t cv = g.channels / kVec;
+      const Plan p = PlanLast(g.outer, g.channels, cv, kUnroll, false);
+      BnApplyLastKernel<T, kVec, kUnroll, kMode>
+          <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
+              x, dy, out, a, g.outer, cv, g.channels, p.rows_per_cta, reverse);
+    } else {
+      const Plan p = PlanLast(g.outer, g.channels, g.channels, kUnroll, false);
+      BnApplyLastKernel<T, 1, kUnroll, kMode>
+          <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
+              x, dy, out, a, g.outer, g.channels, g.channels, p.rows_per_cta,
+              reverse);
+    }
+    return;
+  }
+  const int64_t n = g.outer * g.channels * g.inner;
+  if (g.inner % kVec == 0 && aligned) {
+    const int64_t n_packs = n / kVec;
+    int64_t blocks = CeilDiv(n_packs, kThreads);
+    const int64_t cap = static_cast<int64_t>(SmCount()) * 16;
+    if (blocks > cap) blocks = cap;
+    BnApplyInnerKernel<T, kVec, kMode>
+        <<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
+            x, dy, out, a, n_packs, g.inner / kVec, g.channels);
+  } else {
+    int64_t blocks = CeilDiv(n, kThreads);
+    const int64_t cap = static_cast<int64_t>(SmCount()) * 16;
+    if (blocks > cap) blocks = cap;
+    BnApplyInnerKernel<T, 1, kMode>
+        <<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
+            x, dy, out, a, n, g.inner, g.channels);
+  }
+}
+
+inline int LastError() { return static_cast<int>(cudaGetLastError()); }
+
+template <typename T>
+int FwdTrain(const void* x, const float* scale, const float* offset,
+             const float* est_mean, const float* est_var, void* y,
+             float* batch_mean, float* batch_var, float* saved_mean,
+             float* saved_var, int64_t outer, int64_t channels, int64_t inner,
+             float epsilon, float exp_avg_factor, void* workspace,
+             size_t workspace_bytes, cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (IsEmpty(g)) return MUSA_KERNELS_OK;
+  if (!x || !y || !scale || !offset || !saved_mean || !saved_var) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  if (exp_avg_factor != 1.0f && (!est_mean || !est_var)) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
+      !Aligned16(workspace)) {
+    return MUSA_KERNELS_EWORKSPACE;
+  }
+  float* partial = static_cast<float*>(workspace);
+  const T* xt = static_cast<const T*>(x);
+  const int splits = LaunchStats<T, kFwd>(xt, nullptr, nullptr, partial, g, stream);
+  if (splits < 0) return splits;
+  FinalizeArgs f{};
+  f.partial = partial;
+  f.splits = splits;
+  f.channels = channels;
+  f.count = static_cast<double>(g.rows());
+  f.x_first = x;
+  f.x_dtype = DtypeCode<T>::value;
+  f.shift_stride = inner == 1 ? 1 : inner;
+  f.est_mean = est_mean;
+  f.est_var = est_var;
+  f.batch_mean = batch_mean;
+  f.batch_var = batch_var;
+  f.saved_mean = saved_mean;
+  f.saved_var = saved_var;
+  f.exp_avg_factor = exp_avg_factor;
+  LaunchFinalize<0>(f, stream);
+  ApplyArgs a{};
+  a.scale = scale;
+  a.offset = offset;
+  a.mean = saved_mean;
+  a.variance = saved_var;
+  a.epsilon = epsilon;
+  LaunchApply<T, kFwd>(xt, nullptr, static_cast<T*>(y), a, g, stream);
+  return LastError();
+}
+
+template <typename T>
+int FwdInfer(const void* x, const float* scale, const float* offset,
+             const float* est_mean, const float* est_var, void* y,
+             int64_t outer, int64_t channels, int64_t inner, float epsilon,
+             cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (IsEmpty(g)) return MUSA_KERNELS_OK;
+  if (!x || !y || !scale || !offset || !est_mean || !est_var) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  ApplyArgs a{};
+  a.scale = scale;
+  a.offset = offset;
+  a.mean = est_mean;
+  a.variance = est_var;
+  a.epsilon = epsilon;
+  LaunchApply<T, kFwd>(static_cast<const T*>(x), nullptr, static_cast<T*>(y), a,
+                       g, stream);
+  return LastError();
+}
+
+template <typename T>
+int Grad(const void* dy, const void* x, const float* scale, const float* mean,
+         const float* variance, void* dx, float* dscale, float* doffset,
+         int64_t outer, int64_t channels, int64_t inner, float epsilon,
+         bool is_training, void* workspace, size_t workspace_bytes,
+         cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (IsEmpty(g)) return MUSA_KERNELS_OK;
+  if (!dy || !x || !scale || !mean || !variance || !dx || !dscale || !doffset) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
+      !Aligned16(workspace)) {
+    return MUSA_KERNELS_EWORKSPACE;
+  }
+  float* partial = static_cast<float*>(workspace);
+  float* sums = partial + MaxSplits(g.outer, g.channels) * 2 * g.channels;
+  const T* xt = static_cast<const T*>(x);
+  const T* dyt = static_cast<const T*>(dy);
+  const int splits = LaunchStats<T, kGrad>(xt, dyt, mean, partial, g, stream);
+  if (splits < 0) return splits;
+  FinalizeArgs f{};
+  f.partial = partial;
+  f.splits = splits;
+  f.channels = channels;
+  f.count = static_cast<double>(g.rows());
+  f.variance = variance;
+  f.dscale = dscale;
+  f.doffset = doffset;
+  f.epsilon = epsilon;
+  f.sums = sums;
+  LaunchFinalize<2>(f, stream);
+  ApplyArgs a{};
+  a.scale = scale;
+  a.mean = mean;
+  a.variance = variance;
+  a.epsilon = epsilon;
+  a.sums = is_training ? sums : nullptr;
+  a.inv_count = static_cast<float>(1.0 / static_cast<double>(g.rows()));
+  LaunchApply<T, kGrad>(xt, dyt, static_cast<T*>(dx), a, g, stream);
+  return LastError();
+}
+
+template <typename T>
+int StatsSums(const void* x, float* sums, const Geom& g, void* workspace,
+              size_t workspace_bytes, cudaStream_t stream) {
+  if (!x || !sums) return MUSA_KERNELS_EINVAL;
+  if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
+      !Aligned16(workspace)) {
+    return MUSA_KERNELS_EWORKSPACE;
+  }
+  float* partial = static_cast<float*>(workspace);
+  const int splits = LaunchStats<T, kFwd>(static_cast<const T*>(x), nullptr,
+                                          nullptr, partial, g, stream);
+  if (splits < 0) return splits;
+  FinalizeArgs f{};
+  f.partial = partial;
+  f.splits = splits;
+  f.channels = g.channels;
+  f.count = static_cast<double>(g.rows());
+  f.x_first = x;
+  f.x_dtype = DtypeCode<T>::value;
+  f.shift_stride = g.inner == 1 ? 1 : g.inner;
+  f.sums = sums;
+  LaunchFinalize<1>(f, stream);
+  return LastError();
+}
+
+template <typename T>
+int GradStatsSums(const void* dy, const void* x, const float* mean, float* sums,
+                  const Geom& g, void* workspace, size_t workspace_bytes,
+                  cudaStream_t stream) {
+  if (!dy || !x || !mean || !sums) return MUSA_KERNELS_EINVAL;
+  if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
+      !Aligned16(workspace)) {
+    return MUSA_KERNELS_EWORKSPACE;
+  }
+  float* partial = static_cast<float*>(workspace);
+  const int splits =
+      LaunchStats<T, kGrad>(static_cast<const T*>(x), static_cast<const T*>(dy),
+                            mean, partial, g, stream);
+  if (splits < 0) return splits;
+  FinalizeArgs f{};
+  f.partial = partial;
+  f.splits = splits;
+  f.channels = g.channels;
+  f.count = static_cast<double>(g.rows());
+  f.sums = sums;
+  LaunchFinalize<2>(f, stream);
+  return LastError();
+}
+
+template <typename T>
+int GradApplyFromSums(const void* dy, const void* x, const float* scale,
+                      const float* mean, const float* variance,
+                      const float* sums, double total_count, void* dx,
+                      float* dscale, float* doffset, const Geom& g,
+                      float epsilon, cudaStream_t stream) {
+  if (!dy || !x || !scale || !mean || !variance || !sums || !dx) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  if (dscale && doffset) {
+    const int grid = static_cast<int>(CeilDiv(g.channels, 256));
+    BnGradScalesFromSumsKernel<<<grid, 256, 0, stream>>>(
+        sums, variance, epsilon, dscale, doffset, g.channels);
+  }
+  ApplyArgs a{};
+  a.scale = scale;
+  a.mean = mean;
+  a.variance = variance;
+  a.epsilon = epsilon;
+  a.sums = sums;
+  a.inv_count = static_cast<float>(1.0 / total_count);
+  LaunchApply<T, kGrad>(static_cast<const T*>(x), static_cast<const T*>(dy),
+                        static_cast<T*>(dx), a, g, stream);
+  return LastError();
+}
+
+}  // namespace
+}  // namespace musa_b200
+
+using namespace musa_b200;
+
+#define MUSA_BY_DTYPE(dtype, CALL)                      \
+  switch (dtype) {                                      \
+    case MUSA_DT_F32: {                                 \
+      using T = float;                                  \
+      return CALL;                                      \
+    }                                                   \
+    case MUSA_DT_F16: {                                 \
+      using T = __half;                                 \
+      return CALL;                                      \
+    }                                                   \
+    case MUSA_DT_BF16: {                                \
+      using T = __nv_bfloat16;                          \
+      return CALL;                                      \
+    }                                                   \
+    default:                                            \
+      return MUSA_KERNELS_EUNSUPPORTED;                 \
+  }
+
+extern "C" {
+
+size_t BnWorkspaceBytes(int64_t outer, int64_t channels, int64_t inner) {
+  const Geom g{outer, channels, inner};
+  if (CheckGeom(g) != MUSA_KERNELS_OK) return 0;
+  return WorkspaceBytes(g);
+}
+
+#define MUSA_DEFINE_BN(SUFFIX, TYPE)                                           \
+  int LaunchBnFwdTrain_##SUFFIX(                                               \
+      const void* x, const float* scale, const float* offset,                  \
+      const float* est_mean, const float* est_var, void* y, float* batch_mean, \
+      float* batch_var, float* saved_mean, float* saved_var, int64_t outer,    \
+      int64_t channels, int64_t inner, float epsilon, float exp_avg_factor,    \
+      void* workspace, size_t workspace_bytes, cudaStream_t stream) {          \
+    return FwdTrain<TYPE>(x, scale, offset, est_mean, est_var, y, batch_mean,  \
+                          batch_var, saved_mean, saved_var, outer, channels,   \
+                          inner, epsilon, exp_avg_factor, workspace,           \
+                          workspace_bytes, stream);                            \
+  }                                                                            \
+  int LaunchBnFwdInfer_##SUFFIX(                                               \
+      const void* x, const float* scale, const float* offset,                  \
+      const float* est_mean, const float* est_var, void* y, int64_t outer,     \
+      int64_t channels, int64_t inner, float epsilon, cudaStream_t stream) {   \
+    return FwdInfer<TYPE>(x, scale, offset, est_mean, est_var, y, outer,       \
+                          channels, inner, epsilon, stream);                   \
+  }                                                                            \
+  int LaunchBnGrad_##SUFFIX(                                                   \
+      const void* dy, const void* x, const float* scale, const float* mean,    \
+      const float* variance, void* dx, float* dscale, float* doffset,          \
+      int64_t outer, int64_t channels, int64_t inner, float epsilon,           \
+      bool is_training, void* workspace, size_t workspace_bytes,               \
+      cudaStream_t stream) {                                                   \
+    return Grad<TYPE>(dy, x, scale, mean, variance, dx, dscale, doffset,       \
+                      outer, channels, inner, epsilon, is_training, workspace, \
+                      workspace_bytes, stream);                                \
+  }
+
+MUSA_DEFINE_BN(F32, float)
+MUSA_DEFINE_BN(F16, __half)
+MUSA_DEFINE_BN(BF16, __nv_bfloat16)
+#undef MUSA_DEFINE_BN
+
+void LaunchBesselCorrection(float* data, float factor, int count,
+                            cudaStream_t stream) {
+  if (count <= 0) return;
+  ScaleKernel<<<(count + 255) / 256, 256, 0, stream>>>(data, factor, count);
+}
+
+void LaunchVarianceToInvStd(const float* variance, float* inv_std,
+                            float epsilon, int count, cudaStream_t stream) {
+  if (count <= 0) return;
+  InvStdKernel<<<(count + 255) / 256, 256, 0, stream>>>(variance, inv_std,
+                                                       epsilon, count);
+}
+
+int LaunchBnStatsSums(int dtype, const void* x, float* sums, int64_t outer,
+                      int64_t channels, int64_t inner, void* workspace,
+                      size_t workspace_bytes, cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!sums) return MUSA_KERNELS_EINVAL;
+  if (IsEmpty(g)) {
+    // A replica with no rows contributes zeros to the all-reduce.
+    return static_cast<int>(
+        cudaMemsetAsync(sums, 0, sizeof(float) * 2 * channels, stream));
+  }
+  MUSA_BY_DTYPE(dtype,
+                StatsSums<T>(x, sums, g, workspace, workspace_bytes, stream));
+}
+
+int LaunchBnFinalizeFromSums(const float* sums, double total_count,
+                             const float* est_mean, const float* est_var,
+                             float* batch_mean, float* batch_var,
+                             float* saved_mean, float* saved_var,
+                             int64_t channels, float exp_avg_factor,
+                             cudaStream_t stream) {
+  if (channels < 0 || !(total_count > 0.0)) return MUSA_KERNELS_EINVAL;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!sums || !saved_mean || !saved_var) return MUSA_KERNELS_EINVAL;
+  if (exp_avg_factor != 1.0f && (!est_mean || !est_var)) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  FinalizeArgs f{};
+  f.channels = channels;
+  f.count = total_count;
+  f.est_mean = est_mean;
+  f.est_var = est_var;
+  f.batch_mean = batch_mean;
+  f.batch_var = batch_var;
+  f.saved_mean = saved_mean;
+  f.saved_var = saved_var;
+  f.exp_avg_factor = exp_avg_factor;
+  const int grid = static_cast<int>(CeilDiv(channels, 256));
+  BnFinalizeFromSumsKernel<<<grid, 256, 0, stream>>>(f, sums);
+  return LastError();
+}
+
+int LaunchBnApply(int dtype, const void* x, const float* scale,
+                  const float* offset, const float* mean, const float* variance,
+                  void* y, int64_t outer, int64_t channels, int64_t inner,
+                  float epsilon, cudaStream_t stream) {
+  MUSA_BY_DTYPE(dtype, FwdInfer<T>(x, scale, offset, mean, variance, y, outer,
+                                   channels, inner, epsilon, stream));
+}
+
+int LaunchBnGradStatsSums(int dtype, const void* dy, const void* x,
+                          const float* mean, float* sums, int64_t outer,
+                          int64_t channels, int64_t inner, void* workspace,
+                          size_t workspace_bytes, cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!sums) return MUSA_KERNELS_EINVAL;
+  if (IsEmpty(g)) {
+    return static_cast<int>(
+        cudaMemsetAsync(sums, 0, sizeof(float) * 2 * channels, stream));
+  }
+  MUSA_BY_DTYPE(dtype, GradStatsSums<T>(dy, x, mean, sums, g, workspace,
+                                        workspace_bytes, stream));
+}
+
+int LaunchBnGradApplyFromSums(int dtype, const void* dy, const void* x,
+                              const float* scale, const float* mean,
+                              const float* variance, const float* sums,
+                              double total_count, void* dx, float* dscale,
+                              float* doffset, int64_t outer, int64_t channels,
+                              int64_t inner, float epsilon,
+                              cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (IsEmpty(g)) return MUSA_KERNELS_OK;
+  if (!(total_count > 0.0)) return MUSA_KERNELS_EINVAL;
+  MUSA_BY_DTYPE(dtype, GradApplyFromSums<T>(dy, x, scale, mean, variance, sums,
+                                            total_count, dx, dscale, doffset,
+                                            g, epsilon, stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,292 @@
+// BiasAdd + activation chains as one read of x and one write of y.
+//
+// y = act(x + bias[channel]) with act in {identity, relu, swish, sigmoid};
+// `swish` is the three-op chain Mul(x, Sigmoid(BiasAdd(x, b))).  The tensor is
+// viewed as [outer, channels, inner]; channels-last inputs (inner == 1) take a
+// 128-bit path where the bias pack comes from L1, everything else a pack path
+// with one bias value per pack or an element-wise path.
+//
+// Semantics follow the un-fused ops the chain replaces: BiasAdd
+// (musa_ext/kernels/nn/musa_biasadd_op.cc:23-61), Relu
+// (musa_ext/kernels/nn/musa_relu_op.cc:19-57), Sigmoid
+// (musa_ext/kernels/nn/musa_sigmoid_op.cc:18-35).
+#include "common.cuh"
+#include "tuning.h"
+#include "../../include/musa_plugin_kernels.h"
+
+namespace musa_b200 {
+namespace {
+
+// fp32 keeps libm-grade exp and an IEEE divide (rtol 1e-5 against the CPU op,
+// inputs up to +-100); the 16-bit types round to 8 or 11 mantissa bits on
+// store, so the hardware exp2/rcp approximations (1e-6 relative) are exact
+// after rounding for all practical purposes and halve the instruction count.
+template <bool kFast>
+__device__ __forceinline__ float Sigmoid(float t) {
+  if constexpr (kFast) {
+    return __fdividef(1.0f, 1.0f + __expf(-t));
+  } else {
+    return 1.0f / (1.0f + expf(-t));
+  }
+}
+
+template <int kAct, bool kFast>
+__device__ __forceinline__ float Activate(float x, float b) {
+  const float t = x + b;
+  if constexpr (kAct == MUSA_ACT_IDENTITY) {
+    return t;
+  } else if constexpr (kAct == MUSA_ACT_RELU) {
+    // max(t, 0) that lets NaN through, as the CPU op does.
+    return t < 0.0f ? 0.0f : t;
+  } else if constexpr (kAct == MUSA_ACT_SWISH) {
+    return x * Sigmoid<kFast>(t);
+  } else {
+    return Sigmoid<kFast>(t);
+  }
+}
+
+// Channels-last pack kernel.  Pack p of the flat tensor covers channels
+// [(p % cv) * kEpt, +kEpt); the column is tracked incrementally, no division
+// in the loop.
+template <typename T, int kEpt, int kUnroll, int kAct, bool kHasBias>
+__global__ void __launch_bounds__(256)
+    BiasActLastKernel(const T* __restrict__ x, const T* __restrict__ bias,
+                      T* __restrict__ y, int64_t n_packs, int cv) {
+  using P = Pack<T, kEpt>;
+  constexpr bool kFast = sizeof(T) == 2;
+  const P* xp = reinterpret_cast<const P*>(x);
+  const P* bp = reinterpret_cast<const P*>(bias);
+  P* yp = reinterpret_cast<P*>(y);
+  const int64_t tile = static_cast<int64_t>(blockDim.x) * kUnroll;
+  const int64_t n_tiles = (n_packs + tile - 1) / tile;
+  const int step = static_cast<int>(blockDim.x % cv);
+
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int64_t base = t * tile + threadIdx.x;
+    int col = static_cast<int>(base % cv);
+    P px[kUnroll];
+    P pb[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+      if (i < n_packs) {
+        px[u] = LoadStream(xp + i);
+        if constexpr (kHasBias) pb[u] = LoadKeep(bp + col);
+      }
+      col += step;
+      if (col >= cv) col -= cv;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+      if (i < n_packs) {
+        P out;
+#pragma unroll
+        for (int e = 0; e < kEpt; ++e) {
+          const float b = kHasBias ? ToF32(pb[u].v[e]) : 0.0f;
+          out.v[e] = FromF32<T>(Activate<kAct, kFast>(ToF32(px[u].v[e]), b));
+        }
+        StoreStream(yp + i, out);
+      }
+    }
+  }
+}
+
+// General layout: [outer, channels, inner] with packs of kEpt elements that
+// never straddle a channel (inner % kEpt == 0), or kEpt == 1.
+template <typename T, int kEpt, int kAct, bool kHasBias>
+__global__ void __launch_bounds__(256)
+    BiasActInnerKernel(const T* __restrict__ x, const T* __restrict__ bias,
+                       T* __restrict__ y, int64_t n_packs, int64_t inner_packs,
+                       int64_t channels) {
+  using P = Pack<T, kEpt>;
+  constexpr bool kFast = sizeof(T) == 2;
+  const P* xp = reinterpret_cast<const P*>(x);
+  P* yp = reinterpret_cast<P*>(y);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+       i < n_packs; i += stride) {
+    const P px = LoadStream(xp + i);
+    float b = 0.0f;
+    if constexpr (kHasBias) b = ToF32(bias[(i / inner_packs) % channels]);
+    P out;
+#pragma unroll
+    for (int e = 0; e < kEpt; ++e) {
+      out.v[e] = FromF32<T>(Activate<kAct, kFast>(ToF32(px.v[e]), b));
+    }
+    StoreStream(yp + i, out);
+  }
+}
+
+// Exact-arithmetic kernel for the remaining BiasAdd dtypes (double, int32,
+// int64): the add is done in T.
+template <typename T, bool kRelu>
+__global__ void __launch_bounds__(256)
+    BiasAddExactKernel(const T* __restrict__ x, const T* __restrict__ bias,
+                       T* __restrict__ y, int64_t n, int64_t inner,
+                       int64_t channels) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+       i < n; i += stride) {
+    T t = x[i];
+    if (bias != nullptr) t = t + bias[(i / inner) % channels];
+    if (kRelu) t = t < T(0) ? T(0) : t;
+    y[i] = t;
+  }
+}
+
+int GridFor(int64_t work_items, int per_sm_cap) {
+  int64_t blocks = work_items < 1 ? 1 : work_items;
+  const int64_t cap = static_cast<int64_t>(SmCount()) * per_sm_cap;
+  if (per_sm_cap > 0 && blocks > cap) blocks = cap;
+  if (blocks > 0x7fffffffLL) blocks = 0x7fffffffLL;
+  return static_cast<int>(blocks);
+}
+
+template <typename T, int kAct, bool kHasBias>
+int LaunchTyped(const T* x, const T* bias, T* y, int64_t outer,
+                int64_t channels, int64_t inner, cudaStream_t stream) {
+  constexpr int kVec = VecWidth<T>::value;
+  const int64_t n = outer * channels * inner;
+  const bool aligned = Aligned16(x) && Aligned16(y);
+  if (!kHasBias && aligned && n >= kVec) {
+    // Activation alone: the tensor is one flat run of packs plus a tail.
+    const int64_t n_packs = n / kVec;
+    const int grid =
+        GridFor(CeilDiv(n_packs, 256 * 4), GetTuning(kTuneBiasActCtasPerSm));
+    BiasActLastKernel<T, kVec, 4, kAct, false>
+        <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, 1);
+    const int64_t done = n_packs * kVec;
+    if (done < n) {
+      BiasActInnerKernel<T, 1, kAct, false><<<1, 256, 0, stream>>>(
+          x + done, bias, y + done, n - done, 1, 1);
+    }
+    return static_cast<int>(cudaGetLastError());
+  }
+  if (inner == 1 && channels % kVec == 0 && aligned &&
+      (!kHasBias || Aligned16(bias)) && channels / kVec <= 0x7fffffff) {
+    const int64_t n_packs = n / kVec;
+    const int cv = static_cast<int>(channels / kVec);
+    const int per_sm = GetTuning(kTuneBiasActCtasPerSm);
+    const int unroll = GetTuning(kTuneBiasActUnroll);
+    if (unroll == 2) {
+      const int grid = GridFor(CeilDiv(n_packs, 256 * 2), per_sm);
+      BiasActLastKernel<T, kVec, 2, kAct, kHasBias>
+          <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
+    } else if (unroll == 8) {
+      const int grid = GridFor(CeilDiv(n_packs, 256 * 8), per_sm);
+      BiasActLastKernel<T, kVec, 8, kAct, kHasBias>
+          <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
+    } else {
+      const int grid = GridFor(CeilDiv(n_packs, 256 * 4), per_sm);
+      BiasActLastKernel<T, kVec, 4, kAct, kHasBias>
+          <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
+    }
+  } else if (inner % kVec == 0 && aligned) {
+    const int64_t n_packs = n / kVec;
+    const int grid = GridFor(CeilDiv(n_packs, 256), 16);
+    BiasActInnerKernel<T, kVec, kAct, kHasBias><<<grid, 256, 0, stream>>>(
+        x, bias, y, n_packs, inner / kVec, channels);
+  } else {
+    const int grid = GridFor(CeilDiv(n, 256), 16);
+    BiasActInnerKernel<T, 1, kAct, kHasBias>
+        <<<grid, 256, 0, stream>>>(x, bias, y, n, inner, channels);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <typename T>
+int LaunchBiasAct(const void* x, const void* bias, void* y, int64_t outer,
+                  int64_t channels, int64_t inner, int act,
+                  cudaStream_t stream) {
+  if (outer < 0 || channels < 0 || inner < 0) return MUSA_KERNELS_EINVAL;
+  if (outer == 0 || channels == 0 || inner == 0) return MUSA_KERNELS_OK;
+  if (x == nullptr || y == nullptr) return MUSA_KERNELS_EINVAL;
+  const T* xt = static_cast<const T*>(x);
+  const T* bt = static_cast<const T*>(bias);
+  T* yt = static_cast<T*>(y);
+#define MUSA_DISPATCH_ACT(ACT)                                               \
+  case ACT:                                                                  \
+    return bias != nullptr                                                   \
+               ? LaunchTyped<T, ACT, true>(xt, bt, yt, outer, channels,      \
+                                           inner, stream)                    \
+               : LaunchTyped<T, ACT, false>(xt, bt, yt, outer, channels,     \
+                                            inner, stream);
+  switch (act) {
+    MUSA_DISPATCH_ACT(MUSA_ACT_IDENTITY)
+    MUSA_DISPATCH_ACT(MUSA_ACT_RELU)
+    MUSA_DISPATCH_ACT(MUSA_ACT_SWISH)
+    MUSA_DISPATCH_ACT(MUSA_ACT_SIGMOID)
+    default:
+      return MUSA_KERNELS_EUNSUPPORTED;
+  }
+#undef MUSA_DISPATCH_ACT
+}
+
+template <typename T>
+int LaunchBiasAddExact(const void* x, const void* bias, void* y, int64_t outer,
+                       int64_t channels, int64_t inner, int act,
+                       cudaStream_t stream) {
+  if (outer < 0 || channels < 0 || inner < 0) return MUSA_KERNELS_EINVAL;
+  if (outer == 0 || channels == 0 || inner == 0) return MUSA_KERNELS_OK;
+  if (x == nullptr || y == nullptr) return MUSA_KERNELS_EINVAL;
+  if (act != MUSA_ACT_IDENTITY && act != MUSA_ACT_RELU) {
+    return MUSA_KERNELS_EUNSUPPORTED;
+  }
+  const int64_t n = outer * channels * inner;
+  const int grid = GridFor(CeilDiv(n, 256), 16);
+  if (act == MUSA_ACT_RELU) {
+    BiasAddExactKernel<T, true><<<grid, 256, 0, stream>>>(
+        static_cast<const T*>(x), static_cast<const T*>(bias),
+        static_cast<T*>(y), n, inner, channels);
+  } else {
+    BiasAddExactKernel<T, false><<<grid, 256, 0, stream>>>(
+        static_cast<const T*>(x), static_cast<const T*>(bias),
+        static_cast<T*>(y), n, inner, channels);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace musa_b200
+
+using namespace musa_b200;
+
+extern "C" {
+
+int LaunchBiasAct_F32(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream) {
+  return LaunchBiasAct<float>(x, bias, y, outer, channels, inner, act, stream);
+}
+int LaunchBiasAct_F16(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream) {
+  return LaunchBiasAct<__half>(x, bias, y, outer, channels, inner, act, stream);
+}
+int LaunchBiasAct_BF16(const void* x, const void* bias, void* y, int64_t outer,
+                       int64_t channels, int64_t inner, int act,
+                       cudaStream_t stream) {
+  return LaunchBiasAct<__nv_bfloat16>(x, bias, y, outer, channels, inner, act,
+                                      stream);
+}
+int LaunchBiasAct_F64(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream) {
+  return LaunchBiasAddExact<double>(x, bias, y, outer, channels, inner, act,
+                                    stream);
+}
+int LaunchBiasAct_I32(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream) {
+  return LaunchBiasAddExact<int32_t>(x, bias, y, outer, channels, inner, act,
+                                     stream);
+}
+int LaunchBiasAct_I64(const void* x, const void* bias, void* y, int64_t outer,
+                      int64_t channels, int64_t inner, int act,
+                      cudaStream_t stream) {
+  return LaunchBiasAddExact<int64_t>(x, bias, y, outer, channels, inner, act,
+                                     stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,22 @@
+// Process-wide launch-shape knobs.  The defaults are the shipped
+// configuration; MusaKernelsSetTuning() exists so that a sweep can compare
+// launch shapes without rebuilding.  Launchers only read these values.
+#pragma once
+
+namespace musa_b200 {
+
+enum TuningKey {
+  kTuneAdamCtasPerSm = 0,   // 0: one tile per CTA; k: persistent, k CTAs per SM
+  kTuneAdamUnroll = 1,      // packs in flight per thread and stream: 1, 2, 4
+  kTuneBiasActCtasPerSm = 2,
+  kTuneBiasActUnroll = 3,
+  kTuneBnCtasPerSm = 4,     // CTAs per SM of the BatchNorm stats/apply grids
+  kTuneBnFused = 5,         // 1: single cooperative kernel when it applies
+  kTuneBnApplyReverse = 6,  // 1: apply pass walks rows in reverse (L2 reuse)
+  kTuneBnStatsKeep = 7,     // 1: stats pass loads with the default L2 policy
+  kTuneCount = 16
+};
+
+int GetTuning(int key);
+
+}  // namespace musa_b200

@@ -1,0 +1,171 @@
+"""Generates the golden vectors under tests/golden/ (run once, by hand, on a
+machine that has the reference checkout; the .npz files are committed).
+
+    python tests/golden/make_golden.py /path/to/reference
+
+What pins what:
+  adam_reference_numpy.npz
+      Expected values computed by the REFERENCE's own NumPy statement of the
+      Adam update, `MusaResourceSparseApplyAdamTest._compute_expected`
+      (test/ops/musa_resource_sparse_apply_adam_op_test.py:35-69), taken from
+      the reference file with `ast` (the module itself imports TensorFlow, which
+      is not installed) and run on seeded inputs with indices = arange(n), i.e.
+      as a dense update.  Includes the |1 - beta1^t| < 1e-10 first-step case.
+  bn_torch_cpu.npz
+      FusedBatchNorm forward/gradient cases at the shapes of the reference
+      tests (test/ops/fused_batchnorm_op_test.py:25-55, 97-141, 178-216,
+      358-448; test/ops/fused_batchnorm_hcnw_op_test.py:86-107), answered by an
+      INDEPENDENT implementation: PyTorch's CPU batch_norm in float64 and its
+      autograd.  TensorFlow's CPU kernel, the stated oracle, is not available;
+      these vectors pin the restatement to a second implementation, not to
+      TensorFlow.
+  elementwise_literals.npz
+      The literal inputs of the reference's Relu / Sigmoid / BiasAdd tests
+      (test/ops/relu_op_test.py:58-96, test/ops/sigmoid_op_test.py:58-93,
+      test/ops/biasadd_op_test.py:74-116) with closed-form float64 answers.
+"""
+import ast
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def reference_adam_fn(reference_root):
+    path = os.path.join(reference_root, "test", "ops",
+                        "musa_resource_sparse_apply_adam_op_test.py")
+    tree = ast.parse(open(path).read())
+    for node in ast.walk(tree):
+        if isinstance(node, ast.FunctionDef) and node.name == "_compute_expected":
+            mod = ast.Module(body=[node], type_ignores=[])
+            ns = {"np": np}
+            exec(compile(mod, path, "exec"), ns)
+            return ns["_compute_expected"]
+    raise RuntimeError("_compute_expected not found in " + path)
+
+
+def make_adam(reference_root):
+    fn = reference_adam_fn(reference_root)
+    rng = np.random.default_rng(3)
+    out = {}
+    cases = [
+        # name, n, beta1_power, beta2_power
+        ("step10", 4099, 0.9 ** 10, 0.999 ** 10),
+        ("first_step_guard", 257, 1.0, 1.0),
+        ("step1", 1024, 0.9, 0.999),
+    ]
+    for name, n, b1p, b2p in cases:
+        var = rng.normal(0, 0.05, n).astype(np.float32)
+        m = rng.normal(0, 1e-4, n).astype(np.float32)
+        v = rng.uniform(0, 1e-6, n).astype(np.float32)
+        grad = rng.normal(0, 1e-3, n).astype(np.float32)
+        lr, b1, b2, eps = (np.float32(1e-3), np.float32(0.9), np.float32(0.999),
+                           np.float32(1e-7))
+        ev, em, evv = fn(None, var, m, v, lr, b1, b2, eps, np.float32(b1p),
+                         np.float32(b2p), grad, np.arange(n))
+        out.update({
+            name + "/var": var, name + "/m": m, name + "/v": v, name + "/grad": grad,
+            name + "/scalars": np.array([b1p, b2p, lr, b1, b2, eps], np.float32),
+            name + "/expected_var": ev.astype(np.float32),
+            name + "/expected_m": em.astype(np.float32),
+            name + "/expected_v": evv.astype(np.float32),
+        })
+    np.savez_compressed(os.path.join(HERE, "adam_reference_numpy.npz"), **out)
+
+
+def make_bn():
+    import torch
+    import torch.nn.functional as F
+
+    rng = np.random.default_rng(11)
+    out = {}
+    # name, shape, data_format, mean, std
+    cases = [
+        ("nhwc_2x2x2x4", (2, 2, 2, 4), "NHWC", 0.0, 1.0),
+        ("nhwc_4x5x3x16", (4, 5, 3, 16), "NHWC", 0.5, 2.0),
+        ("keras2d_512x64", (512, 1, 1, 64), "NHWC", 0.0, 1.0),
+        ("nchw_2x3x4x5", (2, 3, 4, 5), "NCHW", 0.0, 1.0),
+        ("nchw_2x32x1x1", (2, 32, 1, 1), "NCHW", 0.0, 1.0),
+        ("nhwc_2x1x1x32", (2, 1, 1, 32), "NHWC", 0.0, 1.0),
+        ("nchw_large_var_8x6x16x16", (8, 6, 16, 16), "NCHW", 3.0, 30.0),
+        ("nhwc_large_mean_64x3x3x8", (64, 3, 3, 8), "NHWC", 1000.0, 1.0),
+    ]
+    eps = 1e-3
+    for name, shape, fmt, mu, sd in cases:
+        x = (rng.standard_normal(shape) * sd + mu).astype(np.float32)
+        c = shape[-1] if fmt == "NHWC" else shape[1]
+        scale = rng.uniform(0.5, 1.5, c).astype(np.float32)
+        offset = rng.normal(0, 0.1, c).astype(np.float32)
+        dy = rng.standard_normal(shape).astype(np.float32)
+        xt = torch.from_numpy(x).double()
+        if fmt == "NHWC":
+            xt = xt.permute(0, 3, 1, 2)
+            dyt = torch.from_numpy(dy).double().permute(0, 3, 1, 2)
+        else:
+            dyt = torch.from_numpy(dy).double()
+        xt = xt.contiguous().requires_grad_(True)
+        st = torch.from_numpy(scale).double().requires_grad_(True)
+        ot = torch.from_numpy(offset).double().requires_grad_(True)
+        y = F.batch_norm(xt, None, None, st, ot, training=True, eps=eps)
+        y.backward(dyt.contiguous())
+        red = (0, 2, 3)
+        mean = xt.detach().mean(dim=red)
+        var = xt.detach().var(dim=red, unbiased=False)
+        count = xt.numel() // c
+        unbiased = var * count / (count - 1) if count > 1 else var
+
+        def back(t):
+            t = t.detach()
+            if fmt == "NHWC":
+                t = t.permute(0, 2, 3, 1)
+            return t.contiguous().numpy().astype(np.float32)
+
+        out.update({
+            name + "/x": x, name + "/scale": scale, name + "/offset": offset,
+            name + "/dy": dy, name + "/format": np.array(fmt),
+            name + "/y": back(y), name + "/mean": mean.numpy().astype(np.float32),
+            name + "/var_pop": var.numpy().astype(np.float32),
+            name + "/var_unbiased": unbiased.numpy().astype(np.float32),
+            name + "/dx": back(xt.grad),
+            name + "/dscale": st.grad.numpy().astype(np.float32),
+            name + "/doffset": ot.grad.numpy().astype(np.float32),
+        })
+    np.savez_compressed(os.path.join(HERE, "bn_torch_cpu.npz"), **out)
+
+
+def make_elementwise():
+    out = {}
+    relu_in = np.array([-2.0, -1.0, 0.0, 1.0, 2.0], np.float32)
+    out["relu/in"] = relu_in
+    out["relu/out"] = np.array([0.0, 0.0, 0.0, 1.0, 2.0], np.float32)
+    sig_in = np.array([-100.0, -10.0, -1.0, 0.0, 1.0, 10.0, 100.0], np.float64)
+    out["sigmoid/in"] = sig_in.astype(np.float32)
+    with np.errstate(over="ignore"):
+        out["sigmoid/out"] = 1.0 / (1.0 + np.exp(-sig_in))
+    x = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    b = np.array([0.5, -1.0, 2.0, 10.0], np.float32)
+    out["biasadd/x"] = x
+    out["biasadd/b"] = b
+    out["biasadd/out_nhwc"] = x + b
+    xn = np.arange(48, dtype=np.float32).reshape(2, 3, 2, 4)
+    bn = np.array([1.0, -2.0, 3.0], np.float32)
+    out["biasadd/x_nchw"] = xn
+    out["biasadd/b_nchw"] = bn
+    out["biasadd/out_nchw"] = xn + bn.reshape(1, 3, 1, 1)
+    xi = np.arange(12, dtype=np.int32).reshape(3, 4)
+    bi = np.array([1, -1, 2, -2], np.int32)
+    out["biasadd/x_i32"] = xi
+    out["biasadd/b_i32"] = bi
+    out["biasadd/out_i32"] = xi + bi
+    np.savez_compressed(os.path.join(HERE, "elementwise_literals.npz"), **out)
+
+
+if __name__ == "__main__":
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    make_adam(sys.argv[1])
+    make_bn()
+    make_elementwise()
+    print("wrote golden vectors to", HERE)

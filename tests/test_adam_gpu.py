@@ -1,0 +1,201 @@
+"""ApplyAdam on the GPU (through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import np_ref
+from helpers import (ADAM_HYPER, NP_BF16, RTOL, adam_inputs, assert_close, to_numpy,
+                     to_torch)
+from tensorflow_musa_extension_b200 import errors, raw_ops
+
+pytestmark = pytest.mark.gpu
+
+H = ADAM_HYPER
+
+
+def _step_args():
+    return (H["beta1_power"], H["beta2_power"], H["lr"], H["beta1"], H["beta2"],
+            H["epsilon"])
+
+
+@pytest.mark.parametrize("case", ["step10", "first_step_guard", "step1"])
+def test_reference_numpy_golden(golden, kernel_lib, case):
+    g = golden["adam_reference_numpy"]
+    s = [float(x) for x in g[case + "/scalars"]]
+    var, m, v = (to_torch(g[case + "/" + k].copy()) for k in ("var", "m", "v"))
+    raw_ops.ResourceApplyAdam(var, m, v, s[0], s[1], s[2], s[3], s[4], s[5],
+                              to_torch(g[case + "/grad"]))
+    assert_close(to_numpy(m), g[case + "/expected_m"], RTOL["f32_adam"], 1e-10, "m")
+    assert_close(to_numpy(v), g[case + "/expected_v"], RTOL["f32_adam"], 1e-14, "v")
+    assert_close(to_numpy(var), g[case + "/expected_var"], RTOL["f32_adam"], 1e-8, "var")
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 255, 256, 1025, 262147])
+def test_f32_sizes_and_ragged_tails(kernel_lib, n):
+    rng, var, m, v = adam_inputs(3, n)
+    g = rng.normal(0, 1e-3, n).astype(np.float32)
+    ev, em, evv = np_ref.apply_adam(var, m, v, *_step_args(), g)
+    tv, tm, tvv = to_torch(var), to_torch(m), to_torch(v)
+    raw_ops.ResourceApplyAdam(tv, tm, tvv, *_step_args(), to_torch(g))
+    assert_close(to_numpy(tm), em, RTOL["f32_adam"], 1e-10, "m")
+    assert_close(to_numpy(tvv), evv, RTOL["f32_adam"], 1e-14, "v")
+    assert_close(to_numpy(tv), ev, RTOL["f32_adam"], 1e-8, "var")
+
+
+def test_hundred_steps_fresh_grad_each_step(kernel_lib):
+    """The benchmark protocol (100 steps, a fresh seeded grad per step) at a
+    size the NumPy oracle finishes in seconds; includes a ragged tail."""
+    n = (1 << 20) + 3
+    rng, var, m, v = adam_inputs(3, n)
+    tv, tm, tvv = to_torch(var), to_torch(m), to_torch(v)
+    for _ in range(100):
+        g = rng.normal(0, 1e-3, n).astype(np.float32)
+        var, m, v = np_ref.apply_adam(var, m, v, *_step_args(), g)
+        raw_ops.ResourceApplyAdam(tv, tm, tvv, *_step_args(), to_torch(g))
+    assert_close(to_numpy(tm), m, RTOL["f32_adam"], 1e-9, "m")
+    assert_close(to_numpy(tvv), v, RTOL["f32_adam"], 1e-13, "v")
+    assert_close(to_numpy(tv), var, RTOL["f32_adam"], 1e-7, "var")
+
+
+def test_full_size_parameter_vector(kernel_lib):
+    """ResNet-50's 25,557,032 parameters, three steps against the oracle."""
+    n = 25_557_032
+    rng, var, m, v = adam_inputs(3, n)
+    tv, tm, tvv = to_torch(var), to_torch(m), to_torch(v)
+    for _ in range(3):
+        g = rng.normal(0, 1e-3, n).astype(np.float32)
+        var, m, v = np_ref.apply_adam(var, m, v, *_step_args(), g)
+        raw_ops.ResourceApplyAdam(tv, tm, tvv, *_step_args(), to_torch(g))
+    assert_close(to_numpy(tm), m, RTOL["f32_adam"], 1e-9, "m")
+    assert_close(to_numpy(tvv), v, RTOL["f32_adam"], 1e-13, "v")
+    assert_close(to_numpy(tv), var, RTOL["f32_adam"], 1e-7, "var")
+
+
+def test_update_is_elementwise_independent_of_sharding(kernel_lib):
+    """Range sharding must not change any element: one launch over the whole
+    vector equals 8 launches over contiguous shards, bit for bit."""
+    n = 1_000_003
+    rng, var, m, v = adam_inputs(3, n)
+    g = to_torch(rng.normal(0, 1e-3, n).astype(np.float32))
+    a = [to_torch(t) for t in (var, m, v)]
+    b = [to_torch(t) for t in (var, m, v)]
+    raw_ops.ResourceApplyAdam(*a, *_step_args(), g)
+    per = (n + 7) // 8
+    for r in range(8):
+        lo, hi = r * per, min(n, (r + 1) * per)
+        raw_ops.ResourceApplyAdam(*[t[lo:hi] for t in b], *_step_args(), g[lo:hi])
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_misaligned_pointers_take_the_elementwise_path(kernel_lib):
+    n = 4099
+    rng, var, m, v = adam_inputs(4, n + 1)
+    g = rng.normal(0, 1e-3, n + 1).astype(np.float32)
+    ev, em, evv = np_ref.apply_adam(var[1:], m[1:], v[1:], *_step_args(), g[1:])
+    tv, tm, tvv, tg = (to_torch(t) for t in (var, m, v, g))
+    raw_ops.ResourceApplyAdam(tv[1:], tm[1:], tvv[1:], *_step_args(), tg[1:])
+    assert_close(to_numpy(tv)[1:], ev, RTOL["f32_adam"], 1e-8, "var")
+    assert_close(to_numpy(tm)[1:], em, RTOL["f32_adam"], 1e-10, "m")
+    assert to_numpy(tv)[0] == var[0] and to_numpy(tm)[0] == m[0]
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("nesterov", [False, True])
+def test_same_type_16bit_state(kernel_lib, dtype, nesterov):
+    dt = np.float16 if dtype == "float16" else NP_BF16
+    n = 70001
+    rng = np.random.default_rng(6)
+    var = rng.normal(0, 0.5, n).astype(dt)
+    m = rng.normal(0, 1e-2, n).astype(dt)
+    v = rng.uniform(0, 1e-3, n).astype(dt)
+    g = rng.normal(0, 1e-1, n).astype(dt)
+    args = (0.9 ** 10, 0.999 ** 10, 1e-2, 0.9, 0.999, 1e-4)
+    ev, em, evv = np_ref.apply_adam(var, m, v, *[np.asarray(a).astype(dt) for a in args],
+                                    g, use_nesterov=nesterov)
+    tv, tm, tvv = to_torch(var), to_torch(m), to_torch(v)
+    raw_ops.ResourceApplyAdam(tv, tm, tvv, *args, to_torch(g), use_nesterov=nesterov)
+    # Same fp32 arithmetic, one rounding: at most one 16-bit ulp apart.
+    assert_close(to_numpy(tm), em, RTOL["lowp"], 1e-8, "m")
+    assert_close(to_numpy(tvv), evv, RTOL["lowp"], 1e-8, "v")
+    assert_close(to_numpy(tv), ev, RTOL["lowp"], 1e-6, "var")
+
+
+@pytest.mark.parametrize("gdtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("nesterov", [False, True])
+def test_mixed_precision_op(kernel_lib, gdtype, nesterov):
+    gdt = {"float32": np.float32, "float16": np.float16, "bfloat16": NP_BF16}[gdtype]
+    n = 50003
+    rng, var, m, v = adam_inputs(8, n)
+    g = rng.normal(0, 1e-3, n).astype(gdt)
+    ev, em, evv = np_ref.apply_adam(var, m, v, *_step_args(), g, use_nesterov=nesterov)
+    tv, tm, tvv = to_torch(var), to_torch(m), to_torch(v)
+    raw_ops.MusaResourceApplyAdamMixed(tv, tm, tvv, *_step_args(), to_torch(g),
+                                       use_nesterov=nesterov)
+    assert_close(to_numpy(tm), em, RTOL["f32_adam"], 1e-10, "m")
+    assert_close(to_numpy(tvv), evv, RTOL["f32_adam"], 1e-14, "v")
+    assert_close(to_numpy(tv), ev, RTOL["f32_adam"], 1e-8, "var")
+
+
+def test_f32_nesterov_is_honoured(kernel_lib):
+    n = 1000
+    rng, var, m, v = adam_inputs(9, n)
+    g = rng.normal(0, 1e-3, n).astype(np.float32)
+    ev, _, _ = np_ref.apply_adam(var, m, v, *_step_args(), g, use_nesterov=True)
+    tv, tm, tvv = to_torch(var), to_torch(m), to_torch(v)
+    raw_ops.ResourceApplyAdam(tv, tm, tvv, *_step_args(), to_torch(g), use_nesterov=True)
+    assert_close(to_numpy(tv), ev, RTOL["f32_adam"], 1e-8, "var")
+
+
+def test_apply_adam_forwards_var(kernel_lib):
+    n = 64
+    rng, var, m, v = adam_inputs(10, n)
+    tv = to_torch(var)
+    out = raw_ops.ApplyAdam(tv, to_torch(m), to_torch(v), *_step_args(),
+                            to_torch(rng.normal(0, 1e-3, n).astype(np.float32)))
+    assert out.data_ptr() == tv.data_ptr()
+
+
+def test_variables_errors_and_copy_on_write(kernel_lib):
+    n = 128
+    rng, var, m, v = adam_inputs(11, n)
+    g = to_torch(rng.normal(0, 1e-3, n).astype(np.float32))
+    V = raw_ops.Variable
+    with pytest.raises(errors.FailedPreconditionError, match="uninitialized"):
+        raw_ops.ResourceApplyAdam(V(to_torch(var)), V(None, "m0"), V(to_torch(v)),
+                                  *_step_args(), g)
+    with pytest.raises(errors.InvalidArgumentError, match="var and m do not have the same shape"):
+        raw_ops.ResourceApplyAdam(V(to_torch(var)), V(to_torch(m[:-1])), V(to_torch(v)),
+                                  *_step_args(), g)
+    with pytest.raises(errors.InvalidArgumentError, match="var and grad"):
+        raw_ops.ResourceApplyAdam(V(to_torch(var)), V(to_torch(m)), V(to_torch(v)),
+                                  *_step_args(), g[:-1])
+    with pytest.raises(errors.UnimplementedError):
+        raw_ops.ResourceApplyAdam(to_torch(var.astype(np.float64)),
+                                  to_torch(m.astype(np.float64)),
+                                  to_torch(v.astype(np.float64)), *_step_args(),
+                                  g.double())
+    vv = V(to_torch(var))
+    snapshot = vv.value()
+    raw_ops.ResourceApplyAdam(vv, V(to_torch(m)), V(to_torch(v)), *_step_args(), g)
+    assert np.array_equal(to_numpy(snapshot), var)          # reader's view intact
+    assert not np.array_equal(to_numpy(vv.tensor()), var)   # variable moved on
+    assert not vv.mu.locked()
+
+
+def test_musa_adam_matches_oracle_over_steps(kernel_lib):
+    from tensorflow_musa_extension_b200.optimizers import MusaAdam
+    n = 10000
+    rng, var, _, _ = adam_inputs(12, n)
+    m = np.zeros(n, np.float32)
+    v = np.zeros(n, np.float32)
+    tv = to_torch(var)
+    opt = MusaAdam(learning_rate=1e-3)
+    for step in range(1, 6):
+        g = rng.normal(0, 1e-3, n).astype(NP_BF16)
+        var, m, v = np_ref.apply_adam(var, m, v, 0.9 ** step, 0.999 ** step, 1e-3, 0.9,
+                                      0.999, 1e-7, g)
+        opt.apply_gradients([(to_torch(g), tv)])
+    assert opt.iterations == 5
+    assert_close(to_numpy(tv), var, RTOL["f32_adam"], 1e-8, "var")
+    assert_close(to_numpy(opt.get_slot(tv, "m")), m, RTOL["f32_adam"], 1e-10, "m")

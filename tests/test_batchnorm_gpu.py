@@ -1,0 +1,332 @@
+"""FusedBatchNorm forward / gradient on the GPU (through the C ABI) against the
+CPU oracle and the committed golden vectors."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_ref, np_ref
+from helpers import NP_BF16, RTOL, assert_close, bn_inputs, np_dtype, to_numpy, to_torch
+from tensorflow_musa_extension_b200 import errors, raw_ops
+
+pytestmark = pytest.mark.gpu
+
+EPS = 1e-3
+
+
+def _rt(dtype):
+    return RTOL["f32_bn"] if dtype == "float32" else RTOL["lowp"]
+
+
+def _rms(a):
+    a = np.asarray(a).astype(np.float64)
+    return float(np.sqrt(np.mean(a * a))) if a.size else 0.0
+
+
+def check_forward(got, want, dtype, what=""):
+    rt = _rt(dtype)
+    assert_close(to_numpy(got.y), want[0], rt, rt * max(_rms(want[0]), 1e-6), what + " y")
+    names = ["batch_mean", "batch_variance", "reserve_space_1", "reserve_space_2"]
+    for i, n in enumerate(names, start=1):
+        # Statistics are fp32 for every x dtype.
+        assert_close(to_numpy(got[i]), want[i], RTOL["f32_bn"],
+                     RTOL["f32_bn"] * max(_rms(want[i]), 1e-6), what + " " + n)
+    assert tuple(got.reserve_space_3.shape) == () and float(got.reserve_space_3) == 0.0
+
+
+def check_grad(got, want, dtype, what=""):
+    rt = _rt(dtype)
+    assert_close(to_numpy(got.x_backprop), want[0], rt, rt * max(_rms(want[0]), 1e-12),
+                 what + " dx")
+    srt = RTOL["f32_bn"]
+    assert_close(to_numpy(got.scale_backprop), want[1], srt,
+                 srt * max(_rms(want[1]), 1e-12), what + " dscale")
+    assert_close(to_numpy(got.offset_backprop), want[2], srt,
+                 srt * max(_rms(want[2]), 1e-12), what + " doffset")
+    c = want[1].shape[0]
+    assert tuple(got.reserve_space_4.shape) == (c,) and not to_numpy(got.reserve_space_4).any()
+    assert tuple(got.reserve_space_5.shape) == (c,) and not to_numpy(got.reserve_space_5).any()
+
+
+def run_both(x, scale, offset, dy, fmt):
+    tx = to_torch(x)
+    fwd = raw_ops.FusedBatchNormV3(tx, to_torch(scale), to_torch(offset),
+                                   torch.empty(0, device="cuda"),
+                                   torch.empty(0, device="cuda"), epsilon=EPS,
+                                   data_format=fmt, is_training=True)
+    grad = raw_ops.FusedBatchNormGradV3(to_torch(dy), tx, to_torch(scale),
+                                        fwd.reserve_space_1, fwd.reserve_space_2,
+                                        fwd.reserve_space_3, epsilon=EPS, data_format=fmt,
+                                        is_training=True)
+    return fwd, grad
+
+
+def test_golden_vectors(golden, kernel_lib):
+    g = golden["bn_torch_cpu"]
+    for n in sorted({k.split("/")[0] for k in g.files}):
+        fmt = str(g[n + "/format"])
+        fwd, grad = run_both(g[n + "/x"], g[n + "/scale"], g[n + "/offset"], g[n + "/dy"], fmt)
+        want = (g[n + "/y"], g[n + "/mean"], g[n + "/var_unbiased"], g[n + "/mean"],
+                g[n + "/var_pop"])
+        check_forward(fwd, want, "float32", n)
+        check_grad(grad, (g[n + "/dx"], g[n + "/dscale"], g[n + "/doffset"]), "float32", n)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("c", [1, 3, 8, 64, 65, 256, 520])
+@pytest.mark.parametrize("rows", [2, 31, 32, 33, 1000])
+def test_nhwc_shape_matrix(kernel_lib, dtype, c, rows):
+    x, s, o, dy = bn_inputs(100 + c + rows, (rows, 1, 1, c), dtype, 1.0, 3.0)
+    fwd, grad = run_both(x, s, o, dy, "NHWC")
+    want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
+    check_forward(fwd, want, dtype)
+    wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS)
+    check_grad(grad, wg, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(2, 3, 4, 5), (2, 32, 1, 1), (5, 16, 8, 8), (3, 7, 7, 7),
+                                   (16, 64, 14, 14), (1, 4, 3, 3)])
+def test_nchw_shapes(kernel_lib, dtype, shape):
+    x, s, o, dy = bn_inputs(200 + shape[1], shape, dtype, 0.5, 2.0, channel_axis=1)
+    fwd, grad = run_both(x, s, o, dy, "NCHW")
+    want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS, data_format="NCHW")
+    check_forward(fwd, want, dtype)
+    wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS, "NCHW")
+    check_grad(grad, wg, dtype)
+
+
+def test_keras_2d_batchnorm_shape(kernel_lib):
+    # Keras feeds 2-D inputs as [N, 1, 1, C]; a plain 2-D tensor works as well.
+    x, s, o, dy = bn_inputs(7, (512, 64), "float32", 0.0, 1.0, dy_std=1.0)
+    fwd, grad = run_both(x, s, o, dy, "NHWC")
+    want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
+    check_forward(fwd, want, "float32")
+    check_grad(grad, np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS), "float32")
+
+
+def test_one_value_per_channel(kernel_lib):
+    x = np.array([[[[1.0, -2.0, 3.0, 0.5]]]], np.float32)
+    s, o = np.full(4, 2.0, np.float32), np.full(4, 0.25, np.float32)
+    fwd, _ = run_both(x, s, o, np.ones_like(x), "NHWC")
+    assert_close(to_numpy(fwd.batch_variance), np.zeros(4), 0)      # no 0/0
+    assert_close(to_numpy(fwd.reserve_space_2), np.zeros(4), 0)
+    assert_close(to_numpy(fwd.y), np.full((1, 1, 1, 4), 0.25), 1e-6)
+
+
+def test_large_mean_small_spread_is_stable(kernel_lib):
+    """mean 1000, std 1: a sum-of-squares variance in fp32 would lose every
+    digit; the shifted sums keep rtol 1e-4 on the variance."""
+    x, s, o, dy = bn_inputs(9, (64, 8, 8, 32), "float32", 1000.0, 1.0)
+    fwd, _ = run_both(x, s, o, dy, "NHWC")
+    want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
+    assert_close(to_numpy(fwd.reserve_space_2), want[4], 1e-4, 0, "variance")
+    assert_close(to_numpy(fwd.reserve_space_1), want[3], 1e-6, 0, "mean")
+
+
+def test_large_variance_gradient(kernel_lib):
+    # The gradient takes a VARIANCE (std 30 here), not an inverse std-dev.
+    for dtype in ("float32", "bfloat16"):
+        x, s, o, dy = bn_inputs(10, (8, 6, 16, 16), dtype, 3.0, 30.0, dy_std=1.0,
+                                channel_axis=1)
+        fwd, grad = run_both(x, s, o, dy, "NCHW")
+        want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS, data_format="NCHW")
+        wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS, "NCHW")
+        check_grad(grad, wg, dtype)
+        assert np.abs(to_numpy(grad.x_backprop).astype(np.float64)).max() < 1.0
+
+
+def test_outputs_do_not_depend_on_stale_memory(kernel_lib):
+    """Poison the allocator pool with 999, free it, then run the ops: every
+    output element must be written by the kernels."""
+    x, s, o, dy = bn_inputs(11, (16, 9, 9, 40), "float32", 0.0, 1.0, dy_std=1.0)
+    want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
+    wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS)
+    for _ in range(3):
+        junk = [torch.full((16, 9, 9, 40), 999.0, device="cuda") for _ in range(4)]
+        junk += [torch.full((40,), 999.0, device="cuda") for _ in range(16)]
+        del junk
+        fwd, grad = run_both(x, s, o, dy, "NHWC")
+        check_forward(fwd, want, "float32")
+        check_grad(grad, wg, "float32")
+
+
+def test_exponential_avg_factor(kernel_lib):
+    x, s, o, _ = bn_inputs(12, (4, 5, 5, 24), "float32", 0.5, 2.0)
+    rm = np.random.default_rng(1).normal(0, 1, 24).astype(np.float32)
+    rv = np.random.default_rng(2).uniform(0.5, 2, 24).astype(np.float32)
+    got = raw_ops.FusedBatchNormV3(to_torch(x), to_torch(s), to_torch(o), to_torch(rm),
+                                   to_torch(rv), epsilon=EPS, exponential_avg_factor=0.1)
+    want = np_ref.fused_batch_norm(x, s, o, rm, rv, EPS, 0.1)
+    check_forward(got, want, "float32")
+    with pytest.raises(errors.InvalidArgumentError):
+        raw_ops.FusedBatchNormV3(to_torch(x), to_torch(s), to_torch(o),
+                                 torch.empty(0, device="cuda"), torch.empty(0, device="cuda"),
+                                 exponential_avg_factor=0.1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("fmt,shape", [("NHWC", (4, 6, 6, 48)), ("NCHW", (4, 12, 6, 6))])
+def test_inference_mode(kernel_lib, dtype, fmt, shape):
+    ax = 3 if fmt == "NHWC" else 1
+    x, s, o, dy = bn_inputs(13, shape, dtype, 0.5, 2.0, dy_std=1.0, channel_axis=ax)
+    rng = np.random.default_rng(3)
+    mean = rng.normal(0.5, 0.2, shape[ax]).astype(np.float32)
+    var = rng.uniform(2, 6, shape[ax]).astype(np.float32)
+    got = raw_ops.FusedBatchNormV3(to_torch(x), to_torch(s), to_torch(o), to_torch(mean),
+                                   to_torch(var), epsilon=EPS, data_format=fmt,
+                                   is_training=False)
+    want = np_ref.fused_batch_norm(x, s, o, mean, var, EPS, data_format=fmt,
+                                   is_training=False)
+    rt = _rt(dtype)
+    assert_close(to_numpy(got.y), want[0], rt, rt * _rms(want[0]), "y")
+    g = raw_ops.FusedBatchNormGradV3(to_torch(dy), to_torch(x), to_torch(s), to_torch(mean),
+                                     to_torch(var), None, epsilon=EPS, data_format=fmt,
+                                     is_training=False)
+    check_grad(g, np_ref.fused_batch_norm_grad(dy, x, s, mean, var, EPS, fmt, False), dtype)
+
+
+def test_op_versions_and_errors(kernel_lib):
+    x, s, o, dy = bn_inputs(14, (2, 3, 3, 8), "float32", 0.0, 1.0)
+    e = torch.empty(0, device="cuda")
+    v1 = raw_ops.FusedBatchNorm(to_torch(x), to_torch(s), to_torch(o), e, e, epsilon=EPS)
+    v2 = raw_ops.FusedBatchNormV2(to_torch(x), to_torch(s), to_torch(o), e, e, epsilon=EPS)
+    assert len(v1) == 5 and len(v2) == 5 and torch.equal(v1.y, v2.y)
+    with pytest.raises(errors.InvalidArgumentError, match="scale must have 8 elements"):
+        raw_ops.FusedBatchNormV3(to_torch(x), to_torch(s[:4]), to_torch(o), e, e)
+    with pytest.raises(errors.InvalidArgumentError, match="float, half, bfloat16"):
+        raw_ops.FusedBatchNormV3(to_torch(x).double(), to_torch(s), to_torch(o), e, e)
+    with pytest.raises(errors.InvalidArgumentError, match="is_training=False"):
+        raw_ops.FusedBatchNormV3(to_torch(x), to_torch(s), to_torch(o), e, e,
+                                 is_training=False)
+    with pytest.raises(errors.InvalidArgumentError, match="same shape"):
+        raw_ops.FusedBatchNormGradV3(to_torch(dy[:1]), to_torch(x), to_torch(s),
+                                     v1.reserve_space_1, v1.reserve_space_2)
+    with pytest.raises(errors.InvalidArgumentError):
+        raw_ops.FusedBatchNormV3(to_torch(x), to_torch(s), to_torch(o), e, e,
+                                 data_format="NDHWC")
+
+
+def test_workspace_contract(kernel_lib):
+    x = torch.randn(64, 16, device="cuda")
+    outs = [torch.empty(16, device="cuda") for _ in range(4)]
+    s = torch.ones(16, device="cuda")
+    y = torch.empty_like(x)
+    need = kernel_lib.BnWorkspaceBytes(64, 16, 1)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    args = [x.data_ptr(), s.data_ptr(), s.data_ptr(), None, None, y.data_ptr()] + \
+        [t.data_ptr() for t in outs] + [64, 16, 1, EPS, 1.0]
+    assert kernel_lib.LaunchBnFwdTrain_F32(*args, ws.data_ptr(), need - 1, st) == -2
+    assert kernel_lib.LaunchBnFwdTrain_F32(*args, None, need, st) == -2
+    assert kernel_lib.LaunchBnFwdTrain_F32(*args, ws.data_ptr(), need, st) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(outs[2], x.mean(0), atol=1e-6)
+
+
+def test_host_buffers_round_trip(kernel_lib):
+    x, s, o, dy = bn_inputs(15, (8, 4, 4, 32), "bfloat16", 0.0, 1.0)
+    got = raw_ops.FusedBatchNormV3(x, s, o, np.empty(0, np.float32), np.empty(0, np.float32),
+                                   epsilon=EPS)
+    assert isinstance(got.y, np.ndarray) and got.y.dtype == NP_BF16
+    check_forward(got, np_ref.fused_batch_norm(x, s, o, epsilon=EPS), "bfloat16")
+
+
+# ------------------------------------------------ cross-replica (split) API --
+
+def _split_forward_and_grad(lib, x, dy, scale, offset, parts):
+    """Runs the SyncBN halves on `parts` row blocks as if they were replicas
+    and sums the per-replica sums on the host side of the all-reduce."""
+    dt = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[x.dtype]
+    rows, c = x.shape
+    st = torch.cuda.current_stream().cuda_stream
+    bounds = np.linspace(0, rows, parts + 1).astype(int)
+    need = lib.BnWorkspaceBytes(rows, c, 1)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    total = torch.zeros(2 * c, device="cuda")
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        sums = torch.empty(2 * c, device="cuda")
+        rc = lib.LaunchBnStatsSums(dt, x[lo:hi].data_ptr(), sums.data_ptr(), int(hi - lo),
+                                   c, 1, ws.data_ptr(), ws.numel(), st)
+        assert rc == 0
+        total += sums
+    bm, bv, sm, sv = (torch.empty(c, device="cuda") for _ in range(4))
+    assert lib.LaunchBnFinalizeFromSums(total.data_ptr(), float(rows), None, None,
+                                        bm.data_ptr(), bv.data_ptr(), sm.data_ptr(),
+                                        sv.data_ptr(), c, 1.0, st) == 0
+    y = torch.empty_like(x)
+    gtotal = torch.zeros(2 * c, device="cuda")
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        assert lib.LaunchBnApply(dt, x[lo:hi].data_ptr(), scale.data_ptr(), offset.data_ptr(),
+                                 sm.data_ptr(), sv.data_ptr(), y[lo:hi].data_ptr(),
+                                 int(hi - lo), c, 1, EPS, st) == 0
+        sums = torch.empty(2 * c, device="cuda")
+        assert lib.LaunchBnGradStatsSums(dt, dy[lo:hi].data_ptr(), x[lo:hi].data_ptr(),
+                                         sm.data_ptr(), sums.data_ptr(), int(hi - lo), c, 1,
+                                         ws.data_ptr(), ws.numel(), st) == 0
+        gtotal += sums
+    dx = torch.empty_like(x)
+    dscale, doffset = torch.empty(c, device="cuda"), torch.empty(c, device="cuda")
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        assert lib.LaunchBnGradApplyFromSums(
+            dt, dy[lo:hi].data_ptr(), x[lo:hi].data_ptr(), scale.data_ptr(), sm.data_ptr(),
+            sv.data_ptr(), gtotal.data_ptr(), float(rows), dx[lo:hi].data_ptr(),
+            dscale.data_ptr(), doffset.data_ptr(), int(hi - lo), c, 1, EPS, st) == 0
+    return y, bm, bv, sm, sv, dx, dscale, doffset
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("parts", [1, 2, 8])
+def test_split_api_equals_global_batchnorm(kernel_lib, dtype, parts):
+    x, s, o, dy = bn_inputs(16, (4096, 64), dtype, 0.0, 1.0)
+    got = _split_forward_and_grad(kernel_lib, to_torch(x), to_torch(dy), to_torch(s),
+                                  to_torch(o), parts)
+    want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
+    wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS)
+    rt = _rt(dtype)
+    assert_close(to_numpy(got[0]), want[0], rt, rt * _rms(want[0]), "y")
+    for i in range(1, 5):
+        assert_close(to_numpy(got[i]), want[i], 1e-4, 1e-4 * max(_rms(want[i]), 1e-6))
+    assert_close(to_numpy(got[5]), wg[0], rt, rt * _rms(wg[0]), "dx")
+    assert_close(to_numpy(got[6]), wg[1], 1e-4, 1e-4 * _rms(wg[1]), "dscale")
+    assert_close(to_numpy(got[7]), wg[2], 1e-4, 1e-4 * _rms(wg[2]), "doffset")
+
+
+def test_empty_replica_contributes_zero_sums(kernel_lib):
+    sums = torch.full((16,), 7.0, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert kernel_lib.LaunchBnStatsSums(0, None, sums.data_ptr(), 0, 8, 1, None, 0, st) == 0
+    torch.cuda.synchronize()
+    assert not sums.any()
+
+
+# ------------------------------------------------------- benchmark shapes --
+
+def test_config1_fp32_full_size(kernel_lib):
+    x, s, o, dy = bn_inputs(0, (32, 56, 56, 64), "float32", 0.5, 2.0)
+    fwd, grad = run_both(x, s, o, dy, "NHWC")
+    x2 = x.reshape(-1, 64)
+    want = c_ref.bn_fwd_train(x2, s, o, EPS)
+    check_forward(fwd, (want[0].reshape(x.shape),) + tuple(want[1:]), "float32")
+    wg = c_ref.bn_grad(dy.reshape(-1, 64), x2, s, want[3], want[4], EPS)
+    check_grad(grad, (wg[0].reshape(x.shape), wg[1], wg[2]), "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_config2_16bit_full_size(kernel_lib, dtype):
+    x, s, o, dy = bn_inputs(1, (256, 28, 28, 256), dtype, 1.0, 3.0)
+    fwd, grad = run_both(x, s, o, dy, "NHWC")
+    x2 = x.reshape(-1, 256)
+    want = c_ref.bn_fwd_train(x2, s, o, EPS)
+    check_forward(fwd, (want[0].reshape(x.shape),) + tuple(want[1:]), dtype)
+    wg = c_ref.bn_grad(dy.reshape(-1, 256), x2, s, want[3], want[4], EPS)
+    check_grad(grad, (wg[0].reshape(x.shape), wg[1], wg[2]), dtype)
+    # Size-independent properties: y has zero mean / unit variance per channel
+    # before scale and offset; dx sums to zero per channel.
+    y = fwd.y.float().reshape(-1, 256)
+    z = (y - to_torch(o)) / to_torch(s)
+    assert float(z.mean(0).abs().max()) < 5e-3
+    assert float((z.var(0, unbiased=False) - 1).abs().max()) < 2e-2
+    dxs = grad.x_backprop.float().reshape(-1, 256).sum(0)
+    assert float(dxs.abs().max()) < 5e-2

@@ -1,0 +1,151 @@
+"""The CPU oracle against the committed golden vectors, and the C restatement
+against the NumPy one.  No GPU."""
+import numpy as np
+import pytest
+
+from oracle import c_ref, np_ref
+from helpers import NP_BF16, RTOL, assert_close
+
+
+@pytest.mark.parametrize("case", ["step10", "first_step_guard", "step1"])
+def test_adam_matches_reference_numpy_statement(golden, case):
+    g = golden["adam_reference_numpy"]
+    s = g[case + "/scalars"]
+    var, m, v = np_ref.apply_adam(g[case + "/var"], g[case + "/m"], g[case + "/v"],
+                                  s[0], s[1], s[2], s[3], s[4], s[5], g[case + "/grad"])
+    assert_close(m, g[case + "/expected_m"], 1e-7, what="m")
+    assert_close(v, g[case + "/expected_v"], 1e-7, what="v")
+    assert_close(var, g[case + "/expected_var"], 1e-6, what="var")
+
+
+def test_adam_first_step_guard_uses_lr():
+    assert np_ref.adam_alpha(1e-3, 1.0, 1.0) == np.float32(1e-3)
+    a = np_ref.adam_alpha(1e-3, 0.9, 0.999)
+    assert abs(float(a) - 1e-3 * np.sqrt(1 - 0.999) / 0.1) < 1e-9
+
+
+def test_adam_c_matches_numpy():
+    rng = np.random.default_rng(5)
+    n = 10007
+    var = rng.normal(0, 0.05, n).astype(np.float32)
+    m = rng.normal(0, 1e-4, n).astype(np.float32)
+    v = rng.uniform(0, 1e-6, n).astype(np.float32)
+    g = rng.normal(0, 1e-3, n).astype(np.float32)
+    ev, em, evv = np_ref.apply_adam(var, m, v, 0.9 ** 10, 0.999 ** 10, 1e-3, 0.9,
+                                    0.999, 1e-7, g)
+    alpha = np_ref.adam_alpha(1e-3, np.float32(0.9 ** 10), np.float32(0.999 ** 10))
+    c_ref.adam_f32(var, m, v, g, 0.9, 0.999, 1e-7, alpha)
+    assert_close(m, em, 0, what="m")
+    assert_close(v, evv, 0, what="v")
+    assert_close(var, ev, 1e-6, what="var")
+
+
+def _bn_names(g):
+    return sorted({k.split("/")[0] for k in g.files})
+
+
+def test_bn_oracle_matches_independent_implementation(golden):
+    g = golden["bn_torch_cpu"]
+    for n in _bn_names(g):
+        fmt = str(g[n + "/format"])
+        out = np_ref.fused_batch_norm(g[n + "/x"], g[n + "/scale"], g[n + "/offset"],
+                                      epsilon=1e-3, data_format=fmt)
+        scale_y = np.abs(g[n + "/y"]).max()
+        assert_close(out[0], g[n + "/y"], 1e-5, 1e-5 * scale_y, n + " y")
+        assert_close(out[1], g[n + "/mean"], 1e-6, 1e-7, n + " batch_mean")
+        assert_close(out[2], g[n + "/var_unbiased"], 1e-6, 0, n + " batch_var")
+        assert_close(out[3], g[n + "/mean"], 1e-6, 1e-7, n + " reserve_1")
+        assert_close(out[4], g[n + "/var_pop"], 1e-6, 0, n + " reserve_2")
+        assert out[5].shape == () and out[5] == 0
+        gr = np_ref.fused_batch_norm_grad(g[n + "/dy"], g[n + "/x"], g[n + "/scale"],
+                                          out[3], out[4], 1e-3, fmt)
+        s = np.abs(g[n + "/dx"]).max()
+        assert_close(gr[0], g[n + "/dx"], 1e-4, 1e-5 * s, n + " dx")
+        s = np.abs(g[n + "/dscale"]).max()
+        assert_close(gr[1], g[n + "/dscale"], 1e-4, 1e-4 * s, n + " dscale")
+        assert_close(gr[2], g[n + "/doffset"], 1e-5, 1e-6, n + " doffset")
+        assert gr[3].shape == gr[1].shape and not gr[3].any() and not gr[4].any()
+
+
+def test_bn_single_value_per_channel_skips_bessel():
+    x = np.array([[[[1.0, 2.0, 3.0]]]], np.float32)
+    out = np_ref.fused_batch_norm(x, np.ones(3, np.float32), np.zeros(3, np.float32))
+    assert np.all(out[2] == 0) and np.all(out[4] == 0)
+    assert np.all(np.isfinite(out[0]))
+
+
+def test_bn_exponential_avg_factor_blends():
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((4, 3, 3, 5)).astype(np.float32)
+    s, o = np.ones(5, np.float32), np.zeros(5, np.float32)
+    rm, rv = np.full(5, 2.0, np.float32), np.full(5, 3.0, np.float32)
+    full = np_ref.fused_batch_norm(x, s, o)
+    half = np_ref.fused_batch_norm(x, s, o, rm, rv, exponential_avg_factor=0.5)
+    assert_close(half[1], 0.5 * rm + 0.5 * full[1], 1e-6)
+    assert_close(half[2], 0.5 * rv + 0.5 * full[2], 1e-6)
+    assert_close(half[3], full[3], 0)
+
+
+def test_bn_inference_uses_given_statistics():
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((2, 3, 3, 4)).astype(np.float32)
+    s = rng.uniform(0.5, 1.5, 4).astype(np.float32)
+    o = rng.normal(0, 0.1, 4).astype(np.float32)
+    mean = rng.normal(0, 1, 4).astype(np.float32)
+    var = rng.uniform(0.5, 2, 4).astype(np.float32)
+    y = np_ref.fused_batch_norm(x, s, o, mean, var, is_training=False)[0]
+    assert_close(y, (x - mean) / np.sqrt(var + 1e-3) * s + o, 1e-5, 1e-6)
+    dy = rng.standard_normal(x.shape).astype(np.float32)
+    dx = np_ref.fused_batch_norm_grad(dy, x, s, mean, var, is_training=False)[0]
+    assert_close(dx, dy * s / np.sqrt(var + 1e-3), 1e-5, 1e-7)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+def test_bn_c_matches_numpy(dtype):
+    rng = np.random.default_rng(7)
+    dt = {"float32": np.float32, "float16": np.float16, "bfloat16": NP_BF16}[dtype]
+    x = (rng.standard_normal((3000, 24)) * 3 + 1).astype(dt)
+    dy = (rng.standard_normal((3000, 24)) * 1e-2).astype(dt)
+    s = rng.uniform(0.5, 1.5, 24).astype(np.float32)
+    o = rng.normal(0, 0.1, 24).astype(np.float32)
+    rt = RTOL["f32_bn"] if dtype == "float32" else RTOL["lowp"]
+    c = c_ref.bn_fwd_train(x, s, o, 1e-3)
+    e = np_ref.fused_batch_norm(x, s, o, epsilon=1e-3)
+    assert_close(c[0], e[0], rt, rt, "y")
+    for i in range(1, 5):
+        assert_close(c[i], e[i], 1e-5, 1e-6, "stat %d" % i)
+    cg = c_ref.bn_grad(dy, x, s, e[3], e[4], 1e-3)
+    eg = np_ref.fused_batch_norm_grad(dy, x, s, e[3], e[4], 1e-3)
+    assert_close(cg[0], eg[0], rt, rt * np.abs(eg[0].astype(np.float64)).max(), "dx")
+    assert_close(cg[1], eg[1], 1e-4, 1e-5, "dscale")
+    assert_close(cg[2], eg[2], 1e-4, 1e-6, "doffset")
+
+
+def test_elementwise_literals(golden):
+    g = golden["elementwise_literals"]
+    assert_close(np_ref.relu(g["relu/in"]), g["relu/out"], 0)
+    assert_close(np_ref.sigmoid(g["sigmoid/in"]), g["sigmoid/out"], 1e-6, 1e-45)
+    assert_close(np_ref.bias_add(g["biasadd/x"], g["biasadd/b"]), g["biasadd/out_nhwc"], 0)
+    assert_close(np_ref.bias_add(g["biasadd/x_nchw"], g["biasadd/b_nchw"], "NCHW"),
+                 g["biasadd/out_nchw"], 0)
+    out = np_ref.bias_add(g["biasadd/x_i32"], g["biasadd/b_i32"])
+    assert out.dtype == np.int32 and np.array_equal(out, g["biasadd/out_i32"])
+
+
+def test_bias_add_edge_cases():
+    with pytest.raises(ValueError, match="Dimension mismatch in BiasAdd"):
+        np_ref.bias_add(np.zeros((2, 3), np.float32), np.zeros(4, np.float32))
+    assert np_ref.bias_add(np.zeros((0, 3), np.float32), np.zeros(3, np.float32)).shape == (0, 3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("act,fn", [(0, np_ref.bias_add), (1, np_ref.bias_add_relu),
+                                    (2, np_ref.bias_add_swish),
+                                    (3, np_ref.bias_add_sigmoid)])
+def test_bias_act_c_matches_numpy(dtype, act, fn):
+    rng = np.random.default_rng(9)
+    dt = {"float32": np.float32, "float16": np.float16, "bfloat16": NP_BF16}[dtype]
+    x = rng.standard_normal((257, 40)).astype(dt)
+    b = rng.normal(0, 0.1, 40).astype(dt)
+    rt = 1e-6 if dtype == "float32" else 0.0
+    assert_close(c_ref.bias_act(x, b, act), fn(x, b), rt, 0, "act %d" % act)
