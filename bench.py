@@ -69,7 +69,7 @@ def measured_peak():
 # ------------------------------------------------------------ clock sampler --
 
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -84,12 +84,15 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples whose timestamp lies in [t_begin, t_end]
+        (epoch seconds; all samples when not given)."""
+        import datetime
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
@@ -106,6 +109,11 @@ class ClockSampler:
                 if len(f) < 9:
                     continue
                 try:
+                    if t_begin is not None:
+                        ts = datetime.datetime.strptime(
+                            f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                        if ts < t_begin - 0.05 or ts > t_end + 0.05:
+                            continue
                     sm.append(float(f[1]))
                     mx.append(float(f[2]))
                 except ValueError:
@@ -190,6 +198,15 @@ def run_ours(args):
 
     launches_per_step = sum(b.launches_per_step for b in bns)
 
+    if args.profile_step:
+        # One eager pass and nothing else: the target of an ncu launch list.
+        step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
     # Warm up eagerly, then capture the step in a CUDA graph (the launchers
     # neither allocate nor synchronise, so a step is a pure launch sequence).
     for _ in range(2):
@@ -226,21 +243,23 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        run_step()
     sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
                            int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
-    barrier()
     if rank == 0:
-        sampler.start()
+        sampler.start()   # nvidia-smi needs a moment to start: begin before the warm-up
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.time()
     e0.record()
     for _ in range(args.steps):
         run_step()
     e1.record()
     barrier()
+    t_end = time.time()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -249,7 +268,8 @@ def run_ours(args):
     value = world * elems_per_step / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end: pinned host buffers through the public op API
-    e2e = measure_e2e(torch, dist, raw_ops, layers, world, rank, dev, args)
+    e2e = None if args.skip_e2e else \
+        measure_e2e(torch, dist, raw_ops, layers, world, rank, dev, args)
 
     result = None
     if rank == 0:
@@ -276,10 +296,15 @@ def run_ours(args):
             "e2e": e2e,
         }
     if world == 1:
-        ops, roof = measure_ops(torch, lib, raw_ops, dev, args)
+        # Free the workload before the per-op section allocates its own inputs.
+        del xs, dys, out_y, out_dx, bns, graph
+        torch.cuda.empty_cache()
+        ops, roof = (None, None) if args.skip_ops else \
+            measure_ops(torch, lib, raw_ops, dev, args)
         result["roofline"] = roof
         result["ops"] = ops
-        result["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_seconds)
+        result["cpu_baseline"] = None if args.skip_cpu else \
+            cpu_baseline(budget_s=args.cpu_seconds)
     else:
         if rank == 0:
             result["roofline"] = None
@@ -381,9 +406,15 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     peak, peak_kind = measured_peak()
     st = torch.cuda.current_stream().cuda_stream
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    flush_src = torch.ones(64 << 20, dtype=torch.float32, device=dev)
+    flush_dst = torch.empty(1, dtype=torch.float32, device=dev)
 
     def flush():
+        # Write 512 MB (evicts everything), then read 256 MB of other data so
+        # that the dirty lines of the write are back in HBM before the timed
+        # launch starts; otherwise their write-back lands inside it.
         flush_buf.fill_(1)
+        torch.sum(flush_src, dim=(0,), out=flush_dst[0])
 
     iters = 20
     ops = {}
@@ -563,11 +594,16 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="time eager launches")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-ops", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="run one eager pass of the workload and exit (ncu target)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     if args.impl == "reference":

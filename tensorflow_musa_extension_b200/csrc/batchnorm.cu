@@ -65,14 +65,16 @@ struct Plan {
 };
 
 // Channels-last plan.  `cv` = channel packs per row.
+// `resident`: CTAs of this kernel that fit on one SM; the grid is one full
+// wave of them (a second, partly filled wave would idle SMs at the end).
 inline Plan PlanLast(int64_t rows, int64_t channels, int64_t cv, int unroll,
-                     bool cap_by_workspace) {
+                     bool cap_by_workspace, int resident) {
   Plan p;
   p.tx = Pow2Ceil(cv);
   p.ty = kThreads / p.tx;
   p.gx = static_cast<int>(CeilDiv(cv, p.tx));
   int per_sm = GetTuning(kTuneBnCtasPerSm);
-  if (per_sm < 1) per_sm = 8;
+  if (per_sm < 1) per_sm = resident > 0 ? resident : 4;
   int64_t target = static_cast<int64_t>(SmCount()) * per_sm / p.gx;
   if (target < 1) target = 1;
   // Do not split below one unrolled sweep of the row lanes.
@@ -218,6 +220,168 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// ---- Pipelined channels-last stats (128-bit packs only).
+//
+// Same mapping as BnStatsLastKernel, but the row stream is staged through
+// shared memory with per-thread asynchronous 16-byte copies (cp.async): every
+// thread owns kStages * kStreams * kU private 16-byte slots, keeps
+// (kStages - 1) * kStreams * kU copies in flight and reads back only its own
+// slots, so no barrier is needed in the loop and the bytes in flight per SM
+// (~150 KB at 3 CTAs) no longer depend on registers.  With register-held loads
+// the kernel was latency-bound at about half of the HBM rate.
+__device__ __forceinline__ void CpAsync16(void* smem_dst, const void* gmem_src) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst),
+               "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void CpAsyncCommit() {
+  asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+template <int kPending>
+__device__ __forceinline__ void CpAsyncWait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(kPending) : "memory");
+}
+
+template <int kMode>
+struct StatsPipe {
+  static constexpr int kStages = 4;
+  static constexpr int kStreams = kMode == 0 ? 1 : 2;
+  static constexpr int kU = kMode == 0 ? 4 : 2;  // rows per stage and stream
+  static constexpr int kSlots = kStages * kStreams * kU;
+  static constexpr int kSmemBytes = kSlots * 256 * 16;
+};
+
+template <typename T, int kMode>
+__global__ void __launch_bounds__(kThreads)
+    BnStatsPipeKernel(const T* __restrict__ x, const T* __restrict__ dy,
+                      const float* __restrict__ mean,
+                      float* __restrict__ partial, int64_t rows, int64_t cv,
+                      int64_t channels, int64_t rows_per_cta) {
+  constexpr int kVec = VecWidth<T>::value;
+  using P = Pack<T, kVec>;
+  using Cfg = StatsPipe<kMode>;
+  constexpr int kStages = Cfg::kStages, kU = Cfg::kU, kStreams = Cfg::kStreams;
+  extern __shared__ uint4 pipe_smem[];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int TX = blockDim.x, TY = blockDim.y;
+  const int tid = ty * TX + tx;
+  const int64_t col = static_cast<int64_t>(blockIdx.x) * TX + tx;
+  const bool active = col < cv;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_cta;
+  int64_t r1 = r0 + rows_per_cta;
+  if (r1 > rows) r1 = rows;
+
+  float shift[kVec], s1[kVec], s2[kVec];
+#pragma unroll
+  for (int e = 0; e < kVec; ++e) {
+    s1[e] = 0.0f;
+    s2[e] = 0.0f;
+    shift[e] = 0.0f;
+  }
+
+  if (active) {
+    if constexpr (kMode == kFwd) {
+      const P first = LoadKeep(reinterpret_cast<const P*>(x) + col);
+#pragma unroll
+      for (int e = 0; e < kVec; ++e) shift[e] = ToF32(first.v[e]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < kVec; ++e) shift[e] = mean[col * kVec + e];
+    }
+    const P* xp = reinterpret_cast<const P*>(x) + col;
+    const P* dp = reinterpret_cast<const P*>(dy) + col;
+    // This thread's rows: r0 + ty + j * TY, j = 0 .. n_j - 1.
+    const int64_t span = r1 - r0 - ty;
+    const int64_t n_j = span > 0 ? (span + TY - 1) / TY : 0;
+    const int64_t n_it = (n_j + kU - 1) / kU;
+    // Slot (stage, stream, u) of this thread.
+    auto slot = [&](int stage, int stream, int u) -> uint4* {
+      return pipe_smem + ((stage * kStreams + stream) * kU + u) * kThreads + tid;
+    };
+    auto issue = [&](int64_t it) {
+      if (it < n_it) {
+        const int stage = static_cast<int>(it % kStages);
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const int64_t j = it * kU + u;
+          if (j < n_j) {
+            const int64_t off = (r0 + ty + j * TY) * cv;
+            CpAsync16(slot(stage, 0, u), xp + off);
+            if constexpr (kMode == kGrad) CpAsync16(slot(stage, 1, u), dp + off);
+          }
+        }
+      }
+      CpAsyncCommit();
+    };
+#pragma unroll
+    for (int st = 0; st < kStages - 1; ++st) issue(st);
+    for (int64_t it = 0; it < n_it; ++it) {
+      issue(it + kStages - 1);
+      CpAsyncWait<kStages - 1>();
+      const int stage = static_cast<int>(it % kStages);
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int64_t j = it * kU + u;
+        if (j < n_j) {
+          const uint4 rx = *slot(stage, 0, u);
+          const P px = *reinterpret_cast<const P*>(&rx);
+          P pd;
+          if constexpr (kMode == kGrad) {
+            const uint4 rd = *slot(stage, 1, u);
+            pd = *reinterpret_cast<const P*>(&rd);
+          }
+#pragma unroll
+          for (int e = 0; e < kVec; ++e) {
+            const float d = ToF32(px.v[e]) - shift[e];
+            if constexpr (kMode == kFwd) {
+              s1[e] += d;
+              s2[e] = fmaf(d, d, s2[e]);
+            } else {
+              const float g = ToF32(pd.v[e]);
+              s1[e] += g;
+              s2[e] = fmaf(g, d, s2[e]);
+            }
+          }
+        }
+      }
+    }
+  }
+  CpAsyncWait<0>();
+  __syncthreads();  // every thread is done with its slots: reuse the buffer
+
+  float* red = reinterpret_cast<float*>(pipe_smem);
+  if (TY > 1) {
+#pragma unroll
+    for (int e = 0; e < kVec; ++e) {
+      red[((0 * kVec + e) * TY + ty) * TX + tx] = s1[e];
+      red[((1 * kVec + e) * TY + ty) * TX + tx] = s2[e];
+    }
+    __syncthreads();
+    const int n_out = 2 * kVec * TX;
+    for (int o = tid; o < n_out; o += kThreads) {
+      const int otx = o % TX;
+      const int se = o / TX;
+      float acc = 0.0f;
+      for (int j = 0; j < TY; ++j) acc += red[(se * TY + j) * TX + otx];
+      const int64_t ocol = static_cast<int64_t>(blockIdx.x) * TX + otx;
+      if (ocol < cv) {
+        const int sidx = se / kVec, e = se % kVec;
+        partial[(static_cast<int64_t>(blockIdx.y) * 2 + sidx) * channels +
+                ocol * kVec + e] = acc;
+      }
+    }
+  } else if (active) {
+#pragma unroll
+    for (int e = 0; e < kVec; ++e) {
+      partial[(static_cast<int64_t>(blockIdx.y) * 2 + 0) * channels +
+              col * kVec + e] = s1[e];
+      partial[(static_cast<int64_t>(blockIdx.y) * 2 + 1) * channels +
+              col * kVec + e] = s2[e];
+    }
+  }
+}
+
 // General layout stats ([outer, C, inner], inner > 1 or unaligned): grid
 // (C, gy); a CTA walks the planes (n, c) of its split with all 256 threads.
 template <typename T, int kVec, int kMode>
@@ -339,7 +503,24 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
   const int64_t c = static_cast<int64_t>(blockIdx.x) * 8 + cx;
   double t1 = 0.0, t2 = 0.0;
   if (c < a.channels) {
-    for (int p = py; p < a.splits; p += 128) {
+    // Four independent loads per sum in flight: the loop is a chain of L2
+    // round trips otherwise.
+    int p = py;
+    for (; p + 3 * 128 < a.splits; p += 4 * 128) {
+      float u1[4], u2[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int64_t row = static_cast<int64_t>(p + q * 128) * 2;
+        u1[q] = a.partial[(row + 0) * a.channels + c];
+        u2[q] = a.partial[(row + 1) * a.channels + c];
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        t1 += static_cast<double>(u1[q]);
+        t2 += static_cast<double>(u2[q]);
+      }
+    }
+    for (; p < a.splits; p += 128) {
       t1 += static_cast<double>(
           a.partial[(static_cast<int64_t>(p) * 2 + 0) * a.channels + c]);
       t2 += static_cast<double>(
@@ -614,14 +795,32 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
   if (g.inner == 1) {
     if (g.channels % kVec == 0 && aligned) {
       const int64_t cv = g.channels / kVec;
-      const Plan p = PlanLast(g.outer, g.channels, cv, kUnroll, true);
+      if (GetTuning(kTuneBnStatsPipe) != 0) {
+        using Cfg = StatsPipe<kMode>;
+        auto kernel = BnStatsPipeKernel<T, kMode>;
+        static const int resident = [&] {
+          cudaFuncSetAttribute(kernel,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               Cfg::kSmemBytes);
+          int n = 0;
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads,
+                                                        Cfg::kSmemBytes);
+          return n > 0 ? n : 1;
+        }();
+        const Plan p =
+            PlanLast(g.outer, g.channels, cv, Cfg::kU, true, resident);
+        kernel<<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), Cfg::kSmemBytes, stream>>>(
+            x, dy, mean, partial, g.outer, cv, g.channels, p.rows_per_cta);
+        return p.gy;
+      }
+      const Plan p = PlanLast(g.outer, g.channels, cv, kUnroll, true, 3);
       BnStatsLastKernel<T, kVec, kUnroll, kMode>
           <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
               x, dy, mean, partial, g.outer, cv, g.channels, p.rows_per_cta,
               keep);
       return p.gy;
     }
-    const Plan p = PlanLast(g.outer, g.channels, g.channels, kUnroll, true);
+    const Plan p = PlanLast(g.outer, g.channels, g.channels, kUnroll, true, 4);
     BnStatsLastKernel<T, 1, kUnroll, kMode>
         <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
             x, dy, mean, partial, g.outer, g.channels, g.channels,
@@ -666,12 +865,34 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
   if (g.inner == 1) {
     if (g.channels % kVec == 0 && aligned) {
       const int64_t cv = g.channels / kVec;
-      const Plan p = PlanLast(g.outer, g.channels, cv, kUnroll, false);
-      BnApplyLastKernel<T, kVec, kUnroll, kMode>
-          <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
-              x, dy, out, a, g.outer, cv, g.channels, p.rows_per_cta, reverse);
+      // The forward pass has one input stream: twice the rows in flight.
+      const bool deep = kMode == kFwd && GetTuning(kTuneBnApplyDeep) != 0;
+      if (deep) {
+        constexpr int kDeep = kMode == kFwd ? 8 : kUnroll;
+        auto kernel = BnApplyLastKernel<T, kVec, kDeep, kMode>;
+        static const int resident = [&] {
+          int n = 0;
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0);
+          return n > 0 ? n : 1;
+        }();
+        const Plan p = PlanLast(g.outer, g.channels, cv, kDeep, false, resident);
+        kernel<<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
+            x, dy, out, a, g.outer, cv, g.channels, p.rows_per_cta, reverse);
+      } else {
+        auto kernel = BnApplyLastKernel<T, kVec, kUnroll, kMode>;
+        static const int resident = [&] {
+          int n = 0;
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0);
+          return n > 0 ? n : 1;
+        }();
+        const Plan p =
+            PlanLast(g.outer, g.channels, cv, kUnroll, false, resident);
+        kernel<<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
+            x, dy, out, a, g.outer, cv, g.channels, p.rows_per_cta, reverse);
+      }
     } else {
-      const Plan p = PlanLast(g.outer, g.channels, g.channels, kUnroll, false);
+      const Plan p =
+          PlanLast(g.outer, g.channels, g.channels, kUnroll, false, 4);
       BnApplyLastKernel<T, 1, kUnroll, kMode>
           <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
               x, dy, out, a, g.outer, g.channels, g.channels, p.rows_per_cta,

@@ -45,6 +45,61 @@ __device__ __forceinline__ float Activate(float x, float b) {
   }
 }
 
+// 16-bit element pairs.  BiasAdd is a packed half-precision add: IEEE-rounded,
+// so it returns exactly what the un-fused BiasAdd op stores (a float add of two
+// 16-bit values followed by one rounding gives the same bits).  Relu is a packed
+// max.  The sigmoid runs in fp32 as 1 / (1 + 2^(-t * log2 e)) on the exp2 and
+// reciprocal units (relative error ~1e-6 over the whole range, including the
+// far negative side where a tanh form would cancel).
+__device__ __forceinline__ float2 Widen2(__half2 v) { return __half22float2(v); }
+__device__ __forceinline__ float2 Widen2(__nv_bfloat162 v) {
+  return __bfloat1622float2(v);
+}
+__device__ __forceinline__ void Narrow2(float a, float b, __half2& out) {
+  out = __floats2half2_rn(a, b);
+}
+__device__ __forceinline__ void Narrow2(float a, float b, __nv_bfloat162& out) {
+  out = __floats2bfloat162_rn(a, b);
+}
+
+template <typename T2, int kAct, bool kHasBias>
+__device__ __forceinline__ T2 ActivatePair(T2 x, T2 b) {
+  const T2 t = kHasBias ? __hadd2(x, b) : x;
+  if constexpr (kAct == MUSA_ACT_IDENTITY) {
+    return t;
+  } else if constexpr (kAct == MUSA_ACT_RELU) {
+    const float2 z = make_float2(0.0f, 0.0f);
+    T2 zero;
+    Narrow2(z.x, z.y, zero);
+    return __hmax2(t, zero);
+  } else {
+    const float2 tf = Widen2(t);
+    const float s0 = Sigmoid<true>(tf.x);
+    const float s1 = Sigmoid<true>(tf.y);
+    T2 out;
+    if constexpr (kAct == MUSA_ACT_SWISH) {
+      const float2 xf = Widen2(x);
+      Narrow2(xf.x * s0, xf.y * s1, out);
+    } else {
+      Narrow2(s0, s1, out);
+    }
+    return out;
+  }
+}
+
+template <typename T>
+struct PairOf {
+  using type = void;
+};
+template <>
+struct PairOf<__half> {
+  using type = __half2;
+};
+template <>
+struct PairOf<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+};
+
 // Channels-last pack kernel.  Pack p of the flat tensor covers channels
 // [(p % cv) * kEpt, +kEpt); the column is tracked incrementally, no division
 // in the loop.
@@ -81,10 +136,21 @@ __global__ void __launch_bounds__(256)
       const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
       if (i < n_packs) {
         P out;
+        if constexpr (sizeof(T) == 2 && kEpt % 2 == 0) {
+          using T2 = typename PairOf<T>::type;
+          const T2* x2 = reinterpret_cast<const T2*>(&px[u]);
+          const T2* b2 = reinterpret_cast<const T2*>(&pb[u]);
+          T2* o2 = reinterpret_cast<T2*>(&out);
 #pragma unroll
-        for (int e = 0; e < kEpt; ++e) {
-          const float b = kHasBias ? ToF32(pb[u].v[e]) : 0.0f;
-          out.v[e] = FromF32<T>(Activate<kAct, kFast>(ToF32(px[u].v[e]), b));
+          for (int e = 0; e < kEpt / 2; ++e) {
+            o2[e] = ActivatePair<T2, kAct, kHasBias>(x2[e], b2[e]);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < kEpt; ++e) {
+            const float b = kHasBias ? ToF32(pb[u].v[e]) : 0.0f;
+            out.v[e] = FromF32<T>(Activate<kAct, kFast>(ToF32(px[u].v[e]), b));
+          }
         }
         StoreStream(yp + i, out);
       }

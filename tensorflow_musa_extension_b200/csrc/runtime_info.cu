@@ -18,8 +18,9 @@ void InitTuningOnce() {
   std::call_once(g_tuning_once, [] {
     static const int defaults[kTuneCount] = {
         /*AdamCtasPerSm*/ 0, /*AdamUnroll*/ 2, /*BiasActCtasPerSm*/ 0,
-        /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 8, /*BnFused*/ 0,
-        /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1};
+        /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 0, /*BnFused*/ 0,
+        /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1, /*BnStatsPipe*/ 1,
+        /*BnApplyDeep*/ 0};
     for (int i = 0; i < kTuneCount; ++i) g_tuning[i].store(defaults[i]);
   });
 }

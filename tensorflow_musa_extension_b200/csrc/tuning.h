@@ -10,10 +10,12 @@ enum TuningKey {
   kTuneAdamUnroll = 1,      // packs in flight per thread and stream: 1, 2, 4
   kTuneBiasActCtasPerSm = 2,
   kTuneBiasActUnroll = 3,
-  kTuneBnCtasPerSm = 4,     // CTAs per SM of the BatchNorm stats/apply grids
+  kTuneBnCtasPerSm = 4,     // CTAs per SM of the BatchNorm grids; 0: what fits
   kTuneBnFused = 5,         // 1: single cooperative kernel when it applies
   kTuneBnApplyReverse = 6,  // 1: apply pass walks rows in reverse (L2 reuse)
   kTuneBnStatsKeep = 7,     // 1: stats pass loads with the default L2 policy
+  kTuneBnStatsPipe = 8,     // 1: cp.async-staged stats kernel (128-bit path)
+  kTuneBnApplyDeep = 9,     // 1: forward element-wise pass keeps 8 rows in flight
   kTuneCount = 16
 };
 

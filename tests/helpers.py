@@ -29,6 +29,8 @@ def to_torch(a, device="cuda"):
 
 def to_numpy(t):
     import torch
+    if isinstance(t, np.ndarray):
+        return t
     t = t.detach().cpu()
     if t.dtype == torch.bfloat16:
         return t.view(torch.int16).numpy().view(NP_BF16)

@@ -35,10 +35,13 @@ def check_forward(got, want, dtype, what=""):
     assert tuple(got.reserve_space_3.shape) == () and float(got.reserve_space_3) == 0.0
 
 
-def check_grad(got, want, dtype, what=""):
+def check_grad(got, want, dtype, what="", dx_scale=None):
+    """`dx_scale`: magnitude of the terms dx is a difference of (|dy| * scale *
+    inv_std); with a handful of rows dx is what is left after they cancel, so
+    the absolute tolerance follows the terms, not the residue."""
     rt = _rt(dtype)
-    assert_close(to_numpy(got.x_backprop), want[0], rt, rt * max(_rms(want[0]), 1e-12),
-                 what + " dx")
+    floor = max(_rms(want[0]), 1e-12) if dx_scale is None else max(dx_scale, _rms(want[0]))
+    assert_close(to_numpy(got.x_backprop), want[0], rt, rt * floor, what + " dx")
     srt = RTOL["f32_bn"]
     assert_close(to_numpy(got.scale_backprop), want[1], srt,
                  srt * max(_rms(want[1]), 1e-12), what + " dscale")
@@ -82,7 +85,8 @@ def test_nhwc_shape_matrix(kernel_lib, dtype, c, rows):
     want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
     check_forward(fwd, want, dtype)
     wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS)
-    check_grad(grad, wg, dtype)
+    terms = _rms(dy) * float(np.max(s / np.sqrt(want[4] + EPS)))
+    check_grad(grad, wg, dtype, dx_scale=terms)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
@@ -328,5 +332,8 @@ def test_config2_16bit_full_size(kernel_lib, dtype):
     z = (y - to_torch(o)) / to_torch(s)
     assert float(z.mean(0).abs().max()) < 5e-3
     assert float((z.var(0, unbiased=False) - 1).abs().max()) < 2e-2
-    dxs = grad.x_backprop.float().reshape(-1, 256).sum(0)
-    assert float(dxs.abs().max()) < 5e-2
+    # dx sums to zero per channel in exact arithmetic; after rounding dx to 16
+    # bits the sum is whatever the rounding leaves, which the oracle shares.
+    dxs = grad.x_backprop.double().reshape(-1, 256).sum(0).cpu().numpy()
+    want_dxs = wg[0].astype(np.float64).sum(0)
+    assert float(np.abs(dxs - want_dxs).max()) < 5e-2
