@@ -134,6 +134,36 @@ class ClockSampler:
 
 # ------------------------------------------------------------------ ours ----
 
+def finish(torch, dist, world):
+    """Leaves a multi-rank run: every rank drains its GPU, meets the others at
+    a barrier and exits at once.  The process group is not torn down
+    collectively: tearing down NCCL communicators that captured CUDA graphs
+    still reference has hung, and nothing is in flight at this point."""
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def arm_watchdog(seconds):
+    """Ends the process if the run has not finished after `seconds` (a hung
+    collective must not hold the GPUs)."""
+    import threading
+
+    def bail():
+        sys.stderr.write("bench.py: watchdog fired after %d s\n" % seconds)
+        sys.stderr.flush()
+        os._exit(3)
+
+    t = threading.Timer(seconds, bail)
+    t.daemon = True
+    t.start()
+    return t
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -148,7 +178,11 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    arm_watchdog(args.watchdog)
     if world > 1:
+        # Plain peer-to-peer rings: the exchanged messages are a few KiB, and a
+        # rank never sits bound to an NVLink multicast object.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
 
     import tensorflow_musa_extension_b200 as pkg
@@ -201,10 +235,7 @@ def run_ours(args):
     if args.profile_step:
         # One eager pass and nothing else: the target of an ncu launch list.
         step()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
+        finish(torch, dist, world)
         return
 
     # Warm up eagerly, then capture the step in a CUDA graph (the launchers
@@ -311,9 +342,7 @@ def run_ours(args):
             result["cpu_baseline"] = None
     if rank == 0:
         print(json.dumps(result), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    finish(torch, dist, world)
 
 
 def measure_e2e(torch, dist, raw_ops, layers, world, rank, dev, args):
@@ -605,6 +634,8 @@ def main():
     ap.add_argument("--profile-step", action="store_true",
                     help="run one eager pass of the workload and exit (ncu target)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--watchdog", type=int, default=600,
+                    help="seconds after which a run that has not finished is ended")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

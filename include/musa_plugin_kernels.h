@@ -245,6 +245,12 @@ void LaunchVarianceToInvStd(const float* variance, float* inv_std,
 int LaunchBnStatsSums(int dtype, const void* x, float* sums, int64_t outer,
                       int64_t channels, int64_t inner, void* workspace,
                       size_t workspace_bytes, cudaStream_t stream);
+/* Same, and sums[2C] = the local row count, so that replicas with different
+ * batch sizes learn the global count from the same all-reduce (sums holds
+ * 2C + 1 floats). */
+int LaunchBnStatsSumsCount(int dtype, const void* x, float* sums, int64_t outer,
+                           int64_t channels, int64_t inner, void* workspace,
+                           size_t workspace_bytes, cudaStream_t stream);
 /* From all-reduced sums over `total_count` values per channel to the four
  * statistic outputs of the forward op. */
 int LaunchBnFinalizeFromSums(const float* sums, double total_count,
@@ -258,6 +264,17 @@ int LaunchBnApply(int dtype, const void* x, const float* scale,
                   const float* offset, const float* mean, const float* variance,
                   void* y, int64_t outer, int64_t channels, int64_t inner,
                   float epsilon, cudaStream_t stream);
+/* LaunchBnFinalizeFromSums and LaunchBnApply as one launch: the element-wise
+ * kernel derives mean and variance from the all-reduced sums in its prologue
+ * and writes the four statistic outputs itself. */
+int LaunchBnApplyFromSums(int dtype, const void* x, const float* scale,
+                          const float* offset, const float* sums,
+                          double total_count, const float* est_mean,
+                          const float* est_var, float exp_avg_factor, void* y,
+                          float* batch_mean, float* batch_var,
+                          float* saved_mean, float* saved_var, int64_t outer,
+                          int64_t channels, int64_t inner, float epsilon,
+                          cudaStream_t stream);
 /* sums[0:C] = sum(dy), sums[C:2C] = sum(dy * (x - mean)) over local rows. */
 int LaunchBnGradStatsSums(int dtype, const void* dy, const void* x,
                           const float* mean, float* sums, int64_t outer,

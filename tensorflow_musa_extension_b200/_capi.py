@@ -48,6 +48,11 @@ PROTOTYPES = {
     "LaunchVarianceToInvStd": (None, [c_vp, c_vp, c_f32, c_int, c_vp]),
     "LaunchBnStatsSums":
         (c_int, [c_int, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]),
+    "LaunchBnStatsSumsCount":
+        (c_int, [c_int, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]),
+    "LaunchBnApplyFromSums":
+        (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_f64, c_vp, c_vp, c_f32, c_vp,
+                 c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_f32, c_vp]),
     "LaunchBnFinalizeFromSums":
         (c_int, [c_vp, c_f64] + [c_vp] * 6 + [c_i64, c_f32, c_vp]),
     "LaunchBnApply":

@@ -56,23 +56,21 @@ class _DeviceKernels:
         return self.lib.BnWorkspaceBytes(rows, c, 1)
 
     def stats_sums(self, x, sums, ws):
+        """sums[0:2C] = local sums, sums[2C] = local row count."""
         rows, c = x.shape
-        raw_ops._check(self.lib.LaunchBnStatsSums(
+        raw_ops._check(self.lib.LaunchBnStatsSumsCount(
             _DT_CODE[x.dtype], x.data_ptr(), sums.data_ptr(), rows, c, 1,
-            ws.data_ptr(), ws.numel(), self._st()), "LaunchBnStatsSums")
+            ws.data_ptr(), ws.numel(), self._st()), "LaunchBnStatsSumsCount")
 
-    def finalize(self, sums, count, stats, c):
-        raw_ops._check(self.lib.LaunchBnFinalizeFromSums(
-            sums.data_ptr(), float(count), None, None, stats[0].data_ptr(),
-            stats[1].data_ptr(), stats[2].data_ptr(), stats[3].data_ptr(), c, 1.0,
-            self._st()), "LaunchBnFinalizeFromSums")
-
-    def apply(self, x, scale, offset, mean, var, y, eps):
+    def apply_from_sums(self, x, scale, offset, sums, count, stats, y, eps):
+        """Statistics from the all-reduced sums and the element-wise pass, one
+        launch."""
         rows, c = x.shape
-        raw_ops._check(self.lib.LaunchBnApply(
+        raw_ops._check(self.lib.LaunchBnApplyFromSums(
             _DT_CODE[x.dtype], x.data_ptr(), scale.data_ptr(), offset.data_ptr(),
-            mean.data_ptr(), var.data_ptr(), y.data_ptr(), rows, c, 1, eps, self._st()),
-            "LaunchBnApply")
+            sums.data_ptr(), float(count), None, None, 1.0, y.data_ptr(),
+            stats[0].data_ptr(), stats[1].data_ptr(), stats[2].data_ptr(),
+            stats[3].data_ptr(), rows, c, 1, eps, self._st()), "LaunchBnApplyFromSums")
 
     def grad_stats_sums(self, dy, x, mean, sums, ws):
         rows, c = x.shape
@@ -139,7 +137,7 @@ class SyncBatchNorm:
         self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         self._ws_rows = int(max_rows)
         self.global_count = None
-        self.launches_per_step = 6 if self.world == 1 else 8
+        self.launches_per_step = 6
 
     def _stats(self):
         return (self.batch_mean, self.batch_var, self.saved_mean, self.saved_var)
@@ -162,14 +160,13 @@ class SyncBatchNorm:
             self.global_count = float(rows)
             return y
         self.k.stats_sums(x, self.sums, self.ws)
-        self.sums[2 * self.c:].fill_(float(rows))
         dist.all_reduce(self.sums, op=dist.ReduceOp.SUM, group=self.group)
         # Static shapes: the global count is rows * world unless a replica is
         # ragged; read it on the host only in that case.
         self.global_count = float(rows) * self.world if self._uniform_rows else \
             float(self.sums[2 * self.c].item())
-        self.k.finalize(self.sums, self.global_count, self._stats(), self.c)
-        self.k.apply(x, scale, offset, self.saved_mean, self.saved_var, y, self.eps)
+        self.k.apply_from_sums(x, scale, offset, self.sums, self.global_count,
+                               self._stats(), y, self.eps)
         return y
 
     _uniform_rows = True

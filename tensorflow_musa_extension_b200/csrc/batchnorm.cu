@@ -466,6 +466,7 @@ struct FinalizeArgs {
   float epsilon;
   // both: totals for the apply pass / the all-reduce
   float* sums;           // [2, C] or NULL
+  float* count_out;      // optional: receives `count` (rides in the all-reduce)
 };
 
 __device__ __forceinline__ float LoadAsF32(const void* base, int dtype,
@@ -552,6 +553,9 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
       const double md = S1 / a.count;
       WriteFwdStats(a, c, K + md, S2 / a.count - md * md);
     } else if constexpr (kOut == 1) {
+      if (a.count_out != nullptr && c == 0) {
+        *a.count_out = static_cast<float>(a.count);
+      }
       const double K =
           static_cast<double>(LoadAsF32(a.x_first, a.x_dtype, c * a.shift_stride));
       // Local rows only: count is this replica's.
@@ -618,6 +622,15 @@ struct ApplyArgs {
   const float* sums;      // gradient: [2, C] totals (NULL for inference grad)
   float inv_count;        // gradient: 1 / R over all replicas
   float epsilon;
+  // Forward from all-reduced sums: when stat_sums is set, mean / variance are
+  // derived from [sum x, sum x^2] over `count` values in the kernel prologue
+  // and the first row of CTAs writes the four statistic outputs.
+  const float* stat_sums;
+  double count;
+  FinalizeArgs stat_out;  // est_*, batch_*, saved_*, exp_avg_factor
+  // Gradient: the first row of CTAs writes dscale / doffset when set.
+  float* dscale;
+  float* doffset;
 };
 
 template <typename T, int kVec, int kUnroll, int kMode>
@@ -637,12 +650,24 @@ __global__ void __launch_bounds__(kThreads)
   int64_t r1 = r0 + rows_per_cta;
   if (r1 > rows) r1 = rows;
 
+  const bool writer = blockIdx.y == 0 && ty == 0;
   float mean[kVec], ca[kVec], cb[kVec], cc[kVec];
 #pragma unroll
   for (int e = 0; e < kVec; ++e) {
     const int64_t c = col * kVec + e;
-    const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
-    mean[e] = a.mean[c];
+    float var_c;
+    if (kMode == kFwd && a.stat_sums != nullptr) {
+      const double m = static_cast<double>(a.stat_sums[c]) / a.count;
+      double v = static_cast<double>(a.stat_sums[channels + c]) / a.count - m * m;
+      if (v < 0.0) v = 0.0;
+      mean[e] = static_cast<float>(m);
+      var_c = static_cast<float>(v);
+      if (writer) WriteFwdStats(a.stat_out, c, m, v);
+    } else {
+      mean[e] = a.mean[c];
+      var_c = a.variance[c];
+    }
+    const float inv = 1.0f / sqrtf(var_c + a.epsilon);
     ca[e] = a.scale[c] * inv;
     if constexpr (kMode == kFwd) {
       cb[e] = a.offset[c];
@@ -654,6 +679,10 @@ __global__ void __launch_bounds__(kThreads)
       } else {
         cb[e] = 0.0f;
         cc[e] = 0.0f;
+      }
+      if (writer && a.dscale != nullptr && a.sums != nullptr) {
+        a.doffset[c] = a.sums[c];
+        a.dscale[c] = a.sums[channels + c] * inv;
       }
     }
   }
@@ -1038,8 +1067,8 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
 }
 
 template <typename T>
-int StatsSums(const void* x, float* sums, const Geom& g, void* workspace,
-              size_t workspace_bytes, cudaStream_t stream) {
+int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
+              void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   if (!x || !sums) return MUSA_KERNELS_EINVAL;
   if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
       !Aligned16(workspace)) {
@@ -1058,6 +1087,7 @@ int StatsSums(const void* x, float* sums, const Geom& g, void* workspace,
   f.x_dtype = DtypeCode<T>::value;
   f.shift_stride = g.inner == 1 ? 1 : g.inner;
   f.sums = sums;
+  f.count_out = count_out;
   LaunchFinalize<1>(f, stream);
   return LastError();
 }
@@ -1095,12 +1125,17 @@ int GradApplyFromSums(const void* dy, const void* x, const float* scale,
   if (!dy || !x || !scale || !mean || !variance || !sums || !dx) {
     return MUSA_KERNELS_EINVAL;
   }
-  if (dscale && doffset) {
-    const int grid = static_cast<int>(CeilDiv(g.channels, 256));
-    BnGradScalesFromSumsKernel<<<grid, 256, 0, stream>>>(
-        sums, variance, epsilon, dscale, doffset, g.channels);
-  }
   ApplyArgs a{};
+  if (dscale && doffset) {
+    if (g.inner == 1) {
+      a.dscale = dscale;  // written by the element-wise kernel's first CTA row
+      a.doffset = doffset;
+    } else {
+      const int grid = static_cast<int>(CeilDiv(g.channels, 256));
+      BnGradScalesFromSumsKernel<<<grid, 256, 0, stream>>>(
+          sums, variance, epsilon, dscale, doffset, g.channels);
+    }
+  }
   a.scale = scale;
   a.mean = mean;
   a.variance = variance;
@@ -1203,8 +1238,75 @@ int LaunchBnStatsSums(int dtype, const void* x, float* sums, int64_t outer,
     return static_cast<int>(
         cudaMemsetAsync(sums, 0, sizeof(float) * 2 * channels, stream));
   }
-  MUSA_BY_DTYPE(dtype,
-                StatsSums<T>(x, sums, g, workspace, workspace_bytes, stream));
+  MUSA_BY_DTYPE(dtype, StatsSums<T>(x, sums, nullptr, g, workspace,
+                                    workspace_bytes, stream));
+}
+
+int LaunchBnStatsSumsCount(int dtype, const void* x, float* sums, int64_t outer,
+                           int64_t channels, int64_t inner, void* workspace,
+                           size_t workspace_bytes, cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!sums) return MUSA_KERNELS_EINVAL;
+  if (IsEmpty(g)) {
+    return static_cast<int>(
+        cudaMemsetAsync(sums, 0, sizeof(float) * (2 * channels + 1), stream));
+  }
+  MUSA_BY_DTYPE(dtype, StatsSums<T>(x, sums, sums + 2 * channels, g, workspace,
+                                    workspace_bytes, stream));
+}
+
+int LaunchBnApplyFromSums(int dtype, const void* x, const float* scale,
+                          const float* offset, const float* sums,
+                          double total_count, const float* est_mean,
+                          const float* est_var, float exp_avg_factor, void* y,
+                          float* batch_mean, float* batch_var,
+                          float* saved_mean, float* saved_var, int64_t outer,
+                          int64_t channels, int64_t inner, float epsilon,
+                          cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (!(total_count > 0.0)) return MUSA_KERNELS_EINVAL;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!sums || !scale || !offset || !saved_mean || !saved_var) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  if (exp_avg_factor != 1.0f && (!est_mean || !est_var)) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  if (g.inner != 1 || IsEmpty(g)) {
+    // General layout (or a replica without rows): statistics first, then the
+    // element-wise pass.
+    if (int rc = LaunchBnFinalizeFromSums(sums, total_count, est_mean, est_var,
+                                          batch_mean, batch_var, saved_mean,
+                                          saved_var, channels, exp_avg_factor,
+                                          stream)) {
+      return rc;
+    }
+    if (IsEmpty(g)) return MUSA_KERNELS_OK;
+    return LaunchBnApply(dtype, x, scale, offset, saved_mean, saved_var, y,
+                         outer, channels, inner, epsilon, stream);
+  }
+  if (!x || !y) return MUSA_KERNELS_EINVAL;
+  ApplyArgs a{};
+  a.scale = scale;
+  a.offset = offset;
+  a.epsilon = epsilon;
+  a.stat_sums = sums;
+  a.count = total_count;
+  a.stat_out.channels = channels;
+  a.stat_out.count = total_count;
+  a.stat_out.est_mean = est_mean;
+  a.stat_out.est_var = est_var;
+  a.stat_out.batch_mean = batch_mean;
+  a.stat_out.batch_var = batch_var;
+  a.stat_out.saved_mean = saved_mean;
+  a.stat_out.saved_var = saved_var;
+  a.stat_out.exp_avg_factor = exp_avg_factor;
+  MUSA_BY_DTYPE(dtype, (LaunchApply<T, kFwd>(static_cast<const T*>(x), nullptr,
+                                             static_cast<T*>(y), a, g, stream),
+                        LastError()));
 }
 
 int LaunchBnFinalizeFromSums(const float* sums, double total_count,

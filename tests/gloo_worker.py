@@ -27,6 +27,11 @@ class CpuStages:
         xf = x.double()
         sums[:c] = xf.sum(0).float()
         sums[c:2 * c] = (xf * xf).sum(0).float()
+        sums[2 * c] = float(x.shape[0])
+
+    def apply_from_sums(self, x, scale, offset, sums, count, stats, y, eps):
+        self.finalize(sums, count, stats, x.shape[1])
+        self.apply(x, scale, offset, stats[2], stats[3], y, eps)
 
     def finalize(self, sums, count, stats, c):
         mean = sums[:c].double() / count

@@ -239,7 +239,7 @@ def test_host_buffers_round_trip(kernel_lib):
 
 # ------------------------------------------------ cross-replica (split) API --
 
-def _split_forward_and_grad(lib, x, dy, scale, offset, parts):
+def _split_forward_and_grad(lib, x, dy, scale, offset, parts, fused=False):
     """Runs the SyncBN halves on `parts` row blocks as if they were replicas
     and sums the per-replica sums on the host side of the all-reduce."""
     dt = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[x.dtype]
@@ -248,23 +248,34 @@ def _split_forward_and_grad(lib, x, dy, scale, offset, parts):
     bounds = np.linspace(0, rows, parts + 1).astype(int)
     need = lib.BnWorkspaceBytes(rows, c, 1)
     ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
-    total = torch.zeros(2 * c, device="cuda")
+    total = torch.zeros(2 * c + 1, device="cuda")
     for lo, hi in zip(bounds[:-1], bounds[1:]):
-        sums = torch.empty(2 * c, device="cuda")
-        rc = lib.LaunchBnStatsSums(dt, x[lo:hi].data_ptr(), sums.data_ptr(), int(hi - lo),
-                                   c, 1, ws.data_ptr(), ws.numel(), st)
+        sums = torch.zeros(2 * c + 1, device="cuda")
+        fn = lib.LaunchBnStatsSumsCount if fused else lib.LaunchBnStatsSums
+        rc = fn(dt, x[lo:hi].data_ptr(), sums.data_ptr(), int(hi - lo), c, 1,
+                ws.data_ptr(), ws.numel(), st)
         assert rc == 0
         total += sums
+    if fused:   # the row count rode along with the sums
+        assert float(total[2 * c]) == float(rows)
     bm, bv, sm, sv = (torch.empty(c, device="cuda") for _ in range(4))
-    assert lib.LaunchBnFinalizeFromSums(total.data_ptr(), float(rows), None, None,
-                                        bm.data_ptr(), bv.data_ptr(), sm.data_ptr(),
-                                        sv.data_ptr(), c, 1.0, st) == 0
+    if not fused:
+        assert lib.LaunchBnFinalizeFromSums(total.data_ptr(), float(rows), None, None,
+                                            bm.data_ptr(), bv.data_ptr(), sm.data_ptr(),
+                                            sv.data_ptr(), c, 1.0, st) == 0
     y = torch.empty_like(x)
     gtotal = torch.zeros(2 * c, device="cuda")
     for lo, hi in zip(bounds[:-1], bounds[1:]):
-        assert lib.LaunchBnApply(dt, x[lo:hi].data_ptr(), scale.data_ptr(), offset.data_ptr(),
-                                 sm.data_ptr(), sv.data_ptr(), y[lo:hi].data_ptr(),
-                                 int(hi - lo), c, 1, EPS, st) == 0
+        if fused:
+            assert lib.LaunchBnApplyFromSums(
+                dt, x[lo:hi].data_ptr(), scale.data_ptr(), offset.data_ptr(),
+                total.data_ptr(), float(rows), None, None, 1.0, y[lo:hi].data_ptr(),
+                bm.data_ptr(), bv.data_ptr(), sm.data_ptr(), sv.data_ptr(), int(hi - lo),
+                c, 1, EPS, st) == 0
+        else:
+            assert lib.LaunchBnApply(dt, x[lo:hi].data_ptr(), scale.data_ptr(),
+                                     offset.data_ptr(), sm.data_ptr(), sv.data_ptr(),
+                                     y[lo:hi].data_ptr(), int(hi - lo), c, 1, EPS, st) == 0
         sums = torch.empty(2 * c, device="cuda")
         assert lib.LaunchBnGradStatsSums(dt, dy[lo:hi].data_ptr(), x[lo:hi].data_ptr(),
                                          sm.data_ptr(), sums.data_ptr(), int(hi - lo), c, 1,
@@ -282,10 +293,11 @@ def _split_forward_and_grad(lib, x, dy, scale, offset, parts):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("parts", [1, 2, 8])
-def test_split_api_equals_global_batchnorm(kernel_lib, dtype, parts):
+@pytest.mark.parametrize("fused", [False, True])
+def test_split_api_equals_global_batchnorm(kernel_lib, dtype, parts, fused):
     x, s, o, dy = bn_inputs(16, (4096, 64), dtype, 0.0, 1.0)
     got = _split_forward_and_grad(kernel_lib, to_torch(x), to_torch(dy), to_torch(s),
-                                  to_torch(o), parts)
+                                  to_torch(o), parts, fused)
     want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
     wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS)
     rt = _rt(dtype)
