@@ -221,6 +221,40 @@ int LaunchBnGrad_BF16(const void* dy, const void* x, const float* scale,
                       bool is_training, void* workspace, size_t workspace_bytes,
                       cudaStream_t stream);
 
+/* Training-mode forward for callers that may not allocate device memory.
+ * No counterpart in the reference.
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits - inside a
+ * serving or training loop that forbids allocation after start-up because
+ * cudaMalloc synchronises the whole device, inside a host callback or a
+ * library hook that has no framework allocator (no OpKernelContext to ask for
+ * a temporary) at hand, or in a process whose memory budget was handed out in
+ * full at start.  Such a caller cannot supply the workspace that
+ * LaunchBnFwdTrain_* asks for, so this entry point brings its own: a 4 MiB +
+ * 64 KiB array that is part of the library image on every GPU that loads it.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * Same arguments and results as LaunchBnFwdTrain_{F32,F16,BF16} (dtype:
+ * MUSA_DT_*), minus the workspace.  Limits: channels <= BnNoAllocMaxChannels()
+ * (8192); beyond that, or if the geometry would need more scratch than the
+ * array holds, it returns MUSA_KERNELS_ETOOLARGE and launches nothing.
+ *
+ * The first call on each device looks up the array's device address (with
+ * that device current); make that first call outside any stream capture.
+ * All calls share the one array per device: it keeps whatever the last call
+ * left there (nothing in it has to start at zero - every word that is read was
+ * written earlier in the same call), and two calls whose kernels can overlap
+ * on the GPU - different streams, or the same stream from two threads without
+ * ordering - race on it.  Issue them on one stream, or order them with events. */
+size_t BnNoAllocMaxChannels(void);
+int LaunchBnFwdTrainNoAlloc(int dtype, const void* x, const float* scale,
+                            const float* offset, const float* est_mean,
+                            const float* est_var, void* y, float* batch_mean,
+                            float* batch_var, float* saved_mean,
+                            float* saved_var, int64_t outer, int64_t channels,
+                            int64_t inner, float epsilon, float exp_avg_factor,
+                            cudaStream_t stream);
+
 /* The two BatchNorm fix-up launchers of the reference, kept for callers that
  * still hold muDNN-convention statistics: data[i] *= factor, and
  * inv_std[i] = rsqrt(variance[i] + epsilon).  Replace LaunchBesselCorrection

@@ -44,6 +44,9 @@ PROTOTYPES = {
     "LaunchBnGrad_F32": (c_int, _BN_GRAD),
     "LaunchBnGrad_F16": (c_int, _BN_GRAD),
     "LaunchBnGrad_BF16": (c_int, _BN_GRAD),
+    "BnNoAllocMaxChannels": (c_size, []),
+    "LaunchBnFwdTrainNoAlloc":
+        (c_int, [c_int] + [c_vp] * 10 + [c_i64, c_i64, c_i64, c_f32, c_f32, c_vp]),
     "LaunchBesselCorrection": (None, [c_vp, c_f32, c_int, c_vp]),
     "LaunchVarianceToInvStd": (None, [c_vp, c_vp, c_f32, c_int, c_vp]),
     "LaunchBnStatsSums":

@@ -26,6 +26,8 @@
 // Bessel-corrected, saved_var is the population variance, no correction when
 // there is one value per channel; :265-277: the gradient receives a variance
 // and turns it into 1/sqrt(var + eps)).
+#include <mutex>
+
 #include "common.cuh"
 #include "tuning.h"
 #include "../../include/musa_plugin_kernels.h"
@@ -1147,6 +1149,45 @@ int GradApplyFromSums(const void* dy, const void* x, const float* scale,
   return LastError();
 }
 
+// ---- Scratch that lives in the library image, for callers that cannot
+// allocate device memory (see LaunchBnFwdTrainNoAlloc below).
+//
+// 4 MiB of level-1 partial sums plus the [2, C] totals for up to 8192
+// channels.  Every GPU that loads the library carries this array until the
+// process exits.  In host code the array's NAME is only a handle of the
+// runtime, not a device address: the address a kernel may use is obtained
+// with cudaGetSymbolAddress, once per device, with that device current.
+constexpr int64_t kStaticScratchMaxChannels = 8192;
+constexpr size_t kStaticScratchBytes =
+    sizeof(float) * (kMaxPartialFloats + 2 * kStaticScratchMaxChannels);
+static __device__ __align__(256) unsigned char
+    g_bn_static_scratch[kStaticScratchBytes];
+
+constexpr int kScratchMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_addr[kScratchMaxDevices] = {};
+
+// Device address of g_bn_static_scratch on the current device; resolves it on
+// the first call per device.  Returns a cudaError_t (0 on success).
+int StaticScratchAddress(void** out) {
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (dev < 0 || dev >= kScratchMaxDevices) {
+    return static_cast<int>(cudaErrorInvalidDevice);
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_bn_static_scratch);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    if (ptr == nullptr) return static_cast<int>(cudaErrorInvalidSymbol);
+    g_scratch_addr[dev] = ptr;
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+
 }  // namespace
 }  // namespace musa_b200
 
@@ -1212,6 +1253,33 @@ MUSA_DEFINE_BN(F32, float)
 MUSA_DEFINE_BN(F16, __half)
 MUSA_DEFINE_BN(BF16, __nv_bfloat16)
 #undef MUSA_DEFINE_BN
+
+size_t BnNoAllocMaxChannels(void) {
+  return static_cast<size_t>(kStaticScratchMaxChannels);
+}
+
+int LaunchBnFwdTrainNoAlloc(int dtype, const void* x, const float* scale,
+                            const float* offset, const float* est_mean,
+                            const float* est_var, void* y, float* batch_mean,
+                            float* batch_var, float* saved_mean,
+                            float* saved_var, int64_t outer, int64_t channels,
+                            int64_t inner, float epsilon, float exp_avg_factor,
+                            cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (IsEmpty(g)) return MUSA_KERNELS_OK;
+  if (channels > kStaticScratchMaxChannels ||
+      WorkspaceBytes(g) > kStaticScratchBytes) {
+    return MUSA_KERNELS_ETOOLARGE;
+  }
+  void* scratch = nullptr;
+  if (int rc = StaticScratchAddress(&scratch)) return rc;
+  MUSA_BY_DTYPE(dtype,
+                FwdTrain<T>(x, scale, offset, est_mean, est_var, y, batch_mean,
+                            batch_var, saved_mean, saved_var, outer, channels,
+                            inner, epsilon, exp_avg_factor, scratch,
+                            kStaticScratchBytes, stream));
+}
 
 void LaunchBesselCorrection(float* data, float factor, int count,
                             cudaStream_t stream) {
