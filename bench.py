@@ -620,6 +620,74 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_profile_case(args):
+    """Small fixed launch sequences for `ncu` captures (one kernel family per
+    case, inputs beyond L2, a few hundred MB on the device):
+      bn      FusedBatchNorm forward + gradient, bf16 [256,28,28,256], twice
+      bnsmall the same on bf16 [256,28,28,128] (S = 51 MB, inside L2)
+      bnbig   gradient element-wise pass alone, bf16 [256,56,56,256], twice
+      adam    ResourceApplyAdam fp32, 25,557,032 parameters, twice
+      bias    Relu(BiasAdd) and x*sigmoid(x+b), fp16 [65536,1024], twice each"""
+    import torch
+    import tensorflow_musa_extension_b200 as pkg
+    from tensorflow_musa_extension_b200 import raw_ops
+    pkg.load_plugin()
+    lib = raw_ops._lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    st = torch.cuda.current_stream().cuda_stream
+    case = args.profile_case
+    if case in ("bn", "bnbig", "bnsmall"):
+        rows, c = {"bn": (256 * 28 * 28, 256), "bnbig": (256 * 56 * 56, 256),
+                   "bnsmall": (256 * 28 * 28, 128)}[case]
+        x = torch.randn(rows, c, device=dev).to(torch.bfloat16)
+        dy = (torch.randn(rows, c, device=dev) * 1e-2).to(torch.bfloat16)
+        out = torch.empty_like(x)
+        sc = torch.rand(c, device=dev) + 0.5
+        of = torch.randn(c, device=dev) * 0.1
+        stats = [torch.empty(c, device=dev) for _ in range(6)]
+        sums = torch.zeros(2 * c, device=dev)
+        need = lib.BnWorkspaceBytes(rows, c, 1)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        for _ in range(2):
+            if case != "bnbig":
+                lib.LaunchBnFwdTrain_BF16(
+                    x.data_ptr(), sc.data_ptr(), of.data_ptr(), None, None, out.data_ptr(),
+                    stats[0].data_ptr(), stats[1].data_ptr(), stats[2].data_ptr(),
+                    stats[3].data_ptr(), rows, c, 1, EPS, 1.0, ws.data_ptr(), need, st)
+                lib.LaunchBnGrad_BF16(
+                    dy.data_ptr(), x.data_ptr(), sc.data_ptr(), stats[2].data_ptr(),
+                    stats[3].data_ptr(), out.data_ptr(), stats[4].data_ptr(),
+                    stats[5].data_ptr(), rows, c, 1, EPS, True, ws.data_ptr(), need, st)
+            else:
+                stats[2].zero_()
+                stats[3].fill_(1.0)
+                lib.LaunchBnGradApplyFromSums(
+                    2, dy.data_ptr(), x.data_ptr(), sc.data_ptr(), stats[2].data_ptr(),
+                    stats[3].data_ptr(), sums.data_ptr(), float(rows), out.data_ptr(), None,
+                    None, rows, c, 1, EPS, st)
+    elif case == "adam":
+        n = 25_557_032
+        var = torch.randn(n, device=dev) * 0.05
+        m = torch.randn(n, device=dev) * 1e-4
+        v = torch.rand(n, device=dev) * 1e-6
+        g = torch.randn(n, device=dev) * 1e-3
+        for _ in range(2):
+            lib.LaunchResourceApplyAdamFloat(var.data_ptr(), m.data_ptr(), v.data_ptr(),
+                                             g.data_ptr(), 0.9, 0.999, 1e-7, 3e-4, n, st)
+    elif case == "bias":
+        x = torch.randn(65536, 1024, device=dev, dtype=torch.float16)
+        b = (torch.randn(1024, device=dev) * 0.1).half()
+        y = torch.empty_like(x)
+        for _ in range(2):
+            for act in (1, 2):
+                lib.LaunchBiasAct_F16(x.data_ptr(), b.data_ptr(), y.data_ptr(), 65536, 1024,
+                                      1, act, st)
+    else:
+        raise SystemExit("unknown --profile-case " + case)
+    torch.cuda.synchronize()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -636,7 +704,13 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--watchdog", type=int, default=600,
                     help="seconds after which a run that has not finished is ended")
+    ap.add_argument("--profile-case", default=None,
+                    help="run a small fixed launch sequence and exit (ncu target): "
+                         "bn | bnsmall | bnbig | adam | bias")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -108,6 +108,8 @@ __global__ void __launch_bounds__(kThreads)
                       float* __restrict__ partial, int64_t rows, int64_t cv,
                       int64_t channels, int64_t rows_per_cta, bool keep) {
   using P = Pack<T, kVec>;
+  GridDepWait();
+  GridDepLaunch();
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
   const int64_t col = static_cast<int64_t>(blockIdx.x) * TX + tx;
@@ -237,6 +239,38 @@ __device__ __forceinline__ void CpAsync16(void* smem_dst, const void* gmem_src) 
                "l"(gmem_src)
                : "memory");
 }
+// L2 eviction-priority policies.  The statistics pass marks the lines it
+// brings in "evict last" when the tensor is small enough to stay in L2 until
+// the element-wise pass re-reads it; that pass marks them "evict first" as it
+// consumes them.
+__device__ __forceinline__ uint64_t PolicyEvictLast() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t PolicyEvictFirst() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void CpAsync16Hint(void* smem_dst,
+                                              const void* gmem_src,
+                                              uint64_t policy) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile(
+      "cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(dst),
+      "l"(gmem_src), "l"(policy)
+      : "memory");
+}
+template <typename P>
+__device__ __forceinline__ P LoadHint16(const P* p, uint64_t policy) {
+  static_assert(sizeof(P) == 16, "128-bit packs only");
+  uint4 r;
+  asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p), "l"(policy));
+  return *reinterpret_cast<const P*>(&r);
+}
 __device__ __forceinline__ void CpAsyncCommit() {
   asm volatile("cp.async.commit_group;\n" ::: "memory");
 }
@@ -245,24 +279,26 @@ __device__ __forceinline__ void CpAsyncWait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(kPending) : "memory");
 }
 
-template <int kMode>
+template <int kMode, int kStagesT>
 struct StatsPipe {
-  static constexpr int kStages = 4;
+  static constexpr int kStages = kStagesT;
   static constexpr int kStreams = kMode == 0 ? 1 : 2;
   static constexpr int kU = kMode == 0 ? 4 : 2;  // rows per stage and stream
   static constexpr int kSlots = kStages * kStreams * kU;
   static constexpr int kSmemBytes = kSlots * 256 * 16;
 };
 
-template <typename T, int kMode>
+template <typename T, int kMode, int kStagesT>
 __global__ void __launch_bounds__(kThreads)
     BnStatsPipeKernel(const T* __restrict__ x, const T* __restrict__ dy,
                       const float* __restrict__ mean,
                       float* __restrict__ partial, int64_t rows, int64_t cv,
-                      int64_t channels, int64_t rows_per_cta) {
+                      int64_t channels, int64_t rows_per_cta, bool keep_in_l2) {
   constexpr int kVec = VecWidth<T>::value;
   using P = Pack<T, kVec>;
-  using Cfg = StatsPipe<kMode>;
+  GridDepWait();
+  GridDepLaunch();
+  using Cfg = StatsPipe<kMode, kStagesT>;
   constexpr int kStages = Cfg::kStages, kU = Cfg::kU, kStreams = Cfg::kStreams;
   extern __shared__ uint4 pipe_smem[];
   const int tx = threadIdx.x, ty = threadIdx.y;
@@ -274,77 +310,97 @@ __global__ void __launch_bounds__(kThreads)
   int64_t r1 = r0 + rows_per_cta;
   if (r1 > rows) r1 = rows;
 
-  float shift[kVec], s1[kVec], s2[kVec];
+  // Channel pairs: accumulators and the negated shift as packed fp32 pairs.
+  constexpr int kPairs = kVec / 2;
+  float2 nshift[kPairs], a1[kPairs], a2[kPairs];
 #pragma unroll
-  for (int e = 0; e < kVec; ++e) {
-    s1[e] = 0.0f;
-    s2[e] = 0.0f;
-    shift[e] = 0.0f;
+  for (int q = 0; q < kPairs; ++q) {
+    a1[q] = make_float2(0.0f, 0.0f);
+    a2[q] = make_float2(0.0f, 0.0f);
+    nshift[q] = make_float2(0.0f, 0.0f);
   }
 
   if (active) {
     if constexpr (kMode == kFwd) {
       const P first = LoadKeep(reinterpret_cast<const P*>(x) + col);
+      WidenPack<kVec>(first, nshift);
 #pragma unroll
-      for (int e = 0; e < kVec; ++e) shift[e] = ToF32(first.v[e]);
+      for (int q = 0; q < kPairs; ++q) nshift[q] = Neg2(nshift[q]);
     } else {
 #pragma unroll
-      for (int e = 0; e < kVec; ++e) shift[e] = mean[col * kVec + e];
+      for (int q = 0; q < kPairs; ++q) {
+        nshift[q] = make_float2(-mean[col * kVec + 2 * q],
+                                -mean[col * kVec + 2 * q + 1]);
+      }
     }
-    const P* xp = reinterpret_cast<const P*>(x) + col;
-    const P* dp = reinterpret_cast<const P*>(dy) + col;
-    // This thread's rows: r0 + ty + j * TY, j = 0 .. n_j - 1.
-    const int64_t span = r1 - r0 - ty;
-    const int64_t n_j = span > 0 ? (span + TY - 1) / TY : 0;
-    const int64_t n_it = (n_j + kU - 1) / kU;
-    // Slot (stage, stream, u) of this thread.
-    auto slot = [&](int stage, int stream, int u) -> uint4* {
-      return pipe_smem + ((stage * kStreams + stream) * kU + u) * kThreads + tid;
-    };
-    auto issue = [&](int64_t it) {
-      if (it < n_it) {
-        const int stage = static_cast<int>(it % kStages);
+    // This thread's rows: r0 + ty + j * TY, j = 0 .. n_j - 1 (32-bit counters:
+    // a CTA never owns 2^31 rows).
+    const int n_rows = static_cast<int>(r1 - r0);
+    const int n_j = n_rows > ty ? (n_rows - ty + TY - 1) / TY : 0;
+    const int n_it = (n_j + kU - 1) / kU;
+    const int64_t row_stride = static_cast<int64_t>(TY) * cv;  // packs per row step
+    const P* xi = reinterpret_cast<const P*>(x) + col + (r0 + ty) * cv;
+    const P* di = reinterpret_cast<const P*>(dy) + col + (r0 + ty) * cv;
+    uint4* const my = pipe_smem + tid;
+    int j_issue = 0;
+    // Slot (stage, stream, u) of this thread: my + index * kThreads, with a
+    // compile-time index once the stage loop below is unrolled.
+    const uint64_t keep_policy = PolicyEvictLast();
+    auto issue = [&](int stage) {
 #pragma unroll
-        for (int u = 0; u < kU; ++u) {
-          const int64_t j = it * kU + u;
-          if (j < n_j) {
-            const int64_t off = (r0 + ty + j * TY) * cv;
-            CpAsync16(slot(stage, 0, u), xp + off);
-            if constexpr (kMode == kGrad) CpAsync16(slot(stage, 1, u), dp + off);
+      for (int u = 0; u < kU; ++u) {
+        if (j_issue + u < n_j) {
+          uint4* sx = my + ((stage * kStreams + 0) * kU + u) * kThreads;
+          uint4* sd = my + ((stage * kStreams + 1) * kU + u) * kThreads;
+          if (keep_in_l2) {
+            CpAsync16Hint(sx, xi + u * row_stride, keep_policy);
+            if constexpr (kMode == kGrad) {
+              CpAsync16Hint(sd, di + u * row_stride, keep_policy);
+            }
+          } else {
+            CpAsync16(sx, xi + u * row_stride);
+            if constexpr (kMode == kGrad) CpAsync16(sd, di + u * row_stride);
           }
         }
       }
+      xi += kU * row_stride;
+      di += kU * row_stride;
+      j_issue += kU;
       CpAsyncCommit();
     };
 #pragma unroll
     for (int st = 0; st < kStages - 1; ++st) issue(st);
-    for (int64_t it = 0; it < n_it; ++it) {
-      issue(it + kStages - 1);
-      CpAsyncWait<kStages - 1>();
-      const int stage = static_cast<int>(it % kStages);
+    int j_done = 0;
+    for (int it = 0; it < n_it; it += kStages) {
 #pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        const int64_t j = it * kU + u;
-        if (j < n_j) {
-          const uint4 rx = *slot(stage, 0, u);
-          const P px = *reinterpret_cast<const P*>(&rx);
-          P pd;
-          if constexpr (kMode == kGrad) {
-            const uint4 rd = *slot(stage, 1, u);
-            pd = *reinterpret_cast<const P*>(&rd);
-          }
+      for (int sg = 0; sg < kStages; ++sg) {
+        if (it + sg < n_it) {
+          issue((sg + kStages - 1) % kStages);
+          CpAsyncWait<kStages - 1>();
 #pragma unroll
-          for (int e = 0; e < kVec; ++e) {
-            const float d = ToF32(px.v[e]) - shift[e];
-            if constexpr (kMode == kFwd) {
-              s1[e] += d;
-              s2[e] = fmaf(d, d, s2[e]);
-            } else {
-              const float g = ToF32(pd.v[e]);
-              s1[e] += g;
-              s2[e] = fmaf(g, d, s2[e]);
+          for (int u = 0; u < kU; ++u) {
+            if (j_done + u < n_j) {
+              const uint4 rx = my[((sg * kStreams + 0) * kU + u) * kThreads];
+              float2 xv[kPairs], gv[kPairs];
+              WidenPack<kVec>(*reinterpret_cast<const P*>(&rx), xv);
+              if constexpr (kMode == kGrad) {
+                const uint4 rd = my[((sg * kStreams + 1) * kU + u) * kThreads];
+                WidenPack<kVec>(*reinterpret_cast<const P*>(&rd), gv);
+              }
+#pragma unroll
+              for (int q = 0; q < kPairs; ++q) {
+                const float2 d = Add2(xv[q], nshift[q]);
+                if constexpr (kMode == kFwd) {
+                  a1[q] = Add2(a1[q], d);
+                  a2[q] = Fma2(d, d, a2[q]);
+                } else {
+                  a1[q] = Add2(a1[q], gv[q]);
+                  a2[q] = Fma2(gv[q], d, a2[q]);
+                }
+              }
             }
           }
+          j_done += kU;
         }
       }
     }
@@ -352,6 +408,14 @@ __global__ void __launch_bounds__(kThreads)
   CpAsyncWait<0>();
   __syncthreads();  // every thread is done with its slots: reuse the buffer
 
+  float s1[kVec], s2[kVec];
+#pragma unroll
+  for (int q = 0; q < kPairs; ++q) {
+    s1[2 * q] = a1[q].x;
+    s1[2 * q + 1] = a1[q].y;
+    s2[2 * q] = a2[q].x;
+    s2[2 * q + 1] = a2[q].y;
+  }
   float* red = reinterpret_cast<float*>(pipe_smem);
   if (TY > 1) {
 #pragma unroll
@@ -393,6 +457,8 @@ __global__ void __launch_bounds__(kThreads)
                        float* __restrict__ partial, int64_t outer,
                        int64_t channels, int64_t inner, int64_t outer_per_cta) {
   using P = Pack<T, kVec>;
+  GridDepWait();
+  GridDepLaunch();
   const int64_t c = blockIdx.x;
   const int64_t n0 = static_cast<int64_t>(blockIdx.y) * outer_per_cta;
   int64_t n1 = n0 + outer_per_cta;
@@ -501,9 +567,18 @@ __device__ __forceinline__ void WriteFwdStats(const FinalizeArgs& a, int64_t c,
 // Block (8 channels, 128 partial lanes).
 template <int kOut>
 __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
+  GridDepWait();
+  GridDepLaunch();
   const int cx = threadIdx.x;  // 0..7
   const int py = threadIdx.y;  // 0..127
+  const int tid = py * 8 + cx;
   const int64_t c = static_cast<int64_t>(blockIdx.x) * 8 + cx;
+  // The threads that finish a channel (first 8 of the CTA) fetch the shift
+  // now, so that its latency overlaps the partial-sum loads.
+  float shift_k = 0.0f;
+  if (kOut != 2 && tid < 8 && c < a.channels) {
+    shift_k = LoadAsF32(a.x_first, a.x_dtype, c * a.shift_stride);
+  }
   double t1 = 0.0, t2 = 0.0;
   if (c < a.channels) {
     // Four independent loads per sum in flight: the loop is a chain of L2
@@ -523,11 +598,19 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
         t2 += static_cast<double>(u2[q]);
       }
     }
-    for (; p < a.splits; p += 128) {
-      t1 += static_cast<double>(
-          a.partial[(static_cast<int64_t>(p) * 2 + 0) * a.channels + c]);
-      t2 += static_cast<double>(
-          a.partial[(static_cast<int64_t>(p) * 2 + 1) * a.channels + c]);
+    float v1[3] = {0.0f, 0.0f, 0.0f}, v2[3] = {0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      if (p + q * 128 < a.splits) {
+        const int64_t row = static_cast<int64_t>(p + q * 128) * 2;
+        v1[q] = a.partial[(row + 0) * a.channels + c];
+        v2[q] = a.partial[(row + 1) * a.channels + c];
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      t1 += static_cast<double>(v1[q]);
+      t2 += static_cast<double>(v2[q]);
     }
   }
   // A warp holds 4 partial lanes x 8 channels: fold lanes 8 and 16 apart.
@@ -536,43 +619,52 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
   t1 += __shfl_xor_sync(0xffffffffu, t1, 16);
   t2 += __shfl_xor_sync(0xffffffffu, t2, 16);
   __shared__ double red[2][32][8];
-  const int tid = py * 8 + cx;
   const int warp = tid >> 5, lane = tid & 31;
   if (lane < 8) {
     red[0][warp][lane] = t1;
     red[1][warp][lane] = t2;
   }
   __syncthreads();
-  if (tid < 8 && c < a.channels) {
+  if (warp == 0) {
+    // Lane l folds warps {l/8, l/8 + 4, ...} of channel l % 8, then the four
+    // lane groups fold with two shuffles: a fixed order, so the result does
+    // not depend on scheduling.
+    const int ch = lane & 7, grp = lane >> 3;
     double S1 = 0.0, S2 = 0.0;
-    for (int w = 0; w < 32; ++w) {
-      S1 += red[0][w][tid];
-      S2 += red[1][w][tid];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      S1 += red[0][grp + 4 * w][ch];
+      S2 += red[1][grp + 4 * w][ch];
     }
-    if constexpr (kOut == 0) {
-      const double K =
-          static_cast<double>(LoadAsF32(a.x_first, a.x_dtype, c * a.shift_stride));
-      const double md = S1 / a.count;
-      WriteFwdStats(a, c, K + md, S2 / a.count - md * md);
-    } else if constexpr (kOut == 1) {
-      if (a.count_out != nullptr && c == 0) {
-        *a.count_out = static_cast<float>(a.count);
-      }
-      const double K =
-          static_cast<double>(LoadAsF32(a.x_first, a.x_dtype, c * a.shift_stride));
-      // Local rows only: count is this replica's.
-      a.sums[c] = static_cast<float>(S1 + a.count * K);
-      a.sums[a.channels + c] =
-          static_cast<float>(S2 + 2.0 * K * S1 + a.count * K * K);
-    } else {
-      if (a.sums) {
-        a.sums[c] = static_cast<float>(S1);
-        a.sums[a.channels + c] = static_cast<float>(S2);
-      }
-      if (a.doffset) a.doffset[c] = static_cast<float>(S1);
-      if (a.dscale) {
-        const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
-        a.dscale[c] = static_cast<float>(S2) * inv;
+    S1 += __shfl_xor_sync(0xffffffffu, S1, 8);
+    S2 += __shfl_xor_sync(0xffffffffu, S2, 8);
+    S1 += __shfl_xor_sync(0xffffffffu, S1, 16);
+    S2 += __shfl_xor_sync(0xffffffffu, S2, 16);
+    if (lane < 8 && c < a.channels) {
+      const double inv_count = 1.0 / a.count;
+      if constexpr (kOut == 0) {
+        const double K = static_cast<double>(shift_k);
+        const double md = S1 * inv_count;
+        WriteFwdStats(a, c, K + md, S2 * inv_count - md * md);
+      } else if constexpr (kOut == 1) {
+        if (a.count_out != nullptr && c == 0) {
+          *a.count_out = static_cast<float>(a.count);
+        }
+        const double K = static_cast<double>(shift_k);
+        // Local rows only: count is this replica's.
+        a.sums[c] = static_cast<float>(S1 + a.count * K);
+        a.sums[a.channels + c] =
+            static_cast<float>(S2 + 2.0 * K * S1 + a.count * K * K);
+      } else {
+        if (a.sums) {
+          a.sums[c] = static_cast<float>(S1);
+          a.sums[a.channels + c] = static_cast<float>(S2);
+        }
+        if (a.doffset) a.doffset[c] = static_cast<float>(S1);
+        if (a.dscale) {
+          const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
+          a.dscale[c] = static_cast<float>(S2) * inv;
+        }
       }
     }
   }
@@ -580,6 +672,8 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
 
 // Per-channel epilogues when the sums already exist (after an all-reduce).
 __global__ void BnFinalizeFromSumsKernel(FinalizeArgs a, const float* sums) {
+  GridDepWait();
+  GridDepLaunch();
   const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (c >= a.channels) return;
   const double mean = static_cast<double>(sums[c]) / a.count;
@@ -592,6 +686,8 @@ __global__ void BnGradScalesFromSumsKernel(const float* sums,
                                            const float* variance, float epsilon,
                                            float* dscale, float* doffset,
                                            int64_t channels) {
+  GridDepWait();
+  GridDepLaunch();
   const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   doffset[c] = sums[c];
@@ -640,8 +736,10 @@ __global__ void __launch_bounds__(kThreads)
     BnApplyLastKernel(const T* __restrict__ x, const T* __restrict__ dy,
                       T* __restrict__ out, ApplyArgs a, int64_t rows,
                       int64_t cv, int64_t channels, int64_t rows_per_cta,
-                      bool reverse) {
+                      bool reverse, bool last_use) {
   using P = Pack<T, kVec>;
+  GridDepWait();
+  GridDepLaunch();
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
   const int64_t col = static_cast<int64_t>(blockIdx.x) * TX + tx;
@@ -652,6 +750,10 @@ __global__ void __launch_bounds__(kThreads)
   int64_t r1 = r0 + rows_per_cta;
   if (r1 > rows) r1 = rows;
 
+  // 16-bit outputs round to 8 or 11 bits, so the per-channel affine forms are
+  // folded to two (forward) or three (gradient) coefficients and one or two
+  // FMAs per element; fp32 keeps the centred form (x - mean) to the end.
+  constexpr bool kFold = sizeof(T) == 2;
   const bool writer = blockIdx.y == 0 && ty == 0;
   float mean[kVec], ca[kVec], cb[kVec], cc[kVec];
 #pragma unroll
@@ -687,6 +789,18 @@ __global__ void __launch_bounds__(kThreads)
         a.dscale[c] = a.sums[channels + c] * inv;
       }
     }
+    if constexpr (kFold) {
+      if constexpr (kMode == kFwd) {
+        // y = x * ca + (offset - mean * ca)
+        cb[e] = fmaf(-mean[e], ca[e], cb[e]);
+      } else {
+        // dx = dy * ca + x * (-ca * cc) + ca * (cc * mean - cb)
+        const float fb = -ca[e] * cc[e];
+        const float fc = ca[e] * fmaf(cc[e], mean[e], -cb[e]);
+        cb[e] = fb;
+        cc[e] = fc;
+      }
+    }
   }
 
   const P* xp = reinterpret_cast<const P*>(x) + col;
@@ -696,6 +810,7 @@ __global__ void __launch_bounds__(kThreads)
   // Row lane ty visits local rows ty, ty + TY, ...; in reverse mode the local
   // index is mirrored.
   const int64_t step = static_cast<int64_t>(TY) * kUnroll;
+  const uint64_t drop_policy = PolicyEvictFirst();
   for (int64_t l = ty; l < n_rows; l += step) {
     P px[kUnroll];
     P pd[kUnroll];
@@ -707,25 +822,75 @@ __global__ void __launch_bounds__(kThreads)
       const int64_t r = reverse ? (r1 - 1 - li) : (r0 + li);
       off[u] = ok ? r * cv : -1;
       if (ok) {
-        px[u] = LoadKeep(xp + off[u]);
-        if constexpr (kMode == kGrad) pd[u] = LoadKeep(dp + off[u]);
+        if constexpr (sizeof(P) == 16) {
+          if (last_use) {
+            px[u] = LoadHint16(xp + off[u], drop_policy);
+            if constexpr (kMode == kGrad) pd[u] = LoadHint16(dp + off[u], drop_policy);
+          } else {
+            px[u] = LoadKeep(xp + off[u]);
+            if constexpr (kMode == kGrad) pd[u] = LoadKeep(dp + off[u]);
+          }
+        } else {
+          px[u] = LoadKeep(xp + off[u]);
+          if constexpr (kMode == kGrad) pd[u] = LoadKeep(dp + off[u]);
+        }
       }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (off[u] >= 0) {
         P o;
+        if constexpr (kVec >= 2) {
+          // Packed fp32 pairs (same roundings as the scalar forms below).
+          constexpr int kPairs = kVec / 2;
+          float2 xv[kPairs], gv[kPairs], rv[kPairs];
+          WidenPack<kVec>(px[u], xv);
+          if constexpr (kMode == kGrad) WidenPack<kVec>(pd[u], gv);
+#pragma unroll
+          for (int q = 0; q < kPairs; ++q) {
+            const float2 A = make_float2(ca[2 * q], ca[2 * q + 1]);
+            const float2 B = make_float2(cb[2 * q], cb[2 * q + 1]);
+            const float2 C = make_float2(cc[2 * q], cc[2 * q + 1]);
+            if constexpr (kFold) {
+              if constexpr (kMode == kFwd) {
+                rv[q] = Fma2(xv[q], A, B);
+              } else {
+                rv[q] = Fma2(gv[q], A, Fma2(xv[q], B, C));
+              }
+            } else {
+              const float2 d =
+                  Add2(xv[q], make_float2(-mean[2 * q], -mean[2 * q + 1]));
+              if constexpr (kMode == kFwd) {
+                rv[q] = Fma2(d, A, B);
+              } else {
+                // ca * ((g - cb) - d * cc)
+                rv[q] = Mul2(A, Fma2(Neg2(d), C, Add2(gv[q], Neg2(B))));
+              }
+            }
+          }
+          NarrowPack<kVec>(rv, o);
+        } else {
 #pragma unroll
         for (int e = 0; e < kVec; ++e) {
-          const float d = ToF32(px[u].v[e]) - mean[e];
           float r;
-          if constexpr (kMode == kFwd) {
-            r = fmaf(d, ca[e], cb[e]);
+          if constexpr (kFold) {
+            const float xv = ToF32(px[u].v[e]);
+            if constexpr (kMode == kFwd) {
+              r = fmaf(xv, ca[e], cb[e]);
+            } else {
+              r = fmaf(ToF32(pd[u].v[e]), ca[e], fmaf(xv, cb[e], cc[e]));
+            }
           } else {
-            const float g = ToF32(pd[u].v[e]);
-            r = ca[e] * (g - cb[e] - d * cc[e]);
+            const float d = ToF32(px[u].v[e]) - mean[e];
+            if constexpr (kMode == kFwd) {
+              r = fmaf(d, ca[e], cb[e]);
+            } else {
+              const float g = ToF32(pd[u].v[e]);
+              r = ca[e] * (g - cb[e] - d * cc[e]);
+            }
           }
           o.v[e] = FromF32<T>(r);
+        }
         }
         StoreStream(op + off[u], o);
       }
@@ -740,6 +905,8 @@ __global__ void __launch_bounds__(kThreads)
                        T* __restrict__ out, ApplyArgs a, int64_t n_packs,
                        int64_t inner_packs, int64_t channels) {
   using P = Pack<T, kVec>;
+  GridDepWait();
+  GridDepLaunch();
   const P* xp = reinterpret_cast<const P*>(x);
   const P* dp = reinterpret_cast<const P*>(dy);
   P* op = reinterpret_cast<P*>(out);
@@ -815,6 +982,32 @@ inline size_t WorkspaceBytes(const Geom& g) {
   return static_cast<size_t>(floats) * sizeof(float);
 }
 
+template <typename T, int kMode, int kStagesT>
+int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* partial,
+                    const Geom& g, int64_t cv, cudaStream_t stream) {
+  using Cfg = StatsPipe<kMode, kStagesT>;
+  auto kernel = BnStatsPipeKernel<T, kMode, kStagesT>;
+  static const int resident = [&] {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg::kSmemBytes);
+    int n = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads,
+                                                  Cfg::kSmemBytes);
+    return n > 0 ? n : 1;
+  }();
+  const Plan p = PlanLast(g.outer, g.channels, cv, Cfg::kU, true, resident);
+  // Ask L2 to hold on to what this pass reads when the element-wise pass that
+  // follows can find it there: all streams together within the budget.
+  const int64_t bytes = g.outer * g.channels * static_cast<int64_t>(sizeof(T)) *
+                        (kMode == kFwd ? 1 : 2);
+  const int64_t budget = static_cast<int64_t>(GetTuning(kTuneBnL2KeepMb)) << 20;
+  const bool keep_in_l2 = bytes <= budget;
+  LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
+                dim3(p.tx, p.ty), Cfg::kSmemBytes, stream, x, dy, mean, partial,
+                g.outer, cv, g.channels, p.rows_per_cta, keep_in_l2);
+  return p.gy;
+}
+
 // Stats launch: fills partial[splits][2][C]; returns splits (<0: error).
 template <typename T, int kMode>
 int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
@@ -826,23 +1019,12 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
   if (g.inner == 1) {
     if (g.channels % kVec == 0 && aligned) {
       const int64_t cv = g.channels / kVec;
-      if (GetTuning(kTuneBnStatsPipe) != 0) {
-        using Cfg = StatsPipe<kMode>;
-        auto kernel = BnStatsPipeKernel<T, kMode>;
-        static const int resident = [&] {
-          cudaFuncSetAttribute(kernel,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               Cfg::kSmemBytes);
-          int n = 0;
-          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads,
-                                                        Cfg::kSmemBytes);
-          return n > 0 ? n : 1;
-        }();
-        const Plan p =
-            PlanLast(g.outer, g.channels, cv, Cfg::kU, true, resident);
-        kernel<<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), Cfg::kSmemBytes, stream>>>(
-            x, dy, mean, partial, g.outer, cv, g.channels, p.rows_per_cta);
-        return p.gy;
+      const int stages = GetTuning(kTuneBnStatsPipe);
+      if (stages == 3) {
+        return LaunchStatsPipe<T, kMode, 3>(x, dy, mean, partial, g, cv, stream);
+      }
+      if (stages != 0) {
+        return LaunchStatsPipe<T, kMode, 4>(x, dy, mean, partial, g, cv, stream);
       }
       const Plan p = PlanLast(g.outer, g.channels, cv, kUnroll, true, 3);
       BnStatsLastKernel<T, kVec, kUnroll, kMode>
@@ -882,7 +1064,8 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
 template <int kOut>
 void LaunchFinalize(const FinalizeArgs& a, cudaStream_t stream) {
   const int grid = static_cast<int>(CeilDiv(a.channels, 8));
-  BnFinalizeKernel<kOut><<<grid, dim3(8, 128), 0, stream>>>(a);
+  LaunchChained(GetTuning(kTuneBnPdl) != 0, BnFinalizeKernel<kOut>, dim3(grid),
+                dim3(8, 128), 0, stream, a);
 }
 
 template <typename T, int kMode>
@@ -891,6 +1074,13 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
   constexpr int kVec = VecWidth<T>::value;
   constexpr int kUnroll = 4;
   const bool reverse = GetTuning(kTuneBnApplyReverse) != 0;
+  // Evict-first loads pay off while the tensor is of the order of L2 (what the
+  // statistics pass left there is not pushed out); on larger ones they cost.
+  const int64_t in_bytes = g.outer * g.channels * g.inner *
+                           static_cast<int64_t>(sizeof(T)) *
+                           (kMode == kFwd ? 1 : 2);
+  const bool last_use =
+      in_bytes <= (static_cast<int64_t>(GetTuning(kTuneBnL2KeepMb)) << 21);
   const bool aligned =
       Aligned16(x) && Aligned16(out) && (kMode == kFwd || Aligned16(dy));
   if (g.inner == 1) {
@@ -907,8 +1097,9 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
           return n > 0 ? n : 1;
         }();
         const Plan p = PlanLast(g.outer, g.channels, cv, kDeep, false, resident);
-        kernel<<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
-            x, dy, out, a, g.outer, cv, g.channels, p.rows_per_cta, reverse);
+        LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
+                      dim3(p.tx, p.ty), 0, stream, x, dy, out, a, g.outer, cv,
+                      g.channels, p.rows_per_cta, reverse, last_use);
       } else {
         auto kernel = BnApplyLastKernel<T, kVec, kUnroll, kMode>;
         static const int resident = [&] {
@@ -918,8 +1109,9 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
         }();
         const Plan p =
             PlanLast(g.outer, g.channels, cv, kUnroll, false, resident);
-        kernel<<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
-            x, dy, out, a, g.outer, cv, g.channels, p.rows_per_cta, reverse);
+        LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
+                      dim3(p.tx, p.ty), 0, stream, x, dy, out, a, g.outer, cv,
+                      g.channels, p.rows_per_cta, reverse, last_use);
       }
     } else {
       const Plan p =
@@ -927,7 +1119,7 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
       BnApplyLastKernel<T, 1, kUnroll, kMode>
           <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
               x, dy, out, a, g.outer, g.channels, g.channels, p.rows_per_cta,
-              reverse);
+              reverse, false);
     }
     return;
   }

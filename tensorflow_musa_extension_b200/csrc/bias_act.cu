@@ -76,13 +76,11 @@ __device__ __forceinline__ T2 ActivatePair(T2 x, T2 b) {
     const float2 tf = Widen2(t);
     const float s0 = Sigmoid<true>(tf.x);
     const float s1 = Sigmoid<true>(tf.y);
+    // The sigmoid is rounded to T and the product taken in T, which is what
+    // the separate Sigmoid and Mul ops of the un-fused chain store.
     T2 out;
-    if constexpr (kAct == MUSA_ACT_SWISH) {
-      const float2 xf = Widen2(x);
-      Narrow2(xf.x * s0, xf.y * s1, out);
-    } else {
-      Narrow2(s0, s1, out);
-    }
+    Narrow2(s0, s1, out);
+    if constexpr (kAct == MUSA_ACT_SWISH) out = __hmul2(x, out);
     return out;
   }
 }
@@ -116,9 +114,15 @@ __global__ void __launch_bounds__(256)
   const int64_t n_tiles = (n_packs + tile - 1) / tile;
   const int step = static_cast<int>(blockDim.x % cv);
 
+  // When the block width is a multiple of the row width in packs, a thread
+  // meets the same bias pack in every pack it handles: fetch it once.
+  const bool fixed_col = kHasBias && step == 0;
+  P fixed_bias;
+  if (fixed_col) fixed_bias = LoadKeep(bp + (threadIdx.x % cv));
+
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
     const int64_t base = t * tile + threadIdx.x;
-    int col = static_cast<int>(base % cv);
+    int col = fixed_col ? 0 : static_cast<int>(base % cv);
     P px[kUnroll];
     P pb[kUnroll];
 #pragma unroll
@@ -126,10 +130,18 @@ __global__ void __launch_bounds__(256)
       const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
       if (i < n_packs) {
         px[u] = LoadStream(xp + i);
-        if constexpr (kHasBias) pb[u] = LoadKeep(bp + col);
+        if constexpr (kHasBias) {
+          if (fixed_col) {
+            pb[u] = fixed_bias;
+          } else {
+            pb[u] = LoadKeep(bp + col);
+          }
+        }
       }
-      col += step;
-      if (col >= cv) col -= cv;
+      if (!fixed_col) {
+        col += step;
+        if (col >= cv) col -= cv;
+      }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {

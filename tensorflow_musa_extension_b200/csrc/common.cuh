@@ -93,6 +93,103 @@ __device__ __forceinline__ P LoadKeep(const P* p) {
   }
 }
 
+// ---- Packed fp32 pairs.  sm_100 executes add / mul / fma on two fp32 lanes
+// per instruction (add.rn.f32x2, fma.rn.f32x2); each lane rounds exactly like
+// the scalar instruction, so results are unchanged while the FP instruction
+// count of the 16-bit kernels halves.
+__device__ __forceinline__ float2 Add2(float2 a, float2 b) {
+  return __fadd2_rn(a, b);
+}
+__device__ __forceinline__ float2 Mul2(float2 a, float2 b) {
+  return __fmul2_rn(a, b);
+}
+__device__ __forceinline__ float2 Fma2(float2 a, float2 b, float2 c) {
+  return __ffma2_rn(a, b, c);
+}
+__device__ __forceinline__ float2 Neg2(float2 a) {
+  return make_float2(-a.x, -a.y);
+}
+
+// Widen a pack to kVec / 2 float pairs and back (kVec even).
+template <int kVec>
+__device__ __forceinline__ void WidenPack(const Pack<float, kVec>& p,
+                                          float2 (&out)[kVec / 2]) {
+#pragma unroll
+  for (int i = 0; i < kVec / 2; ++i) out[i] = make_float2(p.v[2 * i], p.v[2 * i + 1]);
+}
+template <int kVec>
+__device__ __forceinline__ void WidenPack(const Pack<__nv_bfloat16, kVec>& p,
+                                          float2 (&out)[kVec / 2]) {
+  // bf16 is the upper half of an fp32: one shift or mask per element.
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(&p);
+#pragma unroll
+  for (int i = 0; i < kVec / 2; ++i) {
+    out[i] = make_float2(__uint_as_float(w[i] << 16),
+                         __uint_as_float(w[i] & 0xffff0000u));
+  }
+}
+template <int kVec>
+__device__ __forceinline__ void WidenPack(const Pack<__half, kVec>& p,
+                                          float2 (&out)[kVec / 2]) {
+  const __half2* w = reinterpret_cast<const __half2*>(&p);
+#pragma unroll
+  for (int i = 0; i < kVec / 2; ++i) out[i] = __half22float2(w[i]);
+}
+template <int kVec>
+__device__ __forceinline__ void NarrowPack(const float2 (&in)[kVec / 2],
+                                           Pack<float, kVec>& p) {
+#pragma unroll
+  for (int i = 0; i < kVec / 2; ++i) {
+    p.v[2 * i] = in[i].x;
+    p.v[2 * i + 1] = in[i].y;
+  }
+}
+template <int kVec>
+__device__ __forceinline__ void NarrowPack(const float2 (&in)[kVec / 2],
+                                           Pack<__nv_bfloat16, kVec>& p) {
+  __nv_bfloat162* w = reinterpret_cast<__nv_bfloat162*>(&p);
+#pragma unroll
+  for (int i = 0; i < kVec / 2; ++i) w[i] = __floats2bfloat162_rn(in[i].x, in[i].y);
+}
+template <int kVec>
+__device__ __forceinline__ void NarrowPack(const float2 (&in)[kVec / 2],
+                                           Pack<__half, kVec>& p) {
+  __half2* w = reinterpret_cast<__half2*>(&p);
+#pragma unroll
+  for (int i = 0; i < kVec / 2; ++i) w[i] = __floats2half2_rn(in[i].x, in[i].y);
+}
+
+// ---- Programmatic dependent launch.  Kernels of one launcher form a chain
+// on the stream; launched with the programmatic-serialization attribute, the
+// next kernel's CTAs are scheduled while the current kernel drains, and its
+// GridDepWait() returns once the previous kernel has completed and its writes
+// are visible.  Every kernel calls GridDepWait() before its first global
+// access and GridDepLaunch() right after, so a dependent never starts before
+// its producer has itself seen all of its inputs.
+__device__ __forceinline__ void GridDepWait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void GridDepLaunch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t LaunchChained(bool programmatic, void (*kernel)(KArgs...),
+                                 dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = programmatic ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool Aligned16(const void* p) {
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
 }

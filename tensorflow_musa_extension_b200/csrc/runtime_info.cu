@@ -19,8 +19,8 @@ void InitTuningOnce() {
     static const int defaults[kTuneCount] = {
         /*AdamCtasPerSm*/ 0, /*AdamUnroll*/ 2, /*BiasActCtasPerSm*/ 0,
         /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 0, /*BnFused*/ 0,
-        /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1, /*BnStatsPipe*/ 1,
-        /*BnApplyDeep*/ 0};
+        /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1, /*BnStatsPipe*/ 4,
+        /*BnApplyDeep*/ 0, /*BnPdl*/ 1, /*BnL2KeepMb*/ 64};
     for (int i = 0; i < kTuneCount; ++i) g_tuning[i].store(defaults[i]);
   });
 }

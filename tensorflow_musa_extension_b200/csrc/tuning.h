@@ -14,8 +14,10 @@ enum TuningKey {
   kTuneBnFused = 5,         // 1: single cooperative kernel when it applies
   kTuneBnApplyReverse = 6,  // 1: apply pass walks rows in reverse (L2 reuse)
   kTuneBnStatsKeep = 7,     // 1: stats pass loads with the default L2 policy
-  kTuneBnStatsPipe = 8,     // 1: cp.async-staged stats kernel (128-bit path)
+  kTuneBnStatsPipe = 8,     // cp.async stages of the stats kernel (3 or 4); 0: register loads
   kTuneBnApplyDeep = 9,     // 1: forward element-wise pass keeps 8 rows in flight
+  kTuneBnPdl = 10,          // 1: BatchNorm kernels use programmatic dependent launch
+  kTuneBnL2KeepMb = 11,     // stats pass pins its reads in L2 up to this many MB (0: off)
   kTuneCount = 16
 };
 
