@@ -1,0 +1,322 @@
+"""musa_graph_optimizer: the GraphDef wire codec, the fusion patterns and the
+driver, through the C ABI on serialised GraphDef bytes.  No GPU.
+
+Structure follows the reference's fusion tests
+(test/fusion/linear_relu_fusion_test.py:56-271): a positive case per pattern
+with a downstream consumer, a negative case where an intervening node blocks
+the match, dtype coverage, and a check that the fused op appears under the
+original node name."""
+import os
+
+import pytest
+
+import graph_proto as gp
+from graph_proto import Builder, by_name, parse
+from tensorflow_musa_extension_b200 import _graph_optimizer as go
+from tensorflow_musa_extension_b200 import errors
+
+
+def run(builder_or_bytes, **kw):
+    data = builder_or_bytes.bytes() if isinstance(builder_or_bytes, Builder) else builder_or_bytes
+    out, report = go.optimize_graph_def(data, **kw)
+    return parse(out), report
+
+
+def bias_relu_graph(dtype=gp.DT_FLOAT, device=gp.MUSA, fmt=None):
+    g = Builder()
+    g.node("x", "Placeholder", device=device, dtype=dtype, shape=[8, 16])
+    g.node("b", "Const", device=device, dtype=dtype)
+    extra = {"data_format": fmt} if fmt else {}
+    g.node("bias_add", "BiasAdd", ["x", "b"], device, T=dtype, **extra)
+    g.node("act", "Relu", ["bias_add"], device, T=dtype)
+    g.node("two", "Const", device=device, dtype=dtype)
+    g.node("out", "Mul", ["act", "two"], device, T=dtype)   # downstream reader
+    return g
+
+
+# ------------------------------------------------------------------ codec --
+
+def test_codec_round_trip_preserves_everything():
+    g = Builder()
+    n = g.node("weird", "SomeOp", ["a:1", "^ctrl"], gp.CPU, T=gp.DT_HALF, flag=True,
+               count=-7, ratio=0.25, label="hello", shape=[2, -1, 3])
+    n.attr["types"].list.type.extend([1, 19, 14])
+    n.attr["names"].list.s.extend([b"p", b"q"])
+    g.node("a", "Placeholder", device="", dtype=gp.DT_FLOAT)
+    g.graph.version = 3
+    g.graph.versions.bad_consumers.extend([5, 6])
+    out, report = run(g, parameters={"disabled_fusion_patterns": "all"})
+    assert report["applied"] == 0
+    assert out == g.graph                     # message equality, field by field
+    # and a second trip through the C++ codec is byte-stable
+    again, _ = go.optimize_graph_def(out.SerializeToString(),
+                                     parameters={"disabled_fusion_patterns": "all"})
+    assert parse(again) == g.graph
+
+
+def test_malformed_bytes_are_rejected():
+    with pytest.raises(errors.InvalidArgumentError, match="malformed GraphDef"):
+        go.optimize_graph_def(b"\x0a\xff\xff\xff\xff\x0f\x01")
+    with pytest.raises(errors.InvalidArgumentError, match="unknown"):
+        go.optimize_graph_def(b"", parameters={"no_such_parameter": "1"})
+
+
+def test_empty_graph_is_a_no_op():
+    out, report = run(b"")
+    assert len(out.node) == 0 and report["applied"] == 0
+
+
+# ---------------------------------------------------------- BiasAdd + Relu --
+
+@pytest.mark.parametrize("dtype", [gp.DT_FLOAT, gp.DT_HALF, gp.DT_BFLOAT16])
+def test_bias_add_relu_is_fused(dtype):
+    out, report = run(bias_relu_graph(dtype, fmt="NHWC"))
+    nodes = by_name(out)
+    assert report["applied"] == 1 and report["patterns"] == {"MusaBiasAddReluFusion": 1}
+    fused = nodes["act"]                       # fused op sits under the original name
+    assert fused.op == "MusaBiasAddRelu" and list(fused.input) == ["x", "b"]
+    assert fused.device == gp.MUSA
+    assert fused.attr["T"].type == dtype and fused.attr["data_format"].s == b"NHWC"
+    assert "bias_add" not in nodes and "act_original" not in nodes
+    assert list(nodes["out"].input) == ["act", "two"]      # reader untouched
+    assert out.versions.producer == 808
+
+
+def test_bias_add_v1_and_default_format():
+    g = Builder()
+    g.node("x", "Placeholder", dtype=gp.DT_FLOAT)
+    g.node("b", "Const", dtype=gp.DT_FLOAT)
+    g.node("ba", "BiasAddV1", ["x:0", "b"], T=gp.DT_FLOAT)
+    g.node("r", "Relu", ["ba:0"], T=gp.DT_FLOAT)
+    nodes = by_name(run(g)[0])
+    assert nodes["r"].op == "MusaBiasAddRelu" and list(nodes["r"].input) == ["x:0", "b"]
+    assert nodes["r"].attr["data_format"].s == b"NHWC"
+
+
+def test_intervening_identity_blocks_fusion():
+    g = Builder()
+    g.node("x", "Placeholder", dtype=gp.DT_FLOAT)
+    g.node("b", "Const", dtype=gp.DT_FLOAT)
+    g.node("ba", "BiasAdd", ["x", "b"], T=gp.DT_FLOAT)
+    g.node("id", "Identity", ["ba"], T=gp.DT_FLOAT)
+    g.node("r", "Relu", ["id"], T=gp.DT_FLOAT)
+    out, report = run(g)
+    assert report["applied"] == 0 and out == g.graph
+
+
+def test_second_reader_of_bias_add_blocks_fusion():
+    g = bias_relu_graph()
+    g.node("peek", "Identity", ["bias_add"], T=gp.DT_FLOAT)
+    out, report = run(g)
+    assert report["applied"] == 0 and by_name(out)["act"].op == "Relu"
+    # a control edge is a reader too
+    g2 = bias_relu_graph()
+    g2.node("later", "NoOp", ["^bias_add"])
+    assert run(g2)[1]["applied"] == 0
+
+
+@pytest.mark.parametrize("mutate", ["cpu_relu", "cpu_bias", "int32", "original_suffix",
+                                    "port_one"])
+def test_non_matching_variants(mutate):
+    g = Builder()
+    dt = gp.DT_INT32 if mutate == "int32" else gp.DT_FLOAT
+    g.node("x", "Placeholder", dtype=dt)
+    g.node("b", "Const", dtype=dt)
+    g.node("ba", "BiasAdd", ["x", "b"], gp.CPU if mutate == "cpu_bias" else gp.MUSA, T=dt)
+    name = "r_original" if mutate == "original_suffix" else "r"
+    g.node(name, "Relu", ["ba:1" if mutate == "port_one" else "ba"],
+           gp.CPU if mutate == "cpu_relu" else gp.MUSA, T=dt)
+    out, report = run(g)
+    assert report["applied"] == 0 and out == g.graph
+
+
+def test_control_inputs_are_carried_over():
+    g = Builder()
+    g.node("x", "Placeholder", dtype=gp.DT_FLOAT)
+    g.node("b", "Const", dtype=gp.DT_FLOAT)
+    g.node("init", "NoOp")
+    g.node("ba", "BiasAdd", ["x", "b", "^init"], T=gp.DT_FLOAT)
+    g.node("r", "Relu", ["ba"], T=gp.DT_FLOAT)
+    nodes = by_name(run(g)[0])
+    assert list(nodes["r"].input) == ["x", "b", "^init"] and "init" in nodes
+
+
+def test_optimizer_is_idempotent():
+    once, _ = go.optimize_graph_def(bias_relu_graph().bytes())
+    twice, report = go.optimize_graph_def(once)
+    assert report["applied"] == 0 and parse(twice) == parse(once)
+
+
+# ---------------------------------------------------------------- swish ----
+
+@pytest.mark.parametrize("x_first", [True, False])
+@pytest.mark.parametrize("dtype", [gp.DT_FLOAT, gp.DT_HALF, gp.DT_BFLOAT16])
+def test_swish_chain_is_fused(x_first, dtype):
+    g = Builder()
+    g.node("x", "Placeholder", dtype=dtype)
+    g.node("b", "Const", dtype=dtype)
+    g.node("ba", "BiasAdd", ["x", "b"], T=dtype, data_format="NHWC")
+    g.node("sig", "Sigmoid", ["ba"], T=dtype)
+    g.node("y", "Mul", ["x", "sig"] if x_first else ["sig", "x:0"], T=dtype)
+    g.node("sink", "Identity", ["y"], T=dtype)
+    out, report = run(g)
+    nodes = by_name(out)
+    assert report["patterns"] == {"MusaBiasAddSwishFusion": 1}
+    assert nodes["y"].op == "MusaBiasAddSwish" and list(nodes["y"].input) == ["x", "b"]
+    assert set(nodes) == {"x", "b", "y", "sink"}
+
+
+def test_swish_needs_the_same_tensor_on_both_sides():
+    g = Builder()
+    g.node("x", "Placeholder", dtype=gp.DT_FLOAT)
+    g.node("z", "Placeholder", dtype=gp.DT_FLOAT)
+    g.node("b", "Const", dtype=gp.DT_FLOAT)
+    g.node("ba", "BiasAdd", ["x", "b"], T=gp.DT_FLOAT)
+    g.node("sig", "Sigmoid", ["ba"], T=gp.DT_FLOAT)
+    g.node("y", "Mul", ["z", "sig"], T=gp.DT_FLOAT)
+    nodes = by_name(run(g)[0])
+    # not a swish; the Sigmoid(BiasAdd) inside it is still a chain of its own
+    assert nodes["y"].op == "Mul" and nodes["sig"].op == "MusaBiasAddSigmoid"
+    assert list(nodes["y"].input) == ["z", "sig"]
+
+
+def test_sigmoid_chain_and_priorities():
+    names = [(n, p) for n, p, _ in go.list_fusion_patterns()]
+    assert names == [("MusaBiasAddSwishFusion", 56), ("MusaBiasAddReluFusion", 55),
+                     ("MusaBiasAddSigmoidFusion", 54), ("MusaAdamMixedFusion", 40)]
+    g = Builder()
+    g.node("x", "Placeholder", dtype=gp.DT_HALF)
+    g.node("b", "Const", dtype=gp.DT_HALF)
+    g.node("ba", "BiasAdd", ["x", "b"], T=gp.DT_HALF)
+    g.node("s", "Sigmoid", ["ba"], T=gp.DT_HALF)
+    nodes = by_name(run(g)[0])
+    assert nodes["s"].op == "MusaBiasAddSigmoid" and "ba" not in nodes
+
+
+# ---------------------------------------------------------------- Adam -----
+
+def adam_graph(src=gp.DT_BFLOAT16, extra_cast_reader=False, adam_t=gp.DT_FLOAT):
+    g = Builder()
+    for n in ("var", "m", "v"):
+        g.node(n, "VarHandleOp", dtype=gp.DT_FLOAT)
+    for n in ("b1p", "b2p", "lr", "b1", "b2", "eps"):
+        g.node(n, "Const", dtype=gp.DT_FLOAT)
+    g.node("grad16", "Placeholder", dtype=src)
+    g.node("cast", "Cast", ["grad16"], SrcT=src, DstT=gp.DT_FLOAT)
+    g.node("adam", "ResourceApplyAdam",
+           ["var", "m", "v", "b1p", "b2p", "lr", "b1", "b2", "eps", "cast"],
+           T=adam_t, use_locking=True, use_nesterov=False)
+    if extra_cast_reader:
+        g.node("norm", "L2Loss", ["cast"], T=gp.DT_FLOAT)
+    return g
+
+
+@pytest.mark.parametrize("src", [gp.DT_BFLOAT16, gp.DT_HALF])
+def test_adam_mixed_rewrite(src):
+    out, report = run(adam_graph(src))
+    nodes = by_name(out)
+    assert report["patterns"] == {"MusaAdamMixedFusion": 1}
+    adam = nodes["adam"]
+    assert adam.op == "MusaResourceApplyAdamMixed" and adam.attr["T"].type == src
+    assert adam.input[9] == "grad16" and len(adam.input) == 10
+    assert adam.attr["use_locking"].b is True and adam.attr["use_nesterov"].b is False
+    assert "cast" not in nodes and "grad16" in nodes
+
+
+def test_adam_keeps_a_cast_that_has_another_reader():
+    nodes = by_name(run(adam_graph(extra_cast_reader=True))[0])
+    assert nodes["adam"].op == "MusaResourceApplyAdamMixed"
+    assert "cast" in nodes and list(nodes["norm"].input) == ["cast"]
+
+
+def test_adam_not_rewritten_for_float_grad_or_16bit_state():
+    assert run(adam_graph(src=gp.DT_FLOAT))[1]["applied"] == 0
+    assert run(adam_graph(adam_t=gp.DT_BFLOAT16))[1]["applied"] == 0
+    g = adam_graph()
+    by_name(g.graph)["adam"].device = gp.CPU
+    assert run(g)[1]["applied"] == 0
+
+
+def test_adam_kill_switch(monkeypatch):
+    monkeypatch.setenv("MUSA_DISABLE_ADAM_MIXED_FUSION", "1")
+    out, report = run(adam_graph())
+    assert report["applied"] == 0 and report["fallbacks"] >= 1
+    assert by_name(out)["adam"].op == "ResourceApplyAdam"
+    monkeypatch.setenv("MUSA_DISABLE_ADAM_MIXED_FUSION", "0")
+    assert run(adam_graph())[1]["applied"] == 1
+
+
+# ---------------------------------------------------- driver and parameters --
+
+def many_chains(n):
+    g = Builder()
+    g.node("b", "Const", dtype=gp.DT_FLOAT)
+    prev = "x0"
+    g.node(prev, "Placeholder", dtype=gp.DT_FLOAT)
+    for i in range(n):
+        g.node("ba%d" % i, "BiasAdd", [prev, "b"], T=gp.DT_FLOAT)
+        g.node("r%d" % i, "Relu", ["ba%d" % i], T=gp.DT_FLOAT)
+        prev = "r%d" % i
+    return g
+
+
+def test_fixed_point_over_many_chains():
+    out, report = run(many_chains(40))
+    nodes = by_name(out)
+    assert report["applied"] == 40 and not report["hit_iteration_limit"]
+    assert all(nodes["r%d" % i].op == "MusaBiasAddRelu" for i in range(40))
+    assert nodes["r5"].input[0] == "r4" and len(nodes) == 42
+
+
+@pytest.mark.parametrize("value,fused", [
+    ("MusaBiasAddReluFusion", False), ("  musabiasaddrelufusion ,MusaAdamMixedFusion", False),
+    ("all", False), (" ALL ", False), ("MusaAdamMixedFusion", True), ("", True)])
+def test_disabled_fusion_patterns_parameter(value, fused):
+    out, _ = run(bias_relu_graph(), parameters={"disabled_fusion_patterns": value})
+    assert (by_name(out)["act"].op == "MusaBiasAddRelu") == fused
+
+
+def test_set_pattern_enabled():
+    lib = go._graph_lib()
+    assert lib.MusaGraphSetPatternEnabled(b"NoSuchPattern", 0) == 5
+    assert lib.MusaGraphSetPatternEnabled(b"MusaBiasAddReluFusion", 0) == 0
+    try:
+        assert run(bias_relu_graph())[1]["applied"] == 0
+    finally:
+        lib.MusaGraphSetPatternEnabled(b"MusaBiasAddReluFusion", 1)
+    assert run(bias_relu_graph())[1]["applied"] == 1
+
+
+def test_biasadd_kill_switch(monkeypatch):
+    monkeypatch.setenv("MUSA_DISABLE_BIASADD_ACT_FUSION", "true")
+    assert run(bias_relu_graph())[1]["applied"] == 0
+
+
+# ------------------------------------------------------ Python config layer --
+
+def test_config_helpers_mirror_the_reference_api():
+    cfg = go.enable_musa_graph_optimizer(add_to_optimizer_list=True,
+                                         disabled_fusion_patterns=[" A ", "b,c", "A"])
+    ro = cfg.graph_options.rewrite_options
+    assert go.is_musa_graph_optimizer_enabled(cfg)
+    assert ro.optimizers == [go.MUSA_GRAPH_OPTIMIZER_NAME]
+    assert go.get_musa_disabled_fusion_patterns(cfg) == ["A", "b", "c"]
+    go.set_musa_disabled_fusion_patterns(cfg, "x, all ,y")
+    assert go.get_musa_disabled_fusion_patterns(cfg) == ["all"]
+    go.clear_musa_disabled_fusion_patterns(cfg)
+    assert go.get_musa_disabled_fusion_patterns(cfg) == []
+    go.enable_musa_graph_optimizer(cfg)       # enabling twice keeps one entry
+    assert len(ro.custom_optimizers) == 1
+    go.disable_musa_graph_optimizer(cfg)
+    assert not go.is_musa_graph_optimizer_enabled(cfg) and ro.optimizers == []
+    assert go._graph_lib().MusaGraphOptimizerName() == b"musa_graph_optimizer"
+
+
+def test_config_drives_the_optimizer():
+    data = bias_relu_graph().bytes()
+    off = go.disable_musa_graph_optimizer()
+    assert go.optimize_graph_def(data, config=off)[0] == data
+    on = go.enable_musa_graph_optimizer()
+    assert by_name(parse(go.optimize_graph_def(data, config=on)[0]))["act"].op == "MusaBiasAddRelu"
+    go.disable_musa_fusion_patterns("MusaBiasAddReluFusion", on)
+    assert by_name(parse(go.optimize_graph_def(data, config=on)[0]))["act"].op == "Relu"
