@@ -9,10 +9,13 @@ import pytest
 from conftest import ROOT
 
 HEADER = os.path.join(ROOT, "include", "musa_plugin_kernels.h")
+ALL_HEADERS = [os.path.join(ROOT, "include", n)
+               for n in ("musa_plugin_kernels.h", "musa_plugin_graph.h",
+                         "musa_plugin_runtime.h")]
 
 
-def declared_functions():
-    text = open(HEADER).read()
+def declared_functions(header=HEADER):
+    text = open(header).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     text = re.sub(r"^\s*#.*$", "", text, flags=re.M)
     names = re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{]*\)\s*;", text)
@@ -31,8 +34,14 @@ def test_header_declares_the_expected_families():
 
 
 def test_library_exports_every_declared_symbol(kernel_lib):
-    for name in declared_functions():
-        assert hasattr(kernel_lib, name), "missing export: " + name
+    total = 0
+    for header in ALL_HEADERS:
+        names = declared_functions(header)
+        assert names, header
+        for name in names:
+            assert hasattr(kernel_lib, name), "missing export: %s (%s)" % (name, header)
+        total += len(names)
+    assert total >= 90
 
 
 def test_prototype_table_covers_the_header(kernel_lib):
