@@ -220,8 +220,25 @@ def run_ours(args):
     sum_s = sum(x.numel() * 2 for x in xs)       # bytes of all x
     algo_bytes_step = 5 * sum_s                  # 2*S forward + 3*S gradient
 
+    # N > 1: the per-channel sums are exchanged by a peer-memory kernel fused
+    # into the launch chain; --sync nccl keeps the NCCL all-reduce instead.
+    exchange = None
+    sync_kind = "none (1 GPU)"
+    if world > 1:
+        sync_kind = "nccl all-reduce of 2*C(+1) fp32 per layer and pass"
+        if args.sync == "peer":
+            from tensorflow_musa_extension_b200.cross_replica import PeerExchange
+            try:
+                exchange = PeerExchange(dist.group.WORLD, 2 * max(c for (_, _, c) in layers) + 1,
+                                        dev)
+                sync_kind = ("peer-memory exchange kernel (NVLink stores into every replica, "
+                             "bounded wait, rank-ordered sum) of 2*C(+1) fp32 per layer and pass")
+            except Exception as e:  # not one node / no peer access
+                if rank == 0:
+                    print("peer exchange unavailable (%r): using NCCL" % (e,), file=sys.stderr)
     bns = [SyncBatchNorm(c, eps=EPS, dtype=torch.bfloat16, device=dev,
-                         max_rows=BATCH * h * w, group=(dist.group.WORLD if world > 1 else None))
+                         max_rows=BATCH * h * w, group=(dist.group.WORLD if world > 1 else None),
+                         exchange=exchange)
            for (h, w, c) in layers]
 
     def step():
@@ -230,7 +247,8 @@ def run_ours(args):
         for i in reversed(range(n_layers)):
             bns[i].backward(dys[i], xs[i], scales[i], out_dx[tuple(xs[i].shape)])
 
-    launches_per_step = sum(b.launches_per_step for b in bns)
+    launches_per_step = sum(b.launches_per_step for b in bns) + \
+        (2 * n_layers if exchange is not None else 0)
 
     if args.profile_step:
         # One eager pass and nothing else: the target of an ncu launch list.
@@ -291,6 +309,10 @@ def run_ours(args):
     t_end = time.time()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+    if exchange is not None:
+        st = exchange.status()
+        if st != 0:
+            raise SystemExit("peer exchange: a wait for replica %d ran out" % (st - 1))
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -315,8 +337,7 @@ def run_ours(args):
                        "layout": "NHWC", "stats_dtype": "f32",
                        "elements_per_step_per_gpu": elems_per_step,
                        "algorithmic_bytes_per_step_per_gpu": algo_bytes_step,
-                       "sync": "nccl all-reduce of 2*C fp32 per layer and pass"
-                               if world > 1 else "none (1 GPU)",
+                       "sync": sync_kind,
                        "l2": "every layer has its own x and dy (10.8 GB per GPU), "
                              "so inputs exceed L2 between reuses",
                        "launch": "cuda graph replay" if graph is not None else "eager"},
@@ -704,6 +725,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--watchdog", type=int, default=600,
                     help="seconds after which a run that has not finished is ended")
+    ap.add_argument("--sync", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the per-channel sums cross the replicas")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed launch sequence and exit (ncu target): "
                          "bn | bnsmall | bnbig | adam | bias")

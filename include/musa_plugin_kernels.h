@@ -323,6 +323,35 @@ int LaunchBnGradApplyFromSums(int dtype, const void* dy, const void* x,
                               int64_t inner, float epsilon,
                               cudaStream_t stream);
 
+/* ---- Peer-memory exchange of the cross-replica sums (one process per GPU on
+ * one NVLink-connected node).  Replaces the NCCL all-reduce between
+ * LaunchBnStatsSumsCount and LaunchBnApplyFromSums (and between the two
+ * gradient halves) by ONE single-CTA kernel per replica that pushes its vector
+ * into every replica's memory with peer stores, waits (bounded) for the others'
+ * vectors to land in its own memory and sums them in rank order, so all
+ * replicas get bit-identical totals.  No counterpart in the reference.
+ *
+ * Set-up (allocates; not for the hot path): MusaExchangeCreate on every rank
+ * with the device current, exchange the 64-byte handles of
+ * MusaExchangeIpcHandle between the processes, MusaExchangeOpenPeers.
+ * Per exchange: LaunchExchangeSums(handle, vector, n, stream) - in place, no
+ * host synchronisation, works inside CUDA graph capture (the epoch counter
+ * lives on the device).  MusaExchangeStatus (synchronises; call between steps)
+ * returns 1 + q if a wait for replica q ever ran out, which leaves that
+ * exchange's totals incomplete instead of hanging the GPU. */
+void* MusaExchangeCreate(int rank, int world, int64_t max_floats);
+int MusaExchangeIpcHandle(void* handle, void* out64);
+int MusaExchangeOpenPeers(void* handle, const void* handles);
+int LaunchExchangeSums(void* handle, float* vector, int64_t n, cudaStream_t stream);
+int MusaExchangeStatus(void* handle);
+void MusaExchangeDestroy(void* handle);
+/* Test hook: `world` (<= 8) replicas emulated on one GPU by one cooperative
+ * launch of `world` CTAs; `vectors` is a device array of `world` device
+ * pointers to n floats each.  missing_rank = world - 1 leaves that replica out
+ * to check that the others' waits run out (returns 1000 + world). */
+int MusaExchangeSelfTest(int world, int64_t n, float* const* vectors, int rounds,
+                         int missing_rank, cudaStream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

@@ -67,6 +67,16 @@ PROTOTYPES = {
          + [c_i64, c_i64, c_i64, c_f32, c_vp]),
 }
 
+PROTOTYPES.update({
+    "MusaExchangeCreate": (c_vp, [c_int, c_int, c_i64]),
+    "MusaExchangeIpcHandle": (c_int, [c_vp, c_vp]),
+    "MusaExchangeOpenPeers": (c_int, [c_vp, c_vp]),
+    "LaunchExchangeSums": (c_int, [c_vp, c_vp, c_i64, c_vp]),
+    "MusaExchangeStatus": (c_int, [c_vp]),
+    "MusaExchangeDestroy": (None, [c_vp]),
+    "MusaExchangeSelfTest": (c_int, [c_int, c_i64, c_vp, c_int, c_int, c_vp]),
+})
+
 # Hooks outside the reference boundary (launch-shape sweeps).
 EXTRA_PROTOTYPES = {
     "MusaKernelsSetTuning": (c_int, [c_int, c_int]),

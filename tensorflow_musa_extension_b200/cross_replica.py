@@ -104,6 +104,64 @@ class _DeviceKernels:
                           ws.numel(), self._st()), "LaunchBnGrad")
 
 
+class PeerExchange:
+    """Sum of small fp32 vectors across the replicas of one node, done by the
+    GPUs themselves over NVLink peer memory (LaunchExchangeSums) instead of a
+    collective-library call: one single-CTA kernel per replica pushes its
+    vector into every replica's memory, waits (bounded) for the others' and
+    adds them in rank order.  Works inside CUDA graph capture.
+
+    Set-up allocates one buffer per replica and exchanges its CUDA IPC handle
+    through `group` (any backend); all replicas must sit on one node with
+    peer access between their GPUs, else the constructor raises and the caller
+    stays on the all-reduce."""
+
+    def __init__(self, group, max_floats, device):
+        import ctypes
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.lib = raw_ops._lib()
+        self.max_floats = int(max_floats)
+        with torch.cuda.device(device):
+            self.handle = self.lib.MusaExchangeCreate(self.rank, self.world, self.max_floats)
+            ok = self.handle is not None
+            raw = ctypes.create_string_buffer(64)
+            if ok:
+                ok = self.lib.MusaExchangeIpcHandle(self.handle, raw) == 0
+            # Every rank takes part in the gathers, also one that failed, so that
+            # all of them fall back together.
+            handles = [None] * self.world
+            dist.all_gather_object(handles, raw.raw if ok else None, group=group)
+            if ok and all(h is not None for h in handles):
+                ok = self.lib.MusaExchangeOpenPeers(self.handle, b"".join(handles)) == 0
+            else:
+                ok = False
+            flags = [None] * self.world
+            dist.all_gather_object(flags, bool(ok), group=group)
+        if not all(flags):
+            self.close()
+            raise RuntimeError("peer-memory exchange is not available between these GPUs")
+
+    def sum_(self, vector):
+        """In place: `vector` (fp32, contiguous, on this replica's GPU) becomes
+        the element-wise sum over all replicas."""
+        n = vector.numel()
+        raw_ops._check(self.lib.LaunchExchangeSums(
+            self.handle, vector.data_ptr(), n, torch.cuda.current_stream().cuda_stream),
+            "LaunchExchangeSums")
+        return vector
+
+    def status(self):
+        """0, or 1 + q if a wait for replica q ran out since the last call."""
+        return int(self.lib.MusaExchangeStatus(self.handle))
+
+    def close(self):
+        if getattr(self, "handle", None) is not None:
+            self.lib.MusaExchangeDestroy(self.handle)
+            self.handle = None
+
+
 class SyncBatchNorm:
     """One BatchNorm layer of a replica: channels-last [rows, C] activations,
     preallocated statistics and workspace, no allocation per call.
@@ -116,10 +174,12 @@ class SyncBatchNorm:
     """
 
     def __init__(self, channels, eps=1e-3, dtype=torch.bfloat16, device="cuda",
-                 max_rows=0, group=None, kernels=None):
+                 max_rows=0, group=None, kernels=None, exchange=None):
         self.c = int(channels)
         self.eps = float(eps)
         self.group = group
+        # A PeerExchange replaces the two all-reduces when given.
+        self.exchange = exchange
         self.world = _world(group)
         self.k = kernels if kernels is not None else _DeviceKernels()
         dev = torch.device(device)
@@ -160,7 +220,10 @@ class SyncBatchNorm:
             self.global_count = float(rows)
             return y
         self.k.stats_sums(x, self.sums, self.ws)
-        dist.all_reduce(self.sums, op=dist.ReduceOp.SUM, group=self.group)
+        if self.exchange is not None:
+            self.exchange.sum_(self.sums)
+        else:
+            dist.all_reduce(self.sums, op=dist.ReduceOp.SUM, group=self.group)
         # Static shapes: the global count is rows * world unless a replica is
         # ragged; read it on the host only in that case.
         self.global_count = float(rows) * self.world if self._uniform_rows else \
@@ -184,7 +247,10 @@ class SyncBatchNorm:
                               self.dscale, self.doffset, self.ws, self.eps)
             return dx
         self.k.grad_stats_sums(dy, x, self.saved_mean, self.gsums, self.ws)
-        dist.all_reduce(self.gsums, op=dist.ReduceOp.SUM, group=self.group)
+        if self.exchange is not None:
+            self.exchange.sum_(self.gsums)
+        else:
+            dist.all_reduce(self.gsums, op=dist.ReduceOp.SUM, group=self.group)
         count = self.global_count if self.global_count is not None else float(rows) * self.world
         self.k.grad_apply(dy, x, scale, self.saved_mean, self.saved_var, self.gsums, count,
                           dx, self.dscale, self.doffset, self.eps)
