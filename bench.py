@@ -247,6 +247,16 @@ def run_ours(args):
         for i in reversed(range(n_layers)):
             bns[i].backward(dys[i], xs[i], scales[i], out_dx[tuple(xs[i].shape)])
 
+    if world == 1 and args.force_split != "off":
+        # Diagnostic: the cross-replica launch chain with a single replica, with
+        # ("exchange") or without ("bare") the exchange kernel.
+        if args.force_split == "exchange":
+            from tensorflow_musa_extension_b200.cross_replica import PeerExchange
+            exchange = PeerExchange(None, 2 * max(c for (_, _, c) in layers) + 1, dev)
+        for b in bns:
+            b.force_split = True
+            b.exchange = exchange
+        sync_kind = "split launch chain on one replica (%s)" % args.force_split
     launches_per_step = sum(b.launches_per_step for b in bns) + \
         (2 * n_layers if exchange is not None else 0)
 
@@ -727,6 +737,8 @@ def main():
                     help="seconds after which a run that has not finished is ended")
     ap.add_argument("--sync", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the per-channel sums cross the replicas")
+    ap.add_argument("--force-split", default="off", choices=["off", "bare", "exchange"],
+                    help="N = 1 diagnostic: run the cross-replica launch chain anyway")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed launch sequence and exit (ncu target): "
                          "bn | bnsmall | bnbig | adam | bias")

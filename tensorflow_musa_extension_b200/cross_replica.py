@@ -119,8 +119,8 @@ class PeerExchange:
     def __init__(self, group, max_floats, device):
         import ctypes
         self.group = group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
         self.lib = raw_ops._lib()
         self.max_floats = int(max_floats)
         with torch.cuda.device(device):
@@ -132,13 +132,18 @@ class PeerExchange:
             # Every rank takes part in the gathers, also one that failed, so that
             # all of them fall back together.
             handles = [None] * self.world
-            dist.all_gather_object(handles, raw.raw if ok else None, group=group)
+            if self.world == 1:
+                handles = [raw.raw if ok else None]
+            else:
+                dist.all_gather_object(handles, raw.raw if ok else None, group=group)
             if ok and all(h is not None for h in handles):
                 ok = self.lib.MusaExchangeOpenPeers(self.handle, b"".join(handles)) == 0
             else:
                 ok = False
-            flags = [None] * self.world
-            dist.all_gather_object(flags, bool(ok), group=group)
+            flags = [bool(ok)]
+            if self.world > 1:
+                flags = [None] * self.world
+                dist.all_gather_object(flags, bool(ok), group=group)
         if not all(flags):
             self.close()
             raise RuntimeError("peer-memory exchange is not available between these GPUs")
@@ -180,6 +185,7 @@ class SyncBatchNorm:
         self.group = group
         # A PeerExchange replaces the two all-reduces when given.
         self.exchange = exchange
+        self.force_split = False  # run the split launch chain even with one replica
         self.world = _world(group)
         self.k = kernels if kernels is not None else _DeviceKernels()
         dev = torch.device(device)
@@ -215,14 +221,14 @@ class SyncBatchNorm:
     def forward(self, x, scale, offset, y):
         self._check(x)
         rows = x.shape[0]
-        if self.world == 1:
+        if self.world == 1 and not self.force_split:
             self.k.fwd_local(x, scale, offset, y, self._stats(), self.ws, self.eps)
             self.global_count = float(rows)
             return y
         self.k.stats_sums(x, self.sums, self.ws)
         if self.exchange is not None:
             self.exchange.sum_(self.sums)
-        else:
+        elif self.world > 1:
             dist.all_reduce(self.sums, op=dist.ReduceOp.SUM, group=self.group)
         # Static shapes: the global count is rows * world unless a replica is
         # ragged; read it on the host only in that case.
@@ -242,14 +248,14 @@ class SyncBatchNorm:
     def backward(self, dy, x, scale, dx):
         self._check(x)
         rows = x.shape[0]
-        if self.world == 1:
+        if self.world == 1 and not self.force_split:
             self.k.grad_local(dy, x, scale, self.saved_mean, self.saved_var, dx,
                               self.dscale, self.doffset, self.ws, self.eps)
             return dx
         self.k.grad_stats_sums(dy, x, self.saved_mean, self.gsums, self.ws)
         if self.exchange is not None:
             self.exchange.sum_(self.gsums)
-        else:
+        elif self.world > 1:
             dist.all_reduce(self.gsums, op=dist.ReduceOp.SUM, group=self.group)
         count = self.global_count if self.global_count is not None else float(rows) * self.world
         self.k.grad_apply(dy, x, scale, self.saved_mean, self.saved_var, self.gsums, count,

@@ -516,6 +516,8 @@ struct FinalizeArgs {
   int splits;
   int64_t channels;
   double count;          // values per channel behind the sums (all replicas)
+  double inv_count;      // 1 / count
+  double bessel;         // count / (count - 1), or 1 when count <= 1
   // forward
   const void* x_first;   // tensor base: the shift K is re-read from it
   int x_dtype;
@@ -547,8 +549,9 @@ __device__ __forceinline__ float LoadAsF32(const void* base, int dtype,
 __device__ __forceinline__ void WriteFwdStats(const FinalizeArgs& a, int64_t c,
                                               double mean, double var) {
   if (var < 0.0) var = 0.0;
-  const double n = a.count;
-  const double unbiased = n > 1.0 ? var * (n / (n - 1.0)) : var;
+  // bessel = R / (R - 1), or 1 when there is one value per channel; taken on
+  // the host (an fp64 divide per thread is not free on the device).
+  const double unbiased = var * a.bessel;
   if (a.saved_mean) a.saved_mean[c] = static_cast<float>(mean);
   if (a.saved_var) a.saved_var[c] = static_cast<float>(var);
   const double f = static_cast<double>(a.exp_avg_factor);
@@ -560,6 +563,12 @@ __device__ __forceinline__ void WriteFwdStats(const FinalizeArgs& a, int64_t c,
   }
   if (a.batch_mean) a.batch_mean[c] = static_cast<float>(bm);
   if (a.batch_var) a.batch_var[c] = static_cast<float>(bv);
+}
+
+inline void SetCount(FinalizeArgs* f, double count) {
+  f->count = count;
+  f->inv_count = 1.0 / count;
+  f->bessel = count > 1.0 ? count / (count - 1.0) : 1.0;
 }
 
 // kOut: 0 forward statistics, 1 forward raw sums (sum x, sum x^2) for the
@@ -641,7 +650,7 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
     S1 += __shfl_xor_sync(0xffffffffu, S1, 16);
     S2 += __shfl_xor_sync(0xffffffffu, S2, 16);
     if (lane < 8 && c < a.channels) {
-      const double inv_count = 1.0 / a.count;
+      const double inv_count = a.inv_count;
       if constexpr (kOut == 0) {
         const double K = static_cast<double>(shift_k);
         const double md = S1 * inv_count;
@@ -676,9 +685,9 @@ __global__ void BnFinalizeFromSumsKernel(FinalizeArgs a, const float* sums) {
   GridDepLaunch();
   const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (c >= a.channels) return;
-  const double mean = static_cast<double>(sums[c]) / a.count;
+  const double mean = static_cast<double>(sums[c]) * a.inv_count;
   const double var =
-      static_cast<double>(sums[a.channels + c]) / a.count - mean * mean;
+      static_cast<double>(sums[a.channels + c]) * a.inv_count - mean * mean;
   WriteFwdStats(a, c, mean, var);
 }
 
@@ -761,8 +770,9 @@ __global__ void __launch_bounds__(kThreads)
     const int64_t c = col * kVec + e;
     float var_c;
     if (kMode == kFwd && a.stat_sums != nullptr) {
-      const double m = static_cast<double>(a.stat_sums[c]) / a.count;
-      double v = static_cast<double>(a.stat_sums[channels + c]) / a.count - m * m;
+      const double m = static_cast<double>(a.stat_sums[c]) * a.stat_out.inv_count;
+      double v =
+          static_cast<double>(a.stat_sums[channels + c]) * a.stat_out.inv_count - m * m;
       if (v < 0.0) v = 0.0;
       mean[e] = static_cast<float>(m);
       var_c = static_cast<float>(v);
@@ -1172,7 +1182,7 @@ int FwdTrain(const void* x, const float* scale, const float* offset,
   f.partial = partial;
   f.splits = splits;
   f.channels = channels;
-  f.count = static_cast<double>(g.rows());
+  SetCount(&f, static_cast<double>(g.rows()));
   f.x_first = x;
   f.x_dtype = DtypeCode<T>::value;
   f.shift_stride = inner == 1 ? 1 : inner;
@@ -1242,7 +1252,7 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
   f.partial = partial;
   f.splits = splits;
   f.channels = channels;
-  f.count = static_cast<double>(g.rows());
+  SetCount(&f, static_cast<double>(g.rows()));
   f.variance = variance;
   f.dscale = dscale;
   f.doffset = doffset;
@@ -1276,7 +1286,7 @@ int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
   f.partial = partial;
   f.splits = splits;
   f.channels = g.channels;
-  f.count = static_cast<double>(g.rows());
+  SetCount(&f, static_cast<double>(g.rows()));
   f.x_first = x;
   f.x_dtype = DtypeCode<T>::value;
   f.shift_stride = g.inner == 1 ? 1 : g.inner;
@@ -1304,7 +1314,7 @@ int GradStatsSums(const void* dy, const void* x, const float* mean, float* sums,
   f.partial = partial;
   f.splits = splits;
   f.channels = g.channels;
-  f.count = static_cast<double>(g.rows());
+  SetCount(&f, static_cast<double>(g.rows()));
   f.sums = sums;
   LaunchFinalize<2>(f, stream);
   return LastError();
@@ -1556,7 +1566,7 @@ int LaunchBnApplyFromSums(int dtype, const void* x, const float* scale,
   a.stat_sums = sums;
   a.count = total_count;
   a.stat_out.channels = channels;
-  a.stat_out.count = total_count;
+  SetCount(&a.stat_out, total_count);
   a.stat_out.est_mean = est_mean;
   a.stat_out.est_var = est_var;
   a.stat_out.batch_mean = batch_mean;
@@ -1583,7 +1593,7 @@ int LaunchBnFinalizeFromSums(const float* sums, double total_count,
   }
   FinalizeArgs f{};
   f.channels = channels;
-  f.count = total_count;
+  SetCount(&f, total_count);
   f.est_mean = est_mean;
   f.est_var = est_var;
   f.batch_mean = batch_mean;

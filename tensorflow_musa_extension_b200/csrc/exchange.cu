@@ -3,19 +3,23 @@
 // (2*C + 1 floats per layer and pass) without a collective-library launch.
 //
 // Every replica owns one buffer in its OWN memory:
-//     data [2 slots][world][slot_floats]   written by the peers (and itself)
-//     flags[2 slots][world]                epoch at which data[s][r] is valid
+//     cell[2 slots][world][slot_floats]    8-byte cells {value bits, epoch}
+// written by the peers (and by itself).  A cell is stored with one aligned
+// 8-byte store, so a reader sees either the old cell or the new one, never a
+// mix: the epoch inside the cell says whether the value is the one it waits
+// for.  No separate flag and no memory fence are needed (the latency of one
+// exchange is one NVLink store plus a poll).
 // One exchange = one single-CTA kernel per replica:
-//   1. epoch = ++local counter (a device-side counter, so a captured CUDA graph
-//      replays correctly); slot = epoch & 1;
-//   2. push: store this replica's vector into data[slot][rank] of EVERY replica
-//      (plain stores to peer-mapped addresses), fence, then store the epoch into
-//      flags[slot][rank] of every replica;
-//   3. wait, in its own memory, until flags[slot][q] == epoch for every q; the
-//      wait is bounded: after kSpinLimit polls the kernel records which peer was
-//      missing in a status word and goes on, so a lost peer never hangs a GPU;
-//   4. total[i] = sum over q = 0..world-1 of data[slot][q][i], in rank order, so
-//      every replica gets bit-identical totals; written over the input vector.
+//   1. epoch = local counter + 1 (a device-side counter, so a captured CUDA
+//      graph replays correctly); slot = epoch & 1;
+//   2. push: store {v[i], epoch} into cell[slot][rank][i] of EVERY replica
+//      (plain stores to peer-mapped addresses);
+//   3. gather, in its own memory: for each i, read cell[slot][q][i] for every
+//      q and poll the ones whose epoch is still old.  The poll is bounded:
+//      after kSpinLimit tries the kernel records which replica was missing in
+//      a status word and goes on, so a lost peer never hangs a GPU;
+//   4. total[i] = sum over q = 0..world-1, in rank order, so every replica
+//      gets bit-identical totals; written over the input vector.
 // Two slots suffice: a replica can publish epoch e+2 only after it consumed
 // e+1, which needs every replica to have published e+1, which each does only
 // after consuming e.
@@ -38,19 +42,18 @@ namespace musa_b200 {
 namespace {
 
 constexpr int kMaxWorld = 16;
-constexpr int kExchangeThreads = 1024;
-// Polls before a wait gives up (each poll is a volatile load plus a short
-// sleep: of the order of a second in total).
+constexpr int kExchangeThreads = 512;
+// Polls of one cell before a wait gives up (each poll is a volatile load plus
+// a short sleep: of the order of a second in total).
 constexpr long long kSpinLimit = 4LL << 20;
 
 struct ExchangeDev {
   int rank;
   int world;
   long long slot_floats;
-  float* data[kMaxWorld];      // data buffer of every replica (peer-mapped)
-  unsigned* flags[kMaxWorld];  // flag array of every replica
-  unsigned* epoch;             // local
-  int* status;                 // local: 0 ok, 1 + q when replica q never arrived
+  uint2* cells[kMaxWorld];  // cell buffer of every replica (peer-mapped)
+  unsigned* epoch;          // local
+  int* status;              // local: 0 ok, 1 + q when replica q never arrived
 };
 
 struct ExchangeHost {
@@ -64,6 +67,64 @@ struct ExchangeHost {
 
 size_t Align256(size_t n) { return (n + 255) / 256 * 256; }
 
+__device__ __forceinline__ uint2 LoadCell(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
+               : "=r"(v.x), "=r"(v.y)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void StoreCell(uint2* p, uint2 v) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y)
+               : "memory");
+}
+
+template <int kWorld>  // 0: run-time world size
+__device__ __forceinline__ void ExchangeBody(const ExchangeDev& c, float* vec, int n,
+                                             unsigned epoch) {
+  const int world = kWorld > 0 ? kWorld : c.world;
+  const int slot = static_cast<int>(epoch & 1u);
+  const long long slot_base = static_cast<long long>(slot) * world * c.slot_floats;
+  const long long mine = slot_base + static_cast<long long>(c.rank) * c.slot_floats;
+
+  // 2. push the local vector into every replica's memory.
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const uint2 cell = make_uint2(__float_as_uint(vec[i]), epoch);
+#pragma unroll
+    for (int p = 0; p < (kWorld > 0 ? kWorld : kMaxWorld); ++p) {
+      if (p < world) StoreCell(c.cells[p] + mine + i, cell);
+    }
+  }
+
+  // 3. + 4. gather from local memory and sum in rank order.
+  const uint2* local = c.cells[c.rank] + slot_base;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    uint2 got[kWorld > 0 ? kWorld : kMaxWorld];
+#pragma unroll
+    for (int q = 0; q < (kWorld > 0 ? kWorld : kMaxWorld); ++q) {
+      if (q < world) got[q] = LoadCell(local + static_cast<long long>(q) * c.slot_floats + i);
+    }
+    float total = 0.0f;
+#pragma unroll
+    for (int q = 0; q < (kWorld > 0 ? kWorld : kMaxWorld); ++q) {
+      if (q < world) {
+        long long polls = 0;
+        while (got[q].y != epoch) {
+          if (++polls > kSpinLimit) {
+            atomicCAS(c.status, 0, 1 + q);
+            break;
+          }
+          __nanosleep(40);
+          got[q] = LoadCell(local + static_cast<long long>(q) * c.slot_floats + i);
+        }
+        total += __uint_as_float(got[q].x);
+      }
+    }
+    vec[i] = total;
+  }
+}
+
 __global__ void __launch_bounds__(kExchangeThreads)
     ExchangeSumsKernel(const ExchangeDev* ctxs, float* const* vectors,
                        float* single_vector, int n) {
@@ -71,51 +132,13 @@ __global__ void __launch_bounds__(kExchangeThreads)
   GridDepLaunch();
   const ExchangeDev& c = ctxs[blockIdx.x];
   float* vec = vectors != nullptr ? vectors[blockIdx.x] : single_vector;
-  __shared__ unsigned s_epoch;
-  if (threadIdx.x == 0) s_epoch = *c.epoch + 1u;
-  __syncthreads();
-  const unsigned epoch = s_epoch;
-  const int slot = static_cast<int>(epoch & 1u);
-  const long long mine = (static_cast<long long>(slot) * c.world + c.rank) * c.slot_floats;
-
-  // 2. push the local vector into every replica's memory.
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = vec[i];
-    for (int p = 0; p < c.world; ++p) c.data[p][mine + i] = v;
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < c.world) {
-    __threadfence_system();
-    volatile unsigned* f = c.flags[threadIdx.x] + slot * c.world + c.rank;
-    *f = epoch;
-  }
-
-  // 3. wait for every replica's vector to land here (bounded).
-  if (threadIdx.x < c.world) {
-    volatile unsigned* f = c.flags[c.rank] + slot * c.world + threadIdx.x;
-    long long polls = 0;
-    while (*f != epoch) {
-      if (++polls > kSpinLimit) {
-        atomicCAS(c.status, 0, 1 + static_cast<int>(threadIdx.x));
-        break;
-      }
-      __nanosleep(100);
-    }
-    __threadfence_system();
-  }
-  __syncthreads();
-
-  // 4. sum in rank order, from local memory.
-  const float* local = c.data[c.rank];
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float total = 0.0f;
-    for (int q = 0; q < c.world; ++q) {
-      const volatile float* src =
-          local + (static_cast<long long>(slot) * c.world + q) * c.slot_floats + i;
-      total += *src;
-    }
-    vec[i] = total;
+  const unsigned epoch = *c.epoch + 1u;  // nobody writes it before the barrier below
+  switch (c.world) {
+    case 1: ExchangeBody<1>(c, vec, n, epoch); break;
+    case 2: ExchangeBody<2>(c, vec, n, epoch); break;
+    case 4: ExchangeBody<4>(c, vec, n, epoch); break;
+    case 8: ExchangeBody<8>(c, vec, n, epoch); break;
+    default: ExchangeBody<0>(c, vec, n, epoch); break;
   }
   __syncthreads();
   if (threadIdx.x == 0) *c.epoch = epoch;
@@ -140,10 +163,8 @@ void* MusaExchangeCreate(int rank, int world, int64_t max_floats) {
     return nullptr;
   }
   const long long slot_floats = static_cast<long long>(Align256(max_floats * 4) / 4);
-  const size_t data_bytes = Align256(sizeof(float) * 2 * world * slot_floats);
-  const size_t flag_bytes = Align256(sizeof(unsigned) * 2 * world);
-  h->bytes = data_bytes + flag_bytes + 256 /*epoch*/ + 256 /*status*/ +
-             Align256(sizeof(ExchangeDev));
+  const size_t cell_bytes = Align256(sizeof(uint2) * 2 * world * slot_floats);
+  h->bytes = cell_bytes + 256 /*epoch*/ + 256 /*status*/ + Align256(sizeof(ExchangeDev));
   if (cudaMalloc(&h->base, h->bytes) != cudaSuccess ||
       cudaMemset(h->base, 0, h->bytes) != cudaSuccess) {
     cudaGetLastError();
@@ -155,11 +176,10 @@ void* MusaExchangeCreate(int rank, int world, int64_t max_floats) {
   h->dev.rank = rank;
   h->dev.world = world;
   h->dev.slot_floats = slot_floats;
-  h->dev.data[rank] = reinterpret_cast<float*>(p);
-  h->dev.flags[rank] = reinterpret_cast<unsigned*>(p + data_bytes);
-  h->dev.epoch = reinterpret_cast<unsigned*>(p + data_bytes + flag_bytes);
-  h->dev.status = reinterpret_cast<int*>(p + data_bytes + flag_bytes + 256);
-  h->dev_copy = reinterpret_cast<ExchangeDev*>(p + data_bytes + flag_bytes + 512);
+  h->dev.cells[rank] = reinterpret_cast<uint2*>(p);
+  h->dev.epoch = reinterpret_cast<unsigned*>(p + cell_bytes);
+  h->dev.status = reinterpret_cast<int*>(p + cell_bytes + 256);
+  h->dev_copy = reinterpret_cast<ExchangeDev*>(p + cell_bytes + 512);
   return h;
 }
 
@@ -180,8 +200,6 @@ int MusaExchangeIpcHandle(void* handle, void* out64) {
 int MusaExchangeOpenPeers(void* handle, const void* handles) {
   auto* h = static_cast<ExchangeHost*>(handle);
   if (h == nullptr || (handles == nullptr && h->dev.world > 1)) return MUSA_KERNELS_EINVAL;
-  const size_t data_bytes =
-      Align256(sizeof(float) * 2 * h->dev.world * h->dev.slot_floats);
   for (int q = 0; q < h->dev.world; ++q) {
     if (q == h->dev.rank) continue;
     cudaIpcMemHandle_t ipc;
@@ -191,8 +209,7 @@ int MusaExchangeOpenPeers(void* handle, const void* handles) {
         cudaIpcOpenMemHandle(&mapped, ipc, cudaIpcMemLazyEnablePeerAccess);
     if (err != cudaSuccess) return static_cast<int>(err);
     h->opened[q] = mapped;
-    h->dev.data[q] = static_cast<float*>(mapped);
-    h->dev.flags[q] = reinterpret_cast<unsigned*>(static_cast<char*>(mapped) + data_bytes);
+    h->dev.cells[q] = static_cast<uint2*>(mapped);
   }
   return static_cast<int>(
       cudaMemcpy(h->dev_copy, &h->dev, sizeof(ExchangeDev), cudaMemcpyHostToDevice));
@@ -255,8 +272,7 @@ int MusaExchangeSelfTest(int world, int64_t n, float* const* vectors, int rounds
   if (rc == 0) {
     for (int r = 0; r < world; ++r) {
       for (int q = 0; q < world; ++q) {
-        hs[r]->dev.data[q] = hs[q]->dev.data[q];
-        hs[r]->dev.flags[q] = hs[q]->dev.flags[q];
+        hs[r]->dev.cells[q] = hs[q]->dev.cells[q];
       }
       cudaMemcpy(table + r, &hs[r]->dev, sizeof(ExchangeDev), cudaMemcpyHostToDevice);
     }
