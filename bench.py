@@ -44,6 +44,9 @@ RESNET50_BN = [(1, 112, 112, 64), (6, 56, 56, 64), (4, 56, 56, 256), (8, 28, 28,
                (4, 7, 7, 2048)]
 BATCH = 256
 EPS = 1e-3
+# DRAM bytes per launch from an ncu capture (the summary under profiles/ names
+# the command): 822.2 MB read + 376.4 MB written for 1233.1 MB algorithmic.
+NCU_TRAFFIC_BYTES = {"bn_grad_apply_bf16_256x56x56x256": 1198591488}
 WORKLOAD = "resnet50_bn_train_bf16_b256"
 METRIC = "bn_fwd_grad_throughput"
 UNIT = "Gelem/s"
@@ -559,12 +562,9 @@ def measure_ops(torch, lib, raw_ops, dev, args):
             "achieved": round(achieved, 1), "peak": peak, "peak_kind": peak_kind,
             "unit": "GB/s", "frac": round(achieved / peak, 4), "ms": round(ms, 4),
             "traffic": None}
-    tr = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tr):
-        try:
-            roof["traffic"] = json.load(open(tr)).get("bn_grad_apply_bf16_256x56x56x256")
-        except Exception:
-            pass
+    roof["traffic"] = NCU_TRAFFIC_BYTES["bn_grad_apply_bf16_256x56x56x256"]
+    roof["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
+                              "kernel and case (profiles/bn_grad_apply_bf16_256x56x56x256_ncu_full.md)")
     return ops, roof
 
 
