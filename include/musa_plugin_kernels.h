@@ -147,6 +147,15 @@ int LaunchBiasAct_I64(const void* x, const void* bias, void* y, int64_t outer,
  * serves forward and gradient.  16-byte aligned memory is expected. */
 size_t BnWorkspaceBytes(int64_t outer, int64_t channels, int64_t inner);
 
+/* When the geometry allows it (channels-last, 128-bit packs, at most 256 packs
+ * per row) LaunchBnFwdTrain_* and LaunchBnGrad_* run as ONE cooperative launch
+ * whose CTAs meet at a barrier kept in the workspace.  Every wait in it is
+ * bounded; if one ever ran out (the outputs of that call are then invalid) the
+ * workspace's status word says so.  This reads and clears it (synchronises the
+ * device: for tests and post-mortems, not for the hot path).  0 = fine. */
+int BnWorkspaceStatus(void* workspace, int64_t outer, int64_t channels,
+                      int64_t inner);
+
 /* Training-mode forward.  Outputs follow TensorFlow's CPU kernel:
  *   y = (x - mean) * rsqrt(var + eps) * scale + offset, mean/var of the batch;
  *   batch_mean = mean, batch_var = var * R/(R-1) (Bessel; R = outer*inner, not

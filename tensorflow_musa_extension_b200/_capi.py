@@ -35,6 +35,7 @@ PROTOTYPES = {
     "LaunchBiasAct_I32": (c_int, _BIAS_ACT),
     "LaunchBiasAct_I64": (c_int, _BIAS_ACT),
     "BnWorkspaceBytes": (c_size, [c_i64, c_i64, c_i64]),
+    "BnWorkspaceStatus": (c_int, [c_vp, c_i64, c_i64, c_i64]),
     "LaunchBnFwdTrain_F32": (c_int, _BN_TRAIN),
     "LaunchBnFwdTrain_F16": (c_int, _BN_TRAIN),
     "LaunchBnFwdTrain_BF16": (c_int, _BN_TRAIN),

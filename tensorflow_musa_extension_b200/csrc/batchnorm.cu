@@ -953,6 +953,387 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// ------------------------------------------------- fused (one launch) -----
+//
+// The whole op in ONE cooperative launch: statistics, grid-wide reduction and
+// element-wise pass, with the tail of every CTA's row range kept in shared
+// memory between the two passes.
+//
+//   A  every thread streams its rows through a ring of kRing row slots per
+//      input stream (cp.async, kAhead batches in flight) and accumulates the
+//      two sums; when the stream ends, the last kRing rows of the thread are
+//      still in the ring;
+//   B  the CTA folds its row lanes and writes one partial row [2, C];
+//   -- grid barrier --
+//   C  CTA b reduces channels b, b + G, ... over all partial rows (fp64) and
+//      writes the statistics outputs / totals;
+//   -- grid barrier --
+//   D  every thread takes the coefficients of its channels;
+//   E  element-wise pass: first the rows still in the ring (no global read),
+//      then the remaining rows newest-first from L2 / HBM.
+// Against the three-kernel chain this saves two kernel boundaries and the
+// finalize launch, and the re-read of up to 16 rows * 16 B * resident threads
+// per SM (about 29 MB over the GPU): everything for the small layers.
+//
+// MEASURED (B200, bf16): it is slower than the programmatically chained three
+// kernels at every size - 38.9 vs 25.5 us forward at S = 25.7 MB, 79.9 vs 57.4
+// at 102.8 MB, 235 vs 213 at 411 MB - a fixed 13-25 us that the cooperative
+// launch (no overlap with the previous kernel's tail, plus the counter memset)
+// and the two grid barriers cost.  It is therefore OFF by default
+// (MusaKernelsSetTuning(5, 1) turns it on) and kept, tested, as the starting
+// point for a version with a cheaper barrier.
+//
+// The grid barrier is a counter in the workspace (zeroed by the launcher),
+// entered once per phase; the cooperative launch guarantees that all CTAs are
+// resident, and every wait is bounded all the same: when a wait runs out the
+// CTA sets the status word and returns.
+constexpr long long kBarrierSpinLimit = 1LL << 24;
+
+__device__ __forceinline__ bool GridBarrier(unsigned* counter, unsigned target,
+                                            int* status) {
+  __shared__ int s_ok;
+  __syncthreads();
+  if (threadIdx.x == 0 && threadIdx.y == 0) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+    long long polls = 0;
+    int ok = 1;
+    while (true) {
+      unsigned seen;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter));
+      if (seen >= target) break;
+      if (++polls > kBarrierSpinLimit) {
+        atomicCAS(status, 0, 1);
+        ok = 0;
+        break;
+      }
+      __nanosleep(32);
+    }
+    s_ok = ok;
+    __threadfence();
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+struct FusedArgs {
+  const void* x;
+  const void* dy;
+  void* out;
+  int64_t rows;
+  int64_t cv;
+  int64_t channels;
+  int64_t rows_per_cta;
+  float* partial;     // [gridDim.y, 2, C]
+  unsigned* barrier;  // zeroed before the launch
+  int* status;
+  FinalizeArgs fin;
+  ApplyArgs app;
+  bool is_training;   // gradient: inference mode skips the batch terms
+};
+
+template <int kMode>
+struct FusedCfg {
+  static constexpr int kStreams = kMode == 0 ? 1 : 2;
+  static constexpr int kU = kMode == 0 ? 4 : 2;   // rows per batch and stream
+  static constexpr int kRingBatches = 4;
+  static constexpr int kAhead = 3;                // batches in flight
+  static constexpr int kRingBytes = kRingBatches * kStreams * kU * kThreads * 16;
+  static constexpr int kScratchBytes = 8 * kThreads * 4;  // fold scratch
+  static constexpr int kSmemBytes = kRingBytes + kScratchBytes;
+};
+
+template <typename T, int kMode>
+__global__ void __launch_bounds__(kThreads) BnFusedKernel(FusedArgs a) {
+  constexpr int kVec = VecWidth<T>::value;
+  constexpr int kPairs = kVec / 2;
+  using P = Pack<T, kVec>;
+  using Cfg = FusedCfg<kMode>;
+  constexpr int kU = Cfg::kU, kStreams = Cfg::kStreams, kRB = Cfg::kRingBatches,
+                kAhead = Cfg::kAhead;
+  extern __shared__ uint4 fused_smem[];
+  float* scratch = reinterpret_cast<float*>(
+      reinterpret_cast<char*>(fused_smem) + Cfg::kRingBytes);
+
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int TX = blockDim.x, TY = blockDim.y;
+  const int tid = ty * TX + tx;
+  const int64_t col = tx;  // one column block: cv <= TX
+  const bool active = col < a.cv;
+  const int64_t cv = a.cv, channels = a.channels;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * a.rows_per_cta;
+  int64_t r1 = r0 + a.rows_per_cta;
+  if (r1 > a.rows) r1 = a.rows;
+  const int n_rows = r1 > r0 ? static_cast<int>(r1 - r0) : 0;
+  const int n_j = n_rows > ty ? (n_rows - ty + TY - 1) / TY : 0;
+  const int n_b = (n_j + kU - 1) / kU;
+  const int64_t row_stride = static_cast<int64_t>(TY) * cv;
+  const P* xbase = static_cast<const P*>(a.x) + col + (r0 + ty) * cv;
+  const P* dbase = static_cast<const P*>(a.dy) + col + (r0 + ty) * cv;
+  P* obase = static_cast<P*>(a.out) + col + (r0 + ty) * cv;
+  uint4* const my = fused_smem + tid;
+
+  // ---- A: statistics over the thread's rows, ring-staged.
+  float2 nshift[kPairs], a1[kPairs], a2[kPairs];
+#pragma unroll
+  for (int q = 0; q < kPairs; ++q) {
+    a1[q] = make_float2(0.0f, 0.0f);
+    a2[q] = make_float2(0.0f, 0.0f);
+    nshift[q] = make_float2(0.0f, 0.0f);
+  }
+  if (active) {
+    if constexpr (kMode == kFwd) {
+      const P first = LoadKeep(static_cast<const P*>(a.x) + col);
+      WidenPack<kVec>(first, nshift);
+#pragma unroll
+      for (int q = 0; q < kPairs; ++q) nshift[q] = Neg2(nshift[q]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < kPairs; ++q) {
+        nshift[q] = make_float2(-a.app.mean[col * kVec + 2 * q],
+                                -a.app.mean[col * kVec + 2 * q + 1]);
+      }
+    }
+    const P* xi = xbase;
+    const P* di = dbase;
+    int j_issue = 0;
+    auto issue = [&](int ring_batch) {
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        if (j_issue + u < n_j) {
+          CpAsync16(my + ((ring_batch * kStreams + 0) * kU + u) * kThreads,
+                    xi + u * row_stride);
+          if constexpr (kMode == kGrad) {
+            CpAsync16(my + ((ring_batch * kStreams + 1) * kU + u) * kThreads,
+                      di + u * row_stride);
+          }
+        }
+      }
+      xi += kU * row_stride;
+      di += kU * row_stride;
+      j_issue += kU;
+      CpAsyncCommit();
+    };
+#pragma unroll
+    for (int b = 0; b < kAhead; ++b) issue(b);
+    int j_done = 0;
+    for (int bi = 0; bi < n_b; bi += kRB) {
+#pragma unroll
+      for (int sg = 0; sg < kRB; ++sg) {
+        if (bi + sg < n_b) {
+          issue((sg + kAhead) % kRB);
+          CpAsyncWait<kAhead>();
+#pragma unroll
+          for (int u = 0; u < kU; ++u) {
+            if (j_done + u < n_j) {
+              const uint4 rx = my[((sg * kStreams + 0) * kU + u) * kThreads];
+              float2 xv[kPairs], gv[kPairs];
+              WidenPack<kVec>(*reinterpret_cast<const P*>(&rx), xv);
+              if constexpr (kMode == kGrad) {
+                const uint4 rd = my[((sg * kStreams + 1) * kU + u) * kThreads];
+                WidenPack<kVec>(*reinterpret_cast<const P*>(&rd), gv);
+              }
+#pragma unroll
+              for (int q = 0; q < kPairs; ++q) {
+                const float2 d = Add2(xv[q], nshift[q]);
+                if constexpr (kMode == kFwd) {
+                  a1[q] = Add2(a1[q], d);
+                  a2[q] = Fma2(d, d, a2[q]);
+                } else {
+                  a1[q] = Add2(a1[q], gv[q]);
+                  a2[q] = Fma2(gv[q], d, a2[q]);
+                }
+              }
+            }
+          }
+          j_done += kU;
+        }
+      }
+    }
+  }
+  CpAsyncWait<0>();
+
+  // ---- B: fold the row lanes, one sum at a time (8 KB of scratch).
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kPairs; ++q) {
+      const float2 v = which == 0 ? a1[q] : a2[q];
+      scratch[((2 * q) * TY + ty) * TX + tx] = v.x;
+      scratch[((2 * q + 1) * TY + ty) * TX + tx] = v.y;
+    }
+    __syncthreads();
+    for (int o = tid; o < kVec * TX; o += kThreads) {
+      const int otx = o % TX, e = o / TX;
+      float acc = 0.0f;
+      for (int j = 0; j < TY; ++j) acc += scratch[(e * TY + j) * TX + otx];
+      if (otx < cv) {
+        a.partial[(static_cast<int64_t>(blockIdx.y) * 2 + which) * channels +
+                  static_cast<int64_t>(otx) * kVec + e] = acc;
+      }
+    }
+  }
+
+  const unsigned G = gridDim.y;
+  if (!GridBarrier(a.barrier, G, a.status)) return;
+
+  // ---- C: CTA b owns channels b, b + G, ...: all partial rows, fp64.
+  {
+    double* red = reinterpret_cast<double*>(scratch);  // [2][8 warps]
+    for (int64_t c = blockIdx.y; c < channels; c += G) {
+      double t1 = 0.0, t2 = 0.0;
+      for (unsigned p = tid; p < G; p += kThreads) {
+        t1 += static_cast<double>(__ldcg(a.partial + (static_cast<int64_t>(p) * 2 + 0) * channels + c));
+        t2 += static_cast<double>(__ldcg(a.partial + (static_cast<int64_t>(p) * 2 + 1) * channels + c));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        t1 += __shfl_xor_sync(0xffffffffu, t1, o);
+        t2 += __shfl_xor_sync(0xffffffffu, t2, o);
+      }
+      __syncthreads();
+      if ((tid & 31) == 0) {
+        red[tid >> 5] = t1;
+        red[8 + (tid >> 5)] = t2;
+      }
+      __syncthreads();
+      if (tid == 0) {
+        double S1 = 0.0, S2 = 0.0;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+          S1 += red[w];
+          S2 += red[8 + w];
+        }
+        if constexpr (kMode == kFwd) {
+          const double K = static_cast<double>(
+              LoadAsF32(a.fin.x_first, a.fin.x_dtype, c * a.fin.shift_stride));
+          const double md = S1 * a.fin.inv_count;
+          WriteFwdStats(a.fin, c, K + md, S2 * a.fin.inv_count - md * md);
+        } else {
+          a.fin.sums[c] = static_cast<float>(S1);
+          a.fin.sums[channels + c] = static_cast<float>(S2);
+          a.fin.doffset[c] = static_cast<float>(S1);
+          const float inv = 1.0f / sqrtf(a.fin.variance[c] + a.fin.epsilon);
+          a.fin.dscale[c] = static_cast<float>(S2) * inv;
+        }
+      }
+    }
+  }
+
+  if (!GridBarrier(a.barrier, 2 * G, a.status)) return;
+  if (!active) return;
+
+  // ---- D: per-channel coefficients (values written by other CTAs during this
+  // launch are read past L1).
+  float mean[kVec], ca[kVec], cb[kVec], cc[kVec];
+  constexpr bool kFold = sizeof(T) == 2;
+#pragma unroll
+  for (int e = 0; e < kVec; ++e) {
+    const int64_t c = col * kVec + e;
+    float var_c;
+    if constexpr (kMode == kFwd) {
+      mean[e] = __ldcg(a.fin.saved_mean + c);
+      var_c = __ldcg(a.fin.saved_var + c);
+    } else {
+      mean[e] = a.app.mean[c];
+      var_c = a.app.variance[c];
+    }
+    const float inv = 1.0f / sqrtf(var_c + a.app.epsilon);
+    ca[e] = a.app.scale[c] * inv;
+    if constexpr (kMode == kFwd) {
+      cb[e] = a.app.offset[c];
+      cc[e] = 0.0f;
+    } else if (a.is_training) {
+      cb[e] = __ldcg(a.fin.sums + c) * a.app.inv_count;
+      cc[e] = __ldcg(a.fin.sums + channels + c) * inv * inv * a.app.inv_count;
+    } else {
+      cb[e] = 0.0f;
+      cc[e] = 0.0f;
+    }
+    if constexpr (kFold) {
+      if constexpr (kMode == kFwd) {
+        cb[e] = fmaf(-mean[e], ca[e], cb[e]);
+      } else {
+        const float fb = -ca[e] * cc[e];
+        const float fc = ca[e] * fmaf(cc[e], mean[e], -cb[e]);
+        cb[e] = fb;
+        cc[e] = fc;
+      }
+    }
+  }
+  auto transform = [&](const P& px, const P& pd) -> P {
+    float2 xv[kPairs], gv[kPairs], rv[kPairs];
+    WidenPack<kVec>(px, xv);
+    if constexpr (kMode == kGrad) WidenPack<kVec>(pd, gv);
+#pragma unroll
+    for (int q = 0; q < kPairs; ++q) {
+      const float2 A = make_float2(ca[2 * q], ca[2 * q + 1]);
+      const float2 B = make_float2(cb[2 * q], cb[2 * q + 1]);
+      const float2 C = make_float2(cc[2 * q], cc[2 * q + 1]);
+      if constexpr (kFold) {
+        if constexpr (kMode == kFwd) {
+          rv[q] = Fma2(xv[q], A, B);
+        } else {
+          rv[q] = Fma2(gv[q], A, Fma2(xv[q], B, C));
+        }
+      } else {
+        const float2 d = Add2(xv[q], make_float2(-mean[2 * q], -mean[2 * q + 1]));
+        if constexpr (kMode == kFwd) {
+          rv[q] = Fma2(d, A, B);
+        } else {
+          rv[q] = Mul2(A, Fma2(Neg2(d), C, Add2(gv[q], Neg2(B))));
+        }
+      }
+    }
+    P o;
+    NarrowPack<kVec>(rv, o);
+    return o;
+  };
+
+  // ---- E1: the rows still in the ring (batch bi sits in ring slot bi % kRB).
+  const int first_resident_b = n_b > kRB ? n_b - kRB : 0;
+  for (int bi = n_b - 1; bi >= first_resident_b; --bi) {
+    const int rb = bi % kRB;
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int j = bi * kU + u;
+      if (j < n_j) {
+        const uint4 rx = my[((rb * kStreams + 0) * kU + u) * kThreads];
+        uint4 rd = rx;
+        if constexpr (kMode == kGrad) rd = my[((rb * kStreams + 1) * kU + u) * kThreads];
+        const P o = transform(*reinterpret_cast<const P*>(&rx),
+                              *reinterpret_cast<const P*>(&rd));
+        StoreStream(obase + static_cast<int64_t>(j) * row_stride, o);
+      }
+    }
+  }
+  // ---- E2: the older rows, newest first, four loads per stream in flight.
+  constexpr int kUnroll = 4;
+  for (int j0 = first_resident_b * kU - 1; j0 >= 0; j0 -= kUnroll) {
+    P px[kUnroll], pd[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int j = j0 - u;
+      if (j >= 0) {
+        px[u] = LoadKeep(xbase + static_cast<int64_t>(j) * row_stride);
+        if constexpr (kMode == kGrad) {
+          pd[u] = LoadKeep(dbase + static_cast<int64_t>(j) * row_stride);
+        } else {
+          pd[u] = px[u];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int j = j0 - u;
+      if (j >= 0) {
+        StoreStream(obase + static_cast<int64_t>(j) * row_stride, transform(px[u], pd[u]));
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------ host side --
 
 template <typename T>
@@ -984,12 +1365,92 @@ inline bool IsEmpty(const Geom& g) {
   return g.outer == 0 || g.channels == 0 || g.inner == 0;
 }
 
+// Workspace layout: [partial rows: MaxSplits * 2 * C floats][totals: 2 * C
+// floats][control block: grid-barrier counter, status word; 256 bytes].
+constexpr size_t kControlBytes = 256;
+
+inline int64_t ControlOffsetFloats(const Geom& g) {
+  const int64_t floats =
+      MaxSplits(g.outer, g.channels) * 2 * g.channels + 2 * g.channels;
+  return (floats + 63) / 64 * 64;  // 256-byte aligned
+}
+
 inline size_t WorkspaceBytes(const Geom& g) {
   if (IsEmpty(g)) return 0;
-  const int64_t floats =
-      MaxSplits(g.outer, g.channels) * 2 * g.channels +
-      2 * g.channels;
-  return static_cast<size_t>(floats) * sizeof(float);
+  return static_cast<size_t>(ControlOffsetFloats(g)) * sizeof(float) + kControlBytes;
+}
+
+// The whole op in one cooperative launch, when the geometry allows it:
+// channels-last, 128-bit packs, one column block.  Returns false when the
+// caller should take the three-kernel chain instead.
+template <typename T, int kMode>
+bool LaunchFused(const T* x, const T* dy, T* out, const FinalizeArgs& fin,
+                 const ApplyArgs& app, bool is_training, float* workspace,
+                 const Geom& g, cudaStream_t stream) {
+  constexpr int kVec = VecWidth<T>::value;
+  using Cfg = FusedCfg<kMode>;
+  if (GetTuning(kTuneBnFused) == 0 || g.inner != 1 || g.channels % kVec != 0) {
+    return false;
+  }
+  const int64_t cv = g.channels / kVec;
+  if (cv > kThreads) return false;
+  if (!Aligned16(x) || !Aligned16(out) || (kMode == kGrad && !Aligned16(dy))) {
+    return false;
+  }
+  auto kernel = BnFusedKernel<T, kMode>;
+  static const int resident = [&] {
+    int dev = 0, coop = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    if (coop == 0) return 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+    int n = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, Cfg::kSmemBytes);
+    return n;
+  }();
+  if (resident <= 0) return false;
+  const Plan p = PlanLast(g.outer, g.channels, cv, Cfg::kU, true, resident);
+  if (p.gx != 1 || p.gy > SmCount() * resident) return false;
+  FusedArgs a{};
+  a.x = x;
+  a.dy = dy;
+  a.out = out;
+  a.rows = g.outer;
+  a.cv = cv;
+  a.channels = g.channels;
+  a.rows_per_cta = p.rows_per_cta;
+  a.partial = workspace;
+  char* control = reinterpret_cast<char*>(workspace + ControlOffsetFloats(g));
+  a.barrier = reinterpret_cast<unsigned*>(control);
+  a.status = reinterpret_cast<int*>(control + 64);
+  a.fin = fin;
+  a.app = app;
+  a.is_training = is_training;
+  // The counter starts every launch at zero; the status word is sticky (a
+  // caller reads and clears it with BnWorkspaceStatus).
+  if (cudaMemsetAsync(a.barrier, 0, sizeof(unsigned), stream) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, p.gy);
+  cfg.blockDim = dim3(p.tx, p.ty);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, a) != cudaSuccess) {
+    cudaGetLastError();
+    return false;  // e.g. the grid does not fit beside other resident work
+  }
+  return true;
 }
 
 template <typename T, int kMode, int kStagesT>
@@ -1176,11 +1637,8 @@ int FwdTrain(const void* x, const float* scale, const float* offset,
   }
   float* partial = static_cast<float*>(workspace);
   const T* xt = static_cast<const T*>(x);
-  const int splits = LaunchStats<T, kFwd>(xt, nullptr, nullptr, partial, g, stream);
-  if (splits < 0) return splits;
   FinalizeArgs f{};
   f.partial = partial;
-  f.splits = splits;
   f.channels = channels;
   SetCount(&f, static_cast<double>(g.rows()));
   f.x_first = x;
@@ -1193,13 +1651,20 @@ int FwdTrain(const void* x, const float* scale, const float* offset,
   f.saved_mean = saved_mean;
   f.saved_var = saved_var;
   f.exp_avg_factor = exp_avg_factor;
-  LaunchFinalize<0>(f, stream);
   ApplyArgs a{};
   a.scale = scale;
   a.offset = offset;
   a.mean = saved_mean;
   a.variance = saved_var;
   a.epsilon = epsilon;
+  if (LaunchFused<T, kFwd>(xt, nullptr, static_cast<T*>(y), f, a, true, partial, g,
+                           stream)) {
+    return LastError();
+  }
+  const int splits = LaunchStats<T, kFwd>(xt, nullptr, nullptr, partial, g, stream);
+  if (splits < 0) return splits;
+  f.splits = splits;
+  LaunchFinalize<0>(f, stream);
   LaunchApply<T, kFwd>(xt, nullptr, static_cast<T*>(y), a, g, stream);
   return LastError();
 }
@@ -1246,11 +1711,8 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
   float* sums = partial + MaxSplits(g.outer, g.channels) * 2 * g.channels;
   const T* xt = static_cast<const T*>(x);
   const T* dyt = static_cast<const T*>(dy);
-  const int splits = LaunchStats<T, kGrad>(xt, dyt, mean, partial, g, stream);
-  if (splits < 0) return splits;
   FinalizeArgs f{};
   f.partial = partial;
-  f.splits = splits;
   f.channels = channels;
   SetCount(&f, static_cast<double>(g.rows()));
   f.variance = variance;
@@ -1258,7 +1720,6 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
   f.doffset = doffset;
   f.epsilon = epsilon;
   f.sums = sums;
-  LaunchFinalize<2>(f, stream);
   ApplyArgs a{};
   a.scale = scale;
   a.mean = mean;
@@ -1266,6 +1727,14 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
   a.epsilon = epsilon;
   a.sums = is_training ? sums : nullptr;
   a.inv_count = static_cast<float>(1.0 / static_cast<double>(g.rows()));
+  if (LaunchFused<T, kGrad>(xt, dyt, static_cast<T*>(dx), f, a, is_training, partial,
+                            g, stream)) {
+    return LastError();
+  }
+  const int splits = LaunchStats<T, kGrad>(xt, dyt, mean, partial, g, stream);
+  if (splits < 0) return splits;
+  f.splits = splits;
+  LaunchFinalize<2>(f, stream);
   LaunchApply<T, kGrad>(xt, dyt, static_cast<T*>(dx), a, g, stream);
   return LastError();
 }
@@ -1361,7 +1830,7 @@ int GradApplyFromSums(const void* dy, const void* x, const float* scale,
 // with cudaGetSymbolAddress, once per device, with that device current.
 constexpr int64_t kStaticScratchMaxChannels = 8192;
 constexpr size_t kStaticScratchBytes =
-    sizeof(float) * (kMaxPartialFloats + 2 * kStaticScratchMaxChannels);
+    sizeof(float) * (kMaxPartialFloats + 2 * kStaticScratchMaxChannels) + 512;
 static __device__ __align__(256) unsigned char
     g_bn_static_scratch[kStaticScratchBytes];
 
@@ -1455,6 +1924,24 @@ MUSA_DEFINE_BN(F32, float)
 MUSA_DEFINE_BN(F16, __half)
 MUSA_DEFINE_BN(BF16, __nv_bfloat16)
 #undef MUSA_DEFINE_BN
+
+int BnWorkspaceStatus(void* workspace, int64_t outer, int64_t channels,
+                      int64_t inner) {
+  const Geom g{outer, channels, inner};
+  if (workspace == nullptr || CheckGeom(g) != MUSA_KERNELS_OK || IsEmpty(g)) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  char* control = reinterpret_cast<char*>(static_cast<float*>(workspace) +
+                                          ControlOffsetFloats(g));
+  int status = 0;
+  if (cudaMemcpy(&status, control + 64, sizeof(int), cudaMemcpyDeviceToHost) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return -100;
+  }
+  if (status != 0) cudaMemset(control + 64, 0, sizeof(int));
+  return status;
+}
 
 size_t BnNoAllocMaxChannels(void) {
   return static_cast<size_t>(kStaticScratchMaxChannels);

@@ -11,7 +11,7 @@ enum TuningKey {
   kTuneBiasActCtasPerSm = 2,
   kTuneBiasActUnroll = 3,
   kTuneBnCtasPerSm = 4,     // CTAs per SM of the BatchNorm grids; 0: what fits
-  kTuneBnFused = 5,         // 1: single cooperative kernel when it applies
+  kTuneBnFused = 5,         // 1: one cooperative launch per op (measured slower: off)
   kTuneBnApplyReverse = 6,  // 1: apply pass walks rows in reverse (L2 reuse)
   kTuneBnStatsKeep = 7,     // 1: stats pass loads with the default L2 policy
   kTuneBnStatsPipe = 8,     // cp.async stages of the stats kernel (3 or 4); 0: register loads

@@ -237,6 +237,27 @@ def test_host_buffers_round_trip(kernel_lib):
     check_forward(got, np_ref.fused_batch_norm(x, s, o, epsilon=EPS), "bfloat16")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,c", [(2, 8), (33, 64), (5000, 256), (70000, 128)])
+def test_single_launch_variant(kernel_lib, dtype, rows, c):
+    """The one-cooperative-launch form of the two ops (off by default) returns
+    what the kernel chain returns, and none of its bounded waits runs out."""
+    x, s, o, dy = bn_inputs(300 + rows, (rows, c), dtype, 1.0, 3.0)
+    want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
+    wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS)
+    old = kernel_lib.MusaKernelsSetTuning(5, 1)
+    try:
+        fwd, grad = run_both(x, s, o, dy, "NHWC")
+        torch.cuda.synchronize()
+        ws = raw_ops._workspace(kernel_lib.BnWorkspaceBytes(rows, c, 1), torch.device("cuda", 0))
+        assert kernel_lib.BnWorkspaceStatus(ws.data_ptr(), rows, c, 1) == 0
+    finally:
+        kernel_lib.MusaKernelsSetTuning(5, old)
+    check_forward(fwd, want, dtype)
+    terms = _rms(dy) * float(np.max(s / np.sqrt(want[4] + EPS)))
+    check_grad(grad, wg, dtype, dx_scale=terms)
+
+
 # ------------------------------------------------ cross-replica (split) API --
 
 def _split_forward_and_grad(lib, x, dy, scale, offset, parts, fused=False):
