@@ -371,9 +371,12 @@ def run_ours(args):
         result["cpu_baseline"] = None if args.skip_cpu else \
             cpu_baseline(budget_s=args.cpu_seconds)
     else:
+        adam = None if args.skip_ops else \
+            measure_adam_sharded(torch, dist, world, rank, dev, exchange, args)
         if rank == 0:
             result["roofline"] = None
             result["cpu_baseline"] = None
+            result["adam_sharded"] = adam
     if rank == 0:
         print(json.dumps(result), flush=True)
     finish(torch, dist, world)
@@ -438,6 +441,91 @@ def measure_e2e(torch, dist, raw_ops, layers, world, rank, dev, args):
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
             "ms_per_step": round(dt / steps * 1e3, 2),
             "api": ("raw_ops.FusedBatchNormV3 / FusedBatchNormGradV3" if world == 1 else "cross_replica.sync_batch_norm_forward / _backward") + " on pinned host tensors"}
+
+
+def measure_adam_sharded(torch, dist, world, rank, dev, exchange, args):
+    """ResourceApplyAdam over the 25,557,032-parameter vector, sharded by
+    contiguous range over the replicas, two ways: update + NCCL all-gather of
+    the updated weights, and the fused update-and-broadcast kernel (peer
+    stores) + one-float exchange.  Strong scaling: the vector is fixed."""
+    from tensorflow_musa_extension_b200 import cross_replica as cr
+    n = 25_557_032
+    peak, _ = measured_peak()
+    nvlink_gbs = 770.0   # measured peer-copy bandwidth per direction on this pool
+    hyper = dict(lr=1e-3, b1p=0.9 ** 10, b2p=0.999 ** 10)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+    out = {}
+
+    def timed(step_fn, label):
+        for _ in range(5):
+            step_fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 50
+        a.record()
+        for _ in range(iters):
+            step_fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        hbm = 28.0 * n / world
+        link = 4.0 * n / world * (world - 1)
+        bound_ms = max(hbm / (peak * 1e9), link / (nvlink_gbs * 1e9)) * 1e3
+        out[label] = {"ms_per_step": round(ms, 4), "gelem_per_s": round(n / (ms * 1e-3) / 1e9, 2),
+                      "hbm_bytes_per_gpu": int(hbm), "nvlink_bytes_out_per_gpu": int(link),
+                      "bound_ms": round(bound_ms, 4), "frac_of_bound": round(bound_ms / ms, 3)}
+
+    # (a) update, then NCCL all-gather in place
+    var = torch.empty(n, device=dev).normal_(0, 0.05, generator=gen)
+    opt = cr.ShardedAdam(var, dist.group.WORLD)
+    shard = opt.hi - opt.lo
+    grads = [torch.empty(max(shard, 1), device=dev).normal_(0, 1e-3, generator=gen)
+             for _ in range(4)]
+    k = [0]
+
+    def step_nccl():
+        k[0] += 1
+        opt.step(grads[k[0] % 4][:shard], hyper["lr"], hyper["b1p"], hyper["b2p"])
+
+    timed(step_nccl, "update_then_nccl_all_gather")
+    del opt, var
+
+    # (b) fused update + broadcast over peer memory
+    if exchange is not None:
+        try:
+            pv = cr.PeerVector(dist.group.WORLD, n, dev)
+            pv.tensor.normal_(0, 0.05, generator=gen)
+            fopt = cr.FusedShardedAdam(pv, exchange)
+            fshard = fopt.hi - fopt.lo
+            fgrads = [torch.empty(max(fshard, 1), device=dev).normal_(0, 1e-3, generator=gen)
+                      for _ in range(4)]
+
+            def step_peer():
+                k[0] += 1
+                fopt.step(fgrads[k[0] % 4][:fshard], hyper["lr"], hyper["b1p"], hyper["b2p"])
+
+            timed(step_peer, "fused_update_and_peer_broadcast")
+            st = exchange.status()
+            if st != 0:
+                out["fused_update_and_peer_broadcast"]["error"] = "wait for replica %d ran out" % (st - 1)
+            # every replica must hold the same vector
+            check = pv.tensor[::4099].double().sum().reshape(1)
+            lo_hi = check.clone()
+            dist.all_reduce(lo_hi, op=dist.ReduceOp.MAX)
+            out["fused_update_and_peer_broadcast"]["replicas_identical"] = bool(
+                (lo_hi == check).all().item())
+            torch.cuda.synchronize()
+            dist.barrier()
+            pv.close()
+        except Exception as e:  # noqa: BLE001
+            out["fused_update_and_peer_broadcast"] = {"unavailable": repr(e)}
+    out["config"] = "ResourceApplyAdam fp32, 25,557,032 parameters, contiguous ranges, strong scaling"
+    return out
 
 
 def time_launch(torch, fn, iters, flush=None):

@@ -354,6 +354,30 @@ int MusaExchangeOpenPeers(void* handle, const void* handles);
 int LaunchExchangeSums(void* handle, float* vector, int64_t n, cudaStream_t stream);
 int MusaExchangeStatus(void* handle);
 void MusaExchangeDestroy(void* handle);
+/* Peer-visible device memory for the set-up of the two peer-memory paths: a
+ * cudaMalloc block, its 64-byte CUDA IPC handle, and the mapping of another
+ * process's handle (all ranks on one node).  Set-up time only. */
+void* MusaPeerAlloc(int64_t bytes);
+int MusaPeerFree(void* ptr);
+int MusaPeerIpcHandle(void* ptr, void* out64);
+void* MusaPeerOpen(const void* handle64);
+int MusaPeerClose(void* mapped);
+
+/* Range-sharded ResourceApplyAdam (fp32) fused with the all-gather of the
+ * updated weights: updates var[lo, lo + n) from this replica's m, v (n
+ * elements each) and grad (the n elements of its range) and stores every new
+ * value into [lo, lo + n) of ALL `world` replicas' var (`var_replicas[q]`:
+ * base of replica q's copy as mapped in this process; entry `rank` is the
+ * local one), over NVLink peer stores.  The update arithmetic is
+ * LaunchResourceApplyAdamFloat's.  The peers may read their var only after
+ * they have learnt that this launch completed (an exchange of one float with
+ * LaunchExchangeSums after it does that).  128-bit path when lo % 4 == 0 and
+ * all pointers are 16-byte aligned.  No counterpart in the reference. */
+int LaunchAdamShardBroadcastFloat(float* const* var_replicas, int world, int rank,
+                                  int64_t lo, float* m, float* v, const float* grad,
+                                  float beta1, float beta2, float epsilon, float alpha,
+                                  int64_t n, cudaStream_t stream);
+
 /* Test hook: `world` (<= 8) replicas emulated on one GPU by one cooperative
  * launch of `world` CTAs; `vectors` is a device array of `world` device
  * pointers to n floats each.  missing_rank = world - 1 leaves that replica out

@@ -360,3 +360,121 @@ class ShardedAdam:
             dist.all_gather_into_tensor(self._padded, shard, group=self.group)
             self.var.copy_(self._padded[:self.n])
         return self.var
+
+
+def aligned_shard_range(n, world, rank, align=4):
+    """Like shard_range, with range starts on a multiple of `align` elements
+    (so that a shard of an aligned vector can take 128-bit accesses)."""
+    per = -(-n // world)
+    per = -(-per // align) * align
+    lo = min(n, rank * per)
+    hi = min(n, lo + per)
+    return lo, hi
+
+
+class PeerVector:
+    """A flat fp32 vector that exists once per replica, each copy in device
+    memory that the other replicas of the node can write: the parameter vector
+    of FusedShardedAdam.  `tensor` is the local copy; `replica_ptrs[q]` is the
+    address of replica q's copy as mapped in this process."""
+
+    def __init__(self, group, n, device):
+        import ctypes
+        self.lib = raw_ops._lib()
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.n = int(n)
+        self._opened = []
+        with torch.cuda.device(device):
+            self.ptr = self.lib.MusaPeerAlloc(self.n * 4)
+            ok = self.ptr is not None
+            raw = ctypes.create_string_buffer(64)
+            if ok:
+                ok = self.lib.MusaPeerIpcHandle(self.ptr, raw) == 0
+            handles = [raw.raw if ok else None]
+            if self.world > 1:
+                handles = [None] * self.world
+                dist.all_gather_object(handles, raw.raw if ok else None, group=group)
+            self.replica_ptrs = [None] * self.world
+            if ok and all(h is not None for h in handles):
+                for q, h in enumerate(handles):
+                    if q == self.rank:
+                        self.replica_ptrs[q] = self.ptr
+                    else:
+                        mapped = self.lib.MusaPeerOpen(h)
+                        if mapped is None:
+                            ok = False
+                            break
+                        self._opened.append(mapped)
+                        self.replica_ptrs[q] = mapped
+            else:
+                ok = False
+            flags = [bool(ok)]
+            if self.world > 1:
+                flags = [None] * self.world
+                dist.all_gather_object(flags, bool(ok), group=group)
+        if not all(flags):
+            self.close()
+            raise RuntimeError("peer-visible memory is not available between these GPUs")
+
+        class _View:
+            pass
+
+        view = _View()
+        view.__cuda_array_interface__ = {"shape": (self.n,), "typestr": "<f4",
+                                         "data": (int(self.ptr), False), "version": 2}
+        self._view = view
+        self.tensor = torch.as_tensor(view, device=device)
+
+    def close(self):
+        for m in getattr(self, "_opened", []):
+            self.lib.MusaPeerClose(m)
+        self._opened = []
+        if getattr(self, "ptr", None) is not None:
+            self.tensor = None
+            self.lib.MusaPeerFree(self.ptr)
+            self.ptr = None
+
+
+class FusedShardedAdam:
+    """Range-sharded ResourceApplyAdam whose update kernel is also the
+    all-gather: each replica updates its range and stores the new weights into
+    that range of every replica's vector over NVLink
+    (LaunchAdamShardBroadcastFloat), then the replicas exchange one float with
+    the peer-memory kernel, after which every copy is complete.  `var` is a
+    PeerVector; m and v exist only for the local range."""
+
+    def __init__(self, var, exchange, beta1=0.9, beta2=0.999, epsilon=1e-7):
+        import ctypes
+        self.var = var
+        self.exchange = exchange
+        self.world, self.rank, self.n = var.world, var.rank, var.n
+        self.lo, self.hi = aligned_shard_range(self.n, self.world, self.rank)
+        dev = var.tensor.device
+        self.m = torch.zeros(self.hi - self.lo, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(self.hi - self.lo, dtype=torch.float32, device=dev)
+        self.beta1, self.beta2, self.epsilon = beta1, beta2, epsilon
+        self._ptrs = (ctypes.c_void_p * self.world)(*var.replica_ptrs)
+        self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.lib = raw_ops._lib()
+
+    def step(self, grad, lr, beta1_power, beta2_power):
+        """`grad`: the full gradient vector or this replica's range of it."""
+        if grad.numel() == self.n:
+            grad = grad[self.lo:self.hi]
+        elif grad.numel() != self.hi - self.lo:
+            raise InvalidArgumentError(
+                "FusedShardedAdam: grad has %d elements, expected %d or %d"
+                % (grad.numel(), self.n, self.hi - self.lo))
+        f32 = np.float32
+        alpha = raw_ops._adam_alpha(float(f32(lr)), float(f32(beta1_power)),
+                                    float(f32(beta2_power)))
+        st = torch.cuda.current_stream().cuda_stream
+        raw_ops._check(self.lib.LaunchAdamShardBroadcastFloat(
+            self._ptrs, self.world, self.rank, self.lo, self.m.data_ptr(), self.v.data_ptr(),
+            grad.data_ptr(), float(f32(self.beta1)), float(f32(self.beta2)),
+            float(f32(self.epsilon)), alpha, self.hi - self.lo, st),
+            "LaunchAdamShardBroadcastFloat")
+        if self.exchange is not None and self.world > 1:
+            self.exchange.sum_(self._token)  # all ranges have landed everywhere
+        return self.var.tensor

@@ -25,13 +25,19 @@ struct AdamParams {
 template <bool kNesterov>
 __device__ __forceinline__ void AdamStep(float& var, float& m, float& v,
                                          float g, const AdamParams& p) {
-  const float m_new = p.beta1 * m + p.one_minus_b1 * g;
-  const float v_new = p.beta2 * v + p.one_minus_b2 * g * g;
+  // Every rounding is spelled out (one fused multiply-add per moment, IEEE
+  // multiply / sqrt / divide / subtract elsewhere) so that all kernels built
+  // from this function - vector, element-wise, sharded, broadcasting - return
+  // the same bits; left to the compiler, the contraction of a*b + c*d differs
+  // from one instantiation to the next by an ulp.
+  const float m_new = fmaf(p.beta1, m, __fmul_rn(p.one_minus_b1, g));
+  const float v_new = fmaf(p.beta2, v, __fmul_rn(__fmul_rn(p.one_minus_b2, g), g));
   const float numer =
-      kNesterov ? (p.beta1 * m_new + p.one_minus_b1 * g) : m_new;
+      kNesterov ? fmaf(p.beta1, m_new, __fmul_rn(p.one_minus_b1, g)) : m_new;
   m = m_new;
   v = v_new;
-  var = var - p.lr_t * numer / (sqrtf(v_new) + p.epsilon);
+  var = __fsub_rn(var, __fdiv_rn(__fmul_rn(p.lr_t, numer),
+                                 __fadd_rn(__fsqrt_rn(v_new), p.epsilon)));
 }
 
 // Each thread owns kUnroll packs of kEpt elements per tile; a tile is
@@ -172,6 +178,76 @@ void LaunchAdam(StateT* var, StateT* m, StateT* v, const GradT* grad,
   }
 }
 
+// ---- Range-sharded Adam whose update IS the all-gather: a replica updates
+// its range [lo, lo + n) of the parameter vector and stores every new value
+// into that range of EVERY replica's copy (its own and, over NVLink, the
+// peers'), so no separate collective re-reads and re-sends the shard.
+struct Replicas {
+  float* var[16];
+  int world;
+  int rank;
+};
+
+template <int kEpt>
+__global__ void __launch_bounds__(256)
+    AdamShardBroadcastKernel(Replicas r, int64_t lo, float* __restrict__ m,
+                             float* __restrict__ v, const float* __restrict__ grad,
+                             AdamParams p, int64_t n) {
+  GridDepWait();
+  GridDepLaunch();
+  using SPack = Pack<float, kEpt>;
+  constexpr int kUnroll = 2;
+  const int64_t n_packs = n / kEpt;
+  const int64_t tile = static_cast<int64_t>(blockDim.x) * kUnroll;
+  const int64_t n_tiles = (n_packs + tile - 1) / tile;
+  const SPack* var_p = reinterpret_cast<const SPack*>(r.var[r.rank] + lo);
+  SPack* m_p = reinterpret_cast<SPack*>(m);
+  SPack* v_p = reinterpret_cast<SPack*>(v);
+  const SPack* g_p = reinterpret_cast<const SPack*>(grad);
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int64_t base = t * tile + threadIdx.x;
+    SPack pv[kUnroll], pm[kUnroll], pvv[kUnroll], pg[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+      if (i < n_packs) {
+        pg[u] = LoadStream(g_p + i);
+        pm[u] = LoadStream(m_p + i);
+        pvv[u] = LoadStream(v_p + i);
+        pv[u] = LoadStream(var_p + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+      if (i < n_packs) {
+#pragma unroll
+        for (int e = 0; e < kEpt; ++e) {
+          AdamStep<false>(pv[u].v[e], pm[u].v[e], pvv[u].v[e], pg[u].v[e], p);
+        }
+        StoreStream(m_p + i, pm[u]);
+        StoreStream(v_p + i, pvv[u]);
+        // Own copy first, then the peers, each replica starting at a
+        // different peer so that the links load evenly.
+        for (int k = 0; k < r.world; ++k) {
+          const int q = (r.rank + k) % r.world;
+          reinterpret_cast<SPack*>(r.var[q] + lo)[i] = pv[u];
+        }
+      }
+    }
+  }
+  if (kEpt > 1 && blockIdx.x == 0) {
+    const int64_t i = n_packs * kEpt + threadIdx.x;
+    if (threadIdx.x < kEpt && i < n) {
+      float fvar = r.var[r.rank][lo + i], fm = m[i], fv = v[i];
+      AdamStep<false>(fvar, fm, fv, grad[i], p);
+      m[i] = fm;
+      v[i] = fv;
+      for (int q = 0; q < r.world; ++q) r.var[q][lo + i] = fvar;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace musa_b200
 
@@ -205,6 +281,46 @@ void LaunchApplyAdamSameType_Half(void* var, void* m, void* v, const void* grad,
                              static_cast<__half*>(v),
                              static_cast<const __half*>(grad), lr_t, beta1,
                              beta2, epsilon, n, use_nesterov, stream);
+}
+
+int LaunchAdamShardBroadcastFloat(float* const* var_replicas, int world, int rank,
+                                  int64_t lo, float* m, float* v, const float* grad,
+                                  float beta1, float beta2, float epsilon, float alpha,
+                                  int64_t n, cudaStream_t stream) {
+  if (var_replicas == nullptr || world < 1 || world > 16 || rank < 0 || rank >= world ||
+      lo < 0 || n < 0) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  if (n == 0) return MUSA_KERNELS_OK;
+  if (m == nullptr || v == nullptr || grad == nullptr) return MUSA_KERNELS_EINVAL;
+  Replicas r{};
+  r.world = world;
+  r.rank = rank;
+  bool vec = (lo % 4 == 0) && Aligned16(m) && Aligned16(v) && Aligned16(grad);
+  for (int q = 0; q < world; ++q) {
+    if (var_replicas[q] == nullptr) return MUSA_KERNELS_EINVAL;
+    r.var[q] = var_replicas[q];
+    vec = vec && Aligned16(var_replicas[q]);
+  }
+  AdamParams p;
+  p.lr_t = alpha;
+  p.beta1 = beta1;
+  p.one_minus_b1 = 1.0f - beta1;
+  p.beta2 = beta2;
+  p.one_minus_b2 = 1.0f - beta2;
+  p.epsilon = epsilon;
+  const int64_t packs = vec ? n / 4 : n;
+  int64_t blocks = CeilDiv(packs, 256 * 2);
+  if (blocks < 1) blocks = 1;
+  if (blocks > 0x7fffffffLL) blocks = 0x7fffffffLL;
+  if (vec) {
+    LaunchChained(true, AdamShardBroadcastKernel<4>, dim3(static_cast<unsigned>(blocks)),
+                  dim3(256), 0, stream, r, lo, m, v, grad, p, n);
+  } else {
+    LaunchChained(true, AdamShardBroadcastKernel<1>, dim3(static_cast<unsigned>(blocks)),
+                  dim3(256), 0, stream, r, lo, m, v, grad, p, n);
+  }
+  return static_cast<int>(cudaGetLastError());
 }
 
 void LaunchApplyAdamMixed_Float(float* var, float* m, float* v,

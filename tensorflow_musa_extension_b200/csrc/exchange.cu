@@ -251,6 +251,50 @@ void MusaExchangeDestroy(void* handle) {
   delete h;
 }
 
+// ---- Peer-visible device memory: plain cudaMalloc blocks whose CUDA IPC
+// handle other processes of the node can open (set-up time only).
+void* MusaPeerAlloc(int64_t bytes) {
+  if (bytes <= 0) return nullptr;
+  void* p = nullptr;
+  if (cudaMalloc(&p, static_cast<size_t>(bytes)) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+
+int MusaPeerFree(void* ptr) {
+  return ptr == nullptr ? 0 : static_cast<int>(cudaFree(ptr));
+}
+
+int MusaPeerIpcHandle(void* ptr, void* out64) {
+  if (ptr == nullptr || out64 == nullptr) return MUSA_KERNELS_EINVAL;
+  cudaIpcMemHandle_t ipc;
+  const cudaError_t err = cudaIpcGetMemHandle(&ipc, ptr);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return static_cast<int>(err);
+  }
+  std::memcpy(out64, &ipc, 64);
+  return 0;
+}
+
+void* MusaPeerOpen(const void* handle64) {
+  if (handle64 == nullptr) return nullptr;
+  cudaIpcMemHandle_t ipc;
+  std::memcpy(&ipc, handle64, 64);
+  void* mapped = nullptr;
+  if (cudaIpcOpenMemHandle(&mapped, ipc, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return mapped;
+}
+
+int MusaPeerClose(void* mapped) {
+  return mapped == nullptr ? 0 : static_cast<int>(cudaIpcCloseMemHandle(mapped));
+}
+
 // Test hook: `world` replicas emulated on ONE GPU by one launch of `world`
 // CTAs (one per replica, each with its own buffer in this GPU's memory), so the
 // protocol can be checked where only one GPU is at hand.  `vectors`: device

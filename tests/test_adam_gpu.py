@@ -199,3 +199,47 @@ def test_musa_adam_matches_oracle_over_steps(kernel_lib):
     assert opt.iterations == 5
     assert_close(to_numpy(tv), var, RTOL["f32_adam"], 1e-8, "var")
     assert_close(to_numpy(opt.get_slot(tv, "m")), m, RTOL["f32_adam"], 1e-10, "m")
+
+
+def test_sharded_broadcast_kernel_on_one_gpu(kernel_lib):
+    """LaunchAdamShardBroadcastFloat with 4 "replicas" that all live on this
+    GPU: each shard's launch must update its range in every copy, so after the
+    4 launches every copy equals the un-sharded update, bit for bit."""
+    import ctypes
+    from tensorflow_musa_extension_b200.cross_replica import aligned_shard_range
+    n, world = 1_000_003, 4
+    rng, var, m, v = adam_inputs(21, n)
+    g = rng.normal(0, 1e-3, n).astype(np.float32)
+    want = [to_torch(t) for t in (var, m, v)]
+    raw_ops.ResourceApplyAdam(*want, *_step_args(), to_torch(g))
+    copies = [to_torch(var) for _ in range(world)]
+    tm, tvv, tg = to_torch(m), to_torch(v), to_torch(g)
+    ptrs = (ctypes.c_void_p * world)(*[c_.data_ptr() for c_ in copies])
+    alpha = raw_ops._adam_alpha(*[float(np.float32(H[k])) for k in
+                                  ("lr", "beta1_power", "beta2_power")])
+    st = torch.cuda.current_stream().cuda_stream
+    spans = [aligned_shard_range(n, world, r) for r in range(world)]
+    assert spans[0][0] == 0 and spans[-1][1] == n and all(lo % 4 == 0 for lo, _ in spans)
+    for r, (lo, hi) in enumerate(spans):
+        rc = kernel_lib.LaunchAdamShardBroadcastFloat(
+            ptrs, world, r, lo, tm[lo:hi].data_ptr(), tvv[lo:hi].data_ptr(),
+            tg[lo:hi].data_ptr(), float(np.float32(H["beta1"])), float(np.float32(H["beta2"])),
+            float(np.float32(H["epsilon"])), alpha, hi - lo, st)
+        assert rc == 0
+    torch.cuda.synchronize()
+    for c_ in copies:
+        assert torch.equal(c_, want[0])
+    assert torch.equal(tm, want[1]) and torch.equal(tvv, want[2])
+    # an unaligned range start takes the element-wise path and still matches
+    copies2 = [to_torch(var) for _ in range(2)]
+    ptrs2 = (ctypes.c_void_p * 2)(*[c_.data_ptr() for c_ in copies2])
+    tm2, tv2 = to_torch(m), to_torch(v)
+    rc = kernel_lib.LaunchAdamShardBroadcastFloat(
+        ptrs2, 2, 1, 3, tm2[3:1000].data_ptr(), tv2[3:1000].data_ptr(), tg[3:1000].data_ptr(),
+        float(np.float32(H["beta1"])), float(np.float32(H["beta2"])),
+        float(np.float32(H["epsilon"])), alpha, 997, st)
+    assert rc == 0
+    torch.cuda.synchronize()
+    for c_ in copies2:
+        assert torch.equal(c_[3:1000], want[0][3:1000]) and torch.equal(c_[1000:], copies2[0][1000:])
+        assert np.array_equal(to_numpy(c_[:3]), var[:3])
