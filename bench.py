@@ -597,7 +597,23 @@ def measure_ops(torch, lib, raw_ops, dev, args):
         ms = time_launch(torch, lambda: lib.LaunchBiasAct_F16(
             x.data_ptr(), b.data_ptr(), y.data_ptr(), 65536, 1024, 1, act, st), iters)
         entry(name, ms, 4 * x.numel(), x.numel(), "inputs exceed L2")
-    del x, y
+    # Backward of the chain at the same shape: gradients and features in,
+    # backprops out (6 B/elem); the un-fused pair reads backprops once more.
+    db = torch.empty(1024, device=dev, dtype=torch.float16)
+    need = lib.BiasGradWorkspaceBytes(65536, 1024, 1, 2)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    gr = torch.randn_like(x)
+    ms = time_launch(torch, lambda: lib.LaunchBiasAddReluGrad_F16(
+        gr.data_ptr(), x.data_ptr(), y.data_ptr(), db.data_ptr(), 65536, 1024, 1,
+        ws.data_ptr(), need, st), iters)
+    entry("bias_relu_grad_fused_f16", ms, 6 * x.numel(), x.numel(), "inputs exceed L2")
+    ms = time_launch(torch, lambda: lib.LaunchReluGrad_F16(
+        gr.data_ptr(), x.data_ptr(), y.data_ptr(), x.numel(), st), iters)
+    entry("relu_grad_f16", ms, 6 * x.numel(), x.numel(), "inputs exceed L2")
+    ms = time_launch(torch, lambda: lib.LaunchBiasAddGrad_F16(
+        y.data_ptr(), db.data_ptr(), 65536, 1024, 1, ws.data_ptr(), need, st), iters, flush)
+    entry("bias_add_grad_f16", ms, 2 * x.numel(), x.numel(), "L2 flushed before each launch")
+    del x, y, gr
 
     # BatchNorm single layers: config 1 (fp32) and config 2 (fp16, bf16).
     for name, shape, dt, sfx in (("cfg1_f32", (32 * 56 * 56, 64), torch.float32, "F32"),

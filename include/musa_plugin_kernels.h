@@ -135,6 +135,80 @@ int LaunchBiasAct_I64(const void* x, const void* bias, void* y, int64_t outer,
                       int64_t channels, int64_t inner, int act,
                       cudaStream_t stream);
 
+/* ------------------------------------- backward of the BiasAdd + Relu chain */
+
+/* Bytes of scratch that LaunchBiasAddGrad_* and LaunchBiasAddReluGrad_* need
+ * for this geometry and element size (2, 4 or 8): the partial rows of the
+ * two-level column sum.  The op allocates it as a temporary, in the place of
+ * the reference's muDNN MemoryMaintainer callback
+ * (musa_ext/kernels/nn/musa_biasadd_grad_op.cc:87-98).  0 for a geometry that
+ * needs none or is invalid. */
+size_t BiasGradWorkspaceBytes(int64_t outer, int64_t channels, int64_t inner,
+                              int elem_bytes);
+
+/* BiasAddGrad: bias_grad[c] = sum of out_backprop[outer, c, inner] over outer
+ * and inner, in a fixed order; bias_grad has the tensor's type.  Floating
+ * types add in fp32 / fp64 and round once, integer types wrap.  An empty
+ * outer or inner axis zero-fills bias_grad
+ * (musa_ext/kernels/nn/musa_biasadd_grad_op.cc:65-70); channels == 0 does
+ * nothing.  Replaces the muDNN Reduce ADD
+ * (musa_ext/kernels/nn/musa_biasadd_grad_op.cc:72-104), registered for the
+ * same six types (:113-118). */
+int LaunchBiasAddGrad_F32(const void* out_backprop, void* bias_grad,
+                          int64_t outer, int64_t channels, int64_t inner,
+                          void* workspace, size_t workspace_bytes,
+                          cudaStream_t stream);
+int LaunchBiasAddGrad_F16(const void* out_backprop, void* bias_grad,
+                          int64_t outer, int64_t channels, int64_t inner,
+                          void* workspace, size_t workspace_bytes,
+                          cudaStream_t stream);
+int LaunchBiasAddGrad_BF16(const void* out_backprop, void* bias_grad,
+                           int64_t outer, int64_t channels, int64_t inner,
+                           void* workspace, size_t workspace_bytes,
+                           cudaStream_t stream);
+int LaunchBiasAddGrad_F64(const void* out_backprop, void* bias_grad,
+                          int64_t outer, int64_t channels, int64_t inner,
+                          void* workspace, size_t workspace_bytes,
+                          cudaStream_t stream);
+int LaunchBiasAddGrad_I32(const void* out_backprop, void* bias_grad,
+                          int64_t outer, int64_t channels, int64_t inner,
+                          void* workspace, size_t workspace_bytes,
+                          cudaStream_t stream);
+int LaunchBiasAddGrad_I64(const void* out_backprop, void* bias_grad,
+                          int64_t outer, int64_t channels, int64_t inner,
+                          void* workspace, size_t workspace_bytes,
+                          cudaStream_t stream);
+
+/* ReluGrad: backprops[i] = gradients[i] * (features[i] > 0) over n elements.
+ * Replaces the muDNN Binary LEAKY_RELU_BW pass
+ * (musa_ext/kernels/nn/musa_relu_grad_op.cc:36-43), registered for float,
+ * half and bfloat16 (:56-58). */
+int LaunchReluGrad_F32(const void* gradients, const void* features,
+                       void* backprops, int64_t n, cudaStream_t stream);
+int LaunchReluGrad_F16(const void* gradients, const void* features,
+                       void* backprops, int64_t n, cudaStream_t stream);
+int LaunchReluGrad_BF16(const void* gradients, const void* features,
+                        void* backprops, int64_t n, cudaStream_t stream);
+
+/* BiasAddGrad(ReluGrad(gradients, features)) in one pass: backprops as
+ * LaunchReluGrad_* stores it and bias_grad = the column sum of those values
+ * before they are rounded to the tensor's type.  The reference runs the two
+ * ops above back to back (5 tensor passes); this reads gradients and features
+ * once and writes backprops once (3 passes).  No counterpart symbol in the
+ * reference. */
+int LaunchBiasAddReluGrad_F32(const void* gradients, const void* features,
+                              void* backprops, void* bias_grad, int64_t outer,
+                              int64_t channels, int64_t inner, void* workspace,
+                              size_t workspace_bytes, cudaStream_t stream);
+int LaunchBiasAddReluGrad_F16(const void* gradients, const void* features,
+                              void* backprops, void* bias_grad, int64_t outer,
+                              int64_t channels, int64_t inner, void* workspace,
+                              size_t workspace_bytes, cudaStream_t stream);
+int LaunchBiasAddReluGrad_BF16(const void* gradients, const void* features,
+                               void* backprops, void* bias_grad, int64_t outer,
+                               int64_t channels, int64_t inner, void* workspace,
+                               size_t workspace_bytes, cudaStream_t stream);
+
 /* ------------------------------------------------------ FusedBatchNorm -- */
 
 /* Tensor geometry: x, y, dy, dx are [outer, channels, inner], the statistics

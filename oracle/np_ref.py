@@ -239,3 +239,41 @@ def bias_add_swish(x, bias, data_format="NHWC"):
 def bias_add_sigmoid(x, bias, data_format="NHWC"):
     """The un-fused chain Sigmoid(BiasAdd(x, b))."""
     return sigmoid(bias_add(x, bias, data_format))
+
+
+def bias_add_grad(out_backprop, data_format="NHWC"):
+    """BiasAddGrad: the sum of `out_backprop` over every axis but the channel
+    axis (last for NHWC, 1 for NCHW), returned in the tensor's type.  A 1-D
+    input is its own result; an input with no elements gives zeros
+    (musa_ext/kernels/nn/musa_biasadd_grad_op.cc:23-70).  Floating types are
+    added in fp64 and rounded once; integer types wrap in their own width."""
+    g = np.asarray(out_backprop)
+    if g.ndim < 1:
+        raise ValueError("Input tensor must be at least 1D")
+    if g.ndim == 1:
+        return g.copy()
+    ax = 1 if data_format == "NCHW" else g.ndim - 1
+    axes = tuple(i for i in range(g.ndim) if i != ax)
+    if np.issubdtype(g.dtype, np.integer):
+        return g.sum(axis=axes, dtype=g.dtype)
+    return g.astype(np.float64).sum(axis=axes).astype(g.dtype)
+
+
+def relu_grad(gradients, features):
+    """ReluGrad: gradients * (features > 0)
+    (musa_ext/kernels/nn/musa_relu_grad_op.cc:19-48)."""
+    g = np.asarray(gradients)
+    f = np.asarray(features)
+    if g.shape != f.shape:
+        raise ValueError("Inputs to ReluGrad must have the same shape")
+    ct = _compute_dtype(g.dtype)
+    with np.errstate(invalid="ignore"):
+        mask = (f.astype(ct) > 0).astype(ct)
+        return (g.astype(ct) * mask).astype(g.dtype)
+
+
+def bias_add_relu_grad(gradients, features, data_format="NHWC"):
+    """The un-fused pair: backprops = ReluGrad(gradients, features) and
+    bias_grad = BiasAddGrad(backprops)."""
+    dx = relu_grad(gradients, features)
+    return dx, bias_add_grad(dx, data_format)

@@ -13,6 +13,9 @@ c_size = ctypes.c_size_t
 
 _ADAM_SAME = [c_vp, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_i64, c_bool, c_vp]
 _BIAS_ACT = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_vp]
+_BIAS_GRAD = [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]
+_RELU_GRAD = [c_vp, c_vp, c_vp, c_i64, c_vp]
+_BIAS_RELU_GRAD = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]
 _BN_TRAIN = [c_vp] * 10 + [c_i64, c_i64, c_i64, c_f32, c_f32, c_vp, c_size, c_vp]
 _BN_INFER = [c_vp] * 6 + [c_i64, c_i64, c_i64, c_f32, c_vp]
 _BN_GRAD = [c_vp] * 8 + [c_i64, c_i64, c_i64, c_f32, c_bool, c_vp, c_size, c_vp]
@@ -34,6 +37,19 @@ PROTOTYPES = {
     "LaunchBiasAct_F64": (c_int, _BIAS_ACT),
     "LaunchBiasAct_I32": (c_int, _BIAS_ACT),
     "LaunchBiasAct_I64": (c_int, _BIAS_ACT),
+    "BiasGradWorkspaceBytes": (c_size, [c_i64, c_i64, c_i64, c_int]),
+    "LaunchBiasAddGrad_F32": (c_int, _BIAS_GRAD),
+    "LaunchBiasAddGrad_F16": (c_int, _BIAS_GRAD),
+    "LaunchBiasAddGrad_BF16": (c_int, _BIAS_GRAD),
+    "LaunchBiasAddGrad_F64": (c_int, _BIAS_GRAD),
+    "LaunchBiasAddGrad_I32": (c_int, _BIAS_GRAD),
+    "LaunchBiasAddGrad_I64": (c_int, _BIAS_GRAD),
+    "LaunchReluGrad_F32": (c_int, _RELU_GRAD),
+    "LaunchReluGrad_F16": (c_int, _RELU_GRAD),
+    "LaunchReluGrad_BF16": (c_int, _RELU_GRAD),
+    "LaunchBiasAddReluGrad_F32": (c_int, _BIAS_RELU_GRAD),
+    "LaunchBiasAddReluGrad_F16": (c_int, _BIAS_RELU_GRAD),
+    "LaunchBiasAddReluGrad_BF16": (c_int, _BIAS_RELU_GRAD),
     "BnWorkspaceBytes": (c_size, [c_i64, c_i64, c_i64]),
     "BnWorkspaceStatus": (c_int, [c_vp, c_i64, c_i64, c_i64]),
     "LaunchBnFwdTrain_F32": (c_int, _BN_TRAIN),

@@ -648,3 +648,111 @@ def MusaBiasAddSigmoid(value, bias, data_format="NHWC", name=None):
     """Fused Sigmoid(BiasAdd(value, bias))."""
     return _bias_act("MusaBiasAddSigmoid", value, bias, data_format, ACT_SIGMOID,
                      _ACT_FLOAT)
+
+
+# ------------------------------------ BiasAddGrad, ReluGrad, fused backward --
+
+MusaBiasAddReluGradOutput = collections.namedtuple(
+    "MusaBiasAddReluGrad", ["backprops", "bias_grad"])
+
+
+def _bias_grad_geometry(shape, data_format, opname):
+    if data_format not in ("NHWC", "NCHW"):
+        raise InvalidArgumentError("Invalid data format")
+    if len(shape) < 1:
+        raise InvalidArgumentError(
+            "Input tensor must be at least 1D: %s" % (tuple(shape),))
+    if len(shape) == 1:
+        return 1, shape[0], 1
+    if data_format == "NCHW":
+        inner = 1
+        for d in shape[2:]:
+            inner *= d
+        return shape[0], shape[1], inner
+    outer = 1
+    for d in shape[:-1]:
+        outer *= d
+    return outer, shape[-1], 1
+
+
+def BiasAddGrad(out_backprop, data_format="NHWC", name=None):
+    """BiasAddGrad for T in {float, double, half, bfloat16, int32, int64}: the
+    sum of `out_backprop` over every axis but the channel axis (last for NHWC,
+    1 for NCHW), in the tensor's type.  A 1-D input is returned as it is; an
+    input with no elements gives zeros
+    (musa_ext/kernels/nn/musa_biasadd_grad_op.cc:23-106, :113-118)."""
+    _require_cuda()
+    hf = _HostForm()
+    g = hf.to_device(out_backprop)
+    if g.dtype not in _BIAS_DTYPES:
+        raise InvalidArgumentError("BiasAddGrad: unsupported dtype %s" % (g.dtype,))
+    outer, c, inner = _bias_grad_geometry(tuple(g.shape), data_format, "BiasAddGrad")
+    if g.dim() == 1:
+        return hf.back(g)
+    g = g.contiguous()
+    with torch.cuda.device(g.device):
+        out = torch.empty((c,), dtype=g.dtype, device=g.device)
+        lib = _lib()
+        nbytes = lib.BiasGradWorkspaceBytes(outer, c, inner, g.element_size())
+        ws = _workspace(nbytes, g.device)
+        fn = getattr(lib, "LaunchBiasAddGrad_" + _SUFFIX[g.dtype])
+        rc = fn(_ptr(g), _ptr(out), outer, c, inner, _ptr(ws), ws.numel(),
+                _stream())
+        _check(rc, "BiasAddGrad")
+    return hf.back(out)
+
+
+def _relu_grad_inputs(opname, gradients, features, hf):
+    g = hf.to_device(gradients)
+    f = hf.to_device(features)
+    if g.dtype not in _ACT_FLOAT:
+        raise InvalidArgumentError("%s: unsupported dtype %s" % (opname, g.dtype))
+    if f.dtype != g.dtype:
+        raise InvalidArgumentError(
+            "%s: features dtype %s does not match gradients dtype %s"
+            % (opname, f.dtype, g.dtype))
+    if tuple(g.shape) != tuple(f.shape):
+        raise InvalidArgumentError(
+            "Inputs to ReluGrad must have the same shape. gradients: %s, "
+            "features: %s" % (tuple(g.shape), tuple(f.shape)))
+    return g.contiguous(), f.contiguous()
+
+
+def ReluGrad(gradients, features, name=None):
+    """ReluGrad for T in {float, half, bfloat16}: gradients * (features > 0)
+    (musa_ext/kernels/nn/musa_relu_grad_op.cc:19-48, :56-58)."""
+    _require_cuda()
+    hf = _HostForm()
+    g, f = _relu_grad_inputs("ReluGrad", gradients, features, hf)
+    with torch.cuda.device(g.device):
+        out = torch.empty_like(g)
+        if g.numel():
+            fn = getattr(_lib(), "LaunchReluGrad_" + _SUFFIX[g.dtype])
+            _check(fn(_ptr(g), _ptr(f), _ptr(out), g.numel(), _stream()),
+                   "ReluGrad")
+    return hf.back(out)
+
+
+def MusaBiasAddReluGrad(gradients, features, data_format="NHWC", name=None):
+    """Fused BiasAddGrad(ReluGrad(gradients, features)): returns (backprops,
+    bias_grad) from one pass over the two inputs.  The op that the
+    ReluGrad->BiasAddGrad fusion pattern emits; the reference runs the two ops
+    separately (musa_ext/kernels/nn/musa_relu_grad_op.cc,
+    musa_ext/kernels/nn/musa_biasadd_grad_op.cc)."""
+    _require_cuda()
+    hf = _HostForm()
+    g, f = _relu_grad_inputs("MusaBiasAddReluGrad", gradients, features, hf)
+    outer, c, inner = _bias_grad_geometry(tuple(g.shape), data_format,
+                                          "MusaBiasAddReluGrad")
+    with torch.cuda.device(g.device):
+        dx = torch.empty_like(g)
+        db = torch.empty((c,), dtype=g.dtype, device=g.device)
+        lib = _lib()
+        nbytes = lib.BiasGradWorkspaceBytes(outer, c, inner, g.element_size())
+        ws = _workspace(nbytes, g.device)
+        fn = getattr(lib, "LaunchBiasAddReluGrad_" + _SUFFIX[g.dtype])
+        rc = fn(_ptr(g), _ptr(f), _ptr(dx), _ptr(db), outer, c, inner, _ptr(ws),
+                ws.numel(), _stream())
+        _check(rc, "MusaBiasAddReluGrad")
+    dx, db = hf.back_many([dx, db])
+    return MusaBiasAddReluGradOutput(dx, db)

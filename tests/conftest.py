@@ -35,7 +35,7 @@ def pytest_collection_modifyitems(config, items):
 def golden():
     return {name: np.load(os.path.join(GOLDEN, name + ".npz"))
             for name in ("adam_reference_numpy", "bn_torch_cpu",
-                         "elementwise_literals")}
+                         "elementwise_literals", "bias_grad_torch_cpu")}
 
 
 @pytest.fixture(scope="session")

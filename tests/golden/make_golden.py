@@ -1,7 +1,7 @@
 """Generates the golden vectors under tests/golden/ (run once, by hand, on a
 machine that has the reference checkout; the .npz files are committed).
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [adam|bn|elementwise|bias_grad ...]
 
 What pins what:
   adam_reference_numpy.npz
@@ -23,6 +23,11 @@ What pins what:
       The literal inputs of the reference's Relu / Sigmoid / BiasAdd tests
       (test/ops/relu_op_test.py:58-96, test/ops/sigmoid_op_test.py:58-93,
       test/ops/biasadd_op_test.py:74-116) with closed-form float64 answers.
+  bias_grad_torch_cpu.npz
+      BiasAddGrad / ReluGrad cases at the shapes of the reference test
+      (test/ops/biasadd_grad_op_test.py:16-86: NHWC [2,8,8,32], NCHW
+      [2,32,8,8]) plus a ragged 2-D case, answered by PyTorch's CPU autograd of
+      relu(x + b) in float64: an independent implementation, not TensorFlow.
 """
 import ast
 import os
@@ -162,10 +167,49 @@ def make_elementwise():
     np.savez_compressed(os.path.join(HERE, "elementwise_literals.npz"), **out)
 
 
+def make_bias_grad():
+    import torch
+    rng = np.random.default_rng(77)
+    out = {}
+    cases = [("nhwc", (2, 8, 8, 32), "NHWC"), ("nchw", (2, 32, 8, 8), "NCHW"),
+             ("ragged2d", (37, 24), "NHWC")]
+    for name, shape, fmt in cases:
+        ax = 1 if fmt == "NCHW" else len(shape) - 1
+        for dt_name, tdt in (("f32", torch.float32), ("f16", torch.float16),
+                             ("bf16", torch.bfloat16)):
+            # Inputs are rounded to the storage type first, so every dtype sees
+            # values that it can hold exactly.
+            x = torch.from_numpy(rng.standard_normal(shape)).to(tdt)
+            b = torch.from_numpy(rng.standard_normal(shape[ax]) * 0.5).to(tdt)
+            dy = torch.from_numpy(rng.standard_normal(shape)).to(tdt)
+            view = [1] * len(shape)
+            view[ax] = shape[ax]
+            z = (x.double() + b.double().reshape(view)).to(tdt)  # BiasAdd in T
+            zt = z.double().requires_grad_(True)
+            y = torch.relu(zt)
+            y.backward(dy.double())
+            dz = zt.grad                      # = ReluGrad(dy, y)
+            red = [i for i in range(len(shape)) if i != ax]
+            db = dz.sum(dim=red)              # = BiasAddGrad(dz)
+            key = "%s/%s" % (name, dt_name)
+            out[key + "/features"] = y.detach().float().numpy()
+            out[key + "/gradients"] = dy.float().numpy()
+            out[key + "/backprops"] = dz.float().numpy()
+            out[key + "/bias_grad"] = db.numpy()
+            out[key + "/dy_colsum"] = dy.double().sum(dim=red).numpy()
+    np.savez_compressed(os.path.join(HERE, "bias_grad_torch_cpu.npz"), **out)
+
+
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
+    if len(sys.argv) < 2:
         sys.exit(__doc__)
-    make_adam(sys.argv[1])
-    make_bn()
-    make_elementwise()
+    which = sys.argv[2:] or ["adam", "bn", "elementwise", "bias_grad"]
+    if "adam" in which:
+        make_adam(sys.argv[1])
+    if "bn" in which:
+        make_bn()
+    if "elementwise" in which:
+        make_elementwise()
+    if "bias_grad" in which:
+        make_bias_grad()
     print("wrote golden vectors to", HERE)

@@ -149,3 +149,50 @@ def test_bias_act_c_matches_numpy(dtype, act, fn):
     b = rng.normal(0, 0.1, 40).astype(dt)
     rt = 1e-6 if dtype == "float32" else 0.0
     assert_close(c_ref.bias_act(x, b, act), fn(x, b), rt, 0, "act %d" % act)
+
+
+def _bias_grad_cases(g):
+    for name, fmt in (("nhwc", "NHWC"), ("nchw", "NCHW"), ("ragged2d", "NHWC")):
+        for dt in ("f32", "f16", "bf16"):
+            yield "%s/%s" % (name, dt), fmt, {"f32": "float32", "f16": "float16",
+                                              "bf16": "bfloat16"}[dt]
+
+
+def test_bias_grad_oracle_matches_independent_implementation(golden):
+    """ReluGrad / BiasAddGrad of the oracle against PyTorch's CPU autograd of
+    relu(x + b) at the shapes of the reference's BiasAddGrad test."""
+    from helpers import np_dtype
+    g = golden["bias_grad_torch_cpu"]
+    for key, fmt, dtype in _bias_grad_cases(g):
+        dt = np_dtype(dtype)
+        feats = g[key + "/features"].astype(dt)
+        grads = g[key + "/gradients"].astype(dt)
+        dx, db = np_ref.bias_add_relu_grad(grads, feats, fmt)
+        assert dx.dtype == dt and db.dtype == dt
+        # backprops is a selection of the gradients: exact in every type.
+        assert np.array_equal(dx.astype(np.float64), g[key + "/backprops"].astype(np.float64)), key
+        assert np.array_equal(db.astype(np.float64),
+                              g[key + "/bias_grad"].astype(dt).astype(np.float64)), key
+        plain = np_ref.bias_add_grad(grads, fmt)
+        assert np.array_equal(plain.astype(np.float64),
+                              g[key + "/dy_colsum"].astype(dt).astype(np.float64)), key
+
+
+def test_bias_grad_oracle_edge_cases():
+    # 1-D input: nothing to reduce, the input is the result
+    # (musa_ext/kernels/nn/musa_biasadd_grad_op.cc:52-58).
+    v = np.array([1.5, -2.0, 3.0], np.float32)
+    assert np.array_equal(np_ref.bias_add_grad(v), v)
+    # Empty inputs give zeros of the channel count (test/ops/biasadd_grad_op_test.py:88-127).
+    for shape in [(4096, 0, 512), (4096, 0, 128), (0, 16)]:
+        out = np_ref.bias_add_grad(np.zeros(shape, np.float16))
+        assert out.shape == (shape[-1],) and out.dtype == np.float16 and not out.any()
+    # Integer sums wrap in the tensor's own width.
+    big = np.full((4, 2), 2 ** 30, np.int32)
+    assert np.array_equal(np_ref.bias_add_grad(big), np.array([0, 0], np.int32))
+    # features == 0 is inactive; a NaN feature is inactive as well.
+    gr = np.array([1.0, 2.0, 3.0, 4.0], np.float32)
+    ft = np.array([0.0, -0.0, np.nan, 1e-30], np.float32)
+    assert np.array_equal(np_ref.relu_grad(gr, ft), np.array([0, 0, 0, 4], np.float32))
+    with pytest.raises(ValueError):
+        np_ref.relu_grad(np.zeros((2, 3), np.float32), np.zeros((3, 2), np.float32))
