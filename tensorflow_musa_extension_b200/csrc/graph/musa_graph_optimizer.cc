@@ -12,6 +12,7 @@ namespace musa_graph {
 
 void LinkBiasAddActivationFusion();
 void LinkAdamMixedFusion();
+void LinkBiasAddReluGradFusion();
 
 std::string OptimizeReport::ToJson() const {
   std::ostringstream os;
@@ -85,6 +86,7 @@ Status MusaGraphOptimizer::Optimize(GraphDef* graph,
                                     OptimizeReport* report) const {
   LinkBiasAddActivationFusion();
   LinkAdamMixedFusion();
+  LinkBiasAddReluGradFusion();
   OptimizeReport local;
   OptimizeReport& rep = report != nullptr ? *report : local;
   rep = OptimizeReport();
@@ -228,6 +230,7 @@ void MusaGraphOptimizerFree(void* graph_def) { std::free(graph_def); }
 int MusaGraphOptimizerListPatterns(char* buf, size_t cap) {
   LinkBiasAddActivationFusion();
   LinkAdamMixedFusion();
+  LinkBiasAddReluGradFusion();
   std::ostringstream os;
   const auto patterns = FusionPatternManager::GetInstance().GetSortedPatterns();
   for (const FusionPattern* p : patterns) {

@@ -22,6 +22,10 @@ OPS = {
     "MusaBiasAddRelu": lambda n, a: raw_ops.MusaBiasAddRelu(a[0], a[1]),
     "MusaBiasAddSwish": lambda n, a: raw_ops.MusaBiasAddSwish(a[0], a[1]),
     "MusaBiasAddSigmoid": lambda n, a: raw_ops.MusaBiasAddSigmoid(a[0], a[1]),
+    "ReluGrad": lambda n, a: raw_ops.ReluGrad(a[0], a[1]),
+    "BiasAddGrad": lambda n, a: raw_ops.BiasAddGrad(a[0]),
+    "MusaBiasAddReluGrad": lambda n, a: tuple(raw_ops.MusaBiasAddReluGrad(a[0], a[1])),
+    "Add": lambda n, a: a[0] + a[1],
 }
 
 
@@ -30,14 +34,18 @@ def execute(graph, feeds, fetch):
     values = dict(feeds)
     executed = []
 
-    def value(name):
-        name = name.split(":")[0]
+    def value(tensor):
+        name, _, port = tensor.partition(":")
         if name not in values:
             n = nodes[name]
             args = [value(i) for i in n.input if not i.startswith("^")]
             values[name] = OPS[n.op](n, args)
             executed.append(n.op)
-        return values[name]
+        out = values[name]
+        if isinstance(out, tuple):
+            return out[int(port or 0)]
+        assert not port or port == "0"
+        return out
 
     return value(fetch), executed
 
@@ -71,3 +79,36 @@ def test_fused_graph_matches_unfused_graph(kernel_lib, dtype, code):
     assert_close(to_numpy(fused), to_numpy(plain), rt, at, "fused vs un-fused")
     h = np_ref.bias_add_relu(x, b1)
     assert_close(to_numpy(fused), np_ref.bias_add_swish(h, b2), rt, at, "fused vs oracle")
+
+
+@pytest.mark.parametrize("dtype,code", [("float32", gp.DT_FLOAT), ("float16", gp.DT_HALF),
+                                        ("bfloat16", gp.DT_BFLOAT16)])
+def test_fused_backward_graph_matches_unfused_graph(kernel_lib, dtype, code):
+    """Forward chain and its backward in one graph; the fetched value depends
+    on both outputs of the fused backward op."""
+    g = Builder()
+    for name in ("x", "b", "dy"):
+        g.node(name, "Placeholder", dtype=code)
+    g.node("z", "BiasAdd", ["x", "b"], T=code)
+    g.node("y", "Relu", ["z"], T=code)
+    g.node("dz", "ReluGrad", ["dy", "y"], T=code)
+    g.node("db", "BiasAddGrad", ["dz"], T=code)
+    g.node("out", "Add", ["dz", "db"], T=code)       # broadcasts db over the rows
+    rewritten, report = go.optimize_graph_def(g.bytes())
+    assert report["patterns"] == {"MusaBiasAddReluFusion": 1, "MusaBiasAddReluGradFusion": 1}
+
+    rng = np.random.default_rng(6)
+    dt = np_dtype(dtype)
+    x = rng.standard_normal((500, 48)).astype(dt)
+    b = rng.normal(0, 0.3, 48).astype(dt)
+    dy = rng.standard_normal((500, 48)).astype(dt)
+    feeds = {"x": to_torch(x), "b": to_torch(b), "dy": to_torch(dy)}
+    plain, ops_plain = execute(g.graph, feeds, "out")
+    fused, ops_fused = execute(parse(rewritten), feeds, "out")
+    assert sorted(ops_fused) == ["Add", "MusaBiasAddRelu", "MusaBiasAddReluGrad"]
+    assert sorted(ops_plain) == ["Add", "BiasAdd", "BiasAddGrad", "Relu", "ReluGrad"]
+    rt, at = (RTOL["f32_bn"], 1e-4) if dtype == "float32" else (RTOL["lowp"], 0.15)
+    assert_close(to_numpy(fused), to_numpy(plain), rt, at, "fused vs un-fused")
+    want_dx, want_db = np_ref.bias_add_relu_grad(dy, np_ref.bias_add_relu(x, b))
+    want = want_dx.astype(np.float64) + want_db.astype(np.float64)
+    assert_close(to_numpy(fused), want, rt, at, "fused vs oracle")

@@ -183,7 +183,8 @@ def test_swish_needs_the_same_tensor_on_both_sides():
 def test_sigmoid_chain_and_priorities():
     names = [(n, p) for n, p, _ in go.list_fusion_patterns()]
     assert names == [("MusaBiasAddSwishFusion", 56), ("MusaBiasAddReluFusion", 55),
-                     ("MusaBiasAddSigmoidFusion", 54), ("MusaAdamMixedFusion", 40)]
+                     ("MusaBiasAddSigmoidFusion", 54), ("MusaBiasAddReluGradFusion", 53),
+                     ("MusaAdamMixedFusion", 40)]
     g = Builder()
     g.node("x", "Placeholder", dtype=gp.DT_HALF)
     g.node("b", "Const", dtype=gp.DT_HALF)
@@ -290,6 +291,95 @@ def test_set_pattern_enabled():
 def test_biasadd_kill_switch(monkeypatch):
     monkeypatch.setenv("MUSA_DISABLE_BIASADD_ACT_FUSION", "true")
     assert run(bias_relu_graph())[1]["applied"] == 0
+
+
+# ------------------------------------------- ReluGrad -> BiasAddGrad backward --
+
+def relu_grad_graph(dtype=gp.DT_FLOAT, fmt=None, reader=True, relu_grad_reader=True,
+                    bias_grad_device=gp.MUSA):
+    g = Builder()
+    g.node("dy", "Placeholder", dtype=dtype)
+    g.node("y", "Placeholder", dtype=dtype)
+    g.node("w", "Placeholder", dtype=dtype)
+    g.node("dz", "ReluGrad", ["dy", "y"], T=dtype)
+    extra = {"data_format": fmt} if fmt else {}
+    g.node("db", "BiasAddGrad", ["dz"], bias_grad_device, T=dtype, **extra)
+    if relu_grad_reader:
+        g.node("dx", "MatMul", ["dz", "w"], T=dtype)       # the layer's input gradient
+    if reader:
+        g.node("lr", "Const", dtype=dtype)
+        g.node("step", "Mul", ["db", "lr"], T=dtype)       # reads the bias gradient
+    return g
+
+
+@pytest.mark.parametrize("dtype", [gp.DT_FLOAT, gp.DT_HALF, gp.DT_BFLOAT16])
+@pytest.mark.parametrize("fmt", [None, "NHWC", "NCHW"])
+def test_relu_grad_bias_add_grad_is_fused(dtype, fmt):
+    out, report = run(relu_grad_graph(dtype, fmt))
+    nodes = by_name(out)
+    assert report["patterns"] == {"MusaBiasAddReluGradFusion": 1}
+    fused = nodes["dz"]                        # takes the ReluGrad's name
+    assert fused.op == "MusaBiasAddReluGrad" and list(fused.input) == ["dy", "y"]
+    assert fused.device == gp.MUSA and fused.attr["T"].type == dtype
+    assert fused.attr["data_format"].s == (fmt or "NHWC").encode()
+    assert "db" not in nodes and "dz_original" not in nodes
+    assert list(nodes["dx"].input) == ["dz", "w"]          # output 0: backprops
+    assert list(nodes["step"].input) == ["dz:1", "lr"]     # output 1: bias gradient
+
+
+def test_relu_grad_fusion_moves_control_edges():
+    g = relu_grad_graph()
+    g.node("gate", "NoOp")
+    g.node("late", "NoOp", ["^db"])
+    for n in g.graph.node:
+        if n.name == "db":
+            n.input.append("^gate")
+    nodes = by_name(run(g)[0])
+    assert list(nodes["dz"].input) == ["dy", "y", "^gate"]
+    assert list(nodes["late"].input) == ["^dz"]
+
+
+@pytest.mark.parametrize("kw", [dict(reader=False), dict(bias_grad_device=gp.CPU),
+                                dict(dtype=gp.DT_DOUBLE)])
+def test_relu_grad_fusion_non_matching_variants(kw):
+    g = relu_grad_graph(**kw)
+    out, report = run(g)
+    assert report["patterns"].get("MusaBiasAddReluGradFusion", 0) == 0
+    assert by_name(out)["db"].op == "BiasAddGrad"
+
+
+def test_bias_add_grad_of_another_producer_is_left_alone():
+    g = Builder()
+    g.node("dy", "Placeholder", dtype=gp.DT_FLOAT)
+    g.node("db", "BiasAddGrad", ["dy"], T=gp.DT_FLOAT)
+    g.node("lr", "Const", dtype=gp.DT_FLOAT)
+    g.node("step", "Mul", ["db", "lr"], T=gp.DT_FLOAT)
+    assert run(g)[1]["applied"] == 0
+
+
+def test_relu_grad_fusion_is_idempotent_and_has_a_kill_switch(monkeypatch):
+    once, _ = go.optimize_graph_def(relu_grad_graph().bytes())
+    twice, report = go.optimize_graph_def(once)
+    assert report["applied"] == 0 and parse(twice) == parse(once)
+    monkeypatch.setenv("MUSA_DISABLE_BIASADD_RELU_GRAD_FUSION", "1")
+    assert run(relu_grad_graph())[1]["applied"] == 0
+
+
+def test_forward_and_backward_chains_fuse_in_one_run():
+    g = Builder()
+    for name in ("x", "b", "dy", "w"):
+        g.node(name, "Placeholder", dtype=gp.DT_HALF)
+    g.node("z", "BiasAdd", ["x", "b"], T=gp.DT_HALF)
+    g.node("y", "Relu", ["z"], T=gp.DT_HALF)
+    g.node("dz", "ReluGrad", ["dy", "y"], T=gp.DT_HALF)
+    g.node("db", "BiasAddGrad", ["dz"], T=gp.DT_HALF)
+    g.node("dx", "MatMul", ["dz", "w"], T=gp.DT_HALF)
+    g.node("loss", "Mul", ["y", "db"], T=gp.DT_HALF)
+    out, report = run(g)
+    assert report["patterns"] == {"MusaBiasAddReluFusion": 1, "MusaBiasAddReluGradFusion": 1}
+    nodes = by_name(out)
+    assert nodes["y"].op == "MusaBiasAddRelu" and nodes["dz"].op == "MusaBiasAddReluGrad"
+    assert list(nodes["dz"].input) == ["dy", "y"] and list(nodes["loss"].input) == ["y", "dz:1"]
 
 
 # ------------------------------------------------------ Python config layer --
