@@ -587,7 +587,23 @@ def measure_ops(torch, lib, raw_ops, dev, args):
         var.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), 0.9, 0.999, 1e-7,
         alpha, n, st), iters)
     entry("adam_f32_25.6M", ms, 28 * n, n, "inputs exceed L2")
-    del var, m, v, g
+    # The other streaming optimizers at the same size (same kernel template).
+    ms = time_launch(torch, lambda: lib.LaunchResourceApplyNadam_Float(
+        var.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), 0.9 ** 10, 0.999 ** 10,
+        1e-3, 0.9, 0.999, 1e-7, n, st), iters)
+    entry("nadam_f32_25.6M", ms, 28 * n, n, "inputs exceed L2")
+    ms = time_launch(torch, lambda: lib.LaunchFusedResourceApplyRMSProp_Float(
+        var.data_ptr(), v.data_ptr(), m.data_ptr(), g.data_ptr(), 1e-3, 0.9, 0.9, 1e-7,
+        n, st), iters)
+    entry("rmsprop_f32_25.6M", ms, 28 * n, n, "inputs exceed L2")
+    ms = time_launch(torch, lambda: lib.LaunchResourceApplyGradientDescentFloat(
+        var.data_ptr(), g.data_ptr(), 1e-3, n, st), iters)
+    entry("sgd_f32_25.6M", ms, 12 * n, n, "inputs exceed L2")
+    gb = g.to(torch.bfloat16)
+    ms = time_launch(torch, lambda: lib.LaunchResourceApplyGradientDescentFloatBFloat16(
+        var.data_ptr(), gb.data_ptr(), 1e-3, n, st), iters)
+    entry("sgd_f32_bf16grad_25.6M", ms, 10 * n, n, "inputs exceed L2")
+    del var, m, v, g, gb
 
     # BiasAdd chains, config 3: fp16 [65536, 1024] (268 MB per launch).
     x = torch.randn(65536, 1024, device=dev, dtype=torch.float16)

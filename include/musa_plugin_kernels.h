@@ -5,7 +5,8 @@
  * The reference plugin keeps its device code behind `extern "C" Launch*()`
  * functions that the C++ OpKernels call from `Compute()`; this header declares
  * the same layer for the memory-bound training path (FusedBatchNorm forward and
- * gradient, ApplyAdam, BiasAdd + activation).  Each declaration cites the
+ * gradient, ApplyAdam and the optimizers of its shape, BiasAdd + activation
+ * and its backward).  Each declaration cites the
  * reference interface it replaces, as `path:line` inside the reference project.
  *
  * Conventions shared by every launcher (they are the reference's):
@@ -94,6 +95,130 @@ void LaunchApplyAdamMixed_BFloat16(float* var, float* m, float* v,
                                    const void* grad, float lr_t, float beta1,
                                    float beta2, float epsilon, int64_t n,
                                    bool use_nesterov, cudaStream_t stream);
+
+/* ------------------------- Nadam, RMSProp, gradient descent (same shape) -- */
+
+/* ResourceApplyNadam over n elements, in place:
+ *   m <- beta1*m + (1-beta1)*g;  v <- beta2*v + (1-beta2)*g*g
+ *   var <- var - lr * ((beta1*m + (1-beta1)*g) / (1-beta1_power))
+ *                   / (sqrt(v / (1-beta2_power)) + epsilon)
+ * Scalars are float for every tensor type and 1-x is formed in float, as in
+ * the reference launcher.  float / half / bfloat16 tensors compute in fp32
+ * and round to nearest even on store (the reference's bfloat16 store
+ * truncates); double tensors compute in fp64 (the reference narrows them to
+ * fp32).  C names for the C++ template LaunchResourceApplyNadamKernel<T>
+ * (musa_ext/kernels/training/musa_resource_apply_nadam_kernel.mu:48-104;
+ * declared in musa_ext/kernels/training/musa_resource_apply_nadam_op.cc). */
+void LaunchResourceApplyNadam_Float(void* var, void* m, void* v, const void* grad,
+                                    float beta1_power, float beta2_power, float lr,
+                                    float beta1, float beta2, float epsilon,
+                                    int64_t n, cudaStream_t stream);
+void LaunchResourceApplyNadam_Half(void* var, void* m, void* v, const void* grad,
+                                   float beta1_power, float beta2_power, float lr,
+                                   float beta1, float beta2, float epsilon,
+                                   int64_t n, cudaStream_t stream);
+void LaunchResourceApplyNadam_BFloat16(void* var, void* m, void* v,
+                                       const void* grad, float beta1_power,
+                                       float beta2_power, float lr, float beta1,
+                                       float beta2, float epsilon, int64_t n,
+                                       cudaStream_t stream);
+void LaunchResourceApplyNadam_Double(void* var, void* m, void* v,
+                                     const void* grad, float beta1_power,
+                                     float beta2_power, float lr, float beta1,
+                                     float beta2, float epsilon, int64_t n,
+                                     cudaStream_t stream);
+
+/* ResourceApplyRMSProp / ApplyRMSProp over n elements, in place:
+ *   ms <- rho*ms + (1-rho)*g*g;  mom <- momentum*mom + lr*g / sqrt(ms + epsilon)
+ *   var <- var - mom
+ * and the centered form with mg <- rho*mg + (1-rho)*g and the denominator
+ * sqrt(ms - mg*mg + epsilon).  Scalars arrive as double and are narrowed to
+ * the compute type (fp32; fp64 for double tensors) before 1-rho is formed.
+ * C names for LaunchFusedResourceApplyRMSPropKernel<T> and
+ * LaunchFusedResourceApplyCenteredRMSPropKernel<T>
+ * (musa_ext/kernels/training/musa_applyrmsprop_kernel.mu:72-133, :236-340),
+ * which return without synchronising the stream, unlike the reference op's
+ * CheckLaunchAndSync (musa_ext/kernels/training/musa_applyrmsprop_op.cc:170-182). */
+void LaunchFusedResourceApplyRMSProp_Float(void* var, void* ms, void* mom,
+                                           const void* grad, double lr, double rho,
+                                           double momentum, double epsilon,
+                                           int64_t n, cudaStream_t stream);
+void LaunchFusedResourceApplyRMSProp_Half(void* var, void* ms, void* mom,
+                                          const void* grad, double lr, double rho,
+                                          double momentum, double epsilon,
+                                          int64_t n, cudaStream_t stream);
+void LaunchFusedResourceApplyRMSProp_BFloat16(void* var, void* ms, void* mom,
+                                              const void* grad, double lr,
+                                              double rho, double momentum,
+                                              double epsilon, int64_t n,
+                                              cudaStream_t stream);
+void LaunchFusedResourceApplyRMSProp_Double(void* var, void* ms, void* mom,
+                                            const void* grad, double lr,
+                                            double rho, double momentum,
+                                            double epsilon, int64_t n,
+                                            cudaStream_t stream);
+void LaunchFusedResourceApplyCenteredRMSProp_Float(
+    void* var, void* mg, void* ms, void* mom, const void* grad, double lr,
+    double rho, double momentum, double epsilon, int64_t n, cudaStream_t stream);
+void LaunchFusedResourceApplyCenteredRMSProp_Half(
+    void* var, void* mg, void* ms, void* mom, const void* grad, double lr,
+    double rho, double momentum, double epsilon, int64_t n, cudaStream_t stream);
+void LaunchFusedResourceApplyCenteredRMSProp_BFloat16(
+    void* var, void* mg, void* ms, void* mom, const void* grad, double lr,
+    double rho, double momentum, double epsilon, int64_t n, cudaStream_t stream);
+void LaunchFusedResourceApplyCenteredRMSProp_Double(
+    void* var, void* mg, void* ms, void* mom, const void* grad, double lr,
+    double rho, double momentum, double epsilon, int64_t n, cudaStream_t stream);
+
+/* ResourceApplyGradientDescent: var <- var - alpha * grad over n elements.
+ * Same names and arguments as the reference
+ * (musa_ext/kernels/training/musa_applygradientdescent_kernel.mu:106-122). */
+void LaunchResourceApplyGradientDescentFloat(float* var, const float* grad,
+                                             float alpha, int64_t n,
+                                             cudaStream_t stream);
+void LaunchResourceApplyGradientDescentFloatBFloat16(float* var, const void* grad,
+                                                     float alpha, int64_t n,
+                                                     cudaStream_t stream);
+/* The same update for half / bfloat16 variables: alpha*grad is rounded to the
+ * tensor's type before the subtraction, like the two stored results of the
+ * muDNN MUL and SUB passes that the reference runs for these types
+ * (musa_ext/kernels/training/musa_applygradientdescent_op.cc:163-199). */
+void LaunchResourceApplyGradientDescent_Half(void* var, const void* grad,
+                                             float alpha, int64_t n,
+                                             cudaStream_t stream);
+void LaunchResourceApplyGradientDescent_BFloat16(void* var, const void* grad,
+                                                 float alpha, int64_t n,
+                                                 cudaStream_t stream);
+
+/* MusaGroupedResourceApplyGradientDescentMixed, table form: the reference's
+ * interface (musa_ext/kernels/training/musa_applygradientdescent_kernel.mu:
+ * 124-146).  All five tables are DEVICE arrays; CTA b of the `total_blocks`
+ * launched belongs to the tensor t with block_offsets[t] <= b <
+ * block_offsets[t + 1] and strides over that tensor together with the other
+ * CTAs of t (256 threads per CTA). */
+void LaunchGroupedResourceApplyGradientDescentFloat(
+    const uint64_t* var_ptrs, const uint64_t* grad_ptrs, const float* alphas,
+    const int64_t* sizes, const int64_t* block_offsets, int num_tensors,
+    int total_blocks, cudaStream_t stream);
+void LaunchGroupedResourceApplyGradientDescentFloatBFloat16(
+    const uint64_t* var_ptrs, const uint64_t* grad_ptrs, const float* alphas,
+    const int64_t* sizes, const int64_t* block_offsets, int num_tensors,
+    int total_blocks, cudaStream_t stream);
+
+/* The grouped update from HOST tables: the descriptors of up to
+ * MUSA_SGD_GROUP_MAX tensors travel in the kernel's parameter space, so the
+ * op needs none of the five temporaries and staging copies of the table form
+ * (musa_ext/kernels/training/musa_applygradientdescent_op.cc:388-428).  More
+ * tensors are split over several launches.  var_ptrs[i] / delta_ptrs[i] are
+ * device pointers to sizes[i] floats and sizes[i] floats or bfloat16s.
+ * No counterpart symbol in the reference. */
+#define MUSA_SGD_GROUP_MAX 256
+int LaunchGroupedGradientDescentHostTable(void* const* var_ptrs,
+                                          const void* const* delta_ptrs,
+                                          const float* alphas,
+                                          const int64_t* sizes, int num_tensors,
+                                          int delta_is_bfloat16,
+                                          cudaStream_t stream);
 
 /* ------------------------------------------------ BiasAdd + activation -- */
 

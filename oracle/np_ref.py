@@ -277,3 +277,94 @@ def bias_add_relu_grad(gradients, features, data_format="NHWC"):
     bias_grad = BiasAddGrad(backprops)."""
     dx = relu_grad(gradients, features)
     return dx, bias_add_grad(dx, data_format)
+
+
+# --------------------------------------------------------------------------
+# Nadam, RMSProp, gradient descent
+# --------------------------------------------------------------------------
+
+def _update_dtype(dt):
+    """Arithmetic type of the optimizer kernels: fp32 for float and the
+    16-bit types, fp64 for double."""
+    return np.float64 if dt == np.float64 else np.float32
+
+
+def apply_nadam(var, m, v, beta1_power, beta2_power, lr, beta1, beta2, epsilon,
+                grad):
+    """ResourceApplyNadam as the reference states it
+    (musa_ext/kernels/training/musa_resource_apply_nadam_kernel.mu:64-76 and the
+    formula in test/ops/resource_apply_nadam_op_test.py:57-67):
+      m' = b1*m + (1-b1)*g;  v' = b2*v + (1-b2)*g^2
+      var' = var - lr * ((b1*m' + (1-b1)*g) / (1-b1^t)) / (sqrt(v' / (1-b2^t)) + eps)
+    The scalars are narrowed to float and 1-x is taken in float, as the
+    launcher does; the state is rounded once to the tensor's type.  Returns
+    (var', m', v')."""
+    var, m, v, grad = (np.asarray(a) for a in (var, m, v, grad))
+    ct = _update_dtype(var.dtype)
+    f = np.float32
+    b1, b2 = f(beta1), f(beta2)
+    omb1, omb2 = ct(f(1) - b1), ct(f(1) - b2)
+    omb1p, omb2p = ct(f(1) - f(beta1_power)), ct(f(1) - f(beta2_power))
+    b1, b2, lr_, eps = ct(b1), ct(b2), ct(f(lr)), ct(f(epsilon))
+    g = grad.astype(ct)
+    m_new = b1 * m.astype(ct) + omb1 * g
+    v_new = b2 * v.astype(ct) + omb2 * g * g
+    m_hat = (b1 * m_new + omb1 * g) / omb1p
+    v_hat = v_new / omb2p
+    var_new = var.astype(ct) - lr_ * m_hat / (np.sqrt(v_hat) + eps)
+    return (var_new.astype(var.dtype), m_new.astype(var.dtype),
+            v_new.astype(var.dtype))
+
+
+def apply_rms_prop(var, ms, mom, lr, rho, momentum, epsilon, grad):
+    """ResourceApplyRMSProp / ApplyRMSProp
+    (musa_ext/kernels/training/musa_applyrmsprop_kernel.mu:84-98):
+      ms' = rho*ms + (1-rho)*g^2;  mom' = momentum*mom + lr*g / sqrt(ms' + eps)
+      var' = var - mom'
+    Returns (var', ms', mom')."""
+    var, ms, mom, grad = (np.asarray(a) for a in (var, ms, mom, grad))
+    ct = _update_dtype(var.dtype)
+    lr_, rho_, mo_, eps = ct(lr), ct(rho), ct(momentum), ct(epsilon)
+    omr = ct(1) - rho_
+    g = grad.astype(ct)
+    ms_new = rho_ * ms.astype(ct) + omr * g * g
+    mom_new = mo_ * mom.astype(ct) + lr_ * g / np.sqrt(ms_new + eps)
+    var_new = var.astype(ct) - mom_new
+    return (var_new.astype(var.dtype), ms_new.astype(var.dtype),
+            mom_new.astype(var.dtype))
+
+
+def apply_centered_rms_prop(var, mg, ms, mom, lr, rho, momentum, epsilon, grad):
+    """ResourceApplyCenteredRMSProp / ApplyCenteredRMSProp
+    (musa_ext/kernels/training/musa_applyrmsprop_kernel.mu:112-132):
+      mg' = rho*mg + (1-rho)*g;  ms' = rho*ms + (1-rho)*g^2
+      mom' = momentum*mom + lr*g / sqrt(ms' - mg'^2 + eps);  var' = var - mom'
+    Returns (var', mg', ms', mom')."""
+    var, mg, ms, mom, grad = (np.asarray(a) for a in (var, mg, ms, mom, grad))
+    ct = _update_dtype(var.dtype)
+    lr_, rho_, mo_, eps = ct(lr), ct(rho), ct(momentum), ct(epsilon)
+    omr = ct(1) - rho_
+    g = grad.astype(ct)
+    mg_new = rho_ * mg.astype(ct) + omr * g
+    ms_new = rho_ * ms.astype(ct) + omr * g * g
+    denom = ms_new - mg_new * mg_new + eps
+    mom_new = mo_ * mom.astype(ct) + lr_ * g / np.sqrt(denom)
+    var_new = var.astype(ct) - mom_new
+    return (var_new.astype(var.dtype), mg_new.astype(var.dtype),
+            ms_new.astype(var.dtype), mom_new.astype(var.dtype))
+
+
+def apply_gradient_descent(var, alpha, delta):
+    """ResourceApplyGradientDescent and its mixed form: var' = var - alpha*delta
+    (musa_ext/kernels/training/musa_applygradientdescent_kernel.mu:14-36).  A
+    float variable takes a float or bfloat16 delta; a 16-bit variable rounds
+    alpha*delta to its own type before the subtraction, like the separately
+    stored product of musa_applygradientdescent_op.cc:186-199."""
+    var, delta = np.asarray(var), np.asarray(delta)
+    if var.dtype == np.float32:
+        step = np.float32(alpha) * delta.astype(np.float32)
+        return (var - step).astype(np.float32)
+    ct = _compute_dtype(var.dtype)
+    a = np.asarray(alpha).astype(var.dtype).astype(ct)
+    step = (a * delta.astype(ct)).astype(var.dtype).astype(ct)
+    return (var.astype(ct) - step).astype(var.dtype)

@@ -13,6 +13,11 @@ c_size = ctypes.c_size_t
 
 _ADAM_SAME = [c_vp, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_i64, c_bool, c_vp]
 _BIAS_ACT = [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_vp]
+_NADAM = [c_vp, c_vp, c_vp, c_vp] + [c_f32] * 6 + [c_i64, c_vp]
+_RMSPROP = [c_vp, c_vp, c_vp, c_vp] + [c_f64] * 4 + [c_i64, c_vp]
+_CRMSPROP = [c_vp] * 5 + [c_f64] * 4 + [c_i64, c_vp]
+_SGD = [c_vp, c_vp, c_f32, c_i64, c_vp]
+_SGD_TABLE = [c_vp] * 5 + [c_int, c_int, c_vp]
 _BIAS_GRAD = [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]
 _RELU_GRAD = [c_vp, c_vp, c_vp, c_i64, c_vp]
 _BIAS_RELU_GRAD = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]
@@ -37,6 +42,26 @@ PROTOTYPES = {
     "LaunchBiasAct_F64": (c_int, _BIAS_ACT),
     "LaunchBiasAct_I32": (c_int, _BIAS_ACT),
     "LaunchBiasAct_I64": (c_int, _BIAS_ACT),
+    "LaunchResourceApplyNadam_Float": (None, _NADAM),
+    "LaunchFusedResourceApplyRMSProp_Float": (None, _RMSPROP),
+    "LaunchFusedResourceApplyCenteredRMSProp_Float": (None, _CRMSPROP),
+    "LaunchResourceApplyNadam_Half": (None, _NADAM),
+    "LaunchFusedResourceApplyRMSProp_Half": (None, _RMSPROP),
+    "LaunchFusedResourceApplyCenteredRMSProp_Half": (None, _CRMSPROP),
+    "LaunchResourceApplyNadam_BFloat16": (None, _NADAM),
+    "LaunchFusedResourceApplyRMSProp_BFloat16": (None, _RMSPROP),
+    "LaunchFusedResourceApplyCenteredRMSProp_BFloat16": (None, _CRMSPROP),
+    "LaunchResourceApplyNadam_Double": (None, _NADAM),
+    "LaunchFusedResourceApplyRMSProp_Double": (None, _RMSPROP),
+    "LaunchFusedResourceApplyCenteredRMSProp_Double": (None, _CRMSPROP),
+    "LaunchResourceApplyGradientDescentFloat": (None, _SGD),
+    "LaunchResourceApplyGradientDescentFloatBFloat16": (None, _SGD),
+    "LaunchResourceApplyGradientDescent_Half": (None, _SGD),
+    "LaunchResourceApplyGradientDescent_BFloat16": (None, _SGD),
+    "LaunchGroupedResourceApplyGradientDescentFloat": (None, _SGD_TABLE),
+    "LaunchGroupedResourceApplyGradientDescentFloatBFloat16": (None, _SGD_TABLE),
+    "LaunchGroupedGradientDescentHostTable":
+        (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
     "BiasGradWorkspaceBytes": (c_size, [c_i64, c_i64, c_i64, c_int]),
     "LaunchBiasAddGrad_F32": (c_int, _BIAS_GRAD),
     "LaunchBiasAddGrad_F16": (c_int, _BIAS_GRAD),

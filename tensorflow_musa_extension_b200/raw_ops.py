@@ -756,3 +756,12 @@ def MusaBiasAddReluGrad(gradients, features, data_format="NHWC", name=None):
         _check(rc, "MusaBiasAddReluGrad")
     dx, db = hf.back_many([dx, db])
     return MusaBiasAddReluGradOutput(dx, db)
+
+
+# ------------------------------ Nadam, RMSProp, gradient descent (re-export) --
+# Defined in training_ops.py; imported last because that module uses the
+# helpers above.
+from .training_ops import (  # noqa: E402,F401
+    ApplyCenteredRMSProp, ApplyRMSProp, MusaGroupedResourceApplyGradientDescentMixed,
+    MusaResourceApplyGradientDescentMixed, ResourceApplyCenteredRMSProp,
+    ResourceApplyGradientDescent, ResourceApplyNadam, ResourceApplyRMSProp)

@@ -35,7 +35,8 @@ def pytest_collection_modifyitems(config, items):
 def golden():
     return {name: np.load(os.path.join(GOLDEN, name + ".npz"))
             for name in ("adam_reference_numpy", "bn_torch_cpu",
-                         "elementwise_literals", "bias_grad_torch_cpu")}
+                         "elementwise_literals", "bias_grad_torch_cpu",
+                         "optimizer_cases")}
 
 
 @pytest.fixture(scope="session")

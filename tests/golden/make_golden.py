@@ -1,7 +1,7 @@
 """Generates the golden vectors under tests/golden/ (run once, by hand, on a
 machine that has the reference checkout; the .npz files are committed).
 
-    python tests/golden/make_golden.py /path/to/reference [adam|bn|elementwise|bias_grad ...]
+    python tests/golden/make_golden.py /path/to/reference [adam|bn|elementwise|bias_grad|optimizers ...]
 
 What pins what:
   adam_reference_numpy.npz
@@ -28,6 +28,14 @@ What pins what:
       (test/ops/biasadd_grad_op_test.py:16-86: NHWC [2,8,8,32], NCHW
       [2,32,8,8]) plus a ragged 2-D case, answered by PyTorch's CPU autograd of
       relu(x + b) in float64: an independent implementation, not TensorFlow.
+  optimizer_cases.npz
+      Nadam at the shapes and hyper-parameters of the reference test
+      (test/ops/resource_apply_nadam_op_test.py:26-40, 88-106) with the formula
+      that test states (:57-67), RMSProp / centered RMSProp and gradient descent
+      at the literal inputs of their tests (test/ops/apply_rmsprop_op_test.py:
+      77-199, 256-330; test/ops/apply_gradient_descent_op_test.py:64-78,
+      97-101), all evaluated in float64.  The reference tests compare with
+      TensorFlow's CPU ops on a live device and hold no expected values.
 """
 import ast
 import os
@@ -200,10 +208,80 @@ def make_bias_grad():
     np.savez_compressed(os.path.join(HERE, "bias_grad_torch_cpu.npz"), **out)
 
 
+def make_optimizers():
+    out = {}
+    rng = np.random.default_rng(123)
+    f8 = np.float64
+    # Nadam: uniform inputs as the reference test draws them.
+    for name, shape in (("basic", (128, 128)), ("small", (7,)), ("half", (64, 64))):
+        var = rng.uniform(-1, 1, shape).astype(np.float32)
+        m = rng.uniform(-1, 1, shape).astype(np.float32)
+        v = rng.uniform(0.1, 1, shape).astype(np.float32)
+        g = rng.uniform(-1, 1, shape).astype(np.float32)
+        b1p, b2p, lr, b1, b2, eps = 0.9, 0.99, 0.01, 0.9, 0.99, 1e-8
+        m_new = b1 * m.astype(f8) + (1 - b1) * g.astype(f8)
+        v_new = b2 * v.astype(f8) + (1 - b2) * np.square(g.astype(f8))
+        m_hat = (b1 * m_new + (1 - b1) * g.astype(f8)) / (1 - b1p)
+        v_hat = v_new / (1 - b2p)
+        var_new = var.astype(f8) - lr * m_hat / (np.sqrt(v_hat) + eps)
+        k = "nadam/" + name
+        out.update({k + "/var": var, k + "/m": m, k + "/v": v, k + "/grad": g,
+                    k + "/hyper": np.array([b1p, b2p, lr, b1, b2, eps]),
+                    k + "/var_out": var_new, k + "/m_out": m_new, k + "/v_out": v_new})
+    # RMSProp: literal cases of the reference test.
+    rms_cases = {
+        "basic": ([1.0, 2.0, 3.0, 4.0], [0, 0, 0, 0], [0, 0, 0, 0], [0.1, 0.2, 0.3, 0.4],
+                  (0.01, 0.9, 0.9, 1e-8)),
+        "dtypes": ([1.0, 2.0, 3.0, 4.0], [0.1, 0.2, 0.3, 0.4], [0, 0, 0, 0],
+                   [0.1, 0.2, 0.3, 0.4], (0.01, 0.9, 0.9, 1e-7)),
+        "zero_grad": ([1.0, 2.0, 3.0, 4.0], [0.5, 0.6, 0.7, 0.8], [0, 0, 0, 0], [0, 0, 0, 0],
+                      (0.01, 0.9, 0.9, 1e-7)),
+        "negative_grad": ([1.0, 2.0, 3.0, 4.0], [0, 0, 0, 0], [0, 0, 0, 0],
+                          [-10.0, -5.0, -2.0, -1.0], (0.01, 0.9, 0.9, 1e-7)),
+    }
+    for name, (var, ms, mom, g, (lr, rho, mo, eps)) in rms_cases.items():
+        var, ms, mom, g = (np.array(a, np.float32) for a in (var, ms, mom, g))
+        ms_new = rho * ms.astype(f8) + (1 - rho) * np.square(g.astype(f8))
+        mom_new = mo * mom.astype(f8) + lr * g.astype(f8) / np.sqrt(ms_new + eps)
+        k = "rmsprop/" + name
+        out.update({k + "/var": var, k + "/ms": ms, k + "/mom": mom, k + "/grad": g,
+                    k + "/hyper": np.array([lr, rho, mo, eps]),
+                    k + "/var_out": var.astype(f8) - mom_new, k + "/ms_out": ms_new,
+                    k + "/mom_out": mom_new})
+    crms_cases = {
+        "basic": ([1.0, 2.0, 3.0, 4.0], [0] * 4, [0] * 4, [0] * 4, [0.1, 0.2, 0.3, 0.4],
+                  (0.01, 0.9, 0.9, 1e-8)),
+        "dtypes": ([1.0, 2.0, 3.0, 4.0, 5.0, 6.0], [0] * 6, [0.1, 0.2, 0.3, 0.4, 0.5, 0.6],
+                   [0] * 6, [0.1, 0.2, 0.3, 0.4, 0.5, 0.6], (0.01, 0.9, 0.9, 1e-7)),
+    }
+    for name, (var, mg, ms, mom, g, (lr, rho, mo, eps)) in crms_cases.items():
+        var, mg, ms, mom, g = (np.array(a, np.float32) for a in (var, mg, ms, mom, g))
+        mg_new = rho * mg.astype(f8) + (1 - rho) * g.astype(f8)
+        ms_new = rho * ms.astype(f8) + (1 - rho) * np.square(g.astype(f8))
+        mom_new = mo * mom.astype(f8) + lr * g.astype(f8) / np.sqrt(
+            ms_new - np.square(mg_new) + eps)
+        k = "centered_rmsprop/" + name
+        out.update({k + "/var": var, k + "/mg": mg, k + "/ms": ms, k + "/mom": mom,
+                    k + "/grad": g, k + "/hyper": np.array([lr, rho, mo, eps]),
+                    k + "/var_out": var.astype(f8) - mom_new, k + "/mg_out": mg_new,
+                    k + "/ms_out": ms_new, k + "/mom_out": mom_new})
+    sgd_cases = {
+        "vector": ([1.0, -2.0, 3.5, -4.5], 0.1, [0.5, -1.0, 2.0, 0.25]),
+        "matrix": ([[1.0, 2.0], [3.0, 4.0]], 0.25, [[0.2, 0.4], [0.6, 0.8]]),
+        "locking": ([1.25, -2.5, 5.0, -10.0], 0.5, [0.5, 0.25, -1.0, 2.0]),
+    }
+    for name, (var, alpha, g) in sgd_cases.items():
+        var, g = np.array(var, np.float32), np.array(g, np.float32)
+        k = "sgd/" + name
+        out.update({k + "/var": var, k + "/grad": g, k + "/alpha": np.float64(alpha),
+                    k + "/var_out": var.astype(f8) - np.float64(np.float32(alpha)) * g.astype(f8)})
+    np.savez_compressed(os.path.join(HERE, "optimizer_cases.npz"), **out)
+
+
 if __name__ == "__main__":
     if len(sys.argv) < 2:
         sys.exit(__doc__)
-    which = sys.argv[2:] or ["adam", "bn", "elementwise", "bias_grad"]
+    which = sys.argv[2:] or ["adam", "bn", "elementwise", "bias_grad", "optimizers"]
     if "adam" in which:
         make_adam(sys.argv[1])
     if "bn" in which:
@@ -212,4 +290,6 @@ if __name__ == "__main__":
         make_elementwise()
     if "bias_grad" in which:
         make_bias_grad()
+    if "optimizers" in which:
+        make_optimizers()
     print("wrote golden vectors to", HERE)

@@ -196,3 +196,61 @@ def test_bias_grad_oracle_edge_cases():
     assert np.array_equal(np_ref.relu_grad(gr, ft), np.array([0, 0, 0, 4], np.float32))
     with pytest.raises(ValueError):
         np_ref.relu_grad(np.zeros((2, 3), np.float32), np.zeros((3, 2), np.float32))
+
+
+# ------------------------------------------- Nadam, RMSProp, gradient descent --
+
+def _states(g, key, names):
+    return [g["%s/%s" % (key, n)] for n in names]
+
+
+def test_optimizer_oracle_matches_float64_statements(golden):
+    """fp32 restatements against the float64 evaluation of the formulas at the
+    reference tests' inputs: the difference is fp32 rounding only."""
+    g = golden["optimizer_cases"]
+    for case in ("basic", "small", "half"):
+        key = "nadam/" + case
+        var, m, v, grad = _states(g, key, ("var", "m", "v", "grad"))
+        got = np_ref.apply_nadam(var, m, v, *g[key + "/hyper"], grad)
+        for out, name in zip(got, ("var_out", "m_out", "v_out")):
+            np.testing.assert_allclose(out, g[key + "/" + name], rtol=2e-6, atol=1e-7)
+    for case in ("basic", "dtypes", "zero_grad", "negative_grad"):
+        key = "rmsprop/" + case
+        var, ms, mom, grad = _states(g, key, ("var", "ms", "mom", "grad"))
+        got = np_ref.apply_rms_prop(var, ms, mom, *g[key + "/hyper"], grad)
+        for out, name in zip(got, ("var_out", "ms_out", "mom_out")):
+            np.testing.assert_allclose(out, g[key + "/" + name], rtol=2e-6, atol=1e-7)
+    for case in ("basic", "dtypes"):
+        key = "centered_rmsprop/" + case
+        var, mg, ms, mom, grad = _states(g, key, ("var", "mg", "ms", "mom", "grad"))
+        got = np_ref.apply_centered_rms_prop(var, mg, ms, mom, *g[key + "/hyper"], grad)
+        for out, name in zip(got, ("var_out", "mg_out", "ms_out", "mom_out")):
+            np.testing.assert_allclose(out, g[key + "/" + name], rtol=2e-6, atol=1e-7)
+    for case in ("vector", "matrix", "locking"):
+        key = "sgd/" + case
+        got = np_ref.apply_gradient_descent(g[key + "/var"], float(g[key + "/alpha"]),
+                                            g[key + "/grad"])
+        np.testing.assert_allclose(got, g[key + "/var_out"], rtol=2e-7, atol=1e-7)
+
+
+def test_optimizer_oracle_low_precision_and_double():
+    from helpers import NP_BF16
+    rng = np.random.default_rng(4)
+    var = rng.standard_normal(64)
+    ms = np.abs(rng.standard_normal(64)) * 0.1
+    mom = rng.standard_normal(64) * 0.01
+    grad = rng.standard_normal(64)
+    want = np_ref.apply_rms_prop(*(a.astype(np.float64) for a in (var, ms, mom)),
+                                 0.01, 0.9, 0.9, 1e-7, grad.astype(np.float64))
+    for dt, tol in ((np.float16, 2e-3), (NP_BF16, 2e-2)):
+        got = np_ref.apply_rms_prop(*(a.astype(dt) for a in (var, ms, mom)),
+                                    0.01, 0.9, 0.9, 1e-7, grad.astype(dt))
+        for a, b in zip(got, want):
+            assert a.dtype == dt
+            np.testing.assert_allclose(a.astype(np.float64), b, rtol=tol * 4, atol=tol)
+    # 16-bit gradient descent rounds the product before the subtraction.
+    v16 = np.array([1.0], np.float16)
+    d16 = np.array([0.3333], np.float16)
+    step = np.float16(np.float16(0.1).astype(np.float32) * d16.astype(np.float32))
+    assert np_ref.apply_gradient_descent(v16, 0.1, d16)[0] == np.float16(
+        np.float32(1.0) - np.float32(step[0]))
