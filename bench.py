@@ -384,8 +384,14 @@ def run_ours(args):
 
 def measure_e2e(torch, dist, raw_ops, layers, world, rank, dev, args):
     """The same step through the public ops with HOST buffers: every layer's x
-    and dy start in pinned host memory and y / dx (and the statistics) are read
-    back, all inside the timed region."""
+    and dy start in pinned host memory, y / dx and the statistics are read back
+    to the host, all inside the timed region.  The ops are driven through the
+    package's staging pipeline (upload, compute and download streams), so the
+    PCIe transfers of neighbouring layers overlap the kernels and each other;
+    x stays on the device between a layer's forward and its gradient.
+    `blocking` is the same step with one blocking op call per layer."""
+    import collections
+    from tensorflow_musa_extension_b200.staging import StagedPipeline
     shapes = sorted({(BATCH * h * w, c) for (h, w, c) in layers})
     gen = torch.Generator()
     gen.manual_seed(40 + rank)
@@ -401,46 +407,89 @@ def measure_e2e(torch, dist, raw_ops, layers, world, rank, dev, args):
     empty = torch.empty(0)
     from tensorflow_musa_extension_b200 import cross_replica as cr
     group = dist.group.WORLD if world > 1 else None
+    depth = args.e2e_depth
+    pipe = StagedPipeline(dev, depth=depth)
 
     def step():
-        saved = []
+        pending = collections.deque()
+
+        def collect(limit):
+            while len(pending) > limit:
+                call = pending.popleft()
+                call.result()          # host tensors: y / dx and the statistics
+                call.release()
+
+        fwd = []
         for (h, w, c) in layers:
             x, _ = host[(BATCH * h * w, c)]
             s, o = par[c]
             if world > 1:
-                out = cr.sync_batch_norm_forward(x, s, o, EPS, group)
+                call = pipe.submit(cr.sync_batch_norm_forward, x, s, o, EPS, group)
             else:
-                out = raw_ops.FusedBatchNormV3(x, s, o, empty, empty, epsilon=EPS)
+                call = pipe.submit(raw_ops.FusedBatchNormV3, x, s, o, empty, empty, epsilon=EPS)
+            fwd.append(call)
+            pending.append(call)
+            collect(depth)
+        for (h, w, c), f in zip(reversed(layers), reversed(fwd)):
+            _, dy = host[(BATCH * h * w, c)]
+            s, _ = par[c]
+            if world > 1:
+                call = pipe.submit(cr.sync_batch_norm_backward, dy, f.input(0), s, f.output(3),
+                                   f.output(4), EPS, group)
+            else:
+                call = pipe.submit(raw_ops.FusedBatchNormGradV3, dy, f.input(0), s, f.output(3),
+                                   f.output(4), None, epsilon=EPS)
+            pending.append(call)
+            collect(depth)
+        collect(0)
+
+    def step_blocking():
+        saved = []
+        for (h, w, c) in layers:
+            x, _ = host[(BATCH * h * w, c)]
+            s, o = par[c]
+            out = raw_ops.FusedBatchNormV3(x, s, o, empty, empty, epsilon=EPS)
             saved.append((out[3], out[4]))
         for (h, w, c), (mean, var) in zip(reversed(layers), reversed(saved)):
             x, dy = host[(BATCH * h * w, c)]
             s, _ = par[c]
-            if world > 1:
-                cr.sync_batch_norm_backward(dy, x, s, mean, var, EPS, group)
-            else:
-                raw_ops.FusedBatchNormGradV3(dy, x, s, mean, var, None, epsilon=EPS)
+            raw_ops.FusedBatchNormGradV3(dy, x, s, mean, var, None, epsilon=EPS)
+
+    def timed(fn, steps):
+        fn()  # warm up: staging pools and allocator growth
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        return dt / steps
 
     elems = 2 * sum(BATCH * h * w * c for (h, w, c) in layers)
-    h2d = sum(BATCH * h * w * c * 2 for (h, w, c) in layers) * 3  # x (fwd), dy + x (grad)
-    d2h = sum(BATCH * h * w * c * 2 for (h, w, c) in layers) * 2  # y, dx
+    tensor_bytes = sum(BATCH * h * w * c * 2 for (h, w, c) in layers)
     steps = max(1, min(args.steps, args.e2e_steps))
-    step()  # warm up: pinned-pool and allocator growth
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([dt], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
-    return {"value": round(world * elems * steps / dt / 1e9, 3), "unit": UNIT,
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
-            "ms_per_step": round(dt / steps * 1e3, 2),
-            "api": ("raw_ops.FusedBatchNormV3 / FusedBatchNormGradV3" if world == 1 else "cross_replica.sync_batch_norm_forward / _backward") + " on pinned host tensors"}
+    sec = timed(step, steps)
+    pipe.close()
+    out = {"value": round(world * elems / sec / 1e9, 3), "unit": UNIT,
+           "h2d_bytes_per_step": 2 * tensor_bytes,   # x (forward), dy (gradient)
+           "d2h_bytes_per_step": 2 * tensor_bytes,   # y, dx
+           "steps": steps, "ms_per_step": round(sec * 1e3, 2), "pipeline_depth": depth,
+           "api": ("staging.StagedPipeline.submit(" +
+                   ("raw_ops.FusedBatchNormV3 / FusedBatchNormGradV3" if world == 1 else
+                    "cross_replica.sync_batch_norm_forward / _backward") +
+                   ") on pinned host tensors")}
+    if world == 1:
+        sec_b = timed(step_blocking, 1)
+        out["blocking"] = {"value": round(elems / sec_b / 1e9, 3), "ms_per_step": round(sec_b * 1e3, 2),
+                           "h2d_bytes_per_step": 3 * tensor_bytes, "d2h_bytes_per_step": 2 * tensor_bytes,
+                           "api": "one blocking raw_ops call per layer (x uploaded again for the gradient)"}
+    return out
 
 
 def measure_adam_sharded(torch, dist, world, rank, dev, exchange, args):
@@ -846,6 +895,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="time eager launches")
+    ap.add_argument("--e2e-depth", type=int, default=6,
+                    help="calls in flight in the staging pipeline of the end-to-end leg")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-ops", action="store_true")

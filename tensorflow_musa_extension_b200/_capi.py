@@ -133,6 +133,29 @@ EXTRA_PROTOTYPES = {
     "MusaKernelsGetTuning": (c_int, [c_int]),
 }
 
+# Entry points of include/musa_plugin_runtime.h that the staging pipeline
+# drives (streams, events, asynchronous copies, the pinned pool).
+c_u64 = ctypes.c_uint64
+_P_VP = ctypes.POINTER(c_vp)
+RUNTIME_PROTOTYPES = {
+    "MusaRtLastError": (ctypes.c_char_p, []),
+    "MusaRtCreateDevice": (c_int, [c_int]),
+    "MusaRtCreateStream": (c_int, [c_int, _P_VP]),
+    "MusaRtDestroyStream": (c_int, [c_int, c_vp]),
+    "MusaRtRawStream": (c_vp, [c_vp]),
+    "MusaRtCreateEvent": (c_int, [c_int, _P_VP]),
+    "MusaRtDestroyEvent": (c_int, [c_int, c_vp]),
+    "MusaRtRecordEvent": (c_int, [c_int, c_vp, c_vp]),
+    "MusaRtGetEventStatus": (c_int, [c_int, c_vp]),
+    "MusaRtWaitForEvent": (c_int, [c_int, c_vp, c_vp]),
+    "MusaRtBlockHostForEvent": (c_int, [c_int, c_vp]),
+    "MusaRtBlockHostUntilDone": (c_int, [c_int, c_vp]),
+    "MusaRtMemcpyDtoH": (c_int, [c_int, c_vp, c_vp, c_vp, c_u64]),
+    "MusaRtMemcpyHtoD": (c_int, [c_int, c_vp, c_vp, c_vp, c_u64]),
+    "MusaRtPinnedAllocate": (c_vp, [c_int, c_u64]),
+    "MusaRtPinnedFreeAsync": (c_int, [c_int, c_vp, c_u64, c_vp]),
+}
+
 ERROR_NAMES = {
     -1: "invalid argument (null pointer or negative size)",
     -2: "workspace missing, misaligned or too small",
@@ -143,7 +166,7 @@ ERROR_NAMES = {
 
 def bind(lib):
     """Attach prototypes; AttributeError names the first missing symbol."""
-    for table in (PROTOTYPES, EXTRA_PROTOTYPES):
+    for table in (PROTOTYPES, EXTRA_PROTOTYPES, RUNTIME_PROTOTYPES):
         for name, (restype, argtypes) in table.items():
             fn = getattr(lib, name)
             fn.restype = restype

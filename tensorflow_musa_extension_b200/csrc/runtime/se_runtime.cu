@@ -94,6 +94,43 @@ int HtoD(int ordinal, StreamHandle stream, void* dst, const void* src, uint64_t 
                            : d->MemcpyAsync(dst, src, size, CopyKind::kHostToDevice, stream),
                       sync ? "cudaMemcpy H2D" : "cudaMemcpyAsync H2D");
   }
+  if (!sync && !EnvIsOne("MUSA_SE_DISABLE_PAGEABLE_H2D_BOUNCE") &&
+      !EnvIsOne("MUSA_SE_DISABLE_ASYNC_H2D_BOUNCE")) {
+    // Pageable source on an asynchronous copy: stage it through pinned chunks.
+    // The host copy of chunk k+1 runs while the DMA of chunk k is in flight,
+    // every chunk goes back to the pool once the stream has passed it, and the
+    // source is fully read by the time this returns, so the caller may reuse
+    // it at once.  (The reference falls back to a blocking cudaMemcpy here.)
+    PinnedMemoryPool* chunk_pool = RegistryPinnedPool(ordinal);
+    if (chunk_pool != nullptr) {
+      constexpr uint64_t kChunk = 8ull << 20;
+      uint64_t done = 0;
+      while (done < size) {
+        const uint64_t len = size - done < kChunk ? size - done : kChunk;
+        void* staging = chunk_pool->Allocate(len);
+        if (staging == nullptr) break;
+        std::memcpy(staging, static_cast<const char*>(src) + done, len);
+        const int rc = d->MemcpyAsync(static_cast<char*>(dst) + done, staging, len,
+                                      CopyKind::kHostToDevice, stream);
+        if (rc != 0) {
+          chunk_pool->FreeCompleted(staging, len);
+          return Fail(kInternal, "cudaMemcpyAsync H2D via pinned bounce buffer failed");
+        }
+        chunk_pool->FreeAsync(staging, len, stream);
+        done += len;
+      }
+      if (done == size) return Ok();
+      // Out of pinned memory part-way: the rest goes the blocking way, after
+      // the chunks already queued on the stream.
+      int rc = d->StreamSynchronize(stream);
+      if (rc == 0) {
+        rc = d->Memcpy(static_cast<char*>(dst) + done,
+                       static_cast<const char*>(src) + done, size - done,
+                       CopyKind::kHostToDevice);
+      }
+      return FromDriver(rc, "cudaMemcpy H2D");
+    }
+  }
   const bool bounce = sync && !EnvIsOne("MUSA_SE_DISABLE_PAGEABLE_H2D_BOUNCE") &&
                       !EnvIsOne("MUSA_SE_DISABLE_SYNC_H2D_BOUNCE");
   PinnedMemoryPool* pool = bounce ? RegistryPinnedPool(ordinal) : nullptr;

@@ -242,11 +242,26 @@ def case_pageable_bounce():
         ok(L.MusaRtSyncMemcpyHtoD(0, a, nparr(src), n))
         assert stats()["reuse_hits"] == 1, var           # pool untouched
         del os.environ[var]
-    # the asynchronous form never stages a pageable source
+    # the asynchronous form stages a pageable source too: the call returns with
+    # the source fully read, the staging block goes back to the pool only after
+    # the stream has passed the copy
     s = new_stream()
-    ok(L.MusaRtMemcpyHtoD(0, s, a, nparr(src), n))
+    gate = L.MusaRtFakeBlockStream(s)
+    src2 = src.copy()
+    ok(L.MusaRtMemcpyHtoD(0, s, a, nparr(src2), n))
+    src2[:] = 0                                          # caller reuses its buffer at once
+    st = stats()
+    assert st["reuse_hits"] == 2 and st["pending_blocks"] == 1 and st["free_blocks"] == 0
+    L.MusaRtFakeReleaseGate(gate)
     ok(L.MusaRtBlockHostUntilDone(0, s))
-    assert stats()["reuse_hits"] == 1
+    wait_for(lambda: stats()["free_blocks"] == 1)
+    back[:] = 0
+    ok(L.MusaRtSyncMemcpyDtoH(0, nparr(back), a, n))
+    assert np.array_equal(src, back)
+    os.environ["MUSA_SE_DISABLE_ASYNC_H2D_BOUNCE"] = "1"   # the reference's blocking copy
+    ok(L.MusaRtMemcpyHtoD(0, s, a, nparr(src), n))
+    assert stats()["reuse_hits"] == 2
+    del os.environ["MUSA_SE_DISABLE_ASYNC_H2D_BOUNCE"]
     ok(L.MusaRtHostDeallocate(0, pinned))
     ok(L.MusaRtDeallocate(0, a))
     ok(L.MusaRtDestroyStream(0, s))
