@@ -680,6 +680,37 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     entry("bias_add_grad_f16", ms, 2 * x.numel(), x.numel(), "L2 flushed before each launch")
     del x, y, gr
 
+    # Row normalisations at the chain's shape, bf16 [65536, 1024] (S = 134 MB).
+    rows, n = 65536, 1024
+    x = (torch.randn(rows, n, device=dev) * 3 + 1).to(torch.bfloat16)
+    dy = torch.randn(rows, n, device=dev).to(torch.bfloat16)
+    y = torch.empty_like(x)
+    y2 = torch.empty_like(x)
+    gam = torch.ones(n, device=dev, dtype=torch.bfloat16)
+    bet = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+    dgam, dbet = torch.empty_like(gam), torch.empty_like(bet)
+    inv = torch.empty(rows, device=dev, dtype=torch.bfloat16)
+    need = lib.LayerNormGradWorkspaceBytes(rows, n)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    s_bytes = x.numel() * 2
+    ms = time_launch(torch, lambda: lib.LaunchLayerNorm_BF16(
+        x.data_ptr(), gam.data_ptr(), bet.data_ptr(), y.data_ptr(), None, None, rows, n, 1e-5,
+        st), iters)
+    entry("layer_norm_bf16", ms, 2 * s_bytes, x.numel(), "inputs exceed L2")
+    ms = time_launch(torch, lambda: lib.LaunchLayerNormGrad_BF16(
+        dy.data_ptr(), x.data_ptr(), gam.data_ptr(), y.data_ptr(), dgam.data_ptr(),
+        dbet.data_ptr(), rows, n, 1e-5, ws.data_ptr(), need, st), iters)
+    entry("layer_norm_grad_bf16", ms, 3 * s_bytes, x.numel(), "inputs exceed L2")
+    ms = time_launch(torch, lambda: lib.LaunchRmsNormBFloat16(
+        x.data_ptr(), gam.data_ptr(), y.data_ptr(), y2.data_ptr(), inv.data_ptr(), rows, n,
+        1e-5, st), iters)
+    entry("rms_norm_bf16", ms, 3 * s_bytes, x.numel(), "inputs exceed L2")
+    ms = time_launch(torch, lambda: lib.LaunchRmsNormGradDxBFloat16(
+        x.data_ptr(), inv.data_ptr(), gam.data_ptr(), dy.data_ptr(), y.data_ptr(), rows, n, st),
+        iters)
+    entry("rms_norm_grad_dx_bf16", ms, 3 * s_bytes, x.numel(), "inputs exceed L2")
+    del x, dy, y, y2
+
     # BatchNorm single layers: config 1 (fp32) and config 2 (fp16, bf16).
     for name, shape, dt, sfx in (("cfg1_f32", (32 * 56 * 56, 64), torch.float32, "F32"),
                                  ("cfg2_f16", (256 * 28 * 28, 256), torch.float16, "F16"),

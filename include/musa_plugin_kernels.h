@@ -334,6 +334,69 @@ int LaunchBiasAddReluGrad_BF16(const void* gradients, const void* features,
                                int64_t channels, int64_t inner, void* workspace,
                                size_t workspace_bytes, cudaStream_t stream);
 
+/* --------------------------------------------- LayerNorm and RMSNorm rows -- */
+
+/* MusaLayerNorm over [rows, row_size] (the op normalises the last axis):
+ *   y = (x - mean) * rsqrt(var + epsilon) * gamma + beta, population variance,
+ * statistics in fp32.  `mean` / `inv_std` are optional fp32 [rows] outputs
+ * (NULL: not stored).  One read of x, one write of y.  Replaces the muDNN
+ * LayerNorm call and its MemoryMaintainer
+ * (musa_ext/kernels/fusion/musa_layernorm_op.cc:61-98), registered for float,
+ * half and bfloat16 (:106-116). */
+int LaunchLayerNorm_F32(const void* x, const void* gamma, const void* beta, void* y,
+                        float* mean, float* inv_std, int64_t rows, int64_t row_size,
+                        float epsilon, cudaStream_t stream);
+int LaunchLayerNorm_F16(const void* x, const void* gamma, const void* beta, void* y,
+                        float* mean, float* inv_std, int64_t rows, int64_t row_size,
+                        float epsilon, cudaStream_t stream);
+int LaunchLayerNorm_BF16(const void* x, const void* gamma, const void* beta, void* y,
+                         float* mean, float* inv_std, int64_t rows, int64_t row_size,
+                         float epsilon, cudaStream_t stream);
+
+/* Scratch of LaunchLayerNormGrad_*: the partial rows of the dgamma / dbeta
+ * column sums. */
+size_t LayerNormGradWorkspaceBytes(int64_t rows, int64_t row_size);
+
+/* MusaLayerNormGrad: with x_hat = (x - mean) * inv_std and g = dy * gamma,
+ *   dx = inv_std * (g - mean_row(g) - x_hat * mean_row(g * x_hat)),
+ *   dgamma = sum_rows dy * x_hat,  dbeta = sum_rows dy   (type T, fixed order).
+ * The row statistics are recomputed from x (the op has no saved statistics).
+ * One read of dy and x, one write of dx.  rows == 0 zero-fills dgamma / dbeta.
+ * Replaces the muDNN LayerNorm backward of
+ * musa_ext/kernels/fusion/musa_layernorm_grad_op.cc. */
+int LaunchLayerNormGrad_F32(const void* dy, const void* x, const void* gamma, void* dx,
+                            void* dgamma, void* dbeta, int64_t rows, int64_t row_size,
+                            float epsilon, void* workspace, size_t workspace_bytes,
+                            cudaStream_t stream);
+int LaunchLayerNormGrad_F16(const void* dy, const void* x, const void* gamma, void* dx,
+                            void* dgamma, void* dbeta, int64_t rows, int64_t row_size,
+                            float epsilon, void* workspace, size_t workspace_bytes,
+                            cudaStream_t stream);
+int LaunchLayerNormGrad_BF16(const void* dy, const void* x, const void* gamma, void* dx,
+                             void* dgamma, void* dbeta, int64_t rows, int64_t row_size,
+                             float epsilon, void* workspace, size_t workspace_bytes,
+                             cudaStream_t stream);
+
+/* MusaRmsNorm: inv_rms[row] = rsqrt(mean(x^2) + epsilon); normalized = x *
+ * inv_rms; y = normalized * gamma.  Names and arguments of the reference
+ * (musa_ext/kernels/nn/musa_rmsnorm_kernel.mu:357-428; declared for the op at
+ * musa_ext/kernels/nn/musa_rmsnorm_op.cc:8-19); bfloat16 pointers are passed
+ * as void*.  bfloat16 results round to nearest even (the reference truncates). */
+void LaunchRmsNormFloat(const float* x, const float* gamma, float* y, float* normalized,
+                        float* inv_rms, int64_t num_rows, int64_t row_size,
+                        float epsilon, cudaStream_t stream);
+void LaunchRmsNormBFloat16(const void* x, const void* gamma, void* y, void* normalized,
+                           void* inv_rms, int64_t num_rows, int64_t row_size,
+                           float epsilon, cudaStream_t stream);
+/* MusaRmsNormGradDx: dx = dy * gamma * inv_rms - x * (sum_row(x * dy * gamma) *
+ * inv_rms^3 / row_size) (musa_ext/kernels/nn/musa_rmsnorm_kernel.mu:381-451). */
+void LaunchRmsNormGradDxFloat(const float* x, const float* inv_rms, const float* gamma,
+                              const float* dy, float* dx, int64_t num_rows,
+                              int64_t row_size, cudaStream_t stream);
+void LaunchRmsNormGradDxBFloat16(const void* x, const void* inv_rms, const void* gamma,
+                                 const void* dy, void* dx, int64_t num_rows,
+                                 int64_t row_size, cudaStream_t stream);
+
 /* ------------------------------------------------------ FusedBatchNorm -- */
 
 /* Tensor geometry: x, y, dy, dx are [outer, channels, inner], the statistics

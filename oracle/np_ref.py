@@ -368,3 +368,66 @@ def apply_gradient_descent(var, alpha, delta):
     a = np.asarray(alpha).astype(var.dtype).astype(ct)
     step = (a * delta.astype(ct)).astype(var.dtype).astype(ct)
     return (var.astype(ct) - step).astype(var.dtype)
+
+
+# --------------------------------------------------------------------------
+# LayerNorm and RMSNorm over the last axis
+# --------------------------------------------------------------------------
+
+def layer_norm(x, gamma, beta, epsilon=1e-5):
+    """MusaLayerNorm: y = (x - mean) / sqrt(var + eps) * gamma + beta over the
+    last axis, population variance, statistics in fp64, one rounding to the
+    tensor's type (musa_ext/kernels/fusion/musa_layernorm_op.cc:26-100; the
+    reference test compares with Keras LayerNormalization,
+    test/ops/layernorm_op_test.py:32-70)."""
+    x = np.asarray(x)
+    xf = x.astype(np.float64)
+    mean = xf.mean(axis=-1, keepdims=True)
+    var = np.square(xf - mean).mean(axis=-1, keepdims=True)
+    y = (xf - mean) / np.sqrt(var + epsilon) * np.asarray(gamma).astype(np.float64) \
+        + np.asarray(beta).astype(np.float64)
+    return y.astype(x.dtype)
+
+
+def layer_norm_grad(dy, x, gamma, epsilon=1e-5):
+    """MusaLayerNormGrad: (dx, dgamma, dbeta)
+    (musa_ext/kernels/fusion/musa_layernorm_grad_op.cc:23-141)."""
+    x = np.asarray(x)
+    xf, d = x.astype(np.float64), np.asarray(dy).astype(np.float64)
+    g = np.asarray(gamma).astype(np.float64)
+    mean = xf.mean(axis=-1, keepdims=True)
+    var = np.square(xf - mean).mean(axis=-1, keepdims=True)
+    inv = 1.0 / np.sqrt(var + epsilon)
+    xh = (xf - mean) * inv
+    gd = d * g
+    dx = inv * (gd - gd.mean(axis=-1, keepdims=True)
+                - xh * (gd * xh).mean(axis=-1, keepdims=True))
+    red = tuple(range(x.ndim - 1))
+    return (dx.astype(x.dtype), (d * xh).sum(axis=red).astype(x.dtype),
+            d.sum(axis=red).astype(x.dtype))
+
+
+def rms_norm(x, gamma, epsilon=1e-5):
+    """MusaRmsNorm: inv = 1/sqrt(mean(x^2) + eps); normalized = x * inv;
+    y = normalized * gamma; returns (y, normalized, inv_rms[..., 1])
+    (musa_ext/kernels/nn/musa_rmsnorm_kernel.mu:58-92).  y is computed from the
+    unrounded normalized value, as the kernel does."""
+    x = np.asarray(x)
+    xf = x.astype(np.float64)
+    inv = 1.0 / np.sqrt(np.square(xf).mean(axis=-1, keepdims=True) + epsilon)
+    norm = xf * inv
+    return ((norm * np.asarray(gamma).astype(np.float64)).astype(x.dtype),
+            norm.astype(x.dtype), inv.astype(x.dtype))
+
+
+def rms_norm_grad_dx(x, inv_rms, gamma, dy):
+    """MusaRmsNormGradDx: dx = dy*gamma*inv - x * (sum(x*dy*gamma) * inv^3 / n)
+    with inv read in the tensor's type
+    (musa_ext/kernels/nn/musa_rmsnorm_kernel.mu:171-204)."""
+    x = np.asarray(x)
+    xf, d = x.astype(np.float64), np.asarray(dy).astype(np.float64)
+    g = np.asarray(gamma).astype(np.float64)
+    inv = np.asarray(inv_rms).astype(np.float64).reshape(x.shape[:-1] + (1,))
+    dot = (xf * d * g).sum(axis=-1, keepdims=True)
+    coeff = dot * inv ** 3 / x.shape[-1]
+    return (d * g * inv - xf * coeff).astype(x.dtype)

@@ -18,6 +18,10 @@ _RMSPROP = [c_vp, c_vp, c_vp, c_vp] + [c_f64] * 4 + [c_i64, c_vp]
 _CRMSPROP = [c_vp] * 5 + [c_f64] * 4 + [c_i64, c_vp]
 _SGD = [c_vp, c_vp, c_f32, c_i64, c_vp]
 _SGD_TABLE = [c_vp] * 5 + [c_int, c_int, c_vp]
+_LAYER_NORM = [c_vp] * 6 + [c_i64, c_i64, c_f32, c_vp]
+_LAYER_NORM_GRAD = [c_vp] * 6 + [c_i64, c_i64, c_f32, c_vp, c_size, c_vp]
+_RMS_NORM = [c_vp] * 5 + [c_i64, c_i64, c_f32, c_vp]
+_RMS_NORM_GRAD = [c_vp] * 5 + [c_i64, c_i64, c_vp]
 _BIAS_GRAD = [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]
 _RELU_GRAD = [c_vp, c_vp, c_vp, c_i64, c_vp]
 _BIAS_RELU_GRAD = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]
@@ -62,6 +66,17 @@ PROTOTYPES = {
     "LaunchGroupedResourceApplyGradientDescentFloatBFloat16": (None, _SGD_TABLE),
     "LaunchGroupedGradientDescentHostTable":
         (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp]),
+    "LaunchLayerNorm_F32": (c_int, _LAYER_NORM),
+    "LaunchLayerNorm_F16": (c_int, _LAYER_NORM),
+    "LaunchLayerNorm_BF16": (c_int, _LAYER_NORM),
+    "LayerNormGradWorkspaceBytes": (c_size, [c_i64, c_i64]),
+    "LaunchLayerNormGrad_F32": (c_int, _LAYER_NORM_GRAD),
+    "LaunchLayerNormGrad_F16": (c_int, _LAYER_NORM_GRAD),
+    "LaunchLayerNormGrad_BF16": (c_int, _LAYER_NORM_GRAD),
+    "LaunchRmsNormFloat": (None, _RMS_NORM),
+    "LaunchRmsNormBFloat16": (None, _RMS_NORM),
+    "LaunchRmsNormGradDxFloat": (None, _RMS_NORM_GRAD),
+    "LaunchRmsNormGradDxBFloat16": (None, _RMS_NORM_GRAD),
     "BiasGradWorkspaceBytes": (c_size, [c_i64, c_i64, c_i64, c_int]),
     "LaunchBiasAddGrad_F32": (c_int, _BIAS_GRAD),
     "LaunchBiasAddGrad_F16": (c_int, _BIAS_GRAD),

@@ -765,3 +765,5 @@ from .training_ops import (  # noqa: E402,F401
     ApplyCenteredRMSProp, ApplyRMSProp, MusaGroupedResourceApplyGradientDescentMixed,
     MusaResourceApplyGradientDescentMixed, ResourceApplyCenteredRMSProp,
     ResourceApplyGradientDescent, ResourceApplyNadam, ResourceApplyRMSProp)
+from .norm_ops import (  # noqa: E402,F401
+    MusaLayerNorm, MusaLayerNormGrad, MusaRmsNorm, MusaRmsNormGradDx)

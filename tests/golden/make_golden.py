@@ -1,7 +1,7 @@
 """Generates the golden vectors under tests/golden/ (run once, by hand, on a
 machine that has the reference checkout; the .npz files are committed).
 
-    python tests/golden/make_golden.py /path/to/reference [adam|bn|elementwise|bias_grad|optimizers ...]
+    python tests/golden/make_golden.py /path/to/reference [adam|bn|elementwise|bias_grad|optimizers|row_norm ...]
 
 What pins what:
   adam_reference_numpy.npz
@@ -36,6 +36,12 @@ What pins what:
       77-199, 256-330; test/ops/apply_gradient_descent_op_test.py:64-78,
       97-101), all evaluated in float64.  The reference tests compare with
       TensorFlow's CPU ops on a live device and hold no expected values.
+  row_norm_torch_cpu.npz
+      LayerNorm forward / gradient at shapes of the reference test
+      (test/ops/layernorm_op_test.py:143-157, 211-240: [16,32], [8,16,32],
+      [32,128], [2,4,8,16], [100,1], [100,2], [1,1], [10,8192] (2 rows of it)) and RMSNorm
+      forward / gradient, answered by PyTorch's CPU layer_norm / rms_norm in
+      float64 and its autograd: an independent implementation.
 """
 import ast
 import os
@@ -278,10 +284,45 @@ def make_optimizers():
     np.savez_compressed(os.path.join(HERE, "optimizer_cases.npz"), **out)
 
 
+def make_row_norm():
+    import torch
+    import torch.nn.functional as F
+    rng = np.random.default_rng(321)
+    out = {}
+    shapes = {"s16x32": (16, 32), "s8x16x32": (8, 16, 32), "s32x128": (32, 128),
+              "s2x4x8x16": (2, 4, 8, 16), "s100x1": (100, 1), "s100x2": (100, 2),
+              "s1x1": (1, 1), "s2x8192": (2, 8192), "s7x1000": (7, 1000)}
+    for name, shape in shapes.items():
+        n = shape[-1]
+        x = rng.uniform(-2, 2, shape).astype(np.float32)
+        dy = rng.uniform(-1, 1, shape).astype(np.float32)
+        gamma = rng.uniform(0.5, 1.5, n).astype(np.float32)
+        beta = rng.uniform(-0.5, 0.5, n).astype(np.float32)
+        eps = 1e-5
+        xt = torch.from_numpy(x).double().requires_grad_(True)
+        gt = torch.from_numpy(gamma).double().requires_grad_(True)
+        bt = torch.from_numpy(beta).double().requires_grad_(True)
+        y = F.layer_norm(xt, (n,), gt, bt, eps)
+        y.backward(torch.from_numpy(dy).double())
+        k = "layer_norm/" + name
+        out.update({k + "/x": x, k + "/dy": dy, k + "/gamma": gamma, k + "/beta": beta,
+                    k + "/y": y.detach().numpy(), k + "/dx": xt.grad.numpy(),
+                    k + "/dgamma": gt.grad.numpy(), k + "/dbeta": bt.grad.numpy()})
+        xt2 = torch.from_numpy(x).double().requires_grad_(True)
+        g2 = torch.from_numpy(gamma).double()
+        y2 = F.rms_norm(xt2, (n,), g2, eps)
+        y2.backward(torch.from_numpy(dy).double())
+        inv = torch.rsqrt(xt2.detach().pow(2).mean(-1, keepdim=True) + eps)
+        k = "rms_norm/" + name
+        out.update({k + "/y": y2.detach().numpy(), k + "/normalized": (xt2.detach() * inv).numpy(),
+                    k + "/inv_rms": inv.numpy(), k + "/dx": xt2.grad.numpy()})
+    np.savez_compressed(os.path.join(HERE, "row_norm_torch_cpu.npz"), **out)
+
+
 if __name__ == "__main__":
     if len(sys.argv) < 2:
         sys.exit(__doc__)
-    which = sys.argv[2:] or ["adam", "bn", "elementwise", "bias_grad", "optimizers"]
+    which = sys.argv[2:] or ["adam", "bn", "elementwise", "bias_grad", "optimizers", "row_norm"]
     if "adam" in which:
         make_adam(sys.argv[1])
     if "bn" in which:
@@ -292,4 +333,6 @@ if __name__ == "__main__":
         make_bias_grad()
     if "optimizers" in which:
         make_optimizers()
+    if "row_norm" in which:
+        make_row_norm()
     print("wrote golden vectors to", HERE)

@@ -254,3 +254,33 @@ def test_optimizer_oracle_low_precision_and_double():
     step = np.float16(np.float16(0.1).astype(np.float32) * d16.astype(np.float32))
     assert np_ref.apply_gradient_descent(v16, 0.1, d16)[0] == np.float16(
         np.float32(1.0) - np.float32(step[0]))
+
+
+# ------------------------------------------------------ LayerNorm, RMSNorm --
+
+ROW_NORM_SHAPES = ["s16x32", "s8x16x32", "s32x128", "s2x4x8x16", "s100x1", "s100x2", "s1x1",
+                   "s2x8192", "s7x1000"]
+
+
+def test_row_norm_oracle_matches_independent_implementation(golden):
+    """LayerNorm / RMSNorm restatements against PyTorch's CPU layer_norm /
+    rms_norm (float64) and its autograd."""
+    g = golden["row_norm_torch_cpu"]
+    for name in ROW_NORM_SHAPES:
+        k = "layer_norm/" + name
+        x, dy, gamma, beta = (g[k + "/" + n] for n in ("x", "dy", "gamma", "beta"))
+        x64, dy64 = x.astype(np.float64), dy.astype(np.float64)
+        np.testing.assert_allclose(np_ref.layer_norm(x64, gamma, beta), g[k + "/y"],
+                                   rtol=1e-9, atol=1e-9)
+        dx, dgamma, dbeta = np_ref.layer_norm_grad(dy64, x64, gamma)
+        np.testing.assert_allclose(dx, g[k + "/dx"], rtol=1e-8, atol=1e-9)
+        np.testing.assert_allclose(dgamma, g[k + "/dgamma"], rtol=1e-9, atol=1e-9)
+        np.testing.assert_allclose(dbeta, g[k + "/dbeta"], rtol=1e-9, atol=1e-9)
+        r = "rms_norm/" + name
+        y, normalized, inv = np_ref.rms_norm(x64, gamma)
+        np.testing.assert_allclose(y, g[r + "/y"], rtol=1e-10, atol=1e-12)
+        np.testing.assert_allclose(normalized, g[r + "/normalized"], rtol=1e-10, atol=1e-12)
+        np.testing.assert_allclose(inv, g[r + "/inv_rms"], rtol=1e-12)
+        np.testing.assert_allclose(np_ref.rms_norm_grad_dx(x64, inv, gamma, dy64),
+                                   g[r + "/dx"], rtol=1e-8, atol=1e-10)
+        assert np_ref.layer_norm(x, gamma, beta).dtype == np.float32
