@@ -153,3 +153,26 @@ def test_full_size_fp16_chain(kernel_lib, chain, act):
         ulp_off = np.abs(got.view(np.int16).astype(np.int32)
                          - want.view(np.int16).astype(np.int32))
         assert ulp_off.max() <= 4 and (ulp_off > 0).mean() < 0.5
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_sigmoid_quads_with_far_negative_members(kernel_lib, dtype):
+    """Far negative and far positive inputs next to ordinary ones: every
+    element comes out right to relative precision (no cancellation on the
+    negative side, no overflow spilling into neighbours of the same pack)."""
+    dt = np_dtype(dtype)
+    base = np.array([0.5, -1.0, 2.0, -3.0, 10.0, -10.0, 0.0, 4.0], np.float32)
+    rows = []
+    for pos in range(8):
+        for far in (-20.0, -21.0, -30.0, -60.0, -87.0, -100.0, -1000.0, 25.0, 90.0):
+            r = base.copy()
+            r[pos] = far
+            rows.append(r)
+    x = np.stack(rows).astype(dt)
+    got = to_numpy(raw_ops.Sigmoid(to_torch(x)))
+    want = np_ref.sigmoid(x)
+    tiny = 1e-7 if dtype == "float16" else 1e-37      # below these the types flush to zero
+    assert_close(got, want, RTOL["lowp"], tiny, "sigmoid")
+    b = np.zeros(8, dt)
+    sw = to_numpy(raw_ops.MusaBiasAddSwish(to_torch(x), to_torch(b)))
+    assert_close(sw, np_ref.bias_add_swish(x, b), RTOL["lowp"], tiny * 1000, "swish")

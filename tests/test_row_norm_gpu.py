@@ -197,3 +197,39 @@ def test_full_size_properties(kernel_lib):
     assert_close(to_numpy(dbeta.float()), to_numpy(dy.float().sum(0)), 2e-2, 2.0, "dbeta")
     yr, nr, inv = raw_ops.MusaRmsNorm(x, g)
     assert ((nr.float() ** 2).mean(-1) - 1).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_keras_layer_norm_route_through_fused_batch_norm(kernel_lib, dtype):
+    """Keras runs rank-2 LayerNormalization as FusedBatchNormV3 on the NCHW view
+    [1, batch, features, 1] (one "channel" per row) and its gradient through
+    FusedBatchNormGradV3 with the population VARIANCE
+    (test/ops/fused_batchnorm_op_test.py:218-256: x of std 10, dy of std 1e-3).
+    That route and the LayerNorm ops give the same normalisation."""
+    rng = np.random.default_rng(42)
+    dt = np_dtype(dtype)
+    x = (10.0 * rng.normal(size=(128, 1536))).astype(np.float32).astype(dt)
+    dy = rng.normal(scale=1e-3, size=x.shape).astype(np.float32).astype(dt)
+    ones = np.ones(128, np.float32)
+    zeros = np.zeros(128, np.float32)
+    x4, dy4 = to_torch(x).reshape(1, 128, 1536, 1), to_torch(dy).reshape(1, 128, 1536, 1)
+    e = torch.empty(0, device="cuda")
+    fwd = raw_ops.FusedBatchNormV3(x4, to_torch(ones), to_torch(zeros), e, e, epsilon=1e-3,
+                                   data_format="NCHW")
+    grad = raw_ops.FusedBatchNormGradV3(dy4, x4, to_torch(ones), fwd[3], fwd[4], None,
+                                        epsilon=1e-3, data_format="NCHW")
+    g1 = np.ones(1536, dt)
+    b0 = np.zeros(1536, dt)
+    rt, at = (1e-4, 1e-5) if dtype == "float32" else (RTOL["lowp"], 2e-2)
+    assert_close(to_numpy(fwd[0]).reshape(128, 1536), np_ref.layer_norm(x, g1, b0, 1e-3), rt, at, "y")
+    want_dx = np_ref.layer_norm_grad(dy, x, g1, 1e-3)[0]
+    got_dx = to_numpy(grad[0]).reshape(128, 1536)
+    # the reference's own bound for this case: rtol 0.15, atol 5e-5
+    assert_close(got_dx, want_dx, 0.15 if dtype == "bfloat16" else 1e-3, 5e-5 if dtype == "bfloat16" else 1e-8, "dx")
+    assert np.abs(got_dx.astype(np.float64)).max() < 1e-3      # not blown up by the variance
+    ln = raw_ops.MusaLayerNorm(to_torch(x), to_torch(g1), to_torch(b0), epsilon=1e-3)
+    assert_close(to_numpy(ln), to_numpy(fwd[0]).reshape(128, 1536), rt, at, "layer norm op vs route")
+    ln_dx = raw_ops.MusaLayerNormGrad(to_torch(dy), to_torch(x), to_torch(g1), to_torch(b0),
+                                      epsilon=1e-3).dx
+    assert_close(to_numpy(ln_dx), want_dx, 0.15 if dtype == "bfloat16" else 1e-3,
+                 5e-5 if dtype == "bfloat16" else 1e-8, "layer norm grad op")
