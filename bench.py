@@ -858,7 +858,10 @@ def run_profile_case(args):
       bnsmall the same on bf16 [256,28,28,128] (S = 51 MB, inside L2)
       bnbig   gradient element-wise pass alone, bf16 [256,56,56,256], twice
       adam    ResourceApplyAdam fp32, 25,557,032 parameters, twice
-      bias    Relu(BiasAdd) and x*sigmoid(x+b), fp16 [65536,1024], twice each"""
+      bias    Relu(BiasAdd) and x*sigmoid(x+b), fp16 [65536,1024], twice each
+      biasgrad  fused ReluGrad+BiasAddGrad, ReluGrad, BiasAddGrad, fp16 [65536,1024]
+      optim   Nadam, RMSProp, gradient descent fp32, 25,557,032 parameters
+      rownorm LayerNorm fwd/grad and RMSNorm fwd/grad, bf16 [65536,1024]"""
     import torch
     import tensorflow_musa_extension_b200 as pkg
     from tensorflow_musa_extension_b200 import raw_ops
@@ -914,6 +917,53 @@ def run_profile_case(args):
             for act in (1, 2):
                 lib.LaunchBiasAct_F16(x.data_ptr(), b.data_ptr(), y.data_ptr(), 65536, 1024,
                                       1, act, st)
+    elif case == "biasgrad":
+        x = torch.relu(torch.randn(65536, 1024, device=dev, dtype=torch.float16))
+        g = torch.randn_like(x)
+        y = torch.empty_like(x)
+        db = torch.empty(1024, device=dev, dtype=torch.float16)
+        need = lib.BiasGradWorkspaceBytes(65536, 1024, 1, 2)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        for _ in range(2):
+            lib.LaunchBiasAddReluGrad_F16(g.data_ptr(), x.data_ptr(), y.data_ptr(), db.data_ptr(),
+                                          65536, 1024, 1, ws.data_ptr(), need, st)
+            lib.LaunchReluGrad_F16(g.data_ptr(), x.data_ptr(), y.data_ptr(), x.numel(), st)
+            lib.LaunchBiasAddGrad_F16(y.data_ptr(), db.data_ptr(), 65536, 1024, 1, ws.data_ptr(),
+                                      need, st)
+    elif case == "optim":
+        n = 25_557_032
+        var = torch.randn(n, device=dev) * 0.05
+        m = torch.randn(n, device=dev) * 1e-4
+        v = torch.rand(n, device=dev) * 1e-6
+        g = torch.randn(n, device=dev) * 1e-3
+        for _ in range(2):
+            lib.LaunchResourceApplyNadam_Float(var.data_ptr(), m.data_ptr(), v.data_ptr(),
+                                               g.data_ptr(), 0.9 ** 10, 0.999 ** 10, 1e-3, 0.9,
+                                               0.999, 1e-7, n, st)
+            lib.LaunchFusedResourceApplyRMSProp_Float(var.data_ptr(), v.data_ptr(), m.data_ptr(),
+                                                      g.data_ptr(), 1e-3, 0.9, 0.9, 1e-7, n, st)
+            lib.LaunchResourceApplyGradientDescentFloat(var.data_ptr(), g.data_ptr(), 1e-3, n, st)
+    elif case == "rownorm":
+        rows, n = 65536, 1024
+        x = (torch.randn(rows, n, device=dev) * 3 + 1).to(torch.bfloat16)
+        dy = torch.randn(rows, n, device=dev).to(torch.bfloat16)
+        y, y2 = torch.empty_like(x), torch.empty_like(x)
+        gam = torch.ones(n, device=dev, dtype=torch.bfloat16)
+        bet = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        dgam, dbet = torch.empty_like(gam), torch.empty_like(bet)
+        inv = torch.empty(rows, device=dev, dtype=torch.bfloat16)
+        need = lib.LayerNormGradWorkspaceBytes(rows, n)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        for _ in range(2):
+            lib.LaunchLayerNorm_BF16(x.data_ptr(), gam.data_ptr(), bet.data_ptr(), y.data_ptr(),
+                                     None, None, rows, n, 1e-5, st)
+            lib.LaunchLayerNormGrad_BF16(dy.data_ptr(), x.data_ptr(), gam.data_ptr(), y.data_ptr(),
+                                         dgam.data_ptr(), dbet.data_ptr(), rows, n, 1e-5,
+                                         ws.data_ptr(), need, st)
+            lib.LaunchRmsNormBFloat16(x.data_ptr(), gam.data_ptr(), y.data_ptr(), y2.data_ptr(),
+                                      inv.data_ptr(), rows, n, 1e-5, st)
+            lib.LaunchRmsNormGradDxBFloat16(x.data_ptr(), inv.data_ptr(), gam.data_ptr(),
+                                            dy.data_ptr(), y.data_ptr(), rows, n, st)
     else:
         raise SystemExit("unknown --profile-case " + case)
     torch.cuda.synchronize()
@@ -943,7 +993,7 @@ def main():
                     help="N = 1 diagnostic: run the cross-replica launch chain anyway")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed launch sequence and exit (ncu target): "
-                         "bn | bnsmall | bnbig | adam | bias")
+                         "bn | bnsmall | bnbig | adam | bias | biasgrad | optim | rownorm")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args)

@@ -122,16 +122,31 @@ __global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256))
   // accesses of a warp fall on different banks); a thread is the only one that
   // touches its columns of its slab.
   extern __shared__ uint4 ring[];
-  float* slab = reinterpret_cast<float*>(ring + kStages * kInputs * kMaxPacks * kThreads);
+  // After the ring: gamma (and beta for the LayerNorm forward) widened to fp32
+  // once per CTA, in the quad layout of the slabs below, then the slabs.
+  float* gsm = reinterpret_cast<float*>(ring + kStages * kInputs * kMaxPacks * kThreads);
+  float* bsm = gsm + a.row_size;
+  float* slab = gsm + (kOp == kOpLnFwd ? 2 : 1) * a.row_size;
 
   const int t = threadIdx.x % kGroup;
   const int lane_row = threadIdx.x / kGroup;
   const int packs = a.row_size / kVec;
   const float inv_n = 1.0f / static_cast<float>(a.row_size);
-  const P* gamma_p = reinterpret_cast<const P*>(a.gamma);
-  const P* beta_p = reinterpret_cast<const P*>(a.beta);
   float* my_slab = slab + static_cast<size_t>(lane_row) * 2 * a.row_size;
   uint4* const mine = ring + threadIdx.x;
+  // Quad h of pack p (elements 4h .. 4h+3) sits at ((h * packs + p) * 4): the
+  // 128-bit accesses of neighbouring lanes are 16 bytes apart.
+  const auto Quad = [&](const float* base, int h, int p) {
+    return *reinterpret_cast<const float4*>(base + (h * packs + p) * 4);
+  };
+  const auto LoadRowVector = [&](const float* base, int p, float2 (&out)[kPairs]) {
+#pragma unroll
+    for (int h = 0; h < kQuads; ++h) {
+      const float4 v = Quad(base, h, p);
+      out[2 * h] = make_float2(v.x, v.y);
+      out[2 * h + 1] = make_float2(v.z, v.w);
+    }
+  };
 
   if constexpr (kOp == kOpLnGrad) {
 #pragma unroll
@@ -149,6 +164,14 @@ __global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256))
 
   GridDepWait();
   GridDepLaunch();
+
+  for (int c = threadIdx.x; c < a.row_size; c += kThreads) {
+    const int e = c % kVec;
+    const int at = ((e / 4) * packs + c / kVec) * 4 + (e & 3);
+    gsm[at] = ToF32(static_cast<const T*>(a.gamma)[c]);
+    if constexpr (kOp == kOpLnFwd) bsm[at] = ToF32(static_cast<const T*>(a.beta)[c]);
+  }
+  __syncthreads();
 
   const int64_t n_blocks = (a.rows + kRows - 1) / kRows;
   // Queues the copies of row block `rb` into ring stage `stage`; always one
@@ -263,8 +286,8 @@ __global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256))
           const int p = t + j * kGroup;
           if (live && p < packs) {
             float2 gm[kPairs], bt[kPairs], o2[kPairs];
-            WidenPack<kVec>(LoadKeep(gamma_p + p), gm);
-            WidenPack<kVec>(LoadKeep(beta_p + p), bt);
+            LoadRowVector(gsm, p, gm);
+            LoadRowVector(bsm, p, bt);
 #pragma unroll
             for (int q = 0; q < kPairs; ++q) {
               o2[q] = Fma2(Mul2(xv[j][q], inv2), gm[q], bt[q]);
@@ -283,7 +306,7 @@ __global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256))
           const int p = t + j * kGroup;
           if (live && p < packs) {
             float2 gm[kPairs], dv[kPairs];
-            WidenPack<kVec>(LoadKeep(gamma_p + p), gm);
+            LoadRowVector(gsm, p, gm);
             WidenPack<kVec>(cd[j], dv);
 #pragma unroll
             for (int q = 0; q < kPairs; ++q) {
@@ -303,7 +326,7 @@ __global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256))
           const int p = t + j * kGroup;
           if (live && p < packs) {
             float2 gm[kPairs], dv[kPairs], o2[kPairs];
-            WidenPack<kVec>(LoadKeep(gamma_p + p), gm);
+            LoadRowVector(gsm, p, gm);
             WidenPack<kVec>(cd[j], dv);
 #pragma unroll
             for (int q = 0; q < kPairs; ++q) {
@@ -348,7 +371,7 @@ __global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256))
         const int p = t + j * kGroup;
         if (live && p < packs) {
           float2 gm[kPairs], n2[kPairs], o2[kPairs];
-          WidenPack<kVec>(LoadKeep(gamma_p + p), gm);
+          LoadRowVector(gsm, p, gm);
 #pragma unroll
           for (int q = 0; q < kPairs; ++q) {
             n2[q] = Mul2(xv[j][q], inv2);
@@ -369,7 +392,7 @@ __global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256))
         const int p = t + j * kGroup;
         if (live && p < packs) {
           float2 gm[kPairs], dv[kPairs];
-          WidenPack<kVec>(LoadKeep(gamma_p + p), gm);
+          LoadRowVector(gsm, p, gm);
           WidenPack<kVec>(cd[j], dv);
 #pragma unroll
           for (int q = 0; q < kPairs; ++q) {
@@ -561,14 +584,25 @@ constexpr int kMaxGradCtasPerSm = 4;  // bounds the partial rows of the gradient
 
 inline int MaxGradCtas() { return SmCount() * kMaxGradCtasPerSm; }
 
+// Dynamic shared memory of RowNormKernel: ring, widened gamma (and beta), and
+// the column-sum slabs of the LayerNorm gradient.
+template <int kOp>
+size_t RowSmemBytes(int threads, int rows_per_cta, int max_packs, int row_size) {
+  size_t bytes = static_cast<size_t>(RowPipe<kOp>::kStages) * RowPipe<kOp>::kInputs *
+                 max_packs * threads * 16;
+  bytes += static_cast<size_t>(kOp == kOpLnFwd ? 2 : 1) * row_size * sizeof(float);
+  if (kOp == kOpLnGrad) {
+    bytes += static_cast<size_t>(rows_per_cta) * 2 * row_size * sizeof(float);
+  }
+  return bytes;
+}
+
 template <typename T, int kGroup, int kMaxPacks, int kOp>
 int LaunchGroup(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   constexpr int kThreads = kGroup > 256 ? kGroup : 256;
   constexpr int kRows = kThreads / kGroup;
   auto kernel = RowNormKernel<T, kGroup, kMaxPacks, kOp>;
-  size_t smem = static_cast<size_t>(RowPipe<kOp>::kStages) * RowPipe<kOp>::kInputs *
-                kMaxPacks * kThreads * 16;
-  if (kOp == kOpLnGrad) smem += static_cast<size_t>(kRows) * 2 * a.row_size * sizeof(float);
+  size_t smem = RowSmemBytes<kOp>(kThreads, kRows, kMaxPacks, a.row_size);
   if (smem > 40 * 1024) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess) {
@@ -602,27 +636,36 @@ int LaunchLoop(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
                                         stream, a));
 }
 
+template <typename T, int kOp, int kMaxPacks>
+int DispatchPacks(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
+  constexpr int kVec = VecWidth<T>::value;
+  const int packs = a.row_size / kVec;
+  const auto fits = [&](int group) {
+    if (packs > group * kMaxPacks) return false;
+    const int threads = group > 256 ? group : 256;
+    return RowSmemBytes<kOp>(threads, threads / group, kMaxPacks, a.row_size) <= 200 * 1024;
+  };
+  if (fits(8)) return LaunchGroup<T, 8, kMaxPacks, kOp>(a, ctas_out, stream);
+  if (fits(32)) return LaunchGroup<T, 32, kMaxPacks, kOp>(a, ctas_out, stream);
+  if (fits(128)) return LaunchGroup<T, 128, kMaxPacks, kOp>(a, ctas_out, stream);
+  if (fits(256)) return LaunchGroup<T, 256, kMaxPacks, kOp>(a, ctas_out, stream);
+  if (fits(512)) return LaunchGroup<T, 512, kMaxPacks, kOp>(a, ctas_out, stream);
+  return -1;  // no register layout holds this row
+}
+
 template <typename T, int kOp>
 int Dispatch(const RowArgs& a, bool aligned, int* ctas_out, cudaStream_t stream) {
   constexpr int kVec = VecWidth<T>::value;
-  constexpr int kMaxPacks = 4;
   if (aligned && a.row_size % kVec == 0) {
-    const int packs = a.row_size / kVec;
-    const auto fits = [&](int group) {
-      if (packs > group * kMaxPacks) return false;
-      if (kOp != kOpLnGrad) return true;
-      // The column sums of the LayerNorm gradient live in shared memory, one
-      // slab per row lane.
-      const int threads = group > 256 ? group : 256;
-      const size_t smem = static_cast<size_t>(threads / group) * 2 * a.row_size * 4 +
-                          static_cast<size_t>(2) * 2 * kMaxPacks * threads * 16;
-      return smem <= 200 * 1024;
-    };
-    if (fits(8)) return LaunchGroup<T, 8, kMaxPacks, kOp>(a, ctas_out, stream);
-    if (fits(32)) return LaunchGroup<T, 32, kMaxPacks, kOp>(a, ctas_out, stream);
-    if (fits(128)) return LaunchGroup<T, 128, kMaxPacks, kOp>(a, ctas_out, stream);
-    if (fits(256)) return LaunchGroup<T, 256, kMaxPacks, kOp>(a, ctas_out, stream);
-    if (fits(512)) return LaunchGroup<T, 512, kMaxPacks, kOp>(a, ctas_out, stream);
+    // Four packs per thread keep short rows inside one warp (shuffle-only
+    // sums) and measured faster than one pack per thread on every op and
+    // shape tried; the tuning value 1 selects the other layout.
+    int want = GetTuning(kTuneRowNormPacks);
+    if (want != 1) want = 4;
+    int rc = -1;
+    if (want == 1) rc = DispatchPacks<T, kOp, 1>(a, ctas_out, stream);
+    if (rc == -1) rc = DispatchPacks<T, kOp, 4>(a, ctas_out, stream);
+    if (rc != -1) return rc;
   }
   return LaunchLoop<T, kOp>(a, ctas_out, stream);
 }
