@@ -337,7 +337,13 @@ class ShardedAdam:
 
     @staticmethod
     def _device_update(var, m, v, grad, b1p, b2p, lr, b1, b2, eps):
-        raw_ops.ResourceApplyAdam(var, m, v, b1p, b2p, lr, b1, b2, eps, grad)
+        # A 16-bit gradient against fp32 state is the mixed-precision op
+        # (musa_ext/kernels/training/musa_applyadam_mixed_op.cc:125-258): the
+        # gradient shard crosses HBM at half the width, nothing else changes.
+        if grad.dtype != var.dtype and var.dtype == torch.float32:
+            raw_ops.MusaResourceApplyAdamMixed(var, m, v, b1p, b2p, lr, b1, b2, eps, grad)
+        else:
+            raw_ops.ResourceApplyAdam(var, m, v, b1p, b2p, lr, b1, b2, eps, grad)
 
     def step(self, grad, lr, beta1_power, beta2_power):
         """`grad` is the full gradient vector or this replica's range of it."""

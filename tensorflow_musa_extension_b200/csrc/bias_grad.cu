@@ -23,6 +23,10 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxCtasPerSm = 8;
+// Column packs per CTA of the channels-last kernel: one warp reads 512
+// contiguous bytes of a row, and a CTA folds 8 rows at a time, which keeps the
+// number of partial rows (and with it the second level) small.
+constexpr int kColsPerCta = 32;
 
 // Accumulator of level 1 and the wider type of level 2.  Floating types
 // accumulate in fp32 (a thread adds a few dozen rows), level 2 in fp64.
@@ -412,7 +416,7 @@ inline int MaxSplits(const Geom& g, size_t elem) {
   if (g.inner == 1) {
     const int vec = static_cast<int>(16 / elem);
     const int64_t cv = CeilDiv(g.channels, vec);
-    const int64_t cols = cv < kThreads ? cv : kThreads;
+    const int64_t cols = cv < kColsPerCta ? cv : kColsPerCta;
     const int64_t grid_x = CeilDiv(cv, cols);
     const int64_t lanes = kThreads / cols;
     int64_t s = budget / grid_x;
@@ -441,7 +445,7 @@ int LaunchLast(const T* dy, const T* feat, T* dx,
   LastGeom lg;
   lg.rows = g.outer;
   lg.cv = static_cast<int>(g.channels / kVec);
-  lg.cols = lg.cv < kThreads ? lg.cv : kThreads;
+  lg.cols = lg.cv < kColsPerCta ? lg.cv : kColsPerCta;
   lg.lanes = kThreads / lg.cols;
   const int grid_x = static_cast<int>(CeilDiv(lg.cv, lg.cols));
 

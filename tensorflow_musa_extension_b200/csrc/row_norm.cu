@@ -103,8 +103,11 @@ struct RowPipe {
 // kStages - 1 blocks are in flight, whatever the register budget.  A thread
 // keeps its packs of the current row in registers in stored form and widens
 // them on each use.
+// The single-input forms fit three 256-thread CTAs per SM (56 KB of shared
+// memory each) when the compiler keeps them to 85 registers.
 template <typename T, int kGroup, int kMaxPacks, int kOp>
-__global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256))
+__global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256),
+                                  (kGroup <= 256 && (kOp == kOpLnFwd || kOp == kOpRmsFwd)) ? 3 : 1)
     RowNormKernel(RowArgs a) {
   constexpr int kThreads = kGroup > 256 ? kGroup : 256;
   constexpr int kRows = kThreads / kGroup;
@@ -609,6 +612,10 @@ int LaunchGroup(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
       return static_cast<int>(cudaGetLastError());
     }
   }
+  // Ask for the largest shared-memory carve-out: the ring, not L1, is what
+  // these kernels live on, and the default carve-out fits fewer CTAs.
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) !=
           cudaSuccess ||

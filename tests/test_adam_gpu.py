@@ -4,8 +4,8 @@ import pytest
 import torch
 
 from oracle import np_ref
-from helpers import (ADAM_HYPER, NP_BF16, RTOL, adam_inputs, assert_close, to_numpy,
-                     to_torch)
+from helpers import (ADAM_HYPER, NP_BF16, RTOL, adam_inputs, assert_close, np_dtype,
+                     to_numpy, to_torch)
 from tensorflow_musa_extension_b200 import errors, raw_ops
 
 pytestmark = pytest.mark.gpu
@@ -243,3 +243,34 @@ def test_sharded_broadcast_kernel_on_one_gpu(kernel_lib):
     for c_ in copies2:
         assert torch.equal(c_[3:1000], want[0][3:1000]) and torch.equal(c_[1000:], copies2[0][1000:])
         assert np.array_equal(to_numpy(c_[:3]), var[:3])
+
+
+@pytest.mark.parametrize("gdtype", ["float16", "bfloat16"])
+def test_sharded_adam_takes_16bit_gradients(kernel_lib, gdtype):
+    """The range-sharded optimizer with fp32 state and a 16-bit gradient runs
+    the mixed-precision op on its range: same bits as the op on the whole
+    vector (world size 1 here; the ranges of a larger world are disjoint
+    slices of the same update)."""
+    from tensorflow_musa_extension_b200.cross_replica import ShardedAdam
+    n = 100003
+    rng = np.random.default_rng(12)
+    var = rng.normal(0, 0.05, n).astype(np.float32)
+    grad = rng.normal(0, 1e-3, n).astype(np_dtype(gdtype))
+    h = ADAM_HYPER
+    tv = to_torch(var)
+    opt = ShardedAdam(tv, None, h["beta1"], h["beta2"], h["epsilon"])
+    opt.step(to_torch(grad), h["lr"], h["beta1_power"], h["beta2_power"])
+    wv, wm, wvv = (to_torch(a) for a in (var, np.zeros(n, np.float32), np.zeros(n, np.float32)))
+    raw_ops.MusaResourceApplyAdamMixed(wv, wm, wvv, h["beta1_power"], h["beta2_power"], h["lr"],
+                                       h["beta1"], h["beta2"], h["epsilon"], to_torch(grad))
+    assert torch.equal(tv, wv) and torch.equal(opt.m, wm) and torch.equal(opt.v, wvv)
+    # two disjoint ranges updated separately give the same bits
+    a, b = to_torch(var), to_torch(var)
+    cut = 50001
+    for lo, hi in ((0, cut), (cut, n)):
+        m0 = torch.zeros(hi - lo, device="cuda")
+        v0 = torch.zeros(hi - lo, device="cuda")
+        raw_ops.MusaResourceApplyAdamMixed(a[lo:hi], m0, v0, h["beta1_power"], h["beta2_power"],
+                                           h["lr"], h["beta1"], h["beta2"], h["epsilon"],
+                                           to_torch(grad)[lo:hi])
+    assert torch.equal(a, wv)
