@@ -48,6 +48,32 @@ int MusaGraphOptimizerListPatterns(char* buf, size_t cap);
  * unknown name. */
 int MusaGraphSetPatternEnabled(const char* pattern_name, int enabled);
 
+/* GraphDef dumps around the fusion pass: with dumping on, every optimizer run
+ * writes <dir>/musa_graph_optimizer_<id:04>_{initial,before_fusion,
+ * after_fusion,final}.pb (wire bytes, unknown fields included), plus .slim.pb
+ * (scalar attrs only) and .pbtxt (name / op / input / device / scalar attrs)
+ * when asked.  The override set here wins over the environment variables
+ * MUSA_DUMP_GRAPHDEF, MUSA_DUMP_GRAPHDEF_DIR, MUSA_DUMP_GRAPHDEF_TEXT,
+ * MUSA_DUMP_GRAPHDEF_SLIM until it is cleared.  Same names and arguments as
+ * the reference (musa_ext/mu/runtime_config_c_api.h:11-17, defined at
+ * musa_ext/mu/optimizer/graph_utils.cc:552-589). */
+void TFMusaSetGraphDumpConfig(int enabled, const char* dump_dir, int dump_text,
+                              int dump_slim);
+void TFMusaClearGraphDumpConfig(void);
+int TFMusaGraphDumpIsEnabled(void);
+const char* TFMusaGetGraphDumpDirectory(void);
+int TFMusaGraphDumpTextIsEnabled(void);
+int TFMusaGraphDumpSlimIsEnabled(void);
+
+/* Allow-growth switch that the platform registration reads when TensorFlow
+ * sets up the device allocator (musa_ext/mu/runtime_config_c_api.h:6, defined at
+ * musa_ext/mu/device_register.cc:155-157).  TFMusaGetAllowGrowth returns the
+ * effective value: TF_FORCE_GPU_ALLOW_GROWTH=true|false wins over the call
+ * (musa_ext/mu/device_register.cc:55-67); the getter has no counterpart symbol
+ * in the reference, which reads the value in-process. */
+void TFMusaSetAllowGrowth(int enabled);
+int TFMusaGetAllowGrowth(void);
+
 #ifdef __cplusplus
 }
 #endif

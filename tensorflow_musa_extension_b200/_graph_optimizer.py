@@ -163,6 +163,13 @@ def _graph_lib():
         lib.MusaGraphOptimizerListPatterns.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
         lib.MusaGraphSetPatternEnabled.restype = ctypes.c_int
         lib.MusaGraphSetPatternEnabled.argtypes = [ctypes.c_char_p, ctypes.c_int]
+        lib.TFMusaSetGraphDumpConfig.restype = None
+        lib.TFMusaSetGraphDumpConfig.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_int,
+                                                 ctypes.c_int]
+        lib.TFMusaClearGraphDumpConfig.restype = None
+        lib.TFMusaGetGraphDumpDirectory.restype = ctypes.c_char_p
+        lib.TFMusaSetAllowGrowth.restype = None
+        lib.TFMusaSetAllowGrowth.argtypes = [ctypes.c_int]
         lib._graph_bound = True
     return lib
 
@@ -209,3 +216,55 @@ def optimize_graph_def(graph_def_bytes, config=None, parameters=None):
     finally:
         lib.MusaGraphOptimizerFree(out)
     return result, json.loads(report.value.decode())
+
+
+# -------------------------------------------------- runtime configuration --
+# The reference's python/_graph_optimizer.py:275-345 and python/__init__.py:59.
+
+def set_musa_graph_dump_config(enabled=True, dump_dir=".", dump_text=False, dump_slim=False):
+    """Configure GraphDef dumping of `musa_graph_optimizer`; overrides the
+    MUSA_DUMP_GRAPHDEF, MUSA_DUMP_GRAPHDEF_DIR, MUSA_DUMP_GRAPHDEF_TEXT and
+    MUSA_DUMP_GRAPHDEF_SLIM environment variables for this process."""
+    _graph_lib().TFMusaSetGraphDumpConfig(
+        int(bool(enabled)), ("." if dump_dir is None else str(dump_dir)).encode(),
+        int(bool(dump_text)), int(bool(dump_slim)))
+
+
+def enable_musa_graph_dump(dump_dir=".", dump_text=False, dump_slim=False):
+    set_musa_graph_dump_config(True, dump_dir, dump_text, dump_slim)
+
+
+def disable_musa_graph_dump():
+    set_musa_graph_dump_config(enabled=False)
+
+
+def clear_musa_graph_dump_config():
+    """Drop the override and fall back to the environment variables."""
+    _graph_lib().TFMusaClearGraphDumpConfig()
+
+
+def is_musa_graph_dump_enabled():
+    return bool(_graph_lib().TFMusaGraphDumpIsEnabled())
+
+
+def get_musa_graph_dump_directory():
+    return _graph_lib().TFMusaGetGraphDumpDirectory().decode()
+
+
+def is_musa_graph_dump_text_enabled():
+    return bool(_graph_lib().TFMusaGraphDumpTextIsEnabled())
+
+
+def is_musa_graph_dump_slim_enabled():
+    return bool(_graph_lib().TFMusaGraphDumpSlimIsEnabled())
+
+
+def set_musa_allow_growth(enabled=True):
+    """Ask for on-demand growth of the device memory pool instead of one
+    up-front reservation (read by the platform registration; the
+    TF_FORCE_GPU_ALLOW_GROWTH environment variable wins when it is set)."""
+    _graph_lib().TFMusaSetAllowGrowth(int(bool(enabled)))
+
+
+def get_musa_allow_growth():
+    return bool(_graph_lib().TFMusaGetAllowGrowth())

@@ -1,4 +1,5 @@
 #include "musa_graph_optimizer.h"
+#include "graph_dump.h"
 
 #include <algorithm>
 #include <cctype>
@@ -92,6 +93,20 @@ Status MusaGraphOptimizer::Optimize(GraphDef* graph,
   rep = OptimizeReport();
   if (graph == nullptr) return Status::InvalidArgument("null graph");
   if (graph->node.empty()) return Status::OK();
+  // Dumps at the stages of the reference's Optimize()
+  // (musa_ext/mu/optimizer/musa_graph_optimizer.cc:5486-5517); the layout and
+  // AMP passes are not part of this build, so only the fusion pass appears.
+  GraphDefDumper dumper("musa_graph_optimizer");
+  dumper.DumpInitial(*graph);
+  dumper.DumpBeforePass(*graph, "fusion");
+  struct FinalDump {
+    GraphDefDumper* d;
+    GraphDef* g;
+    ~FinalDump() {
+      d->DumpAfterPass(*g, "fusion");
+      d->DumpFinal(*g);
+    }
+  } final_dump{&dumper, graph};
 
   const auto patterns = FusionPatternManager::GetInstance().GetSortedPatterns();
   std::map<int, std::vector<const FusionPattern*>, std::greater<int>> groups;

@@ -410,3 +410,78 @@ def test_config_drives_the_optimizer():
     assert by_name(parse(go.optimize_graph_def(data, config=on)[0]))["act"].op == "MusaBiasAddRelu"
     go.disable_musa_fusion_patterns("MusaBiasAddReluFusion", on)
     assert by_name(parse(go.optimize_graph_def(data, config=on)[0]))["act"].op == "Relu"
+
+
+# ------------------------------------------------------------ graph dumps --
+
+def test_graph_dump_files(tmp_path):
+    d = tmp_path / "dumps"
+    go.enable_musa_graph_dump(str(d), dump_text=True, dump_slim=True)
+    try:
+        assert go.is_musa_graph_dump_enabled() and go.get_musa_graph_dump_directory() == str(d)
+        assert go.is_musa_graph_dump_text_enabled() and go.is_musa_graph_dump_slim_enabled()
+        g = bias_relu_graph(gp.DT_HALF, fmt="NHWC")
+        out, report = run(g)
+        assert report["applied"] == 1
+        names = sorted(p.name for p in d.iterdir())
+        ids = {n.split("_")[3] for n in names}
+        assert len(ids) == 1 and len(next(iter(ids))) == 4          # one run, id width 4
+        rid = next(iter(ids))
+        for stage in ("initial", "before_fusion", "after_fusion", "final"):
+            for ext in (".pb", ".slim.pb", ".pbtxt"):
+                assert "musa_graph_optimizer_%s_%s%s" % (rid, stage, ext) in names
+        base = d / ("musa_graph_optimizer_%s_" % rid)
+        # the binary dumps are the graphs themselves
+        assert parse((d / ("musa_graph_optimizer_%s_initial.pb" % rid)).read_bytes()) == g.graph
+        assert parse((d / ("musa_graph_optimizer_%s_final.pb" % rid)).read_bytes()) == out
+        text = (d / ("musa_graph_optimizer_%s_final.pbtxt" % rid)).read_text()
+        assert 'op: "MusaBiasAddRelu"' in text and 'name: "act"' in text
+        assert 's: "NHWC"' in text and "type: DT_HALF" in text
+        slim = parse((d / ("musa_graph_optimizer_%s_initial.slim.pb" % rid)).read_bytes())
+        full = {n.name: n for n in g.graph.node}
+        for n in slim.node:
+            assert n.op == full[n.name].op and list(n.input) == list(full[n.name].input)
+            assert "shape" not in n.attr                               # non-scalar attrs dropped
+        assert any("shape" in n.attr for n in g.graph.node)
+        # a second run gets the next id
+        run(g)
+        ids2 = {p.name.split("_")[3] for p in d.iterdir()}
+        assert len(ids2) == 2
+    finally:
+        go.clear_musa_graph_dump_config()
+
+
+def test_graph_dump_environment_and_override(tmp_path, monkeypatch):
+    go.clear_musa_graph_dump_config()
+    monkeypatch.delenv("MUSA_DUMP_GRAPHDEF", raising=False)
+    assert not go.is_musa_graph_dump_enabled() and go.get_musa_graph_dump_directory() == "."
+    monkeypatch.setenv("MUSA_DUMP_GRAPHDEF", "1")
+    monkeypatch.setenv("MUSA_DUMP_GRAPHDEF_DIR", str(tmp_path))
+    monkeypatch.setenv("MUSA_DUMP_GRAPHDEF_SLIM", "true")
+    assert go.is_musa_graph_dump_enabled() and go.get_musa_graph_dump_directory() == str(tmp_path)
+    assert go.is_musa_graph_dump_slim_enabled() and not go.is_musa_graph_dump_text_enabled()
+    run(bias_relu_graph())
+    assert any(p.name.endswith("_final.pb") for p in tmp_path.iterdir())
+    # the programmatic setting wins over the environment until it is cleared
+    go.disable_musa_graph_dump()
+    try:
+        assert not go.is_musa_graph_dump_enabled()
+        before = len(list(tmp_path.iterdir()))
+        run(bias_relu_graph())
+        assert len(list(tmp_path.iterdir())) == before
+    finally:
+        go.clear_musa_graph_dump_config()
+    assert go.is_musa_graph_dump_enabled()
+
+
+def test_allow_growth_switch(monkeypatch):
+    monkeypatch.delenv("TF_FORCE_GPU_ALLOW_GROWTH", raising=False)
+    go.set_musa_allow_growth(False)
+    assert not go.get_musa_allow_growth()
+    go.set_musa_allow_growth(True)
+    assert go.get_musa_allow_growth()
+    monkeypatch.setenv("TF_FORCE_GPU_ALLOW_GROWTH", "false")
+    assert not go.get_musa_allow_growth()                  # the environment wins
+    monkeypatch.setenv("TF_FORCE_GPU_ALLOW_GROWTH", "maybe")
+    assert go.get_musa_allow_growth()                      # unparsable: ignored
+    go.set_musa_allow_growth(False)
