@@ -60,9 +60,18 @@ __device__ __forceinline__ float GroupSum(float v, float* smem) {
     constexpr int kWarps = kGroup / 32;
     const int warp = threadIdx.x >> 5;
     const int first = (warp / kWarps) * kWarps;  // first warp of this group
-    __syncthreads();                              // smem free again
+    // Only the warps of one group meet: a named barrier per group when the CTA
+    // holds several (ids 1 .., barrier 0 stays with __syncthreads).
+    const auto meet = [&]() {
+      if constexpr (kGroup == kThreads) {
+        __syncthreads();
+      } else {
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + warp / kWarps), "n"(kGroup) : "memory");
+      }
+    };
+    meet();  // smem free again
     if ((threadIdx.x & 31) == 0) smem[warp] = v;
-    __syncthreads();
+    meet();
     float t = 0.0f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) t += smem[first + w];
@@ -654,6 +663,9 @@ int DispatchPacks(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   };
   if (fits(8)) return LaunchGroup<T, 8, kMaxPacks, kOp>(a, ctas_out, stream);
   if (fits(32)) return LaunchGroup<T, 32, kMaxPacks, kOp>(a, ctas_out, stream);
+  if constexpr (kMaxPacks == 2) {
+    if (fits(64)) return LaunchGroup<T, 64, kMaxPacks, kOp>(a, ctas_out, stream);
+  }
   if (fits(128)) return LaunchGroup<T, 128, kMaxPacks, kOp>(a, ctas_out, stream);
   if (fits(256)) return LaunchGroup<T, 256, kMaxPacks, kOp>(a, ctas_out, stream);
   if (fits(512)) return LaunchGroup<T, 512, kMaxPacks, kOp>(a, ctas_out, stream);
@@ -664,13 +676,19 @@ template <typename T, int kOp>
 int Dispatch(const RowArgs& a, bool aligned, int* ctas_out, cudaStream_t stream) {
   constexpr int kVec = VecWidth<T>::value;
   if (aligned && a.row_size % kVec == 0) {
-    // Four packs per thread keep short rows inside one warp (shuffle-only
-    // sums) and measured faster than one pack per thread on every op and
-    // shape tried; the tuning value 1 selects the other layout.
+    // Packs per thread.  Four keep short rows inside one warp (shuffle-only
+    // sums): best for the forward ops and the RMSNorm gradient.  The
+    // LayerNorm gradient carries ring + column-sum slabs in shared memory and
+    // two inputs in registers; two packs per thread (rows spread over two
+    // warps that meet at a named barrier) fit three CTAs per SM where four
+    // packs fit one.  Tuning values 1, 2 (gradient only), 4 force a layout.
     int want = GetTuning(kTuneRowNormPacks);
-    if (want != 1) want = 4;
+    if (want != 1 && want != 2 && want != 4) want = kOp == kOpLnGrad ? 2 : 4;
     int rc = -1;
     if (want == 1) rc = DispatchPacks<T, kOp, 1>(a, ctas_out, stream);
+    if constexpr (kOp == kOpLnGrad) {
+      if (want == 2) rc = DispatchPacks<T, kOp, 2>(a, ctas_out, stream);
+    }
     if (rc == -1) rc = DispatchPacks<T, kOp, 4>(a, ctas_out, stream);
     if (rc != -1) return rc;
   }

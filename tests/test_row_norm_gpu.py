@@ -233,3 +233,37 @@ def test_keras_layer_norm_route_through_fused_batch_norm(kernel_lib, dtype):
                                       epsilon=1e-3).dx
     assert_close(to_numpy(ln_dx), want_dx, 0.15 if dtype == "bfloat16" else 1e-3,
                  5e-5 if dtype == "bfloat16" else 1e-8, "layer norm grad op")
+
+
+@pytest.mark.parametrize("packs", [1, 2, 4])
+@pytest.mark.parametrize("n", [64, 256, 1024, 2048, 4096])
+def test_every_register_layout_gives_the_same_answers(kernel_lib, packs, n):
+    """The packs-per-thread layouts (tuning key 12) differ in how a row is
+    spread over threads and warps, not in what they compute."""
+    lib = raw_ops._lib()
+    rng = np.random.default_rng(n + packs)
+    for dtype in ("float32", "bfloat16"):
+        dt = np_dtype(dtype)
+        x = rng.uniform(-4, 4, (300, n)).astype(dt)
+        dy = rng.uniform(-1, 1, (300, n)).astype(dt)
+        gamma = rng.uniform(0.5, 1.5, n).astype(dt)
+        beta = rng.uniform(-0.5, 0.5, n).astype(dt)
+        tx, td, tg, tb = (to_torch(a) for a in (x, dy, gamma, beta))
+        lib.MusaKernelsSetTuning(12, packs)
+        try:
+            y = raw_ops.MusaLayerNorm(tx, tg, tb)
+            dx, dgamma, dbeta = raw_ops.MusaLayerNormGrad(td, tx, tg, tb)
+            ry, rn, rinv = raw_ops.MusaRmsNorm(tx, tg)
+            rdx = raw_ops.MusaRmsNormGradDx(tx, rinv, tg, td)
+            torch.cuda.synchronize()
+        finally:
+            lib.MusaKernelsSetTuning(12, 0)
+        rt, at = _tol(dtype)
+        assert_close(to_numpy(y), np_ref.layer_norm(x, gamma, beta), rt, at, "y")
+        want = np_ref.layer_norm_grad(dy, x, gamma)
+        assert_close(to_numpy(dx), want[0], rt * 10, at * 2 + 1e-5, "dx")
+        assert_close(to_numpy(dgamma), want[1], rt * 10, (at + 1e-5) * 18, "dgamma")
+        assert_close(to_numpy(dbeta), want[2], rt * 10, (at + 1e-5) * 18, "dbeta")
+        assert_close(to_numpy(ry), np_ref.rms_norm(x, gamma)[0], rt, at, "rms y")
+        assert_close(to_numpy(rdx), np_ref.rms_norm_grad_dx(x, to_numpy(rinv), gamma, dy),
+                     rt * 5, at * 5 + 1e-5, "rms dx")
