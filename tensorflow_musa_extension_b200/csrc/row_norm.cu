@@ -677,13 +677,15 @@ int Dispatch(const RowArgs& a, bool aligned, int* ctas_out, cudaStream_t stream)
   constexpr int kVec = VecWidth<T>::value;
   if (aligned && a.row_size % kVec == 0) {
     // Packs per thread.  Four keep short rows inside one warp (shuffle-only
-    // sums): best for the forward ops and the RMSNorm gradient.  The
-    // LayerNorm gradient carries ring + column-sum slabs in shared memory and
-    // two inputs in registers; two packs per thread (rows spread over two
-    // warps that meet at a named barrier) fit three CTAs per SM where four
-    // packs fit one.  Tuning values 1, 2 (gradient only), 4 force a layout.
+    // sums) and measured best for every op and shape tried but one: the
+    // fp32 LayerNorm gradient, whose ring, column-sum slabs and two inputs fit
+    // three CTAs per SM with two packs per thread (rows spread over two warps
+    // that meet at a named barrier) and one CTA with four.  Tuning values 1,
+    // 2 (gradient only), 4 force a layout.
     int want = GetTuning(kTuneRowNormPacks);
-    if (want != 1 && want != 2 && want != 4) want = kOp == kOpLnGrad ? 2 : 4;
+    if (want != 1 && want != 2 && want != 4) {
+      want = (kOp == kOpLnGrad && sizeof(T) == 4) ? 2 : 4;
+    }
     int rc = -1;
     if (want == 1) rc = DispatchPacks<T, kOp, 1>(a, ctas_out, stream);
     if constexpr (kOp == kOpLnGrad) {
