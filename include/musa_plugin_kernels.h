@@ -170,6 +170,26 @@ void LaunchFusedResourceApplyCenteredRMSProp_Double(
     void* var, void* mg, void* ms, void* mom, const void* grad, double lr,
     double rho, double momentum, double epsilon, int64_t n, cudaStream_t stream);
 
+/* ResourceApplyAdagradV2 / ApplyAdagradV2 over n elements, in place:
+ *   accum <- accum + g*g (only with update_slots);
+ *   var <- var - lr * g / (sqrt(accum) + epsilon).
+ * C names for LaunchFusedApplyAdagradV2Kernel<T>
+ * (musa_ext/kernels/training/musa_applyadagrad_kernel.mu:55-79; declared at
+ * musa_ext/kernels/training/musa_applyadagrad_op.cc:36-40); no stream
+ * synchronisation after the launch. */
+void LaunchFusedApplyAdagradV2_Float(void* var, void* accum, const void* grad,
+                                     double lr, double epsilon, bool update_slots,
+                                     int64_t n, cudaStream_t stream);
+void LaunchFusedApplyAdagradV2_Half(void* var, void* accum, const void* grad,
+                                    double lr, double epsilon, bool update_slots,
+                                    int64_t n, cudaStream_t stream);
+void LaunchFusedApplyAdagradV2_BFloat16(void* var, void* accum, const void* grad,
+                                        double lr, double epsilon, bool update_slots,
+                                        int64_t n, cudaStream_t stream);
+void LaunchFusedApplyAdagradV2_Double(void* var, void* accum, const void* grad,
+                                      double lr, double epsilon, bool update_slots,
+                                      int64_t n, cudaStream_t stream);
+
 /* ResourceApplyGradientDescent: var <- var - alpha * grad over n elements.
  * Same names and arguments as the reference
  * (musa_ext/kernels/training/musa_applygradientdescent_kernel.mu:106-122). */

@@ -431,3 +431,17 @@ def rms_norm_grad_dx(x, inv_rms, gamma, dy):
     dot = (xf * d * g).sum(axis=-1, keepdims=True)
     coeff = dot * inv ** 3 / x.shape[-1]
     return (d * g * inv - xf * coeff).astype(x.dtype)
+
+
+def apply_adagrad_v2(var, accum, lr, epsilon, grad, update_slots=True):
+    """ResourceApplyAdagradV2 / ApplyAdagradV2: accum' = accum + g^2 (with
+    update_slots); var' = var - lr * g / (sqrt(accum') + epsilon)
+    (musa_ext/kernels/training/musa_applyadagrad_kernel.mu:65-77; the same
+    statement as the reference test's NumPy helper,
+    test/ops/apply_adagrad_op_test.py:53-62).  Returns (var', accum')."""
+    var, accum, grad = (np.asarray(a) for a in (var, accum, grad))
+    ct = _update_dtype(var.dtype)
+    g = grad.astype(ct)
+    acc = accum.astype(ct) + g * g if update_slots else accum.astype(ct)
+    var_new = var.astype(ct) - ct(lr) * g / (np.sqrt(acc) + ct(epsilon))
+    return var_new.astype(var.dtype), acc.astype(var.dtype)

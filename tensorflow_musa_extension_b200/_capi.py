@@ -17,6 +17,7 @@ _NADAM = [c_vp, c_vp, c_vp, c_vp] + [c_f32] * 6 + [c_i64, c_vp]
 _RMSPROP = [c_vp, c_vp, c_vp, c_vp] + [c_f64] * 4 + [c_i64, c_vp]
 _CRMSPROP = [c_vp] * 5 + [c_f64] * 4 + [c_i64, c_vp]
 _SGD = [c_vp, c_vp, c_f32, c_i64, c_vp]
+_ADAGRAD = [c_vp, c_vp, c_vp, c_f64, c_f64, c_bool, c_i64, c_vp]
 _SGD_TABLE = [c_vp] * 5 + [c_int, c_int, c_vp]
 _LAYER_NORM = [c_vp] * 6 + [c_i64, c_i64, c_f32, c_vp]
 _LAYER_NORM_GRAD = [c_vp] * 6 + [c_i64, c_i64, c_f32, c_vp, c_size, c_vp]
@@ -58,6 +59,10 @@ PROTOTYPES = {
     "LaunchResourceApplyNadam_Double": (None, _NADAM),
     "LaunchFusedResourceApplyRMSProp_Double": (None, _RMSPROP),
     "LaunchFusedResourceApplyCenteredRMSProp_Double": (None, _CRMSPROP),
+    "LaunchFusedApplyAdagradV2_Float": (None, _ADAGRAD),
+    "LaunchFusedApplyAdagradV2_Half": (None, _ADAGRAD),
+    "LaunchFusedApplyAdagradV2_BFloat16": (None, _ADAGRAD),
+    "LaunchFusedApplyAdagradV2_Double": (None, _ADAGRAD),
     "LaunchResourceApplyGradientDescentFloat": (None, _SGD),
     "LaunchResourceApplyGradientDescentFloatBFloat16": (None, _SGD),
     "LaunchResourceApplyGradientDescent_Half": (None, _SGD),

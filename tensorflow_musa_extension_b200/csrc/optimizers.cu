@@ -7,6 +7,7 @@
 //   RMSProp          musa_ext/kernels/training/musa_applyrmsprop_kernel.mu:72-99
 //   centered RMSProp musa_ext/kernels/training/musa_applyrmsprop_kernel.mu:101-133
 //   gradient descent musa_ext/kernels/training/musa_applygradientdescent_kernel.mu:14-96
+//   Adagrad (V2)     musa_ext/kernels/training/musa_applyadagrad_kernel.mu:55-79
 //
 // Arithmetic: fp32 for float / half / bfloat16 tensors with one round-to-
 // nearest-even on store, fp64 for double tensors.  Every rounding is spelled
@@ -124,6 +125,26 @@ struct CenteredRmsPropRule {
     s[1] = mg;
     s[2] = ms;
     s[3] = mom;
+  }
+};
+
+// accum += g*g (with update_slots); var -= lr * g / (sqrt(accum) + epsilon).
+template <typename T, bool kUpdateSlots>
+struct AdagradRule {
+  using StateT = T;
+  using GradT = T;
+  using C = typename ComputeOf<T>::type;
+  static constexpr int kStates = 2;  // var, accum
+  struct Params {
+    C lr, epsilon;
+  };
+  static __device__ __forceinline__ void Step(C (&s)[kStates], C g,
+                                              const Params& p) {
+    // Without update_slots the accumulator is read but stays as it is (it is
+    // stored back unchanged).
+    const C accum = kUpdateSlots ? Fma(g, g, s[1]) : s[1];
+    s[0] = Sub(s[0], Div(Mul(p.lr, g), Add(Sqrt(accum), p.epsilon)));
+    s[1] = accum;
   }
 };
 
@@ -323,6 +344,27 @@ void CenteredRmsProp(void* var, void* mg, void* ms, void* mom, const void* grad,
   LaunchUpdate<Rule>(a, n, stream);
 }
 
+template <typename T>
+void Adagrad(void* var, void* accum, const void* grad, double lr, double epsilon,
+             bool update_slots, int64_t n, cudaStream_t stream) {
+  using C = typename ComputeOf<T>::type;
+  auto run = [&](auto rule) {
+    using Rule = decltype(rule);
+    UpdateArgs<Rule> a;
+    a.state[0] = static_cast<T*>(var);
+    a.state[1] = static_cast<T*>(accum);
+    a.grad = static_cast<const T*>(grad);
+    a.p.lr = static_cast<C>(lr);
+    a.p.epsilon = static_cast<C>(epsilon);
+    LaunchUpdate<Rule>(a, n, stream);
+  };
+  if (update_slots) {
+    run(AdagradRule<T, true>());
+  } else {
+    run(AdagradRule<T, false>());
+  }
+}
+
 template <typename VarT, typename DeltaT>
 void Sgd(void* var, const void* delta, float alpha, int64_t n,
          cudaStream_t stream) {
@@ -513,6 +555,12 @@ extern "C" {
       cudaStream_t stream) {                                                   \
     CenteredRmsProp<TYPE>(var, mg, ms, mom, grad, lr, rho, momentum, epsilon,  \
                           n, stream);                                          \
+  }                                                                            \
+  void LaunchFusedApplyAdagradV2_##SUFFIX(void* var, void* accum,              \
+                                          const void* grad, double lr,         \
+                                          double epsilon, bool update_slots,   \
+                                          int64_t n, cudaStream_t stream) {    \
+    Adagrad<TYPE>(var, accum, grad, lr, epsilon, update_slots, n, stream);     \
   }
 MUSA_DEFINE_STATEFUL(Float, float)
 MUSA_DEFINE_STATEFUL(Half, __half)

@@ -113,10 +113,13 @@ struct RowPipe {
 // keeps its packs of the current row in registers in stored form and widens
 // them on each use.
 // The single-input forms fit three 256-thread CTAs per SM (56 KB of shared
-// memory each) when the compiler keeps them to 85 registers.
+// memory each) when the compiler keeps them to 85 registers, the RMSNorm
+// gradient two (100 KB each, 128 registers).
 template <typename T, int kGroup, int kMaxPacks, int kOp>
 __global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256),
-                                  (kGroup <= 256 && (kOp == kOpLnFwd || kOp == kOpRmsFwd)) ? 3 : 1)
+                                  kGroup > 256 ? 1
+                                  : (kOp == kOpLnFwd || kOp == kOpRmsFwd) ? 3
+                                  : kOp == kOpRmsGrad ? 2 : 1)
     RowNormKernel(RowArgs a) {
   constexpr int kThreads = kGroup > 256 ? kGroup : 256;
   constexpr int kRows = kThreads / kGroup;
@@ -249,37 +252,71 @@ __global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256),
     const auto Dup = [](float v) { return make_float2(v, v); };
 
     if constexpr (kOp == kOpLnFwd || kOp == kOpLnGrad) {
-      float2 s2 = make_float2(0.0f, 0.0f);
+      // A plain fp32 sum of the row can be off by a few ulps of |mean|, which
+      // matters when |mean| >> std.  Sums of residuals are accurate: rows that
+      // live in one warp subtract the row's first element before summing (one
+      // shuffle brings it over); wider groups take a first mean, then correct
+      // it by the mean of the residuals around it.
+      float mean;
+      float2 q2 = make_float2(0.0f, 0.0f);
+      if constexpr (kGroup <= 32) {
+        const float first =
+            __shfl_sync(0xffffffffu, xv[0][0].x, (threadIdx.x & 31) & ~(kGroup - 1));
+        const float2 nfirst = Dup(-first);
+        float2 r2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-      for (int j = 0; j < kMaxPacks; ++j)
+        for (int j = 0; j < kMaxPacks; ++j) {
+          if (live && t + j * kGroup < packs) {
 #pragma unroll
-        for (int q = 0; q < kPairs; ++q) s2 = Add2(s2, xv[j][q]);
-      // A first mean in fp32 can be off by a few ulps of |mean|; the residuals
-      // around it are small, so their mean is accurate and corrects it.
-      const float mean0 = GroupSum<kGroup, kThreads>(s2.x + s2.y, red) * inv_n;
-      const float2 nmean0 = Dup(-mean0);
-      float2 r2 = make_float2(0.0f, 0.0f);
-#pragma unroll
-      for (int j = 0; j < kMaxPacks; ++j) {
-        if (live && t + j * kGroup < packs) {
-#pragma unroll
-          for (int q = 0; q < kPairs; ++q) {
-            xv[j][q] = Add2(xv[j][q], nmean0);
-            r2 = Add2(r2, xv[j][q]);
+            for (int q = 0; q < kPairs; ++q) {
+              xv[j][q] = Add2(xv[j][q], nfirst);
+              r2 = Add2(r2, xv[j][q]);
+            }
           }
         }
-      }
-      const float mean1 = GroupSum<kGroup, kThreads>(r2.x + r2.y, red) * inv_n;
-      const float mean = mean0 + mean1;
-      const float2 nmean1 = Dup(-mean1);
-      float2 q2 = make_float2(0.0f, 0.0f);
+        const float shift = GroupSum<kGroup, kThreads>(r2.x + r2.y, red) * inv_n;
+        mean = first + shift;
+        const float2 nshift = Dup(-shift);
 #pragma unroll
-      for (int j = 0; j < kMaxPacks; ++j) {
-        if (live && t + j * kGroup < packs) {
+        for (int j = 0; j < kMaxPacks; ++j) {
+          if (live && t + j * kGroup < packs) {
 #pragma unroll
-          for (int q = 0; q < kPairs; ++q) {
-            xv[j][q] = Add2(xv[j][q], nmean1);
-            q2 = Fma2(xv[j][q], xv[j][q], q2);
+            for (int q = 0; q < kPairs; ++q) {
+              xv[j][q] = Add2(xv[j][q], nshift);
+              q2 = Fma2(xv[j][q], xv[j][q], q2);
+            }
+          }
+        }
+      } else {
+        float2 s2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < kMaxPacks; ++j)
+#pragma unroll
+          for (int q = 0; q < kPairs; ++q) s2 = Add2(s2, xv[j][q]);
+        const float mean0 = GroupSum<kGroup, kThreads>(s2.x + s2.y, red) * inv_n;
+        const float2 nmean0 = Dup(-mean0);
+        float2 r2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < kMaxPacks; ++j) {
+          if (live && t + j * kGroup < packs) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) {
+              xv[j][q] = Add2(xv[j][q], nmean0);
+              r2 = Add2(r2, xv[j][q]);
+            }
+          }
+        }
+        const float mean1 = GroupSum<kGroup, kThreads>(r2.x + r2.y, red) * inv_n;
+        mean = mean0 + mean1;
+        const float2 nmean1 = Dup(-mean1);
+#pragma unroll
+        for (int j = 0; j < kMaxPacks; ++j) {
+          if (live && t + j * kGroup < packs) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) {
+              xv[j][q] = Add2(xv[j][q], nmean1);
+              q2 = Fma2(xv[j][q], xv[j][q], q2);
+            }
           }
         }
       }

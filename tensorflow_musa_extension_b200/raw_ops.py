@@ -762,7 +762,7 @@ def MusaBiasAddReluGrad(gradients, features, data_format="NHWC", name=None):
 # Defined in training_ops.py; imported last because that module uses the
 # helpers above.
 from .training_ops import (  # noqa: E402,F401
-    ApplyCenteredRMSProp, ApplyRMSProp, MusaGroupedResourceApplyGradientDescentMixed,
+    ApplyAdagradV2, ApplyCenteredRMSProp, ApplyRMSProp, ResourceApplyAdagradV2, MusaGroupedResourceApplyGradientDescentMixed,
     MusaResourceApplyGradientDescentMixed, ResourceApplyCenteredRMSProp,
     ResourceApplyGradientDescent, ResourceApplyNadam, ResourceApplyRMSProp)
 from .norm_ops import (  # noqa: E402,F401

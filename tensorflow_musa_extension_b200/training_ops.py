@@ -1,5 +1,5 @@
 """Op front end of the streaming optimizers next to Adam: Nadam, RMSProp
-(plain and centered) and gradient descent (single, mixed, grouped).
+(plain and centered), Adagrad and gradient descent (single, mixed, grouped).
 
 Each function mirrors one registered op of the reference: same name, argument
 meaning, checks and error text; the update itself is one launch through the C
@@ -187,6 +187,38 @@ def ApplyCenteredRMSProp(var, mg, ms, mom, lr, rho, momentum, epsilon, grad,
     (musa_ext/kernels/training/musa_applyrmsprop_op.cc:387-444, :508-511)."""
     return _centered_rms_prop("ApplyCenteredRMSProp", var, mg, ms, mom, lr, rho, momentum,
                               epsilon, grad, bool(use_locking))
+
+
+# ---------------------------------------------------------------- Adagrad --
+
+def _adagrad(opname, var, accum, lr, epsilon, grad, update_slots, lock):
+    def launch(lib, t, g, n, st):
+        T = t[0].dtype
+        fn = getattr(lib, "LaunchFusedApplyAdagradV2_" + _LONG[T])
+        fn(_r._ptr(t[0]), _r._ptr(t[1]), _r._ptr(g), _scalar(lr, "lr", T),
+           _scalar(epsilon, "epsilon", T), bool(update_slots), n, st)
+
+    return _stateful(opname, ("var", "accum"), (var, accum), grad,
+                     "Fused AdagradV2 variables (var/accum) not initialized.", lock, launch)
+
+
+def ResourceApplyAdagradV2(var, accum, lr, epsilon, grad, use_locking=False,
+                           update_slots=True, name=None):
+    """ResourceApplyAdagradV2 for T in {float, double, half, bfloat16}:
+    accum += grad^2 (with update_slots), var -= lr * grad / (sqrt(accum) +
+    epsilon) (musa_ext/kernels/training/musa_applyadagrad_op.cc:179-235,
+    registrations :292-320).  Returns None."""
+    _adagrad("ResourceApplyAdagradV2", var, accum, lr, epsilon, grad, update_slots, True)
+    return None
+
+
+def ApplyAdagradV2(var, accum, lr, epsilon, grad, use_locking=False, update_slots=True,
+                   name=None):
+    """ApplyAdagradV2 (ref variables): same update, locks only with
+    `use_locking`, output 0 forwards var
+    (musa_ext/kernels/training/musa_applyadagrad_op.cc:237-290)."""
+    return _adagrad("ApplyAdagradV2", var, accum, lr, epsilon, grad, update_slots,
+                    bool(use_locking))
 
 
 # ------------------------------------------------------- gradient descent --

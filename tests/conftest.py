@@ -36,7 +36,8 @@ def golden():
     return {name: np.load(os.path.join(GOLDEN, name + ".npz"))
             for name in ("adam_reference_numpy", "bn_torch_cpu",
                          "elementwise_literals", "bias_grad_torch_cpu",
-                         "optimizer_cases", "row_norm_torch_cpu")}
+                         "optimizer_cases", "row_norm_torch_cpu",
+                         "adagrad_reference_numpy")}
 
 
 @pytest.fixture(scope="session")

@@ -1,7 +1,7 @@
 """Generates the golden vectors under tests/golden/ (run once, by hand, on a
 machine that has the reference checkout; the .npz files are committed).
 
-    python tests/golden/make_golden.py /path/to/reference [adam|bn|elementwise|bias_grad|optimizers|row_norm ...]
+    python tests/golden/make_golden.py /path/to/reference [adam|bn|elementwise|bias_grad|optimizers|row_norm|adagrad ...]
 
 What pins what:
   adam_reference_numpy.npz
@@ -36,6 +36,11 @@ What pins what:
       77-199, 256-330; test/ops/apply_gradient_descent_op_test.py:64-78,
       97-101), all evaluated in float64.  The reference tests compare with
       TensorFlow's CPU ops on a live device and hold no expected values.
+  adagrad_reference_numpy.npz
+      AdagradV2 answered by the REFERENCE's own NumPy statement of the update,
+      `_expected_apply_adagrad_v2` (test/ops/apply_adagrad_op_test.py:53-62),
+      taken from the reference file with `ast` and evaluated in float64 on the
+      test's literal cases and on seeded random inputs.
   row_norm_torch_cpu.npz
       LayerNorm forward / gradient at shapes of the reference test
       (test/ops/layernorm_op_test.py:143-157, 211-240: [16,32], [8,16,32],
@@ -214,6 +219,50 @@ def make_bias_grad():
     np.savez_compressed(os.path.join(HERE, "bias_grad_torch_cpu.npz"), **out)
 
 
+def reference_method(reference_root, rel_path, name):
+    """A method of a reference test class, taken out of its file with `ast`
+    (the module itself imports TensorFlow) and turned into a plain function."""
+    path = os.path.join(reference_root, *rel_path.split("/"))
+    tree = ast.parse(open(path).read())
+    for node in ast.walk(tree):
+        if isinstance(node, ast.FunctionDef) and node.name == name:
+            mod = ast.Module(body=[node], type_ignores=[])
+            ns = {"np": np}
+            exec(compile(mod, path, "exec"), ns)
+            return ns[name]
+    raise RuntimeError("%s not found in %s" % (name, path))
+
+
+def make_adagrad(reference_root):
+    """Expected values from the REFERENCE's own NumPy statement of AdagradV2
+    (test/ops/apply_adagrad_op_test.py:53-62), on the literal cases of that
+    test (:94-112) and on seeded inputs as its shape test draws them
+    (:136-147)."""
+    fn = reference_method(reference_root, "test/ops/apply_adagrad_op_test.py",
+                          "_expected_apply_adagrad_v2")
+    out = {}
+    cases = {
+        "vector": ([1.0, -2.0, 3.5, -4.5], [0.1, 0.2, 0.3, 0.4], 0.01, 1e-7,
+                   [0.5, -1.0, 2.0, 0.25]),
+        "matrix": ([[1.0, 2.0], [3.0, 4.0]], [[0.1, 0.1], [0.1, 0.1]], 0.01, 1e-7,
+                   [[0.2, 0.4], [0.6, 0.8]]),
+    }
+    rng = np.random.default_rng(42)
+    for shape in ((1024,), (33, 65), (4, 8, 16)):
+        cases["random_" + "x".join(map(str, shape))] = (
+            rng.random(shape), rng.random(shape) + 0.01, 0.01, 1e-7, rng.random(shape) * 0.1)
+    for name, (var, accum, lr, eps, grad) in cases.items():
+        var, accum, grad = (np.asarray(a, np.float32) for a in (var, accum, grad))
+        want_var, want_accum = fn(None, var.astype(np.float64), accum.astype(np.float64),
+                                  np.float64(np.float32(lr)), np.float64(np.float32(eps)),
+                                  grad.astype(np.float64))
+        k = "adagrad/" + name
+        out.update({k + "/var": var, k + "/accum": accum, k + "/grad": grad,
+                    k + "/hyper": np.array([np.float32(lr), np.float32(eps)], np.float64),
+                    k + "/var_out": want_var, k + "/accum_out": want_accum})
+    np.savez_compressed(os.path.join(HERE, "adagrad_reference_numpy.npz"), **out)
+
+
 def make_optimizers():
     out = {}
     rng = np.random.default_rng(123)
@@ -322,7 +371,7 @@ def make_row_norm():
 if __name__ == "__main__":
     if len(sys.argv) < 2:
         sys.exit(__doc__)
-    which = sys.argv[2:] or ["adam", "bn", "elementwise", "bias_grad", "optimizers", "row_norm"]
+    which = sys.argv[2:] or ["adam", "bn", "elementwise", "bias_grad", "optimizers", "row_norm", "adagrad"]
     if "adam" in which:
         make_adam(sys.argv[1])
     if "bn" in which:
@@ -335,4 +384,6 @@ if __name__ == "__main__":
         make_optimizers()
     if "row_norm" in which:
         make_row_norm()
+    if "adagrad" in which:
+        make_adagrad(sys.argv[1])
     print("wrote golden vectors to", HERE)

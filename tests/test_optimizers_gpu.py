@@ -311,3 +311,51 @@ def test_full_size_rms_prop_range_sharding_is_bit_identical(kernel_lib):
                                  to_numpy(grad[sl]))
     for got, w in zip(whole, want):
         assert_close(to_numpy(got[sl]), w, RTOL["f32_adam"], 1e-9)
+
+
+# ---------------------------------------------------------------- Adagrad --
+
+def test_adagrad_golden_vectors(golden, kernel_lib):
+    g = golden["adagrad_reference_numpy"]
+    for name in sorted({k.split("/")[1] for k in g.files}):
+        k = "adagrad/" + name
+        lr, eps = g[k + "/hyper"]
+        var, accum = to_torch(g[k + "/var"]), to_torch(g[k + "/accum"])
+        raw_ops.ResourceApplyAdagradV2(var, accum, lr, eps, to_torch(g[k + "/grad"]))
+        assert_close(to_numpy(var), g[k + "/var_out"], 2e-6, 1e-7, k)
+        assert_close(to_numpy(accum), g[k + "/accum_out"], 3e-7, 1e-8, k)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("update_slots", [True, False])
+@pytest.mark.parametrize("n", [1, 7, 4096, 100003])
+def test_adagrad_matches_oracle(kernel_lib, dtype, update_slots, n):
+    rng = np.random.default_rng(n)
+    dt = np_dtype(dtype)
+    var = rng.random(n).astype(dt)
+    accum = (rng.random(n) + 0.01).astype(dt)
+    grad = (rng.random(n) * 0.1).astype(dt)
+    lr, eps = (float(np.asarray(h).astype(dt).astype(np.float64)) for h in (0.01, 1e-7))
+    want = np_ref.apply_adagrad_v2(var, accum, lr, eps, grad, update_slots)
+    tv, ta = Variable(to_torch(var), "var"), Variable(to_torch(accum), "accum")
+    assert raw_ops.ResourceApplyAdagradV2(tv, ta, 0.01, 1e-7, to_torch(grad),
+                                          update_slots=update_slots) is None
+    rt, at = _tol(dtype)
+    assert_close(to_numpy(tv.tensor()), want[0], rt, at, "var")
+    assert_close(to_numpy(ta.tensor()), want[1], rt, at, "accum")
+    if not update_slots:
+        assert np.array_equal(to_numpy(ta.tensor()).view(np.uint8), accum.view(np.uint8))
+
+
+def test_adagrad_errors_and_ref_variable_form(kernel_lib):
+    ok = torch.ones(4, device="cuda")
+    with pytest.raises(errors.FailedPreconditionError, match="Fused AdagradV2 variables"):
+        raw_ops.ResourceApplyAdagradV2(Variable(None), Variable(ok.clone()), 0.1, 1e-7, ok)
+    with pytest.raises(errors.InvalidArgumentError, match="var and accum must have the same shape"):
+        raw_ops.ResourceApplyAdagradV2(ok.clone(), torch.ones(5, device="cuda"), 0.1, 1e-7, ok)
+    with pytest.raises(errors.InvalidArgumentError, match="epsilon must be a scalar"):
+        raw_ops.ResourceApplyAdagradV2(ok.clone(), ok.clone(), 0.1, [1e-7, 1e-7], ok)
+    var = ok.clone()
+    out = raw_ops.ApplyAdagradV2(var, ok.clone(), 0.1, 0.0, ok, use_locking=True)
+    assert out.data_ptr() == var.data_ptr()
+    assert_close(to_numpy(var), np.full(4, 1 - 0.1 / np.sqrt(2.0)), 1e-6)

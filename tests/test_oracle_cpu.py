@@ -284,3 +284,29 @@ def test_row_norm_oracle_matches_independent_implementation(golden):
         np.testing.assert_allclose(np_ref.rms_norm_grad_dx(x64, inv, gamma, dy64),
                                    g[r + "/dx"], rtol=1e-8, atol=1e-10)
         assert np_ref.layer_norm(x, gamma, beta).dtype == np.float32
+
+
+def test_adagrad_oracle_matches_reference_numpy_statement(golden):
+    """AdagradV2 restatement against the reference test's own NumPy helper
+    (evaluated in float64 when the vectors were made)."""
+    g = golden["adagrad_reference_numpy"]
+    names = sorted({k.split("/")[1] for k in g.files})
+    assert "vector" in names and "matrix" in names and len(names) == 5
+    for name in names:
+        k = "adagrad/" + name
+        lr, eps = g[k + "/hyper"]
+        var, accum = np_ref.apply_adagrad_v2(g[k + "/var"], g[k + "/accum"], lr, eps,
+                                             g[k + "/grad"])
+        np.testing.assert_allclose(var, g[k + "/var_out"], rtol=2e-6, atol=1e-7)
+        np.testing.assert_allclose(accum, g[k + "/accum_out"], rtol=2e-7, atol=1e-8)
+        v64, a64 = np_ref.apply_adagrad_v2(*(g[k + "/" + n].astype(np.float64)
+                                             for n in ("var", "accum")), lr, eps,
+                                           g[k + "/grad"].astype(np.float64))
+        np.testing.assert_allclose(v64, g[k + "/var_out"], rtol=1e-13)
+        np.testing.assert_allclose(a64, g[k + "/accum_out"], rtol=1e-13)
+    # without update_slots the accumulator stays and is used as it is
+    v = np.array([1.0, 2.0], np.float32)
+    a = np.array([4.0, 9.0], np.float32)
+    gr = np.array([1.0, 1.0], np.float32)
+    nv, na = np_ref.apply_adagrad_v2(v, a, 0.5, 0.0, gr, update_slots=False)
+    assert np.array_equal(na, a) and np.allclose(nv, [1 - 0.25, 2 - 0.5 / 3])
