@@ -432,9 +432,12 @@ size_t BnWorkspaceBytes(int64_t outer, int64_t channels, int64_t inner);
 /* When the geometry allows it (channels-last, 128-bit packs, at most 256 packs
  * per row) LaunchBnFwdTrain_* and LaunchBnGrad_* run as ONE cooperative launch
  * whose CTAs meet at a barrier kept in the workspace.  Every wait in it is
- * bounded; if one ever ran out (the outputs of that call are then invalid) the
- * workspace's status word says so.  This reads and clears it (synchronises the
- * device: for tests and post-mortems, not for the hot path).  0 = fine. */
+ * bounded; if one ran out (the outputs of that call are then invalid) the
+ * workspace's status word says so.  The word is reset by every such launch, so
+ * this reports on the latest one that used `workspace`; it reads and clears the
+ * word and synchronises the device (for tests and post-mortems, not for the hot
+ * path).  0 = fine.  The result is meaningless for a workspace that no
+ * single-launch op has used since it was allocated. */
 int BnWorkspaceStatus(void* workspace, int64_t outer, int64_t channels,
                       int64_t inner);
 

@@ -1430,9 +1430,10 @@ bool LaunchFused(const T* x, const T* dy, T* out, const FinalizeArgs& fin,
   a.fin = fin;
   a.app = app;
   a.is_training = is_training;
-  // The counter starts every launch at zero; the status word is sticky (a
-  // caller reads and clears it with BnWorkspaceStatus).
-  if (cudaMemsetAsync(a.barrier, 0, sizeof(unsigned), stream) != cudaSuccess) {
+  // Counter and status word start every launch at zero (the workspace arrives
+  // with arbitrary contents); BnWorkspaceStatus reports on the latest
+  // single-launch op that used this workspace.
+  if (cudaMemsetAsync(control, 0, 128, stream) != cudaSuccess) {
     cudaGetLastError();
     return false;
   }
