@@ -448,64 +448,118 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
-// General layout stats ([outer, C, inner], inner > 1 or unaligned): grid
-// (C, gy); a CTA walks the planes (n, c) of its split with all 256 threads.
+// Channel-major layouts ([outer, C, inner], inner > 1): a plane (n, c) is a run
+// of `inner` contiguous elements.  A WARP owns one channel: it walks the planes
+// of its CTA's split of the outer axis as one flattened sequence of packs
+// (lane l takes packs l, l + 32, ... of that sequence, whatever the plane
+// length), with kPlaneUnroll loads in flight per lane.  Planes of any length
+// keep all lanes busy - 7x7 planes as well as 112x112 ones - and the pack
+// width is the widest that divides the plane (down to single elements), so no
+// access ever straddles a plane.  A CTA covers 8 neighbouring channels.
+constexpr int kPlaneUnroll = 8;
+constexpr int kPlaneWarps = kThreads / 32;
+
+struct PlaneCursor {
+  int64_t n, i;       // plane index on the outer axis, pack inside the plane
+  int64_t ip;         // packs per plane
+  int64_t dn, di;     // 32 packs further: n += dn, i += di (+ carry)
+  __device__ __forceinline__ void Init(int64_t n0, int lane, int64_t packs) {
+    ip = packs;
+    n = n0 + lane / ip;
+    i = lane % ip;
+    dn = 32 / ip;
+    di = 32 % ip;
+  }
+  __device__ __forceinline__ void Advance() {
+    n += dn;
+    i += di;
+    if (i >= ip) {
+      i -= ip;
+      ++n;
+    }
+  }
+};
+
 template <typename T, int kVec, int kMode>
 __global__ void __launch_bounds__(kThreads)
-    BnStatsInnerKernel(const T* __restrict__ x, const T* __restrict__ dy,
+    BnStatsPlaneKernel(const T* __restrict__ x, const T* __restrict__ dy,
                        const float* __restrict__ mean,
                        float* __restrict__ partial, int64_t outer,
                        int64_t channels, int64_t inner, int64_t outer_per_cta) {
   using P = Pack<T, kVec>;
   GridDepWait();
   GridDepLaunch();
-  const int64_t c = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * kPlaneWarps + (threadIdx.x >> 5);
+  if (c >= channels) return;  // whole warp; nothing below synchronises the CTA
   const int64_t n0 = static_cast<int64_t>(blockIdx.y) * outer_per_cta;
   int64_t n1 = n0 + outer_per_cta;
   if (n1 > outer) n1 = outer;
-  const float shift =
-      kMode == kFwd ? ToF32(x[c * inner]) : mean[c];
-  const int64_t inner_packs = inner / kVec;
+  const float shift = kMode == kFwd ? ToF32(x[c * inner]) : mean[c];
+  const int64_t plane_stride = channels * inner;
+  const T* xc = x + c * inner;
+  const T* dc = dy + c * inner;
+  PlaneCursor cur;
+  cur.Init(n0, lane, inner / kVec);
   float s1 = 0.0f, s2 = 0.0f;
-  for (int64_t n = n0; n < n1; ++n) {
-    const int64_t base = (n * channels + c) * inner;
-    const P* xp = reinterpret_cast<const P*>(x + base);
-    const P* dp = reinterpret_cast<const P*>(dy + base);
-    for (int64_t i = threadIdx.x; i < inner_packs; i += kThreads) {
-      const P px = LoadKeep(xp + i);
-      P pd;
-      if constexpr (kMode == kGrad) pd = LoadKeep(dp + i);
+  float2 a1 = make_float2(0.0f, 0.0f), a2 = make_float2(0.0f, 0.0f);  // packed lanes
+  const float2 nshift = make_float2(-shift, -shift);
+  while (cur.n < n1) {
+    P px[kPlaneUnroll];
+    P pd[kPlaneUnroll];
+    bool have[kPlaneUnroll];
 #pragma unroll
-      for (int e = 0; e < kVec; ++e) {
-        const float d = ToF32(px.v[e]) - shift;
-        if constexpr (kMode == kFwd) {
-          s1 += d;
-          s2 = fmaf(d, d, s2);
+    for (int u = 0; u < kPlaneUnroll; ++u) {
+      have[u] = cur.n < n1;
+      if (have[u]) {
+        const int64_t at = cur.n * plane_stride + cur.i * kVec;
+        px[u] = LoadKeep(reinterpret_cast<const P*>(xc + at));
+        if constexpr (kMode == kGrad) pd[u] = LoadKeep(reinterpret_cast<const P*>(dc + at));
+      }
+      cur.Advance();
+    }
+#pragma unroll
+    for (int u = 0; u < kPlaneUnroll; ++u) {
+      if (have[u]) {
+        if constexpr (kVec >= 2) {
+          float2 xv[kVec / 2], gv[kVec / 2];
+          WidenPack<kVec>(px[u], xv);
+          if constexpr (kMode == kGrad) WidenPack<kVec>(pd[u], gv);
+#pragma unroll
+          for (int q = 0; q < kVec / 2; ++q) {
+            const float2 d = Add2(xv[q], nshift);
+            if constexpr (kMode == kFwd) {
+              a1 = Add2(a1, d);
+              a2 = Fma2(d, d, a2);
+            } else {
+              a1 = Add2(a1, gv[q]);
+              a2 = Fma2(gv[q], d, a2);
+            }
+          }
         } else {
-          const float g = ToF32(pd.v[e]);
-          s1 += g;
-          s2 = fmaf(g, d, s2);
+          const float d = ToF32(px[u].v[0]) - shift;
+          if constexpr (kMode == kFwd) {
+            s1 += d;
+            s2 = fmaf(d, d, s2);
+          } else {
+            const float g = ToF32(pd[u].v[0]);
+            s1 += g;
+            s2 = fmaf(g, d, s2);
+          }
         }
       }
     }
   }
+  s1 += a1.x + a1.y;
+  s2 += a2.x + a2.y;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     s1 += __shfl_xor_sync(0xffffffffu, s1, o);
     s2 += __shfl_xor_sync(0xffffffffu, s2, o);
   }
-  __shared__ float red[2][kThreads / 32];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (lane == 0) {
-    red[0][warp] = s1;
-    red[1][warp] = s2;
-  }
-  __syncthreads();
-  if (threadIdx.x < 2) {
-    float acc = 0.0f;
-    for (int w = 0; w < kThreads / 32; ++w) acc += red[threadIdx.x][w];
-    partial[(static_cast<int64_t>(blockIdx.y) * 2 + threadIdx.x) * channels +
-            c] = acc;
+    partial[(static_cast<int64_t>(blockIdx.y) * 2 + 0) * channels + c] = s1;
+    partial[(static_cast<int64_t>(blockIdx.y) * 2 + 1) * channels + c] = s2;
   }
 }
 
@@ -908,48 +962,87 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
-// General layout apply: packs never straddle a plane.
+// Channel-major element-wise pass: the warp-per-channel walk of
+// BnStatsPlaneKernel; the channel's coefficients are formed once per warp.
 template <typename T, int kVec, int kMode>
 __global__ void __launch_bounds__(kThreads)
-    BnApplyInnerKernel(const T* __restrict__ x, const T* __restrict__ dy,
-                       T* __restrict__ out, ApplyArgs a, int64_t n_packs,
-                       int64_t inner_packs, int64_t channels) {
+    BnApplyPlaneKernel(const T* __restrict__ x, const T* __restrict__ dy,
+                       T* __restrict__ out, ApplyArgs a, int64_t outer,
+                       int64_t channels, int64_t inner, int64_t outer_per_cta) {
   using P = Pack<T, kVec>;
   GridDepWait();
   GridDepLaunch();
-  const P* xp = reinterpret_cast<const P*>(x);
-  const P* dp = reinterpret_cast<const P*>(dy);
-  P* op = reinterpret_cast<P*>(out);
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-       i < n_packs; i += stride) {
-    const int64_t c = (i / inner_packs) % channels;
-    const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
-    const float mean = a.mean[c];
-    const float ca = a.scale[c] * inv;
-    float cb, cc = 0.0f;
-    if constexpr (kMode == kFwd) {
-      cb = a.offset[c];
-    } else {
-      cb = a.sums ? a.sums[c] * a.inv_count : 0.0f;
-      cc = a.sums ? a.sums[channels + c] * inv * inv * a.inv_count : 0.0f;
-    }
-    const P px = LoadKeep(xp + i);
-    P pd;
-    if constexpr (kMode == kGrad) pd = LoadKeep(dp + i);
-    P o;
+  const int lane = threadIdx.x & 31;
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * kPlaneWarps + (threadIdx.x >> 5);
+  if (c >= channels) return;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * outer_per_cta;
+  int64_t n1 = n0 + outer_per_cta;
+  if (n1 > outer) n1 = outer;
+  const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
+  const float mean = a.mean[c];
+  const float ca = a.scale[c] * inv;
+  float cb, cc = 0.0f;
+  if constexpr (kMode == kFwd) {
+    cb = a.offset[c];
+  } else {
+    cb = a.sums ? a.sums[c] * a.inv_count : 0.0f;
+    cc = a.sums ? a.sums[channels + c] * inv * inv * a.inv_count : 0.0f;
+  }
+  const float2 nmean2 = make_float2(-mean, -mean), ca2 = make_float2(ca, ca);
+  const float2 cb2 = make_float2(cb, cb), ncb2 = make_float2(-cb, -cb);
+  const float2 ncc2 = make_float2(-cc, -cc);
+  const int64_t plane_stride = channels * inner;
+  const T* xc = x + c * inner;
+  const T* dc = dy + c * inner;
+  T* oc = out + c * inner;
+  PlaneCursor cur;
+  cur.Init(n0, lane, inner / kVec);
+  constexpr int kU = kMode == kFwd ? kPlaneUnroll : kPlaneUnroll / 2;
+  while (cur.n < n1) {
+    P px[kU];
+    P pd[kU];
+    int64_t at[kU];
 #pragma unroll
-    for (int e = 0; e < kVec; ++e) {
-      const float d = ToF32(px.v[e]) - mean;
-      float r;
-      if constexpr (kMode == kFwd) {
-        r = fmaf(d, ca, cb);
-      } else {
-        r = ca * (ToF32(pd.v[e]) - cb - d * cc);
+    for (int u = 0; u < kU; ++u) {
+      at[u] = cur.n < n1 ? cur.n * plane_stride + cur.i * kVec : -1;
+      if (at[u] >= 0) {
+        px[u] = LoadStream(reinterpret_cast<const P*>(xc + at[u]));
+        if constexpr (kMode == kGrad) pd[u] = LoadStream(reinterpret_cast<const P*>(dc + at[u]));
       }
-      o.v[e] = FromF32<T>(r);
+      cur.Advance();
     }
-    StoreStream(op + i, o);
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      if (at[u] >= 0) {
+        P o;
+        if constexpr (kVec >= 2) {
+          float2 xv[kVec / 2], gv[kVec / 2], rv[kVec / 2];
+          WidenPack<kVec>(px[u], xv);
+          if constexpr (kMode == kGrad) WidenPack<kVec>(pd[u], gv);
+#pragma unroll
+          for (int q = 0; q < kVec / 2; ++q) {
+            const float2 d = Add2(xv[q], nmean2);
+            if constexpr (kMode == kFwd) {
+              rv[q] = Fma2(d, ca2, cb2);
+            } else {
+              // ca * (dy - cb - d * cc)
+              rv[q] = Mul2(ca2, Fma2(d, ncc2, Add2(gv[q], ncb2)));
+            }
+          }
+          NarrowPack<kVec>(rv, o);
+        } else {
+          const float d = ToF32(px[u].v[0]) - mean;
+          float r;
+          if constexpr (kMode == kFwd) {
+            r = fmaf(d, ca, cb);
+          } else {
+            r = ca * (ToF32(pd[u].v[0]) - cb - d * cc);
+          }
+          o.v[0] = FromF32<T>(r);
+        }
+        StoreStream(reinterpret_cast<P*>(oc + at[u]), o);
+      }
+    }
   }
 }
 
@@ -1480,6 +1573,41 @@ int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* partial,
   return p.gy;
 }
 
+// Grid of the channel-major kernels: 8 channels per CTA along x, the outer
+// axis cut into gy pieces so that about 8 CTAs per SM exist.
+struct PlanePlan {
+  int64_t gx, gy, per;
+};
+inline PlanePlan PlanPlanes(const Geom& g) {
+  PlanePlan p;
+  p.gx = CeilDiv(g.channels, kPlaneWarps);
+  if (p.gx > 0x7fffffffLL) {
+    p.gx = -1;
+    return p;
+  }
+  int64_t target = static_cast<int64_t>(SmCount()) * 8 / p.gx;
+  if (target < 1) target = 1;
+  int64_t gy = target < g.outer ? target : g.outer;
+  const int64_t cap = MaxSplits(g.outer, g.channels);
+  if (gy > cap) gy = cap;
+  if (gy > 65535) gy = 65535;
+  if (gy < 1) gy = 1;
+  p.per = CeilDiv(g.outer, gy);
+  p.gy = CeilDiv(g.outer, p.per);
+  return p;
+}
+
+// Widest pack (in elements, at most 16 bytes) that divides a plane, given
+// 16-byte aligned tensors; single elements otherwise.
+template <typename T>
+inline int PlaneVec(int64_t inner, bool aligned) {
+  if (!aligned) return 1;
+  for (int v = VecWidth<T>::value; v > 1; v >>= 1) {
+    if (inner % v == 0) return v;
+  }
+  return 1;
+}
+
 // Stats launch: fills partial[splits][2][C]; returns splits (<0: error).
 template <typename T, int kMode>
 int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
@@ -1512,25 +1640,30 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
             p.rows_per_cta, keep);
     return p.gy;
   }
-  // [outer, C, inner]: one grid column per channel.
-  int64_t target = static_cast<int64_t>(SmCount()) * 8 / g.channels;
-  if (target < 1) target = 1;
-  int64_t gy = target < g.outer ? target : g.outer;
-  const int64_t cap = MaxSplits(g.outer, g.channels);
-  if (gy > cap) gy = cap;
-  if (gy > 65535) gy = 65535;
-  const int64_t per = CeilDiv(g.outer, gy);
-  gy = CeilDiv(g.outer, per);
-  if (g.channels > 0x7fffffffLL) return MUSA_KERNELS_ETOOLARGE;
-  const dim3 grid(static_cast<unsigned>(g.channels), static_cast<unsigned>(gy));
-  if (g.inner % kVec == 0 && aligned) {
-    BnStatsInnerKernel<T, kVec, kMode><<<grid, kThreads, 0, stream>>>(
-        x, dy, mean, partial, g.outer, g.channels, g.inner, per);
-  } else {
-    BnStatsInnerKernel<T, 1, kMode><<<grid, kThreads, 0, stream>>>(
-        x, dy, mean, partial, g.outer, g.channels, g.inner, per);
+  // [outer, C, inner]: a warp per channel, the outer axis split over grid.y.
+  const PlanePlan pp = PlanPlanes(g);
+  if (pp.gx < 0) return MUSA_KERNELS_ETOOLARGE;
+  const dim3 grid(static_cast<unsigned>(pp.gx), static_cast<unsigned>(pp.gy));
+  switch (PlaneVec<T>(g.inner, aligned)) {
+    case 8:
+      if constexpr (kVec >= 8) {
+        BnStatsPlaneKernel<T, 8, kMode><<<grid, kThreads, 0, stream>>>(
+            x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per);
+      }
+      break;
+    case 4:
+      BnStatsPlaneKernel<T, 4, kMode><<<grid, kThreads, 0, stream>>>(
+          x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per);
+      break;
+    case 2:
+      BnStatsPlaneKernel<T, 2, kMode><<<grid, kThreads, 0, stream>>>(
+          x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per);
+      break;
+    default:
+      BnStatsPlaneKernel<T, 1, kMode><<<grid, kThreads, 0, stream>>>(
+          x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per);
   }
-  return static_cast<int>(gy);
+  return static_cast<int>(pp.gy);
 }
 
 template <int kOut>
@@ -1595,22 +1728,28 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
     }
     return;
   }
-  const int64_t n = g.outer * g.channels * g.inner;
-  if (g.inner % kVec == 0 && aligned) {
-    const int64_t n_packs = n / kVec;
-    int64_t blocks = CeilDiv(n_packs, kThreads);
-    const int64_t cap = static_cast<int64_t>(SmCount()) * 16;
-    if (blocks > cap) blocks = cap;
-    BnApplyInnerKernel<T, kVec, kMode>
-        <<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
-            x, dy, out, a, n_packs, g.inner / kVec, g.channels);
-  } else {
-    int64_t blocks = CeilDiv(n, kThreads);
-    const int64_t cap = static_cast<int64_t>(SmCount()) * 16;
-    if (blocks > cap) blocks = cap;
-    BnApplyInnerKernel<T, 1, kMode>
-        <<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
-            x, dy, out, a, n, g.inner, g.channels);
+  const PlanePlan pp = PlanPlanes(g);
+  if (pp.gx < 0) return;
+  const dim3 grid(static_cast<unsigned>(pp.gx), static_cast<unsigned>(pp.gy));
+  const bool pdl = GetTuning(kTuneBnPdl) != 0;
+  switch (PlaneVec<T>(g.inner, aligned)) {
+    case 8:
+      if constexpr (kVec >= 8) {
+        LaunchChained(pdl, BnApplyPlaneKernel<T, 8, kMode>, grid, dim3(kThreads), 0, stream, x,
+                      dy, out, a, g.outer, g.channels, g.inner, pp.per);
+      }
+      break;
+    case 4:
+      LaunchChained(pdl, BnApplyPlaneKernel<T, 4, kMode>, grid, dim3(kThreads), 0, stream, x, dy,
+                    out, a, g.outer, g.channels, g.inner, pp.per);
+      break;
+    case 2:
+      LaunchChained(pdl, BnApplyPlaneKernel<T, 2, kMode>, grid, dim3(kThreads), 0, stream, x, dy,
+                    out, a, g.outer, g.channels, g.inner, pp.per);
+      break;
+    default:
+      LaunchChained(pdl, BnApplyPlaneKernel<T, 1, kMode>, grid, dim3(kThreads), 0, stream, x, dy,
+                    out, a, g.outer, g.channels, g.inner, pp.per);
   }
 }
 
