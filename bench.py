@@ -712,17 +712,20 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     del x, dy, y, y2
 
     # BatchNorm single layers: config 1 (fp32) and config 2 (fp16, bf16).
+    # The last entry is config 2 in NCHW ([256, 256, 28, 28]: outer 256, inner 784).
     for name, shape, dt, sfx in (("cfg1_f32", (32 * 56 * 56, 64), torch.float32, "F32"),
                                  ("cfg2_f16", (256 * 28 * 28, 256), torch.float16, "F16"),
-                                 ("cfg2_bf16", (256 * 28 * 28, 256), torch.bfloat16, "BF16")):
-        rows, c = shape
-        x = (torch.randn(rows, c, device=dev) * 3 + 1).to(dt)
-        dy = (torch.randn(rows, c, device=dev) * 1e-2).to(dt)
+                                 ("cfg2_bf16", (256 * 28 * 28, 256), torch.bfloat16, "BF16"),
+                                 ("cfg2_bf16_nchw", (256, 256, 784), torch.bfloat16, "BF16")):
+        inner = shape[2] if len(shape) == 3 else 1
+        rows, c = shape[0], shape[1]
+        x = (torch.randn(rows, c * inner, device=dev) * 3 + 1).to(dt)
+        dy = (torch.randn(rows, c * inner, device=dev) * 1e-2).to(dt)
         y = torch.empty_like(x)
         sc = torch.rand(c, device=dev) + 0.5
         of = torch.randn(c, device=dev) * 0.1
         stats = [torch.empty(c, device=dev) for _ in range(6)]
-        need = lib.BnWorkspaceBytes(rows, c, 1)
+        need = lib.BnWorkspaceBytes(rows, c, inner)
         ws = torch.empty(need, dtype=torch.uint8, device=dev)
         fwd = getattr(lib, "LaunchBnFwdTrain_" + sfx)
         bwd = getattr(lib, "LaunchBnGrad_" + sfx)
@@ -730,13 +733,13 @@ def measure_ops(torch, lib, raw_ops, dev, args):
         ms = time_launch(torch, lambda: fwd(
             x.data_ptr(), sc.data_ptr(), of.data_ptr(), None, None, y.data_ptr(),
             stats[0].data_ptr(), stats[1].data_ptr(), stats[2].data_ptr(),
-            stats[3].data_ptr(), rows, c, 1, EPS, 1.0, ws.data_ptr(), need, st),
+            stats[3].data_ptr(), rows, c, inner, EPS, 1.0, ws.data_ptr(), need, st),
             iters, flush)
         entry("bn_fwd_" + name, ms, 2 * s_bytes, x.numel(), "L2 flushed before each launch")
         ms = time_launch(torch, lambda: bwd(
             dy.data_ptr(), x.data_ptr(), sc.data_ptr(), stats[2].data_ptr(),
             stats[3].data_ptr(), y.data_ptr(), stats[4].data_ptr(), stats[5].data_ptr(),
-            rows, c, 1, EPS, True, ws.data_ptr(), need, st), iters, flush)
+            rows, c, inner, EPS, True, ws.data_ptr(), need, st), iters, flush)
         entry("bn_grad_" + name, ms, 3 * s_bytes, x.numel(), "L2 flushed before each launch")
         del x, dy, y
 

@@ -98,6 +98,31 @@ struct PairOf<__nv_bfloat16> {
   using type = __nv_bfloat162;
 };
 
+// One pack of x and the matching pack of bias values -> one pack of y.
+template <typename T, int kEpt, int kAct, bool kHasBias>
+__device__ __forceinline__ Pack<T, kEpt> ActivatePack(const Pack<T, kEpt>& px,
+                                                      const Pack<T, kEpt>& pb) {
+  constexpr bool kFast = sizeof(T) == 2;
+  Pack<T, kEpt> out;
+  if constexpr (sizeof(T) == 2 && kEpt % 2 == 0) {
+    using T2 = typename PairOf<T>::type;
+    const T2* x2 = reinterpret_cast<const T2*>(&px);
+    const T2* b2 = reinterpret_cast<const T2*>(&pb);
+    T2* o2 = reinterpret_cast<T2*>(&out);
+#pragma unroll
+    for (int e = 0; e < kEpt / 2; ++e) {
+      o2[e] = ActivatePair<T2, kAct, kHasBias>(x2[e], b2[e]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < kEpt; ++e) {
+      const float b = kHasBias ? ToF32(pb.v[e]) : 0.0f;
+      out.v[e] = FromF32<T>(Activate<kAct, kFast>(ToF32(px.v[e]), b));
+    }
+  }
+  return out;
+}
+
 // Channels-last pack kernel.  Pack p of the flat tensor covers channels
 // [(p % cv) * kEpt, +kEpt); the column is tracked incrementally, no division
 // in the loop.
@@ -147,24 +172,7 @@ __global__ void __launch_bounds__(256)
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
       if (i < n_packs) {
-        P out;
-        if constexpr (sizeof(T) == 2 && kEpt % 2 == 0) {
-          using T2 = typename PairOf<T>::type;
-          const T2* x2 = reinterpret_cast<const T2*>(&px[u]);
-          const T2* b2 = reinterpret_cast<const T2*>(&pb[u]);
-          T2* o2 = reinterpret_cast<T2*>(&out);
-#pragma unroll
-          for (int e = 0; e < kEpt / 2; ++e) {
-            o2[e] = ActivatePair<T2, kAct, kHasBias>(x2[e], b2[e]);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < kEpt; ++e) {
-            const float b = kHasBias ? ToF32(pb[u].v[e]) : 0.0f;
-            out.v[e] = FromF32<T>(Activate<kAct, kFast>(ToF32(px[u].v[e]), b));
-          }
-        }
-        StoreStream(yp + i, out);
+        StoreStream(yp + i, ActivatePack<T, kEpt, kAct, kHasBias>(px[u], pb[u]));
       }
     }
   }
@@ -193,6 +201,73 @@ __global__ void __launch_bounds__(256)
       out.v[e] = FromF32<T>(Activate<kAct, kFast>(ToF32(px.v[e]), b));
     }
     StoreStream(yp + i, out);
+  }
+}
+
+// Channel-major layouts ([outer, channels, inner], inner >= the pack width):
+// the tensor is read as one flat run of 128-bit packs, whatever the plane
+// length.  A pack starts `r` elements into a plane of channel `c` and crosses
+// into the next plane at most once, so its bias values are bias[c] up to the
+// crossing and bias[c + 1] after it.  Every thread tracks (r, c) of its packs
+// incrementally: no division in the loop.
+template <typename T, int kEpt, int kAct>
+__global__ void __launch_bounds__(256)
+    BiasActFlatKernel(const T* __restrict__ x, const T* __restrict__ bias,
+                      T* __restrict__ y, int64_t n, int64_t inner,
+                      int64_t channels) {
+  using P = Pack<T, kEpt>;
+  constexpr int kUnroll = 4;
+  const int64_t n_packs = n / kEpt;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // Position of pack i, and how it moves when i grows by `stride`.
+  const int64_t e0 = i * kEpt;
+  int64_t r = e0 % inner;
+  int64_t c = (e0 / inner) % channels;
+  const int64_t step = stride * kEpt;
+  const int64_t dr = step % inner;
+  const int64_t dc = (step / inner) % channels;
+  const P* xp = reinterpret_cast<const P*>(x);
+  P* yp = reinterpret_cast<P*>(y);
+  while (i < n_packs) {
+    P px[kUnroll];
+    P pb[kUnroll];
+    int64_t at[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      at[u] = i < n_packs ? i : -1;
+      if (at[u] >= 0) {
+        px[u] = LoadStream(xp + i);
+        const T b0 = bias[c];
+        const T b1 = bias[c + 1 == channels ? 0 : c + 1];
+        const int64_t before = inner - r;  // elements of this pack in plane c
+#pragma unroll
+        for (int e = 0; e < kEpt; ++e) pb[u].v[e] = e < before ? b0 : b1;
+      }
+      i += stride;
+      r += dr;
+      c += dc;
+      if (r >= inner) {
+        r -= inner;
+        ++c;
+      }
+      if (c >= channels) c -= channels;
+      if (c >= channels) c -= channels;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (at[u] >= 0) {
+        StoreStream(yp + at[u], ActivatePack<T, kEpt, kAct, true>(px[u], pb[u]));
+      }
+    }
+  }
+  // Elements past the last whole pack.
+  if (blockIdx.x == 0 && threadIdx.x < kEpt) {
+    const int64_t t = n_packs * kEpt + threadIdx.x;
+    if (t < n) {
+      const float b = ToF32(bias[(t / inner) % channels]);
+      y[t] = FromF32<T>(Activate<kAct, sizeof(T) == 2>(ToF32(x[t]), b));
+    }
   }
 }
 
@@ -261,10 +336,20 @@ int LaunchTyped(const T* x, const T* bias, T* y, int64_t outer,
           <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
     }
   } else if (inner % kVec == 0 && aligned) {
+    // Planes of whole packs: one bias value per pack.
     const int64_t n_packs = n / kVec;
     const int grid = GridFor(CeilDiv(n_packs, 256), 16);
     BiasActInnerKernel<T, kVec, kAct, kHasBias><<<grid, 256, 0, stream>>>(
         x, bias, y, n_packs, inner / kVec, channels);
+  } else if (kHasBias && aligned && inner >= kVec && n >= kVec) {
+    // Any other plane length (14x14, 7x7, ...): flat packs that may cross into
+    // the next plane once.
+    const int64_t n_packs = n / kVec;
+    const int grid = GridFor(CeilDiv(n_packs, 256 * 4), 8);
+    if constexpr (kHasBias) {
+      BiasActFlatKernel<T, kVec, kAct><<<grid, 256, 0, stream>>>(x, bias, y, n, inner,
+                                                               channels);
+    }
   } else {
     const int grid = GridFor(CeilDiv(n, 256), 16);
     BiasActInnerKernel<T, 1, kAct, kHasBias>

@@ -235,73 +235,93 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
-struct InnerGeom {
+struct PlaneGeom {
   int64_t outer;
   int64_t channels;
   int64_t inner;
   int64_t outer_per_split;
-  int tx;  // threads along the run of `inner` elements
 };
 
-// Channel-major ([outer, channels, inner], inner > 1).  CTA (c, split) adds
-// the runs of channel c; threadIdx is split into tx positions inside a run
-// and kThreads / tx runs.
+// Channel-major ([outer, channels, inner], inner > 1).  A plane (n, c) is a run
+// of `inner` contiguous elements.  A warp owns one channel and walks the
+// planes of its CTA's split of the outer axis as ONE flattened sequence of
+// packs (lane l takes packs l, l + 32, ... of it, whatever the plane length),
+// with kPlaneUnroll loads per input in flight; the pack width is the widest
+// that divides the plane, so no access straddles planes.  8 channels per CTA.
+constexpr int kPlaneUnroll = 4;
+constexpr int kPlaneWarps = kThreads / 32;
+
 template <typename T, int kVec, bool kFused>
 __global__ void __launch_bounds__(kThreads)
-    BiasGradInnerKernel(const T* __restrict__ dy, const T* __restrict__ feat,
+    BiasGradPlaneKernel(const T* __restrict__ dy, const T* __restrict__ feat,
                         T* __restrict__ dx,
                         typename AccOf<T>::type* __restrict__ partial,
-                        InnerGeom g) {
+                        PlaneGeom g) {
   using A = typename AccOf<T>::type;
   using P = Pack<T, kVec>;
-  __shared__ A red[kThreads];
-
-  const int c = blockIdx.x;
-  const int px = threadIdx.x % g.tx;
-  const int py = threadIdx.x / g.tx;
-  const int ty = kThreads / g.tx;
-  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * g.outer_per_split;
-  const int64_t n1 = min(g.outer, n0 + g.outer_per_split);
-  const int64_t packs = g.inner / kVec;
-
   GridDepWait();
   GridDepLaunch();
-
-  A acc = A(0);
-  if (py < ty) {
-    for (int64_t n = n0 + py; n < n1; n += ty) {
-      const int64_t base = (n * g.channels + c) * g.inner;
-      const P* gy = reinterpret_cast<const P*>(dy + base);
-      const P* gf = reinterpret_cast<const P*>(feat + base);
-      P* gx = reinterpret_cast<P*>(dx + base);
-      for (int64_t j = px; j < packs; j += g.tx) {
-        const P a = LoadStream(gy + j);
-        if constexpr (kFused) {
-          const P f = LoadStream(gf + j);
-          P o;
+  const int lane = threadIdx.x & 31;
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * kPlaneWarps + (threadIdx.x >> 5);
+  if (c >= g.channels) return;  // whole warp; nothing below synchronises the CTA
+  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * g.outer_per_split;
+  const int64_t n1 = min(g.outer, n0 + g.outer_per_split);
+  const int64_t ip = g.inner / kVec;        // packs per plane
+  const int64_t dn = 32 / ip, di = 32 % ip;  // 32 packs further along the walk
+  int64_t n = n0 + lane / ip, i = lane % ip;
+  const int64_t plane_stride = g.channels * g.inner;
+  const T* yc = dy + c * g.inner;
+  const T* fc = feat + c * g.inner;
+  T* xc = dx + c * g.inner;
+  alignas(8) A acc[kVec];
 #pragma unroll
-          for (int i = 0; i < kVec; ++i) {
-            const float z = MaskGrad(a.v[i], f.v[i]);
-            o.v[i] = NarrowTo<T>(z);
-            acc += z;
-          }
-          StoreStream(gx + j, o);
-        } else {
+  for (int e = 0; e < kVec; ++e) acc[e] = A(0);
+  while (n < n1) {
+    P a[kPlaneUnroll];
+    P f[kPlaneUnroll];
+    int64_t at[kPlaneUnroll];
 #pragma unroll
-          for (int i = 0; i < kVec; ++i) acc += Widen(a.v[i]);
-        }
+    for (int u = 0; u < kPlaneUnroll; ++u) {
+      at[u] = n < n1 ? n * plane_stride + i * kVec : -1;
+      if (at[u] >= 0) {
+        a[u] = LoadStream(reinterpret_cast<const P*>(yc + at[u]));
+        if constexpr (kFused) f[u] = LoadStream(reinterpret_cast<const P*>(fc + at[u]));
+      }
+      n += dn;
+      i += di;
+      if (i >= ip) {
+        i -= ip;
+        ++n;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kPlaneUnroll; ++u) {
+      if (at[u] >= 0) {
+        P o;
+        Accumulate<T, kVec, kFused>(a[u], f[u], o, acc);
+        if constexpr (kFused) StoreStream(reinterpret_cast<P*>(xc + at[u]), o);
       }
     }
   }
-  red[threadIdx.x] = acc;
-  __syncthreads();
-  for (int s = kThreads / 2; s > 0; s >>= 1) {
-    if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
-    __syncthreads();
+  A s = acc[0];
+#pragma unroll
+  for (int e = 1; e < kVec; ++e) s += acc[e];
+  // Lanes of the warp, in a fixed order.
+  if constexpr (sizeof(A) == 4) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned other = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<unsigned*>(&s), o);
+      s += *reinterpret_cast<const A*>(&other);
+    }
+  } else {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other =
+          __shfl_xor_sync(0xffffffffu, *reinterpret_cast<unsigned long long*>(&s), o);
+      s += *reinterpret_cast<const A*>(&other);
+    }
   }
-  if (threadIdx.x == 0) {
-    partial[static_cast<int64_t>(blockIdx.y) * g.channels + c] = red[0];
-  }
+  if (lane == 0) partial[static_cast<int64_t>(blockIdx.y) * g.channels + c] = s;
 }
 
 // Level 2: bias_grad[c] = sum over the partial rows.  A CTA owns 8 channels
@@ -424,8 +444,11 @@ inline int MaxSplits(const Geom& g, size_t elem) {
     if (s > by_rows) s = by_rows;
     return static_cast<int>(s < 1 ? 1 : s);
   }
-  int64_t s = budget / (g.channels > 0 ? g.channels : 1);
+  // Channel-major: 8 channels (warps) per CTA along x.
+  const int64_t gx = CeilDiv(g.channels > 0 ? g.channels : 1, kThreads / 32);
+  int64_t s = budget / gx;
   if (s > g.outer) s = g.outer;
+  if (s > 65535) s = 65535;
   return static_cast<int>(s < 1 ? 1 : s);
 }
 
@@ -471,29 +494,35 @@ int LaunchLast(const T* dy, const T* feat, T* dx,
 }
 
 template <typename T, int kVec, bool kFused>
-int LaunchInner(const T* dy, const T* feat, T* dx,
-                typename AccOf<T>::type* partial, const Geom& g, int splits,
-                cudaStream_t stream, int* splits_used) {
-  InnerGeom ig;
-  ig.outer = g.outer;
-  ig.channels = g.channels;
-  ig.inner = g.inner;
-  const int64_t packs = g.inner / kVec;
-  int tx = 1;
-  while (tx < kThreads && tx < packs) tx <<= 1;
-  ig.tx = tx;
-  int64_t want = splits;
-  const int64_t by_runs = CeilDiv(g.outer, kThreads / tx);
-  if (want > by_runs) want = by_runs;
+int LaunchPlanes(const T* dy, const T* feat, T* dx,
+                 typename AccOf<T>::type* partial, const Geom& g, int splits,
+                 cudaStream_t stream, int* splits_used) {
+  PlaneGeom pg;
+  pg.outer = g.outer;
+  pg.channels = g.channels;
+  pg.inner = g.inner;
+  const int64_t gx = CeilDiv(g.channels, kPlaneWarps);
+  int64_t want = static_cast<int64_t>(SmCount()) * kMaxCtasPerSm / gx;
+  if (want > splits) want = splits;
+  if (want > g.outer) want = g.outer;
   if (want < 1) want = 1;
-  ig.outer_per_split = CeilDiv(g.outer, want);
-  const int used = static_cast<int>(CeilDiv(g.outer, ig.outer_per_split));
+  pg.outer_per_split = CeilDiv(g.outer, want);
+  const int used = static_cast<int>(CeilDiv(g.outer, pg.outer_per_split));
   *splits_used = used;
   const cudaError_t e = LaunchChained(
-      true, BiasGradInnerKernel<T, kVec, kFused>,
-      dim3(static_cast<unsigned>(g.channels), used), dim3(kThreads), 0, stream,
-      dy, feat, dx, partial, ig);
+      true, BiasGradPlaneKernel<T, kVec, kFused>, dim3(static_cast<unsigned>(gx), used),
+      dim3(kThreads), 0, stream, dy, feat, dx, partial, pg);
   return static_cast<int>(e);
+}
+
+// Widest pack (in elements, at most 16 bytes) that divides a plane.
+template <typename T>
+int PlaneVec(int64_t inner, bool aligned) {
+  if (!aligned) return 1;
+  for (int v = VecWidth<T>::value; v > 1; v >>= 1) {
+    if (inner % v == 0) return v;
+  }
+  return 1;
 }
 
 template <typename T, bool kFused>
@@ -537,12 +566,26 @@ int BiasGrad(const void* dy_v, const void* feat_v, void* dx_v, void* out_v,
                                     &used);
     }
   } else {
-    if (aligned && g.inner % kFull == 0) {
-      rc = LaunchInner<T, kFull, kFused>(dy, feat, dx, partial, g, splits,
-                                         stream, &used);
-    } else {
-      rc = LaunchInner<T, 1, kFused>(dy, feat, dx, partial, g, splits, stream,
-                                     &used);
+    switch (PlaneVec<T>(g.inner, aligned)) {
+      case 8:
+        if constexpr (kFull >= 8) {
+          rc = LaunchPlanes<T, 8, kFused>(dy, feat, dx, partial, g, splits, stream, &used);
+        } else {
+          rc = MUSA_KERNELS_EINVAL;
+        }
+        break;
+      case 4:
+        if constexpr (kFull >= 4) {
+          rc = LaunchPlanes<T, 4, kFused>(dy, feat, dx, partial, g, splits, stream, &used);
+        } else {
+          rc = MUSA_KERNELS_EINVAL;
+        }
+        break;
+      case 2:
+        rc = LaunchPlanes<T, 2, kFused>(dy, feat, dx, partial, g, splits, stream, &used);
+        break;
+      default:
+        rc = LaunchPlanes<T, 1, kFused>(dy, feat, dx, partial, g, splits, stream, &used);
     }
   }
   if (rc != 0) return rc;

@@ -55,7 +55,9 @@ def test_chains_channels_last(kernel_lib, dtype, chain, shape):
 
 @pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
 @pytest.mark.parametrize("chain", sorted(FUSED))
-@pytest.mark.parametrize("shape", [(2, 3, 4, 5), (3, 16, 8, 8), (2, 5, 1, 1), (4, 7, 3, 8)])
+@pytest.mark.parametrize("shape", [(2, 3, 4, 5), (3, 16, 8, 8), (2, 5, 1, 1), (4, 7, 3, 8),
+                                   (3, 5, 7, 7), (2, 9, 14, 14), (5, 3, 3, 3), (33, 40, 7, 7),
+                                   (2, 3, 1, 13)])
 def test_chains_nchw(kernel_lib, dtype, chain, shape):
     rng = np.random.default_rng(21)
     dt = np_dtype(dtype)

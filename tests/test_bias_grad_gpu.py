@@ -78,7 +78,8 @@ def test_fused_and_unfused_channels_last(kernel_lib, dtype, shape):
 
 @pytest.mark.parametrize("dtype", FLOATS)
 @pytest.mark.parametrize("shape", [(2, 3, 4, 5), (3, 16, 8, 8), (2, 5, 1, 1), (4, 7, 3, 8),
-                                   (64, 33, 7, 7), (300, 2, 3)])
+                                   (64, 33, 7, 7), (300, 2, 3), (6, 40, 14, 14), (70, 9, 2, 2),
+                                   (3, 1000, 3, 3), (500, 8, 56)])
 def test_fused_and_unfused_nchw(kernel_lib, dtype, shape):
     grads, feats = _inputs(6, shape, dtype)
     want_dx, want_db = np_ref.bias_add_relu_grad(grads, feats, "NCHW")
