@@ -96,6 +96,14 @@ __device__ __forceinline__ void AsyncWait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(kPending) : "memory");
 }
 
+// Threads per CTA: one group when it is wider than 256, else 256 - except the
+// LayerNorm gradient of warp-sized groups, whose per-row-lane column-sum slabs
+// make 128-thread CTAs (4 rows, 68 KB of shared memory at 1024 bf16 columns,
+// three CTAs per SM) the better fit than 256-thread ones (132 KB, one CTA).
+__host__ __device__ constexpr int RowThreads(int group, int op) {
+  return group > 256 ? group : (op == 1 /* kOpLnGrad */ && group <= 32) ? 128 : 256;
+}
+
 template <int kOp>
 struct RowPipe {
   static constexpr bool kGrad = kOp == kOpLnGrad || kOp == kOpRmsGrad;
@@ -116,12 +124,12 @@ struct RowPipe {
 // memory each) when the compiler keeps them to 85 registers, the RMSNorm
 // gradient two (100 KB each, 128 registers).
 template <typename T, int kGroup, int kMaxPacks, int kOp>
-__global__ void __launch_bounds__((kGroup > 256 ? kGroup : 256),
+__global__ void __launch_bounds__(RowThreads(kGroup, kOp),
                                   kGroup > 256 ? 1
                                   : (kOp == kOpLnFwd || kOp == kOpRmsFwd) ? 3
                                   : kOp == kOpRmsGrad ? 2 : 1)
     RowNormKernel(RowArgs a) {
-  constexpr int kThreads = kGroup > 256 ? kGroup : 256;
+  constexpr int kThreads = RowThreads(kGroup, kOp);
   constexpr int kRows = kThreads / kGroup;
   constexpr int kVec = VecWidth<T>::value;
   constexpr bool kGrad = RowPipe<kOp>::kGrad;
@@ -648,7 +656,7 @@ size_t RowSmemBytes(int threads, int rows_per_cta, int max_packs, int row_size) 
 
 template <typename T, int kGroup, int kMaxPacks, int kOp>
 int LaunchGroup(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
-  constexpr int kThreads = kGroup > 256 ? kGroup : 256;
+  constexpr int kThreads = RowThreads(kGroup, kOp);
   constexpr int kRows = kThreads / kGroup;
   auto kernel = RowNormKernel<T, kGroup, kMaxPacks, kOp>;
   size_t smem = RowSmemBytes<kOp>(kThreads, kRows, kMaxPacks, a.row_size);
@@ -695,7 +703,7 @@ int DispatchPacks(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   const int packs = a.row_size / kVec;
   const auto fits = [&](int group) {
     if (packs > group * kMaxPacks) return false;
-    const int threads = group > 256 ? group : 256;
+    const int threads = RowThreads(group, kOp);
     return RowSmemBytes<kOp>(threads, threads / group, kMaxPacks, a.row_size) <= 200 * 1024;
   };
   if (fits(8)) return LaunchGroup<T, 8, kMaxPacks, kOp>(a, ctas_out, stream);
