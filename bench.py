@@ -780,6 +780,10 @@ def _bf16_normal(rng, shape, std):
 
 def cpu_workload(batch, seed=4):
     from oracle import c_ref
+    # A multi-rank launcher pins OMP_NUM_THREADS=1 for its workers; the CPU arm
+    # is one job on this host and takes every core it is allowed to run on.
+    if os.environ.get("OMP_NUM_THREADS") == "1" and "LOCAL_RANK" in os.environ:
+        c_ref.set_num_threads(len(os.sched_getaffinity(0)))
     rng = np.random.default_rng(seed)
     data = {}
     for (_, h, w, c) in RESNET50_BN:

@@ -38,6 +38,8 @@ def lib():
         _lib = ctypes.CDLL(_LIB)
     i64, f32, vp, ci = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_int
     _lib.cpu_ref_num_threads.restype = ci
+    _lib.cpu_ref_set_num_threads.argtypes = [ci]
+    _lib.cpu_ref_set_num_threads.restype = None
     _lib.cpu_bn_fwd_train.argtypes = [ci] + [vp] * 8 + [i64, i64, f32]
     _lib.cpu_bn_fwd_train.restype = None
     _lib.cpu_bn_grad.argtypes = [ci] + [vp] * 8 + [i64, i64, f32, ci]
@@ -51,6 +53,11 @@ def lib():
 
 def num_threads():
     return int(lib().cpu_ref_num_threads())
+
+
+def set_num_threads(n):
+    """Thread count of the following calls."""
+    lib().cpu_ref_set_num_threads(int(n))
 
 
 def _p(a):

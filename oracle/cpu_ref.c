@@ -78,6 +78,16 @@ int cpu_ref_num_threads(void) {
 #endif
 }
 
+/* Thread count of the following calls (a launcher may have pinned
+ * OMP_NUM_THREADS=1 for its worker processes). */
+void cpu_ref_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* Per-channel sums of f(row) over row blocks: each thread keeps double
  * accumulators for all channels, combined in thread order. */
 typedef void (*row_fn)(const void* a, const void* b, int dtype, int64_t row,
