@@ -233,6 +233,11 @@ class StagedPipeline:
         if not isinstance(arg, torch.Tensor):
             return arg, None
         if arg.is_cuda:
+            # A device tensor of the caller: whatever the caller's current
+            # stream still has queued for it is ordered before this call.
+            with torch.cuda.device(self.device):
+                ready = torch.cuda.current_stream().record_event()
+                self._compute_torch.wait_event(ready)
             call._hold.append(arg)
             return arg, StagedValue(arg, None)
         src = arg.contiguous()
