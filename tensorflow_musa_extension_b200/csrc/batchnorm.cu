@@ -563,6 +563,121 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// Channel-major planes whose length is not a whole number of packs (7x7,
+// 5x5, 3x3 ...): single planes cannot be read with 128-bit accesses, but a
+// GROUP of kVec neighbouring channels can - its kVec * inner elements are
+// `inner` whole packs, and the group starts on a 16-byte boundary for every n.
+// A CTA owns one group and a split of the outer axis; thread t reads pack t of
+// the group's run for n = n0, n0 + 1, ... (independent addresses: several in
+// flight).  The position of a pack inside the run is the same for every n, so
+// a thread's pack always covers the same one or two channels: the first
+// `before` elements belong to channel lo, the rest to lo + 1.
+constexpr int kGroupSlots = 4;   // packs of a run per thread (inner <= 4 * 256)
+constexpr int kGroupUnroll = 4;  // values of n in flight per thread
+
+__device__ __forceinline__ void GroupSlot(int p, int inner, int group, int* lo,
+                                          int* before) {
+  const int first = p * group;
+  *lo = first / inner;
+  *before = (*lo + 1) * inner - first;  // >= 1 elements of channel lo
+}
+
+template <typename T, int kMode>
+__global__ void __launch_bounds__(kThreads)
+    BnStatsGroupKernel(const T* __restrict__ x, const T* __restrict__ dy,
+                       const float* __restrict__ mean,
+                       float* __restrict__ partial, int64_t outer,
+                       int64_t channels, int inner, int64_t outer_per_cta) {
+  constexpr int kG = VecWidth<T>::value;
+  using P = Pack<T, kG>;
+  extern __shared__ float4 contrib[];  // [inner]: (s1, s2) of lo, (s1, s2) of lo + 1
+  __shared__ float shift_s[kG + 1];
+  GridDepWait();
+  GridDepLaunch();
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kG;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * outer_per_cta;
+  int64_t n1 = n0 + outer_per_cta;
+  if (n1 > outer) n1 = outer;
+  if (threadIdx.x < kG) {
+    shift_s[threadIdx.x] = kMode == kFwd ? ToF32(x[(c0 + threadIdx.x) * inner])
+                                         : mean[c0 + threadIdx.x];
+  }
+  if (threadIdx.x == 0) shift_s[kG] = 0.0f;
+  __syncthreads();
+  const int64_t run_stride = channels * inner;
+  const T* xg = x + c0 * inner;
+  const T* dg = dy + c0 * inner;
+#pragma unroll 1
+  for (int slot = 0; slot < kGroupSlots; ++slot) {
+    const int p = threadIdx.x + slot * blockDim.x;
+    if (p >= inner) break;
+    int lo, before;
+    GroupSlot(p, inner, kG, &lo, &before);
+    const float sh_lo = shift_s[lo], sh_hi = shift_s[lo + 1];
+    float s1l = 0.0f, s2l = 0.0f, s1h = 0.0f, s2h = 0.0f;
+    for (int64_t n = n0; n < n1; n += kGroupUnroll) {
+      P px[kGroupUnroll];
+      P pd[kGroupUnroll];
+#pragma unroll
+      for (int u = 0; u < kGroupUnroll; ++u) {
+        if (n + u < n1) {
+          const int64_t at = (n + u) * run_stride;
+          px[u] = LoadKeep(reinterpret_cast<const P*>(xg + at) + p);
+          if constexpr (kMode == kGrad) pd[u] = LoadKeep(reinterpret_cast<const P*>(dg + at) + p);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kGroupUnroll; ++u) {
+        if (n + u < n1) {
+#pragma unroll
+          for (int e = 0; e < kG; ++e) {
+            const bool in_lo = e < before;
+            const float d = ToF32(px[u].v[e]) - (in_lo ? sh_lo : sh_hi);
+            float a, b;
+            if constexpr (kMode == kFwd) {
+              a = d;
+              b = d * d;
+            } else {
+              a = ToF32(pd[u].v[e]);
+              b = a * d;
+            }
+            if (in_lo) {
+              s1l += a;
+              s2l += b;
+            } else {
+              s1h += a;
+              s2h += b;
+            }
+          }
+        }
+      }
+    }
+    contrib[p] = make_float4(s1l, s2l, s1h, s2h);
+  }
+  __syncthreads();
+  // Channel k of the group: its packs in run order, a fixed order of adds.
+  if (threadIdx.x < kG) {
+    const int k = threadIdx.x;
+    const int p_first = (k * inner) / kG;
+    const int p_last = ((k + 1) * inner - 1) / kG;
+    float t1 = 0.0f, t2 = 0.0f;
+    for (int p = p_first; p <= p_last; ++p) {
+      int lo, before;
+      GroupSlot(p, inner, kG, &lo, &before);
+      const float4 v = contrib[p];
+      if (lo == k) {
+        t1 += v.x;
+        t2 += v.y;
+      } else {  // lo == k - 1: the pack crosses into this channel
+        t1 += v.z;
+        t2 += v.w;
+      }
+    }
+    partial[(static_cast<int64_t>(blockIdx.y) * 2 + 0) * channels + c0 + k] = t1;
+    partial[(static_cast<int64_t>(blockIdx.y) * 2 + 1) * channels + c0 + k] = t2;
+  }
+}
+
 // ------------------------------------------------------------ level 2 ----
 
 struct FinalizeArgs {
@@ -1041,6 +1156,82 @@ __global__ void __launch_bounds__(kThreads)
           o.v[0] = FromF32<T>(r);
         }
         StoreStream(reinterpret_cast<P*>(oc + at[u]), o);
+      }
+    }
+  }
+}
+
+// Element-wise pass of the channel-group form (see BnStatsGroupKernel): the
+// group's coefficients sit in shared memory, a pack picks those of channel lo
+// for its first `before` elements and those of lo + 1 for the rest.
+template <typename T, int kMode>
+__global__ void __launch_bounds__(kThreads)
+    BnApplyGroupKernel(const T* __restrict__ x, const T* __restrict__ dy,
+                       T* __restrict__ out, ApplyArgs a, int64_t outer,
+                       int64_t channels, int inner, int64_t outer_per_cta) {
+  constexpr int kG = VecWidth<T>::value;
+  using P = Pack<T, kG>;
+  __shared__ float4 coef[kG + 1];  // mean, ca, cb, cc
+  GridDepWait();
+  GridDepLaunch();
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kG;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * outer_per_cta;
+  int64_t n1 = n0 + outer_per_cta;
+  if (n1 > outer) n1 = outer;
+  if (threadIdx.x < kG) {
+    const int64_t c = c0 + threadIdx.x;
+    const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
+    float cb, cc = 0.0f;
+    if constexpr (kMode == kFwd) {
+      cb = a.offset[c];
+    } else {
+      cb = a.sums ? a.sums[c] * a.inv_count : 0.0f;
+      cc = a.sums ? a.sums[channels + c] * inv * inv * a.inv_count : 0.0f;
+    }
+    coef[threadIdx.x] = make_float4(a.mean[c], a.scale[c] * inv, cb, cc);
+  }
+  if (threadIdx.x == 0) coef[kG] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  __syncthreads();
+  const int64_t run_stride = channels * inner;
+  const T* xg = x + c0 * inner;
+  const T* dg = dy + c0 * inner;
+  T* og = out + c0 * inner;
+#pragma unroll 1
+  for (int slot = 0; slot < kGroupSlots; ++slot) {
+    const int p = threadIdx.x + slot * blockDim.x;
+    if (p >= inner) break;
+    int lo, before;
+    GroupSlot(p, inner, kG, &lo, &before);
+    const float4 cl = coef[lo], ch = coef[lo + 1];
+    for (int64_t n = n0; n < n1; n += kGroupUnroll) {
+      P px[kGroupUnroll];
+      P pd[kGroupUnroll];
+#pragma unroll
+      for (int u = 0; u < kGroupUnroll; ++u) {
+        if (n + u < n1) {
+          const int64_t at = (n + u) * run_stride;
+          px[u] = LoadStream(reinterpret_cast<const P*>(xg + at) + p);
+          if constexpr (kMode == kGrad) pd[u] = LoadStream(reinterpret_cast<const P*>(dg + at) + p);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kGroupUnroll; ++u) {
+        if (n + u < n1) {
+          P o;
+#pragma unroll
+          for (int e = 0; e < kG; ++e) {
+            const float4 k = e < before ? cl : ch;
+            const float d = ToF32(px[u].v[e]) - k.x;
+            float r;
+            if constexpr (kMode == kFwd) {
+              r = fmaf(d, k.y, k.z);
+            } else {
+              r = k.y * (ToF32(pd[u].v[e]) - k.z - d * k.w);
+            }
+            o.v[e] = FromF32<T>(r);
+          }
+          StoreStream(reinterpret_cast<P*>(og + (n + u) * run_stride) + p, o);
+        }
       }
     }
   }
@@ -1608,6 +1799,37 @@ inline int PlaneVec(int64_t inner, bool aligned) {
   return 1;
 }
 
+// The channel-group form applies to planes that are not whole packs, when the
+// groups tile the channel axis and a thread has at most kGroupSlots packs.
+template <typename T>
+inline bool UseChannelGroups(const Geom& g, bool aligned) {
+  constexpr int kG = VecWidth<T>::value;
+  return aligned && g.inner % kG != 0 && g.inner >= kG &&
+         g.inner <= static_cast<int64_t>(kGroupSlots) * kThreads && g.channels % kG == 0;
+}
+struct GroupPlan {
+  int64_t gx, gy, per;
+  int threads;
+};
+template <typename T>
+inline GroupPlan PlanGroups(const Geom& g) {
+  constexpr int kG = VecWidth<T>::value;
+  GroupPlan p;
+  p.gx = g.channels / kG;
+  int64_t target = static_cast<int64_t>(SmCount()) * 8 / (p.gx > 0 ? p.gx : 1);
+  if (target < 1) target = 1;
+  int64_t gy = target < g.outer ? target : g.outer;
+  const int64_t cap = MaxSplits(g.outer, g.channels);
+  if (gy > cap) gy = cap;
+  if (gy > 65535) gy = 65535;
+  if (gy < 1) gy = 1;
+  p.per = CeilDiv(g.outer, gy);
+  p.gy = CeilDiv(g.outer, p.per);
+  const int64_t t = (g.inner + 31) / 32 * 32;
+  p.threads = static_cast<int>(t < kThreads ? t : kThreads);
+  return p;
+}
+
 // Stats launch: fills partial[splits][2][C]; returns splits (<0: error).
 template <typename T, int kMode>
 int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
@@ -1639,6 +1861,14 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
             x, dy, mean, partial, g.outer, g.channels, g.channels,
             p.rows_per_cta, keep);
     return p.gy;
+  }
+  if (UseChannelGroups<T>(g, aligned) && g.channels / kVec <= 0x7fffffffLL) {
+    const GroupPlan gp = PlanGroups<T>(g);
+    BnStatsGroupKernel<T, kMode>
+        <<<dim3(static_cast<unsigned>(gp.gx), static_cast<unsigned>(gp.gy)), gp.threads,
+           static_cast<size_t>(g.inner) * sizeof(float4), stream>>>(
+            x, dy, mean, partial, g.outer, g.channels, static_cast<int>(g.inner), gp.per);
+    return static_cast<int>(gp.gy);
   }
   // [outer, C, inner]: a warp per channel, the outer axis split over grid.y.
   const PlanePlan pp = PlanPlanes(g);
@@ -1728,10 +1958,18 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
     }
     return;
   }
+  const bool pdl = GetTuning(kTuneBnPdl) != 0;
+  if (UseChannelGroups<T>(g, aligned) && g.channels / kVec <= 0x7fffffffLL) {
+    const GroupPlan gp = PlanGroups<T>(g);
+    LaunchChained(pdl, BnApplyGroupKernel<T, kMode>,
+                  dim3(static_cast<unsigned>(gp.gx), static_cast<unsigned>(gp.gy)),
+                  dim3(gp.threads), 0, stream, x, dy, out, a, g.outer, g.channels,
+                  static_cast<int>(g.inner), gp.per);
+    return;
+  }
   const PlanePlan pp = PlanPlanes(g);
   if (pp.gx < 0) return;
   const dim3 grid(static_cast<unsigned>(pp.gx), static_cast<unsigned>(pp.gy));
-  const bool pdl = GetTuning(kTuneBnPdl) != 0;
   switch (PlaneVec<T>(g.inner, aligned)) {
     case 8:
       if constexpr (kVec >= 8) {

@@ -91,7 +91,10 @@ def test_nhwc_shape_matrix(kernel_lib, dtype, c, rows):
 
 @pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
 @pytest.mark.parametrize("shape", [(2, 3, 4, 5), (2, 32, 1, 1), (5, 16, 8, 8), (3, 7, 7, 7),
-                                   (16, 64, 14, 14), (1, 4, 3, 3)])
+                                   (16, 64, 14, 14), (1, 4, 3, 3),
+                                   # planes that are not whole packs, channels in whole groups:
+                                   (4, 16, 7, 7), (3, 8, 5, 5), (2, 8, 3, 3), (37, 64, 7, 7),
+                                   (2, 8, 17, 19), (3, 16, 31, 33), (70, 24, 3, 5)])
 def test_nchw_shapes(kernel_lib, dtype, shape):
     x, s, o, dy = bn_inputs(200 + shape[1], shape, dtype, 0.5, 2.0, channel_axis=1)
     fwd, grad = run_both(x, s, o, dy, "NCHW")
