@@ -178,6 +178,46 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Channels-last with a row of packs that divides the CTA width (channel counts
+// of 8 .. 2048 in fp16 / bf16 that are powers of two, and the like): with a grid
+// stride that is a multiple of the CTA width a thread meets the same bias pack
+// in every pack it handles.  It is fetched once, and the loop is nothing but
+// four loads, the math and four stores around two pointer bumps - the index
+// bookkeeping of the general kernel costs as many issue slots as a sigmoid.
+template <typename T, int kEpt, int kAct>
+__global__ void __launch_bounds__(256)
+    BiasActFixedKernel(const T* __restrict__ x, const T* __restrict__ bias,
+                       T* __restrict__ y, int64_t n_packs, int cv) {
+  using P = Pack<T, kEpt>;
+  const P pb = LoadKeep(reinterpret_cast<const P*>(bias) + (threadIdx.x % cv));
+  // A tile is 4 * 256 consecutive packs (16 KB): the four loads of a warp stay
+  // inside one DRAM neighbourhood.
+  const int64_t n_tiles = (n_packs + 1023) / 1024;
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int64_t base = t * 1024 + threadIdx.x;
+    const P* xp = reinterpret_cast<const P*>(x) + base;
+    P* yp = reinterpret_cast<P*>(y) + base;
+    if (base + 768 < n_packs) {
+      const P a0 = LoadStream(xp);
+      const P a1 = LoadStream(xp + 256);
+      const P a2 = LoadStream(xp + 512);
+      const P a3 = LoadStream(xp + 768);
+      StoreStream(yp, ActivatePack<T, kEpt, kAct, true>(a0, pb));
+      StoreStream(yp + 256, ActivatePack<T, kEpt, kAct, true>(a1, pb));
+      StoreStream(yp + 512, ActivatePack<T, kEpt, kAct, true>(a2, pb));
+      StoreStream(yp + 768, ActivatePack<T, kEpt, kAct, true>(a3, pb));
+    } else {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (base + u * 256 < n_packs) {
+          StoreStream(yp + u * 256,
+                      ActivatePack<T, kEpt, kAct, true>(LoadStream(xp + u * 256), pb));
+        }
+      }
+    }
+  }
+}
+
 // General layout: [outer, channels, inner] with packs of kEpt elements that
 // never straddle a channel (inner % kEpt == 0), or kEpt == 1.
 template <typename T, int kEpt, int kAct, bool kHasBias>
@@ -322,6 +362,21 @@ int LaunchTyped(const T* x, const T* bias, T* y, int64_t outer,
     const int cv = static_cast<int>(channels / kVec);
     const int per_sm = GetTuning(kTuneBiasActCtasPerSm);
     const int unroll = GetTuning(kTuneBiasActUnroll);
+    if constexpr (kHasBias) {
+      if (256 % cv == 0 && unroll != 2 && unroll != 8) {
+        auto kernel = BiasActFixedKernel<T, kVec, kAct>;
+        int resident = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, 256, 0) !=
+                cudaSuccess ||
+            resident < 1) {
+          resident = 1;
+        }
+        (void)resident;
+        const int grid = GridFor(CeilDiv(n_packs, 1024), per_sm);
+        kernel<<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
+        return static_cast<int>(cudaGetLastError());
+      }
+    }
     if (unroll == 2) {
       const int grid = GridFor(CeilDiv(n_packs, 256 * 2), per_sm);
       BiasActLastKernel<T, kVec, 2, kAct, kHasBias>
