@@ -123,7 +123,7 @@ struct RowPipe {
 // The single-input forms fit three 256-thread CTAs per SM (56 KB of shared
 // memory each) when the compiler keeps them to 85 registers, the RMSNorm
 // gradient two (100 KB each, 128 registers).
-template <typename T, int kGroup, int kMaxPacks, int kOp>
+template <typename T, int kGroup, int kMaxPacks, int kOp, bool kFull>
 __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
                                   kGroup > 256 ? 1
                                   : (kOp == kOpLnFwd || kOp == kOpRmsFwd) ? 3
@@ -157,6 +157,9 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
   const float inv_n = 1.0f / static_cast<float>(a.row_size);
   float* my_slab = slab + static_cast<size_t>(lane_row) * 2 * a.row_size;
   uint4* const mine = ring + threadIdx.x;
+  // Pack j of this thread exists; known at compile time for rows that fill the
+  // layout (kFull: row_size == kGroup * kMaxPacks packs).
+  const auto Has = [&](int j) { return kFull || t + j * kGroup < packs; };
   // Quad h of pack p (elements 4h .. 4h+3) sits at ((h * packs + p) * 4): the
   // 128-bit accesses of neighbouring lanes are 16 bytes apart.
   const auto Quad = [&](const float* base, int h, int p) {
@@ -175,7 +178,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 #pragma unroll
     for (int j = 0; j < kMaxPacks; ++j) {
       const int p = t + j * kGroup;
-      if (p < packs) {
+      if (Has(j)) {
 #pragma unroll
         for (int h = 0; h < 2 * kQuads; ++h) {
           *reinterpret_cast<float4*>(my_slab + (h * packs + p) * 4) =
@@ -207,7 +210,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 #pragma unroll
       for (int j = 0; j < kMaxPacks; ++j) {
         const int p = t + j * kGroup;
-        if (p < packs) {
+        if (Has(j)) {
           AsyncCopy16(mine + ((stage * kInputs + 0) * kMaxPacks + j) * kThreads, xp + p);
           if constexpr (kGrad) {
             AsyncCopy16(mine + ((stage * kInputs + 1) * kMaxPacks + j) * kThreads, dp + p);
@@ -236,7 +239,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
     P cd[kGrad ? kMaxPacks : 1];
 #pragma unroll
     for (int j = 0; j < kMaxPacks; ++j) {
-      if (live && t + j * kGroup < packs) {
+      if (live && Has(j)) {
         const uint4 rx = mine[((stage * kInputs + 0) * kMaxPacks + j) * kThreads];
         cx[j] = *reinterpret_cast<const P*>(&rx);
         if constexpr (kGrad) {
@@ -250,7 +253,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
     float2 xv[kMaxPacks][kPairs];
 #pragma unroll
     for (int j = 0; j < kMaxPacks; ++j) {
-      if (live && t + j * kGroup < packs) {
+      if (live && Has(j)) {
         WidenPack<kVec>(cx[j], xv[j]);
       } else {
 #pragma unroll
@@ -274,7 +277,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
         float2 r2 = make_float2(0.0f, 0.0f);
 #pragma unroll
         for (int j = 0; j < kMaxPacks; ++j) {
-          if (live && t + j * kGroup < packs) {
+          if (live && Has(j)) {
 #pragma unroll
             for (int q = 0; q < kPairs; ++q) {
               xv[j][q] = Add2(xv[j][q], nfirst);
@@ -287,7 +290,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
         const float2 nshift = Dup(-shift);
 #pragma unroll
         for (int j = 0; j < kMaxPacks; ++j) {
-          if (live && t + j * kGroup < packs) {
+          if (live && Has(j)) {
 #pragma unroll
             for (int q = 0; q < kPairs; ++q) {
               xv[j][q] = Add2(xv[j][q], nshift);
@@ -306,7 +309,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
         float2 r2 = make_float2(0.0f, 0.0f);
 #pragma unroll
         for (int j = 0; j < kMaxPacks; ++j) {
-          if (live && t + j * kGroup < packs) {
+          if (live && Has(j)) {
 #pragma unroll
             for (int q = 0; q < kPairs; ++q) {
               xv[j][q] = Add2(xv[j][q], nmean0);
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
         const float2 nmean1 = Dup(-mean1);
 #pragma unroll
         for (int j = 0; j < kMaxPacks; ++j) {
-          if (live && t + j * kGroup < packs) {
+          if (live && Has(j)) {
 #pragma unroll
             for (int q = 0; q < kPairs; ++q) {
               xv[j][q] = Add2(xv[j][q], nmean1);
@@ -341,7 +344,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 #pragma unroll
         for (int j = 0; j < kMaxPacks; ++j) {
           const int p = t + j * kGroup;
-          if (live && p < packs) {
+          if (live && Has(j)) {
             float2 gm[kPairs], bt[kPairs], o2[kPairs];
             LoadRowVector(gsm, p, gm);
             LoadRowVector(bsm, p, bt);
@@ -361,7 +364,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 #pragma unroll
         for (int j = 0; j < kMaxPacks; ++j) {
           const int p = t + j * kGroup;
-          if (live && p < packs) {
+          if (live && Has(j)) {
             float2 gm[kPairs], dv[kPairs];
             LoadRowVector(gsm, p, gm);
             WidenPack<kVec>(cd[j], dv);
@@ -381,7 +384,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 #pragma unroll
         for (int j = 0; j < kMaxPacks; ++j) {
           const int p = t + j * kGroup;
-          if (live && p < packs) {
+          if (live && Has(j)) {
             float2 gm[kPairs], dv[kPairs], o2[kPairs];
             LoadRowVector(gsm, p, gm);
             WidenPack<kVec>(cd[j], dv);
@@ -426,7 +429,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 #pragma unroll
       for (int j = 0; j < kMaxPacks; ++j) {
         const int p = t + j * kGroup;
-        if (live && p < packs) {
+        if (live && Has(j)) {
           float2 gm[kPairs], n2[kPairs], o2[kPairs];
           LoadRowVector(gsm, p, gm);
 #pragma unroll
@@ -447,7 +450,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 #pragma unroll
       for (int j = 0; j < kMaxPacks; ++j) {
         const int p = t + j * kGroup;
-        if (live && p < packs) {
+        if (live && Has(j)) {
           float2 gm[kPairs], dv[kPairs];
           LoadRowVector(gsm, p, gm);
           WidenPack<kVec>(cd[j], dv);
@@ -466,7 +469,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 #pragma unroll
       for (int j = 0; j < kMaxPacks; ++j) {
         const int p = t + j * kGroup;
-        if (live && p < packs) {
+        if (live && Has(j)) {
           float2 o2[kPairs];
 #pragma unroll
           for (int q = 0; q < kPairs; ++q) {
@@ -654,11 +657,11 @@ size_t RowSmemBytes(int threads, int rows_per_cta, int max_packs, int row_size) 
   return bytes;
 }
 
-template <typename T, int kGroup, int kMaxPacks, int kOp>
-int LaunchGroup(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
+template <typename T, int kGroup, int kMaxPacks, int kOp, bool kFull>
+int LaunchGroupAs(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   constexpr int kThreads = RowThreads(kGroup, kOp);
   constexpr int kRows = kThreads / kGroup;
-  auto kernel = RowNormKernel<T, kGroup, kMaxPacks, kOp>;
+  auto kernel = RowNormKernel<T, kGroup, kMaxPacks, kOp, kFull>;
   size_t smem = RowSmemBytes<kOp>(kThreads, kRows, kMaxPacks, a.row_size);
   if (smem > 40 * 1024) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -684,6 +687,20 @@ int LaunchGroup(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   *ctas_out = static_cast<int>(grid);
   return static_cast<int>(LaunchChained(true, kernel, dim3(static_cast<unsigned>(grid)),
                                         dim3(kThreads), smem, stream, a));
+}
+
+template <typename T, int kGroup, int kMaxPacks, int kOp>
+int LaunchGroup(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
+  // Rows that fill the layout need no per-pack presence checks.  Only the
+  // LayerNorm gradient gains from the specialised form (fp32 rows of 1024:
+  // +8 %); the forward kernels measured the same or, where the compiler then
+  // spills under their register cap, slower.
+  if constexpr (kOp == kOpLnGrad) {
+    if (a.row_size / VecWidth<T>::value == kGroup * kMaxPacks) {
+      return LaunchGroupAs<T, kGroup, kMaxPacks, kOp, true>(a, ctas_out, stream);
+    }
+  }
+  return LaunchGroupAs<T, kGroup, kMaxPacks, kOp, false>(a, ctas_out, stream);
 }
 
 template <typename T, int kOp>
