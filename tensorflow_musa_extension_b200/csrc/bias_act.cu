@@ -364,16 +364,9 @@ int LaunchTyped(const T* x, const T* bias, T* y, int64_t outer,
     const int unroll = GetTuning(kTuneBiasActUnroll);
     if constexpr (kHasBias) {
       if (256 % cv == 0 && unroll != 2 && unroll != 8) {
-        auto kernel = BiasActFixedKernel<T, kVec, kAct>;
-        int resident = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, 256, 0) !=
-                cudaSuccess ||
-            resident < 1) {
-          resident = 1;
-        }
-        (void)resident;
         const int grid = GridFor(CeilDiv(n_packs, 1024), per_sm);
-        kernel<<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
+        BiasActFixedKernel<T, kVec, kAct>
+            <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
         return static_cast<int>(cudaGetLastError());
       }
     }

@@ -14,10 +14,10 @@
 // A row is read from HBM once: a group of kGroup threads holds it in registers
 // (up to kMaxPacks 128-bit packs per thread), reduces with shuffles (and shared
 // memory across warps) and writes the results.  The reference kernels walk the
-// row two or three times.  Statistics are fp32; the variance is taken around
-// the mean (second in-register pass), so it does not cancel.  Rows that do not
-// fit the register form (very long, or not a whole number of aligned packs)
-// take a CTA-per-row kernel with element accesses.
+// row two or three times.  Statistics are fp32; the variance is taken from the
+// residuals around a first mean (second in-register pass), so it does not
+// cancel.  Rows that do not fit the register form (very long, or not a whole
+// number of aligned packs) take a CTA-per-row kernel with element accesses.
 #include "common.cuh"
 #include "tuning.h"
 #include "../../include/musa_plugin_kernels.h"
@@ -47,34 +47,69 @@ struct RowArgs {
   float epsilon;
 };
 
-// Sum over the kGroup threads that share a row; every thread of the group
-// gets the total.  Groups are aligned runs of threads, so a group of 32 or
-// fewer lives inside one warp; larger groups go through shared memory and
-// need every thread of the CTA to take part.
+// Sums over the kGroup threads that share a row; every thread of the group
+// gets the totals.  Groups are aligned runs of threads, so a group of 32 or
+// fewer lives inside one warp (shuffles only); larger groups go through shared
+// memory and meet at a barrier - a named one per group when the CTA holds
+// several (ids 1 .., barrier 0 stays with __syncthreads).  Successive sums
+// alternate between two scratch rows (`parity`), which makes one barrier per
+// sum enough: a warp that writes row A for sum k + 2 has passed the barrier of
+// sum k + 1, which every warp of the group reaches only after reading row A of
+// sum k.  All threads of a group must make the same sequence of calls.
 template <int kGroup, int kThreads>
-__device__ __forceinline__ float GroupSum(float v, float* smem) {
+__device__ __forceinline__ void GroupMeet() {
+  if constexpr (kGroup == kThreads) {
+    __syncthreads();
+  } else {
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + (threadIdx.x >> 5) / (kGroup / 32)), "n"(kGroup)
+                 : "memory");
+  }
+}
+
+template <int kGroup, int kThreads>
+__device__ __forceinline__ float2 GroupSum2(float2 v, float2* smem, int& parity) {
+  constexpr int kWarpSpan = kGroup < 32 ? kGroup : 32;
+#pragma unroll
+  for (int m = kWarpSpan / 2; m > 0; m >>= 1) {
+    v.x += __shfl_xor_sync(0xffffffffu, v.x, m);
+    v.y += __shfl_xor_sync(0xffffffffu, v.y, m);
+  }
+  if constexpr (kGroup > 32) {
+    constexpr int kWarps = kGroup / 32;
+    const int warp = threadIdx.x >> 5;
+    const int first = (warp / kWarps) * kWarps;  // first warp of this group
+    float2* row = smem + parity * (kThreads / 32);
+    parity ^= 1;
+    if ((threadIdx.x & 31) == 0) row[warp] = v;
+    GroupMeet<kGroup, kThreads>();
+    float2 t = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float2 o = row[first + w];
+      t.x += o.x;
+      t.y += o.y;
+    }
+    v = t;
+  }
+  return v;
+}
+
+template <int kGroup, int kThreads>
+__device__ __forceinline__ float GroupSum(float v, float2* smem, int& parity) {
   constexpr int kWarpSpan = kGroup < 32 ? kGroup : 32;
 #pragma unroll
   for (int m = kWarpSpan / 2; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
   if constexpr (kGroup > 32) {
     constexpr int kWarps = kGroup / 32;
     const int warp = threadIdx.x >> 5;
-    const int first = (warp / kWarps) * kWarps;  // first warp of this group
-    // Only the warps of one group meet: a named barrier per group when the CTA
-    // holds several (ids 1 .., barrier 0 stays with __syncthreads).
-    const auto meet = [&]() {
-      if constexpr (kGroup == kThreads) {
-        __syncthreads();
-      } else {
-        asm volatile("bar.sync %0, %1;" ::"r"(1 + warp / kWarps), "n"(kGroup) : "memory");
-      }
-    };
-    meet();  // smem free again
-    if ((threadIdx.x & 31) == 0) smem[warp] = v;
-    meet();
+    const int first = (warp / kWarps) * kWarps;
+    float2* row = smem + parity * (kThreads / 32);
+    parity ^= 1;
+    if ((threadIdx.x & 31) == 0) row[warp].x = v;
+    GroupMeet<kGroup, kThreads>();
     float t = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) t += smem[first + w];
+    for (int w = 0; w < kWarps; ++w) t += row[first + w].x;
     v = t;
   }
   return v;
@@ -97,9 +132,9 @@ __device__ __forceinline__ void AsyncWait() {
 }
 
 // Threads per CTA: one group when it is wider than 256, else 256 - except the
-// LayerNorm gradient of warp-sized groups, whose per-row-lane column-sum slabs
-// make 128-thread CTAs (4 rows, 68 KB of shared memory at 1024 bf16 columns,
-// three CTAs per SM) the better fit than 256-thread ones (132 KB, one CTA).
+// LayerNorm gradient of warp-sized groups: it keeps its column sums in
+// registers (about 190 a thread), and 128-thread CTAs then fill an SM in
+// finer steps.
 __host__ __device__ constexpr int RowThreads(int group, int op) {
   return group > 256 ? group : (op == 1 /* kOpLnGrad */ && group <= 32) ? 128 : 256;
 }
@@ -108,10 +143,15 @@ template <int kOp>
 struct RowPipe {
   static constexpr bool kGrad = kOp == kOpLnGrad || kOp == kOpRmsGrad;
   static constexpr int kInputs = kGrad ? 2 : 1;
-  // The LayerNorm gradient shares the CTA's shared memory with its column
-  // sums, so its ring is one stage shorter.
-  static constexpr int kStages = kOp == kOpLnGrad ? 2 : 3;
 };
+
+#ifndef MUSA_LN_GRAD_STAGES
+#define MUSA_LN_GRAD_STAGES 3
+#endif
+// Ring stages.  The two-input ring of a 512-thread group is 64 KB a stage.
+__host__ __device__ constexpr int RowStages(int op, int group) {
+  return op == 1 /* kOpLnGrad */ ? (group > 256 ? 2 : MUSA_LN_GRAD_STAGES) : 3;
+}
 
 // One launch handles all rows; CTA = max(256, kGroup) threads = kRows rows at
 // a time, grid-stride over blocks of kRows rows.  The rows travel through a
@@ -123,6 +163,11 @@ struct RowPipe {
 // The single-input forms fit three 256-thread CTAs per SM (56 KB of shared
 // memory each) when the compiler keeps them to 85 registers, the RMSNorm
 // gradient two (100 KB each, 128 registers).
+// The LayerNorm gradient keeps the column sums (dgamma, dbeta) of a thread's
+// packs in registers: a thread meets the same columns in every row.  When the
+// rows are done the sums go to shared memory (over the ring, which is free by
+// then), the row lanes of the CTA are added in lane order and the CTA writes
+// one partial row.
 template <typename T, int kGroup, int kMaxPacks, int kOp, bool kFull>
 __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
                                   kGroup > 256 ? 1
@@ -134,22 +179,21 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
   constexpr int kVec = VecWidth<T>::value;
   constexpr bool kGrad = RowPipe<kOp>::kGrad;
   constexpr int kInputs = RowPipe<kOp>::kInputs;
-  constexpr int kStages = RowPipe<kOp>::kStages;
+  constexpr int kStages = RowStages(kOp, kGroup);
   constexpr int kPairs = kVec / 2;
   constexpr int kQuads = kVec / 4;
   using P = Pack<T, kVec>;
-  __shared__ float red[kThreads / 32];
-  // Ring: [stage][input][pack j][thread], 16 bytes each; then, for the
-  // LayerNorm gradient, the column sums: one slab [2][kVec / 4][packs][4] per
-  // row lane (quads of one pack `packs * 4` floats apart, so that the 128-bit
-  // accesses of a warp fall on different banks); a thread is the only one that
-  // touches its columns of its slab.
+  __shared__ float2 red[2 * (kThreads / 32)];
+  int parity = 0;
+  // Ring: [stage][input][pack j][thread], 16 bytes each.  After the ring:
+  // gamma (and beta for the LayerNorm forward) widened to fp32 once per CTA,
+  // in quads (see Quad below).
   extern __shared__ uint4 ring[];
-  // After the ring: gamma (and beta for the LayerNorm forward) widened to fp32
-  // once per CTA, in the quad layout of the slabs below, then the slabs.
   float* gsm = reinterpret_cast<float*>(ring + kStages * kInputs * kMaxPacks * kThreads);
   float* bsm = gsm + a.row_size;
-  float* slab = gsm + (kOp == kOpLnFwd ? 2 : 1) * a.row_size;
+  // LayerNorm gradient, after the last row: one slab [2][kVec / 4][packs][4]
+  // of column sums per row lane, laid over the ring.
+  float* slab = reinterpret_cast<float*>(ring);
 
   const int t = threadIdx.x % kGroup;
   const int lane_row = threadIdx.x / kGroup;
@@ -174,18 +218,17 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
     }
   };
 
+  // Column sums of this thread's packs (dgamma, dbeta), kept in registers.
+  float2 ag[kOp == kOpLnGrad ? kMaxPacks : 1][kPairs];
+  float2 ab[kOp == kOpLnGrad ? kMaxPacks : 1][kPairs];
   if constexpr (kOp == kOpLnGrad) {
 #pragma unroll
-    for (int j = 0; j < kMaxPacks; ++j) {
-      const int p = t + j * kGroup;
-      if (Has(j)) {
+    for (int j = 0; j < kMaxPacks; ++j)
 #pragma unroll
-        for (int h = 0; h < 2 * kQuads; ++h) {
-          *reinterpret_cast<float4*>(my_slab + (h * packs + p) * 4) =
-              make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        }
+      for (int q = 0; q < kPairs; ++q) {
+        ag[j][q] = make_float2(0.0f, 0.0f);
+        ab[j][q] = make_float2(0.0f, 0.0f);
       }
-    }
   }
 
   GridDepWait();
@@ -264,76 +307,38 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 
     if constexpr (kOp == kOpLnFwd || kOp == kOpLnGrad) {
       // A plain fp32 sum of the row can be off by a few ulps of |mean|, which
-      // matters when |mean| >> std.  Sums of residuals are accurate: rows that
-      // live in one warp subtract the row's first element before summing (one
-      // shuffle brings it over); wider groups take a first mean, then correct
-      // it by the mean of the residuals around it.
-      float mean;
-      float2 q2 = make_float2(0.0f, 0.0f);
-      if constexpr (kGroup <= 32) {
-        const float first =
-            __shfl_sync(0xffffffffu, xv[0][0].x, (threadIdx.x & 31) & ~(kGroup - 1));
-        const float2 nfirst = Dup(-first);
-        float2 r2 = make_float2(0.0f, 0.0f);
+      // matters when |mean| >> std.  So: a first mean from the plain sum, then
+      // one pass over the residuals r = x - mean0 that gives both the
+      // correction mean1 = mean(r) and the variance mean(r^2) - mean1^2
+      // (mean1 is of rounding size, nothing cancels).  Two group sums a row.
+      float2 s2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int j = 0; j < kMaxPacks; ++j) {
-          if (live && Has(j)) {
+      for (int j = 0; j < kMaxPacks; ++j)
 #pragma unroll
-            for (int q = 0; q < kPairs; ++q) {
-              xv[j][q] = Add2(xv[j][q], nfirst);
-              r2 = Add2(r2, xv[j][q]);
-            }
-          }
-        }
-        const float shift = GroupSum<kGroup, kThreads>(r2.x + r2.y, red) * inv_n;
-        mean = first + shift;
-        const float2 nshift = Dup(-shift);
+        for (int q = 0; q < kPairs; ++q) s2 = Add2(s2, xv[j][q]);
+      const float mean0 = GroupSum<kGroup, kThreads>(s2.x + s2.y, red, parity) * inv_n;
+      const float2 nmean0 = Dup(-mean0);
+      float2 r2 = make_float2(0.0f, 0.0f), q2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int j = 0; j < kMaxPacks; ++j) {
-          if (live && Has(j)) {
+      for (int j = 0; j < kMaxPacks; ++j) {
+        if (live && Has(j)) {
 #pragma unroll
-            for (int q = 0; q < kPairs; ++q) {
-              xv[j][q] = Add2(xv[j][q], nshift);
-              q2 = Fma2(xv[j][q], xv[j][q], q2);
-            }
-          }
-        }
-      } else {
-        float2 s2 = make_float2(0.0f, 0.0f);
-#pragma unroll
-        for (int j = 0; j < kMaxPacks; ++j)
-#pragma unroll
-          for (int q = 0; q < kPairs; ++q) s2 = Add2(s2, xv[j][q]);
-        const float mean0 = GroupSum<kGroup, kThreads>(s2.x + s2.y, red) * inv_n;
-        const float2 nmean0 = Dup(-mean0);
-        float2 r2 = make_float2(0.0f, 0.0f);
-#pragma unroll
-        for (int j = 0; j < kMaxPacks; ++j) {
-          if (live && Has(j)) {
-#pragma unroll
-            for (int q = 0; q < kPairs; ++q) {
-              xv[j][q] = Add2(xv[j][q], nmean0);
-              r2 = Add2(r2, xv[j][q]);
-            }
-          }
-        }
-        const float mean1 = GroupSum<kGroup, kThreads>(r2.x + r2.y, red) * inv_n;
-        mean = mean0 + mean1;
-        const float2 nmean1 = Dup(-mean1);
-#pragma unroll
-        for (int j = 0; j < kMaxPacks; ++j) {
-          if (live && Has(j)) {
-#pragma unroll
-            for (int q = 0; q < kPairs; ++q) {
-              xv[j][q] = Add2(xv[j][q], nmean1);
-              q2 = Fma2(xv[j][q], xv[j][q], q2);
-            }
+          for (int q = 0; q < kPairs; ++q) {
+            xv[j][q] = Add2(xv[j][q], nmean0);
+            r2 = Add2(r2, xv[j][q]);
+            q2 = Fma2(xv[j][q], xv[j][q], q2);
           }
         }
       }
-      const float var = GroupSum<kGroup, kThreads>(q2.x + q2.y, red) * inv_n;
+      const float2 rq = GroupSum2<kGroup, kThreads>(
+          make_float2(r2.x + r2.y, q2.x + q2.y), red, parity);
+      const float mean1 = rq.x * inv_n;
+      const float mean = mean0 + mean1;
+      const float var = fmaxf(fmaf(-mean1, mean1, rq.y * inv_n), 0.0f);
       const float inv_std = 1.0f / sqrtf(var + a.epsilon);
       const float2 inv2 = Dup(inv_std);
+      // x_hat = (r - mean1) * inv_std = r * inv_std + shift
+      const float2 shift2 = Dup(-mean1 * inv_std);
 
       if constexpr (kOp == kOpLnFwd) {
         if (live && t == 0) {
@@ -350,7 +355,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
             LoadRowVector(bsm, p, bt);
 #pragma unroll
             for (int q = 0; q < kPairs; ++q) {
-              o2[q] = Fma2(Mul2(xv[j][q], inv2), gm[q], bt[q]);
+              o2[q] = Fma2(Fma2(xv[j][q], inv2, shift2), gm[q], bt[q]);
             }
             P o;
             NarrowPack<kVec>(o2, o);
@@ -370,15 +375,16 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
             WidenPack<kVec>(cd[j], dv);
 #pragma unroll
             for (int q = 0; q < kPairs; ++q) {
-              xv[j][q] = Mul2(xv[j][q], inv2);  // x_hat from here on
+              xv[j][q] = Fma2(xv[j][q], inv2, shift2);  // x_hat from here on
               const float2 g = Mul2(dv[q], gm[q]);
               sg2 = Add2(sg2, g);
               sgx2 = Fma2(g, xv[j][q], sgx2);
             }
           }
         }
-        const float mg = GroupSum<kGroup, kThreads>(sg2.x + sg2.y, red) * inv_n;
-        const float mgx = GroupSum<kGroup, kThreads>(sgx2.x + sgx2.y, red) * inv_n;
+        const float2 gs = GroupSum2<kGroup, kThreads>(
+            make_float2(sg2.x + sg2.y, sgx2.x + sgx2.y), red, parity);
+        const float mg = gs.x * inv_n, mgx = gs.y * inv_n;
         const float2 nmg = Dup(-mg), nmgx = Dup(-mgx);
         P* op = reinterpret_cast<P*>(a.out) + row * packs;
 #pragma unroll
@@ -396,20 +402,11 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
             P o;
             NarrowPack<kVec>(o2, o);
             StoreStream(op + p, o);
-            // Column sums: dgamma += dy * x_hat, dbeta += dy, a quad at a time.
+            // Column sums: dgamma += dy * x_hat, dbeta += dy.
 #pragma unroll
-            for (int h = 0; h < kQuads; ++h) {
-              float4* cg = reinterpret_cast<float4*>(my_slab + (h * packs + p) * 4);
-              float4* cb =
-                  reinterpret_cast<float4*>(my_slab + ((kQuads + h) * packs + p) * 4);
-              float4 vg = *cg, vb = *cb;
-              const float2 lo = Fma2(dv[2 * h], xv[j][2 * h], make_float2(vg.x, vg.y));
-              const float2 hi =
-                  Fma2(dv[2 * h + 1], xv[j][2 * h + 1], make_float2(vg.z, vg.w));
-              const float2 blo = Add2(dv[2 * h], make_float2(vb.x, vb.y));
-              const float2 bhi = Add2(dv[2 * h + 1], make_float2(vb.z, vb.w));
-              *cg = make_float4(lo.x, lo.y, hi.x, hi.y);
-              *cb = make_float4(blo.x, blo.y, bhi.x, bhi.y);
+            for (int q = 0; q < kPairs; ++q) {
+              ag[j][q] = Fma2(dv[q], xv[j][q], ag[j][q]);
+              ab[j][q] = Add2(ab[j][q], dv[q]);
             }
           }
         }
@@ -420,7 +417,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
       for (int j = 0; j < kMaxPacks; ++j)
 #pragma unroll
         for (int q = 0; q < kPairs; ++q) s2 = Fma2(xv[j][q], xv[j][q], s2);
-      const float ms = GroupSum<kGroup, kThreads>(s2.x + s2.y, red) * inv_n;
+      const float ms = GroupSum<kGroup, kThreads>(s2.x + s2.y, red, parity) * inv_n;
       const float inv = 1.0f / sqrtf(ms + a.epsilon);
       const float2 inv2 = Dup(inv);
       if (live && t == 0) static_cast<T*>(a.stat_t)[row] = FromF32<T>(inv);
@@ -461,7 +458,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
           }
         }
       }
-      const float dot = GroupSum<kGroup, kThreads>(s2.x + s2.y, red);
+      const float dot = GroupSum<kGroup, kThreads>(s2.x + s2.y, red, parity);
       const float inv = live ? ToF32(static_cast<const T*>(a.inv_in)[row]) : 0.0f;
       const float2 inv2 = Dup(inv);
       const float2 ncoeff = Dup(-(dot * inv * inv * inv * inv_n));
@@ -487,6 +484,23 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
     // One partial row (dgamma part, dbeta part) per CTA: the slabs of the row
     // lanes added in lane order.  Column c of half s sits at
     // ((s * kQuads + (c % kVec) / 4) * packs + c / kVec) * 4 + c % 4.
+    // The ring is free once every thread has left the loop: the slabs of the
+    // row lanes go there.
+    AsyncWait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kMaxPacks; ++j) {
+      const int p = t + j * kGroup;
+      if (Has(j)) {
+#pragma unroll
+        for (int h = 0; h < kQuads; ++h) {
+          *reinterpret_cast<float4*>(my_slab + (h * packs + p) * 4) = make_float4(
+              ag[j][2 * h].x, ag[j][2 * h].y, ag[j][2 * h + 1].x, ag[j][2 * h + 1].y);
+          *reinterpret_cast<float4*>(my_slab + ((kQuads + h) * packs + p) * 4) = make_float4(
+              ab[j][2 * h].x, ab[j][2 * h].y, ab[j][2 * h + 1].x, ab[j][2 * h + 1].y);
+        }
+      }
+    }
     __syncthreads();
     float* out = a.partial + static_cast<int64_t>(blockIdx.x) * 2 * a.row_size;
     for (int c = threadIdx.x; c < 2 * a.row_size; c += kThreads) {
@@ -506,7 +520,8 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
 template <typename T, int kOp>
 __global__ void __launch_bounds__(256) RowNormLoopKernel(RowArgs a) {
   constexpr int kThreads = 256;
-  __shared__ float red[kThreads / 32];
+  __shared__ float2 red[2 * (kThreads / 32)];
+  int parity = 0;
   const T* gamma = static_cast<const T*>(a.gamma);
   const int n = a.row_size;
   const float inv_n = 1.0f / static_cast<float>(n);
@@ -523,16 +538,16 @@ __global__ void __launch_bounds__(256) RowNormLoopKernel(RowArgs a) {
     if constexpr (kOp == kOpLnFwd || kOp == kOpLnGrad) {
       float s = 0.0f;
       for (int i = threadIdx.x; i < n; i += kThreads) s += ToF32(x[i]);
-      const float mean0 = GroupSum<kThreads, kThreads>(s, red) * inv_n;
+      const float mean0 = GroupSum<kThreads, kThreads>(s, red, parity) * inv_n;
       float r = 0.0f;
       for (int i = threadIdx.x; i < n; i += kThreads) r += ToF32(x[i]) - mean0;
-      const float mean = mean0 + GroupSum<kThreads, kThreads>(r, red) * inv_n;
+      const float mean = mean0 + GroupSum<kThreads, kThreads>(r, red, parity) * inv_n;
       float q = 0.0f;
       for (int i = threadIdx.x; i < n; i += kThreads) {
         const float d = ToF32(x[i]) - mean;
         q += d * d;
       }
-      const float var = GroupSum<kThreads, kThreads>(q, red) * inv_n;
+      const float var = GroupSum<kThreads, kThreads>(q, red, parity) * inv_n;
       const float inv_std = 1.0f / sqrtf(var + a.epsilon);
       if constexpr (kOp == kOpLnFwd) {
         const T* beta = static_cast<const T*>(a.beta);
@@ -553,8 +568,8 @@ __global__ void __launch_bounds__(256) RowNormLoopKernel(RowArgs a) {
           sg += g;
           sgx = fmaf(g, xh, sgx);
         }
-        const float mg = GroupSum<kThreads, kThreads>(sg, red) * inv_n;
-        const float mgx = GroupSum<kThreads, kThreads>(sgx, red) * inv_n;
+        const float mg = GroupSum<kThreads, kThreads>(sg, red, parity) * inv_n;
+        const float mgx = GroupSum<kThreads, kThreads>(sgx, red, parity) * inv_n;
         T* dx = static_cast<T*>(a.out) + row * n;
         for (int i = threadIdx.x; i < n; i += kThreads) {
           const float d = ToF32(dy[i]);
@@ -572,7 +587,7 @@ __global__ void __launch_bounds__(256) RowNormLoopKernel(RowArgs a) {
         const float v = ToF32(x[i]);
         s = fmaf(v, v, s);
       }
-      const float ms = GroupSum<kThreads, kThreads>(s, red) * inv_n;
+      const float ms = GroupSum<kThreads, kThreads>(s, red, parity) * inv_n;
       const float inv = 1.0f / sqrtf(ms + a.epsilon);
       if (threadIdx.x == 0) static_cast<T*>(a.stat_t)[row] = FromF32<T>(inv);
       T* y = static_cast<T*>(a.out) + row * n;
@@ -587,7 +602,7 @@ __global__ void __launch_bounds__(256) RowNormLoopKernel(RowArgs a) {
       for (int i = threadIdx.x; i < n; i += kThreads) {
         s = fmaf(ToF32(x[i]), ToF32(dy[i]) * ToF32(gamma[i]), s);
       }
-      const float dot = GroupSum<kThreads, kThreads>(s, red);
+      const float dot = GroupSum<kThreads, kThreads>(s, red, parity);
       const float inv = ToF32(static_cast<const T*>(a.inv_in)[row]);
       const float coeff = dot * inv * inv * inv * inv_n;
       T* dx = static_cast<T*>(a.out) + row * n;
@@ -644,16 +659,15 @@ constexpr int kMaxGradCtasPerSm = 4;  // bounds the partial rows of the gradient
 
 inline int MaxGradCtas() { return SmCount() * kMaxGradCtasPerSm; }
 
-// Dynamic shared memory of RowNormKernel: ring, widened gamma (and beta), and
-// the column-sum slabs of the LayerNorm gradient.
+// Dynamic shared memory of RowNormKernel: ring and widened gamma (and beta).
+// The column-sum slabs of the LayerNorm gradient lie over the ring: the slabs
+// of a CTA (2 * row_size floats per row lane) are never larger than two
+// stages of the two-input ring.
 template <int kOp>
-size_t RowSmemBytes(int threads, int rows_per_cta, int max_packs, int row_size) {
-  size_t bytes = static_cast<size_t>(RowPipe<kOp>::kStages) * RowPipe<kOp>::kInputs *
+size_t RowSmemBytes(int group, int threads, int rows_per_cta, int max_packs, int row_size) {
+  size_t bytes = static_cast<size_t>(RowStages(kOp, group)) * RowPipe<kOp>::kInputs *
                  max_packs * threads * 16;
   bytes += static_cast<size_t>(kOp == kOpLnFwd ? 2 : 1) * row_size * sizeof(float);
-  if (kOp == kOpLnGrad) {
-    bytes += static_cast<size_t>(rows_per_cta) * 2 * row_size * sizeof(float);
-  }
   return bytes;
 }
 
@@ -662,7 +676,7 @@ int LaunchGroupAs(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   constexpr int kThreads = RowThreads(kGroup, kOp);
   constexpr int kRows = kThreads / kGroup;
   auto kernel = RowNormKernel<T, kGroup, kMaxPacks, kOp, kFull>;
-  size_t smem = RowSmemBytes<kOp>(kThreads, kRows, kMaxPacks, a.row_size);
+  size_t smem = RowSmemBytes<kOp>(kGroup, kThreads, kRows, kMaxPacks, a.row_size);
   if (smem > 40 * 1024) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess) {
@@ -721,11 +735,14 @@ int DispatchPacks(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   const auto fits = [&](int group) {
     if (packs > group * kMaxPacks) return false;
     const int threads = RowThreads(group, kOp);
-    return RowSmemBytes<kOp>(threads, threads / group, kMaxPacks, a.row_size) <= 200 * 1024;
+    return RowSmemBytes<kOp>(group, threads, threads / group, kMaxPacks, a.row_size) <= 200 * 1024;
   };
   if (fits(8)) return LaunchGroup<T, 8, kMaxPacks, kOp>(a, ctas_out, stream);
   if (fits(32)) return LaunchGroup<T, 32, kMaxPacks, kOp>(a, ctas_out, stream);
-  if constexpr (kMaxPacks == 2) {
+  // Two-warp groups: measured better than a half-filled 128-thread group for
+  // 16-bit rows (bf16 rows of 2048: LayerNorm 5.6 against 3.8 TB/s), worse for
+  // fp32 rows of the same byte length.
+  if constexpr (kMaxPacks == 2 || sizeof(T) == 2) {
     if (fits(64)) return LaunchGroup<T, 64, kMaxPacks, kOp>(a, ctas_out, stream);
   }
   if (fits(128)) return LaunchGroup<T, 128, kMaxPacks, kOp>(a, ctas_out, stream);
@@ -739,14 +756,27 @@ int Dispatch(const RowArgs& a, bool aligned, int* ctas_out, cudaStream_t stream)
   constexpr int kVec = VecWidth<T>::value;
   if (aligned && a.row_size % kVec == 0) {
     // Packs per thread.  Four keep short rows inside one warp (shuffle-only
-    // sums) and measured best for every op and shape tried but one: the
-    // fp32 LayerNorm gradient, whose ring, column-sum slabs and two inputs fit
-    // three CTAs per SM with two packs per thread (rows spread over two warps
-    // that meet at a named barrier) and one CTA with four.  Tuning values 1,
-    // 2 (gradient only), 4 force a layout.
+    // sums) and measured best for every op and shape tried.  The LayerNorm
+    // gradient, whose column sums live in registers, takes two when the row
+    // fills at most half of the four-pack layout of its group: the same
+    // group then holds the row with half the registers and half the ring
+    // (bf16 rows of 2048: 4.1 against 2.4 TB/s, fp32 rows of 1024: 5.5
+    // against 4.3).  Tuning values 1, 2 (gradient only), 4 force a layout.
     int want = GetTuning(kTuneRowNormPacks);
     if (want != 1 && want != 2 && want != 4) {
-      want = (kOp == kOpLnGrad && sizeof(T) == 4) ? 2 : 4;
+      want = 4;
+      if (kOp == kOpLnGrad) {
+        const int packs = a.row_size / kVec;
+        int group = 512;
+        for (int g : {8, 32, 64, 128, 256}) {
+          if (g == 64 && sizeof(T) != 2) continue;  // as in DispatchPacks
+          if (packs <= 4 * g) {
+            group = g;
+            break;
+          }
+        }
+        if (packs <= 2 * group) want = 2;
+      }
     }
     int rc = -1;
     if (want == 1) rc = DispatchPacks<T, kOp, 1>(a, ctas_out, stream);
