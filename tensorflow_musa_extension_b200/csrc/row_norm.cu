@@ -132,11 +132,13 @@ __device__ __forceinline__ void AsyncWait() {
 }
 
 // Threads per CTA: one group when it is wider than 256, else 256 - except the
-// LayerNorm gradient of warp-sized groups: it keeps its column sums in
-// registers (about 190 a thread), and 128-thread CTAs then fill an SM in
-// finer steps.
+// LayerNorm gradient of groups up to 128 threads: it keeps its column sums in
+// registers, and 128-thread CTAs then fill an SM in finer steps.  Warp-sized
+// groups run two such CTAs per SM at about 190 registers (capping them at 160
+// for three CTAs measured 3-6 % slower), groups of 64 and 128 threads three
+// at 160 (bf16 rows of 4096: +9 %).
 __host__ __device__ constexpr int RowThreads(int group, int op) {
-  return group > 256 ? group : (op == 1 /* kOpLnGrad */ && group <= 32) ? 128 : 256;
+  return group > 256 ? group : (op == 1 /* kOpLnGrad */ && group <= 128) ? 128 : 256;
 }
 
 template <int kOp>
@@ -172,7 +174,8 @@ template <typename T, int kGroup, int kMaxPacks, int kOp, bool kFull>
 __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
                                   kGroup > 256 ? 1
                                   : (kOp == kOpLnFwd || kOp == kOpRmsFwd) ? 3
-                                  : kOp == kOpRmsGrad ? 2 : 1)
+                                  : kOp == kOpRmsGrad ? 2
+                                  : (kGroup >= 64 && kGroup <= 128) ? 3 : 1)
     RowNormKernel(RowArgs a) {
   constexpr int kThreads = RowThreads(kGroup, kOp);
   constexpr int kRows = kThreads / kGroup;
@@ -742,7 +745,7 @@ int DispatchPacks(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   // Two-warp groups: measured better than a half-filled 128-thread group for
   // 16-bit rows (bf16 rows of 2048: LayerNorm 5.6 against 3.8 TB/s), worse for
   // fp32 rows of the same byte length.
-  if constexpr (kMaxPacks == 2 || sizeof(T) == 2) {
+  if constexpr (kMaxPacks == 2 || kMaxPacks == 3 || sizeof(T) == 2) {
     if (fits(64)) return LaunchGroup<T, 64, kMaxPacks, kOp>(a, ctas_out, stream);
   }
   if (fits(128)) return LaunchGroup<T, 128, kMaxPacks, kOp>(a, ctas_out, stream);
@@ -756,26 +759,30 @@ int Dispatch(const RowArgs& a, bool aligned, int* ctas_out, cudaStream_t stream)
   constexpr int kVec = VecWidth<T>::value;
   if (aligned && a.row_size % kVec == 0) {
     // Packs per thread.  Four keep short rows inside one warp (shuffle-only
-    // sums) and measured best for every op and shape tried.  The LayerNorm
+    // sums) and measured best for rows that fill the layout.  Rows of 3 * 2^k
+    // packs (768, 1536, 3072 ... bf16 columns) take three: the layout is then
+    // full again, with three quarters of the registers and of the ring (bf16
+    // LayerNorm gradient of 768 columns: 5.6 against 4.5 TB/s).  The LayerNorm
     // gradient, whose column sums live in registers, takes two when the row
-    // fills at most half of the four-pack layout of its group: the same
-    // group then holds the row with half the registers and half the ring
-    // (bf16 rows of 2048: 4.1 against 2.4 TB/s, fp32 rows of 1024: 5.5
-    // against 4.3).  Tuning values 1, 2 (gradient only), 4 force a layout.
+    // fills at most half of the four-pack layout of its group (bf16 rows of
+    // 2048: 4.6 against 2.4 TB/s, fp32 rows of 1024: 5.6 against 4.3).
+    // Tuning values 1 .. 4 force a layout (2: gradient only).
     int want = GetTuning(kTuneRowNormPacks);
-    if (want != 1 && want != 2 && want != 4) {
+    if (want < 1 || want > 4) {
       want = 4;
-      if (kOp == kOpLnGrad) {
-        const int packs = a.row_size / kVec;
-        int group = 512;
-        for (int g : {8, 32, 64, 128, 256}) {
-          if (g == 64 && sizeof(T) != 2) continue;  // as in DispatchPacks
-          if (packs <= 4 * g) {
-            group = g;
-            break;
-          }
+      const int packs = a.row_size / kVec;
+      int group = 512;
+      for (int g : {8, 32, 64, 128, 256}) {
+        if (g == 64 && sizeof(T) != 2) continue;  // as in DispatchPacks
+        if (packs <= 4 * g) {
+          group = g;
+          break;
         }
-        if (packs <= 2 * group) want = 2;
+      }
+      if (packs <= 2 * group) {
+        if (kOp == kOpLnGrad) want = 2;
+      } else if (packs <= 3 * group) {
+        want = 3;
       }
     }
     int rc = -1;
@@ -783,6 +790,7 @@ int Dispatch(const RowArgs& a, bool aligned, int* ctas_out, cudaStream_t stream)
     if constexpr (kOp == kOpLnGrad) {
       if (want == 2) rc = DispatchPacks<T, kOp, 2>(a, ctas_out, stream);
     }
+    if (want == 3) rc = DispatchPacks<T, kOp, 3>(a, ctas_out, stream);
     if (rc == -1) rc = DispatchPacks<T, kOp, 4>(a, ctas_out, stream);
     if (rc != -1) return rc;
   }

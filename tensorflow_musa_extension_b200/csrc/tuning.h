@@ -18,7 +18,7 @@ enum TuningKey {
   kTuneBnApplyDeep = 9,     // 1: forward element-wise pass keeps 8 rows in flight
   kTuneBnPdl = 10,          // 1: BatchNorm kernels use programmatic dependent launch
   kTuneBnL2KeepMb = 11,     // stats pass pins its reads in L2 up to this many MB (0: off)
-  kTuneRowNormPacks = 12,   // packs per thread of the row kernels: 1 or 4; 0: per-op default
+  kTuneRowNormPacks = 12,   // packs per thread of the row kernels: 1 .. 4; 0: chosen per op and row
   kTuneCount = 16
 };
 

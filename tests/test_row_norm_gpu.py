@@ -13,11 +13,11 @@ pytestmark = pytest.mark.gpu
 
 SHAPES = ["s16x32", "s8x16x32", "s32x128", "s2x4x8x16", "s100x1", "s100x2", "s1x1", "s2x8192",
           "s7x1000"]
-# Row lengths that exercise every register layout (groups of 8, 32, 128, 256,
-# 512 threads), the element-wise form (odd lengths, very long rows) and the
-# ragged last group.
-ROW_SIZES = [1, 2, 3, 8, 31, 32, 64, 100, 128, 256, 384, 1000, 1024, 1536, 2048, 4096, 5000,
-             8192, 16384, 20000]
+# Row lengths that exercise every register layout (groups of 8, 32, 64, 128,
+# 256, 512 threads with two, three or four packs per thread), the element-wise
+# form (odd lengths, very long rows) and the ragged last group.
+ROW_SIZES = [1, 2, 3, 8, 31, 32, 64, 100, 128, 192, 256, 384, 768, 1000, 1024, 1536, 2048, 3072,
+             4096, 5000, 6144, 8192, 12288, 16384, 20000]
 
 
 def _tol(dtype):
@@ -235,8 +235,8 @@ def test_keras_layer_norm_route_through_fused_batch_norm(kernel_lib, dtype):
                  5e-5 if dtype == "bfloat16" else 1e-8, "layer norm grad op")
 
 
-@pytest.mark.parametrize("packs", [1, 2, 4])
-@pytest.mark.parametrize("n", [64, 256, 1024, 2048, 4096])
+@pytest.mark.parametrize("packs", [1, 2, 3, 4])
+@pytest.mark.parametrize("n", [64, 256, 768, 1024, 2048, 3072, 4096])
 def test_every_register_layout_gives_the_same_answers(kernel_lib, packs, n):
     """The packs-per-thread layouts (tuning key 12) differ in how a row is
     spread over threads and warps, not in what they compute."""
