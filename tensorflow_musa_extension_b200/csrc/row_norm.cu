@@ -147,15 +147,14 @@ struct RowPipe {
   static constexpr int kInputs = kGrad ? 2 : 1;
 };
 
-#ifndef MUSA_LN_GRAD_STAGES
-#define MUSA_LN_GRAD_STAGES 3
-#endif
-// Ring stages.  The two-input ring of a 512-thread group is 64 KB a stage.
+// Ring stages: three (two, three and four measured alike for the LayerNorm
+// gradient), two for the two-input ring of a 512-thread group, which is 64 KB
+// a stage.
 __host__ __device__ constexpr int RowStages(int op, int group) {
-  return op == 1 /* kOpLnGrad */ ? (group > 256 ? 2 : MUSA_LN_GRAD_STAGES) : 3;
+  return (op == 1 /* kOpLnGrad */ && group > 256) ? 2 : 3;
 }
 
-// One launch handles all rows; CTA = max(256, kGroup) threads = kRows rows at
+// One launch handles all rows; CTA = RowThreads() threads = kRows rows at
 // a time, grid-stride over blocks of kRows rows.  The rows travel through a
 // ring of shared-memory stages filled by per-thread asynchronous copies:
 // while a row block is being worked on, the copies of the CTA's next
