@@ -761,11 +761,12 @@ int Dispatch(const RowArgs& a, bool aligned, int* ctas_out, cudaStream_t stream)
     // sums) and measured best for rows that fill the layout.  Rows of 3 * 2^k
     // packs (768, 1536, 3072 ... bf16 columns) take three: the layout is then
     // full again, with three quarters of the registers and of the ring (bf16
-    // LayerNorm gradient of 768 columns: 5.6 against 4.5 TB/s).  The LayerNorm
-    // gradient, whose column sums live in registers, takes two when the row
-    // fills at most half of the four-pack layout of its group (bf16 rows of
-    // 2048: 4.6 against 2.4 TB/s, fp32 rows of 1024: 5.6 against 4.3).
-    // Tuning values 1 .. 4 force a layout (2: gradient only).
+    // LayerNorm gradient of 768 columns: 5.6 against 4.5 TB/s).  Rows that
+    // fill less than half of the four-pack layout of their group take two
+    // (fp32 rows of 768: LayerNorm 5.5 against 4.6 TB/s); the LayerNorm
+    // gradient, whose column sums live in registers, also at exactly half
+    // (fp32 rows of 1024: 5.6 against 5.1 - the other ops measured the same
+    // or slower there).  Tuning values 1 .. 4 force a layout.
     int want = GetTuning(kTuneRowNormPacks);
     if (want < 1 || want > 4) {
       want = 4;
@@ -778,17 +779,15 @@ int Dispatch(const RowArgs& a, bool aligned, int* ctas_out, cudaStream_t stream)
           break;
         }
       }
-      if (packs <= 2 * group) {
-        if (kOp == kOpLnGrad) want = 2;
-      } else if (packs <= 3 * group) {
+      if (packs < 2 * group || (packs == 2 * group && kOp == kOpLnGrad)) {
+        want = 2;
+      } else if (packs <= 3 * group && packs > 2 * group) {
         want = 3;
       }
     }
     int rc = -1;
     if (want == 1) rc = DispatchPacks<T, kOp, 1>(a, ctas_out, stream);
-    if constexpr (kOp == kOpLnGrad) {
-      if (want == 2) rc = DispatchPacks<T, kOp, 2>(a, ctas_out, stream);
-    }
+    if (want == 2) rc = DispatchPacks<T, kOp, 2>(a, ctas_out, stream);
     if (want == 3) rc = DispatchPacks<T, kOp, 3>(a, ctas_out, stream);
     if (rc == -1) rc = DispatchPacks<T, kOp, 4>(a, ctas_out, stream);
     if (rc != -1) return rc;
