@@ -136,7 +136,9 @@ __device__ __forceinline__ void AsyncWait() {
 // registers, and 128-thread CTAs then fill an SM in finer steps.  Warp-sized
 // groups run two such CTAs per SM at about 190 registers (capping them at 160
 // for three CTAs measured 3-6 % slower), groups of 64 and 128 threads three
-// at 160 (bf16 rows of 4096: +9 %).
+// at 160 (bf16 rows of 4096: +9 %), groups of 256 threads two 256-thread CTAs
+// at 128 where that needs no spills (bf16 rows of 5120: +19 %; with four
+// 16-bit packs a thread it spills and runs at 0.6 of the one-CTA form).
 __host__ __device__ constexpr int RowThreads(int group, int op) {
   return group > 256 ? group : (op == 1 /* kOpLnGrad */ && group <= 128) ? 128 : 256;
 }
@@ -169,12 +171,20 @@ __host__ __device__ constexpr int RowStages(int op, int group) {
 // rows are done the sums go to shared memory (over the ring, which is free by
 // then), the row lanes of the CTA are added in lane order and the CTA writes
 // one partial row.
+// CTAs per SM that the register allocation aims at (see RowThreads for the
+// LayerNorm gradient).
+constexpr int RowMinCtas(int group, int op, int max_packs, int elem_bytes) {
+  if (group > 256) return 1;
+  if (op == kOpLnFwd || op == kOpRmsFwd) return 3;
+  if (op == kOpRmsGrad) return 2;
+  if (group >= 64 && group <= 128) return 3;
+  if (group == 256 && (max_packs <= 3 || elem_bytes == 4)) return 2;
+  return 1;
+}
+
 template <typename T, int kGroup, int kMaxPacks, int kOp, bool kFull>
 __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
-                                  kGroup > 256 ? 1
-                                  : (kOp == kOpLnFwd || kOp == kOpRmsFwd) ? 3
-                                  : kOp == kOpRmsGrad ? 2
-                                  : (kGroup >= 64 && kGroup <= 128) ? 3 : 1)
+                                  RowMinCtas(kGroup, kOp, kMaxPacks, sizeof(T)))
     RowNormKernel(RowArgs a) {
   constexpr int kThreads = RowThreads(kGroup, kOp);
   constexpr int kRows = kThreads / kGroup;
