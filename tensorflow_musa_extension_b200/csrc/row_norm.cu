@@ -149,11 +149,16 @@ struct RowPipe {
   static constexpr int kInputs = kGrad ? 2 : 1;
 };
 
-// Ring stages: three (two, three and four measured alike for the LayerNorm
-// gradient), two for the two-input ring of a 512-thread group, which is 64 KB
-// a stage.
-__host__ __device__ constexpr int RowStages(int op, int group) {
-  return (op == 1 /* kOpLnGrad */ && group > 256) ? 2 : 3;
+// Ring stages: three, with two exceptions of two.  The two-input ring of a
+// 512-thread LayerNorm-gradient group is 64 KB a stage.  And 16-bit rows of a
+// 256-thread group outside the LayerNorm gradient (for which two, three and
+// four stages measured alike): their fp32 copies of gamma / beta take 20-64 KB,
+// and the shorter ring fits a third CTA per SM (bf16 rows of 5120: LayerNorm
+// +12 %, rows of 8192: RMSNorm gradient +32 %; fp32 rows of 4096 measured 7 %
+// slower that way and keep three).
+__host__ __device__ constexpr int RowStages(int op, int group, int elem_bytes) {
+  if (op == 1 /* kOpLnGrad */) return group > 256 ? 2 : 3;
+  return (group >= 256 && elem_bytes == 2) ? 2 : 3;
 }
 
 // One launch handles all rows; CTA = RowThreads() threads = kRows rows at
@@ -191,7 +196,7 @@ __global__ void __launch_bounds__(RowThreads(kGroup, kOp),
   constexpr int kVec = VecWidth<T>::value;
   constexpr bool kGrad = RowPipe<kOp>::kGrad;
   constexpr int kInputs = RowPipe<kOp>::kInputs;
-  constexpr int kStages = RowStages(kOp, kGroup);
+  constexpr int kStages = RowStages(kOp, kGroup, sizeof(T));
   constexpr int kPairs = kVec / 2;
   constexpr int kQuads = kVec / 4;
   using P = Pack<T, kVec>;
@@ -676,8 +681,8 @@ inline int MaxGradCtas() { return SmCount() * kMaxGradCtasPerSm; }
 // of a CTA (2 * row_size floats per row lane) are never larger than two
 // stages of the two-input ring.
 template <int kOp>
-size_t RowSmemBytes(int group, int threads, int rows_per_cta, int max_packs, int row_size) {
-  size_t bytes = static_cast<size_t>(RowStages(kOp, group)) * RowPipe<kOp>::kInputs *
+size_t RowSmemBytes(int group, int elem_bytes, int threads, int max_packs, int row_size) {
+  size_t bytes = static_cast<size_t>(RowStages(kOp, group, elem_bytes)) * RowPipe<kOp>::kInputs *
                  max_packs * threads * 16;
   bytes += static_cast<size_t>(kOp == kOpLnFwd ? 2 : 1) * row_size * sizeof(float);
   return bytes;
@@ -688,7 +693,7 @@ int LaunchGroupAs(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   constexpr int kThreads = RowThreads(kGroup, kOp);
   constexpr int kRows = kThreads / kGroup;
   auto kernel = RowNormKernel<T, kGroup, kMaxPacks, kOp, kFull>;
-  size_t smem = RowSmemBytes<kOp>(kGroup, kThreads, kRows, kMaxPacks, a.row_size);
+  size_t smem = RowSmemBytes<kOp>(kGroup, sizeof(T), kThreads, kMaxPacks, a.row_size);
   if (smem > 40 * 1024) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess) {
@@ -747,7 +752,7 @@ int DispatchPacks(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   const auto fits = [&](int group) {
     if (packs > group * kMaxPacks) return false;
     const int threads = RowThreads(group, kOp);
-    return RowSmemBytes<kOp>(group, threads, threads / group, kMaxPacks, a.row_size) <= 200 * 1024;
+    return RowSmemBytes<kOp>(group, sizeof(T), threads, kMaxPacks, a.row_size) <= 200 * 1024;
   };
   if (fits(8)) return LaunchGroup<T, 8, kMaxPacks, kOp>(a, ctas_out, stream);
   if (fits(32)) return LaunchGroup<T, 32, kMaxPacks, kOp>(a, ctas_out, stream);
