@@ -105,6 +105,27 @@ def test_adam_bf16_state(kernel_lib):
             assert_close(to_numpy(part), ref, RTOL["lowp"], 1e-6, name)
 
 
+def test_adam_fp32(kernel_lib):
+    n = LIMIT + 8205
+    torch.manual_seed(12)
+    var = torch.randn(n, device="cuda").mul_(0.05)
+    m = torch.randn(n, device="cuda").mul_(1e-4)
+    v = torch.rand(n, device="cuda").mul_(1e-6)
+    g = torch.randn(n, device="cuda").mul_(1e-3)
+    windows = [(0, 4096), (LIMIT - 2048, LIMIT + 2048), (n - 4099, n)]
+    before = [tuple(t[lo:hi].clone() for t in (var, m, v)) for lo, hi in windows]
+    args = (0.9 ** 10, 0.999 ** 10, 1e-3, 0.9, 0.999, 1e-7)
+    raw_ops.ResourceApplyAdam(var, m, v, *args, g)
+    for (lo, hi), (v0, m0, s0) in zip(windows, before):
+        want = np_ref.apply_adam(to_numpy(v0), to_numpy(m0), to_numpy(s0), *args,
+                                 to_numpy(g[lo:hi]))
+        raw_ops.ResourceApplyAdam(v0, m0, s0, *args, g[lo:hi].clone())
+        for name, whole, part, ref, atol in zip(("var", "m", "v"), (var, m, v), (v0, m0, s0),
+                                                want, (1e-8, 1e-10, 1e-14)):
+            assert torch.equal(part, whole[lo:hi]), "%s %d:%d" % (name, lo, hi)
+            assert_close(to_numpy(part), ref, RTOL["f32_adam"], atol, name)
+
+
 def _bn_rows(x, mean, var, scale, offset, lo, hi):
     xs = x[lo:hi].double()
     inv = torch.rsqrt(var.double() + EPS)
