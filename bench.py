@@ -598,6 +598,21 @@ def time_launch(torch, fn, iters, flush=None):
     return float(np.median(times))
 
 
+def time_stream(torch, fn, iters):
+    """Average device time of fn() in ms over `iters` back-to-back launches
+    (one pair of CUDA events around the run)."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b) / iters
+
+
 def measure_ops(torch, lib, raw_ops, dev, args):
     """Per-op device timings at N = 1 for every configuration of the path, each
     with its algorithmic bytes, and the roofline entry of the dominant kernel
@@ -619,11 +634,25 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     iters = 20
     ops = {}
 
+    def both(fn):
+        """(median time of a launch timed on its own, average time of a launch
+        in a run of back-to-back launches) for inputs larger than L2."""
+        return time_launch(torch, fn, iters), time_stream(torch, fn, iters)
+
     def entry(name, ms, algo_bytes, elems, note):
+        ms_stream = None
+        if isinstance(ms, tuple):
+            ms, ms_stream = ms
         gbs = algo_bytes / (ms * 1e-3) / 1e9
         ops[name] = {"ms": round(ms, 4), "algorithmic_bytes": algo_bytes,
                      "achieved_gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
                      "gelem_per_s": round(elems / (ms * 1e-3) / 1e9, 2), "note": note}
+        if ms_stream is not None:
+            # The same launch as one of a run of back-to-back launches (how it
+            # runs inside a training step): no ramp-up / drain per launch.
+            ops[name]["ms_back_to_back"] = round(ms_stream, 4)
+            ops[name]["frac_back_to_back"] = round(
+                algo_bytes / (ms_stream * 1e-3) / 1e9 / peak, 4)
 
     # Adam, config 4: fp32 N = 25,557,032 (715.6 MB per step: beyond L2).
     n = 25_557_032
@@ -632,25 +661,25 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     v = torch.rand(n, device=dev) * 1e-6
     g = torch.randn(n, device=dev) * 1e-3
     alpha = 1e-3 * np.sqrt(1 - 0.999 ** 10) / (1 - 0.9 ** 10)
-    ms = time_launch(torch, lambda: lib.LaunchResourceApplyAdamFloat(
+    ms = both(lambda: lib.LaunchResourceApplyAdamFloat(
         var.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), 0.9, 0.999, 1e-7,
-        alpha, n, st), iters)
+        alpha, n, st))
     entry("adam_f32_25.6M", ms, 28 * n, n, "inputs exceed L2")
     # The other streaming optimizers at the same size (same kernel template).
-    ms = time_launch(torch, lambda: lib.LaunchResourceApplyNadam_Float(
+    ms = both(lambda: lib.LaunchResourceApplyNadam_Float(
         var.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), 0.9 ** 10, 0.999 ** 10,
-        1e-3, 0.9, 0.999, 1e-7, n, st), iters)
+        1e-3, 0.9, 0.999, 1e-7, n, st))
     entry("nadam_f32_25.6M", ms, 28 * n, n, "inputs exceed L2")
-    ms = time_launch(torch, lambda: lib.LaunchFusedResourceApplyRMSProp_Float(
+    ms = both(lambda: lib.LaunchFusedResourceApplyRMSProp_Float(
         var.data_ptr(), v.data_ptr(), m.data_ptr(), g.data_ptr(), 1e-3, 0.9, 0.9, 1e-7,
-        n, st), iters)
+        n, st))
     entry("rmsprop_f32_25.6M", ms, 28 * n, n, "inputs exceed L2")
-    ms = time_launch(torch, lambda: lib.LaunchResourceApplyGradientDescentFloat(
-        var.data_ptr(), g.data_ptr(), 1e-3, n, st), iters)
+    ms = both(lambda: lib.LaunchResourceApplyGradientDescentFloat(
+        var.data_ptr(), g.data_ptr(), 1e-3, n, st))
     entry("sgd_f32_25.6M", ms, 12 * n, n, "inputs exceed L2")
     gb = g.to(torch.bfloat16)
-    ms = time_launch(torch, lambda: lib.LaunchResourceApplyGradientDescentFloatBFloat16(
-        var.data_ptr(), gb.data_ptr(), 1e-3, n, st), iters)
+    ms = both(lambda: lib.LaunchResourceApplyGradientDescentFloatBFloat16(
+        var.data_ptr(), gb.data_ptr(), 1e-3, n, st))
     entry("sgd_f32_bf16grad_25.6M", ms, 10 * n, n, "inputs exceed L2")
     del var, m, v, g, gb
 
@@ -659,8 +688,8 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     b = (torch.randn(1024, device=dev) * 0.1).half()
     y = torch.empty_like(x)
     for name, act in (("bias_relu_f16", 1), ("bias_swish_f16", 2)):
-        ms = time_launch(torch, lambda: lib.LaunchBiasAct_F16(
-            x.data_ptr(), b.data_ptr(), y.data_ptr(), 65536, 1024, 1, act, st), iters)
+        ms = both(lambda: lib.LaunchBiasAct_F16(
+            x.data_ptr(), b.data_ptr(), y.data_ptr(), 65536, 1024, 1, act, st))
         entry(name, ms, 4 * x.numel(), x.numel(), "inputs exceed L2")
     # Backward of the chain at the same shape: gradients and features in,
     # backprops out (6 B/elem); the un-fused pair reads backprops once more.
@@ -668,12 +697,12 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     need = lib.BiasGradWorkspaceBytes(65536, 1024, 1, 2)
     ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
     gr = torch.randn_like(x)
-    ms = time_launch(torch, lambda: lib.LaunchBiasAddReluGrad_F16(
+    ms = both(lambda: lib.LaunchBiasAddReluGrad_F16(
         gr.data_ptr(), x.data_ptr(), y.data_ptr(), db.data_ptr(), 65536, 1024, 1,
-        ws.data_ptr(), need, st), iters)
+        ws.data_ptr(), need, st))
     entry("bias_relu_grad_fused_f16", ms, 6 * x.numel(), x.numel(), "inputs exceed L2")
-    ms = time_launch(torch, lambda: lib.LaunchReluGrad_F16(
-        gr.data_ptr(), x.data_ptr(), y.data_ptr(), x.numel(), st), iters)
+    ms = both(lambda: lib.LaunchReluGrad_F16(
+        gr.data_ptr(), x.data_ptr(), y.data_ptr(), x.numel(), st))
     entry("relu_grad_f16", ms, 6 * x.numel(), x.numel(), "inputs exceed L2")
     ms = time_launch(torch, lambda: lib.LaunchBiasAddGrad_F16(
         y.data_ptr(), db.data_ptr(), 65536, 1024, 1, ws.data_ptr(), need, st), iters, flush)
@@ -693,21 +722,20 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     need = lib.LayerNormGradWorkspaceBytes(rows, n)
     ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
     s_bytes = x.numel() * 2
-    ms = time_launch(torch, lambda: lib.LaunchLayerNorm_BF16(
+    ms = both(lambda: lib.LaunchLayerNorm_BF16(
         x.data_ptr(), gam.data_ptr(), bet.data_ptr(), y.data_ptr(), None, None, rows, n, 1e-5,
-        st), iters)
+        st))
     entry("layer_norm_bf16", ms, 2 * s_bytes, x.numel(), "inputs exceed L2")
-    ms = time_launch(torch, lambda: lib.LaunchLayerNormGrad_BF16(
+    ms = both(lambda: lib.LaunchLayerNormGrad_BF16(
         dy.data_ptr(), x.data_ptr(), gam.data_ptr(), y.data_ptr(), dgam.data_ptr(),
-        dbet.data_ptr(), rows, n, 1e-5, ws.data_ptr(), need, st), iters)
+        dbet.data_ptr(), rows, n, 1e-5, ws.data_ptr(), need, st))
     entry("layer_norm_grad_bf16", ms, 3 * s_bytes, x.numel(), "inputs exceed L2")
-    ms = time_launch(torch, lambda: lib.LaunchRmsNormBFloat16(
+    ms = both(lambda: lib.LaunchRmsNormBFloat16(
         x.data_ptr(), gam.data_ptr(), y.data_ptr(), y2.data_ptr(), inv.data_ptr(), rows, n,
-        1e-5, st), iters)
+        1e-5, st))
     entry("rms_norm_bf16", ms, 3 * s_bytes, x.numel(), "inputs exceed L2")
-    ms = time_launch(torch, lambda: lib.LaunchRmsNormGradDxBFloat16(
-        x.data_ptr(), inv.data_ptr(), gam.data_ptr(), dy.data_ptr(), y.data_ptr(), rows, n, st),
-        iters)
+    ms = both(lambda: lib.LaunchRmsNormGradDxBFloat16(
+        x.data_ptr(), inv.data_ptr(), gam.data_ptr(), dy.data_ptr(), y.data_ptr(), rows, n, st))
     entry("rms_norm_grad_dx_bf16", ms, 3 * s_bytes, x.numel(), "inputs exceed L2")
     del x, dy, y, y2
 
@@ -756,15 +784,17 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     sums = torch.zeros(2 * c, device=dev)
     ds, do = torch.empty(c, device=dev), torch.empty(c, device=dev)
     s_bytes = x.numel() * 2
-    ms = time_launch(torch, lambda: lib.LaunchBnGradApplyFromSums(
+    ms, ms_stream = both(lambda: lib.LaunchBnGradApplyFromSums(
         2, dy.data_ptr(), x.data_ptr(), sc.data_ptr(), mean.data_ptr(), varc.data_ptr(),
-        sums.data_ptr(), float(rows), dx.data_ptr(), None, None, rows, c, 1, EPS, st), iters)
+        sums.data_ptr(), float(rows), dx.data_ptr(), None, None, rows, c, 1, EPS, st))
     achieved = 3 * s_bytes / (ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "kernel": "BnApplyLastKernel<bf16, grad>",
             "case": "[256,56,56,256] bf16, 3*S = %d bytes per launch" % (3 * s_bytes),
             "achieved": round(achieved, 1), "peak": peak, "peak_kind": peak_kind,
             "unit": "GB/s", "frac": round(achieved / peak, 4), "ms": round(ms, 4),
             "traffic": None}
+    roof["ms_back_to_back"] = round(ms_stream, 4)
+    roof["frac_back_to_back"] = round(3 * s_bytes / (ms_stream * 1e-3) / 1e9 / peak, 4)
     roof["traffic"] = NCU_TRAFFIC_BYTES["bn_grad_apply_bf16_256x56x56x256"]
     roof["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
                               "kernel and case (profiles/bn_grad_apply_bf16_256x56x56x256_ncu_full.md)")
