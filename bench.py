@@ -706,7 +706,18 @@ def measure_ops(torch, lib, raw_ops, dev, args):
     entry("relu_grad_f16", ms, 6 * x.numel(), x.numel(), "inputs exceed L2")
     ms = time_launch(torch, lambda: lib.LaunchBiasAddGrad_F16(
         y.data_ptr(), db.data_ptr(), 65536, 1024, 1, ws.data_ptr(), need, st), iters, flush)
-    entry("bias_add_grad_f16", ms, 2 * x.numel(), x.numel(), "L2 flushed before each launch")
+    # One input (134 MB) is about the size of L2: the back-to-back run
+    # alternates between two inputs.
+    turn = [0]
+
+    def alternate():
+        src = (y, gr)[turn[0] & 1]
+        turn[0] += 1
+        lib.LaunchBiasAddGrad_F16(src.data_ptr(), db.data_ptr(), 65536, 1024, 1,
+                                  ws.data_ptr(), need, st)
+
+    entry("bias_add_grad_f16", (ms, time_stream(torch, alternate, iters)), 2 * x.numel(),
+          x.numel(), "L2 flushed before each launch; back-to-back over two alternating inputs")
     del x, y, gr
 
     # Row normalisations at the chain's shape, bf16 [65536, 1024] (S = 134 MB).
