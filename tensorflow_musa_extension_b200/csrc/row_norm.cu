@@ -139,6 +139,8 @@ __device__ __forceinline__ void AsyncWait() {
 // at 160 (bf16 rows of 4096: +9 %), groups of 256 threads two 256-thread CTAs
 // at 128 where that needs no spills (bf16 rows of 5120: +19 %; with four
 // 16-bit packs a thread it spills and runs at 0.6 of the one-CTA form).
+// 64-thread CTAs for warp-sized groups (five per SM) measured slower (bf16
+// rows of 768: 4.7 against 5.6 TB/s).
 __host__ __device__ constexpr int RowThreads(int group, int op) {
   return group > 256 ? group : (op == 1 /* kOpLnGrad */ && group <= 128) ? 128 : 256;
 }
