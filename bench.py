@@ -47,6 +47,9 @@ EPS = 1e-3
 # DRAM bytes per launch from an ncu capture (the summary under profiles/ names
 # the command): 822.2 MB read + 376.4 MB written for 1233.1 MB algorithmic.
 NCU_TRAFFIC_BYTES = {"bn_grad_apply_bf16_256x56x56x256": 1198591488}
+# One-directional rate of a cudaMemcpyAsync between two B200 of one NVSwitch
+# node, as measured by `bench.py --probe peer_copy` (nominal 900 GB/s).
+PEER_COPY_GBS = 770.0
 WORKLOAD = "resnet50_bn_train_bf16_b256"
 METRIC = "bn_fwd_grad_throughput"
 UNIT = "Gelem/s"
@@ -57,6 +60,20 @@ def layer_list():
     for count, h, w, c in RESNET50_BN:
         out += [(h, w, c)] * count
     return out
+
+
+def workload_config():
+    """The description of the workload that both arms print, key for key."""
+    layers = layer_list()
+    elems = 2 * sum(BATCH * h * w * c for (h, w, c) in layers)       # forward + gradient
+    sum_s = sum(BATCH * h * w * c * 2 for (h, w, c) in layers)      # bytes of all x
+    return {"workload": WORKLOAD, "layers": len(layers), "batch_per_gpu": BATCH,
+            "layout": "NHWC", "stats_dtype": "f32",
+            "elements_per_step_per_gpu": elems,
+            "algorithmic_bytes_per_step_per_gpu": 5 * sum_s,   # 2*S forward + 3*S gradient
+            "l2": "inputs exceed the last-level cache between reuses (GPU arm: one x and "
+                  "dy per layer, 10.8 GB per GPU; CPU arm: one x and dy per distinct "
+                  "shape, 2.7 GB)"}
 
 
 def measured_peak():
@@ -72,16 +89,52 @@ def measured_peak():
 # ------------------------------------------------------------ clock sampler --
 
 class ClockSampler:
+    """SM clock and throttle reasons while the timed region runs: a thread that
+    reads NVML every few milliseconds (read-only queries), so that even a timed
+    region of a fraction of a second is covered; `nvidia-smi -lms` is the
+    fall-back when the NVML binding is missing."""
     FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # NVML clocks-event-reason bits (nvml.h).
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"),
+               (0x20, "sw_thermal_slowdown"), (0x4, "sw_power_cap"))
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
         self.proc = None
         self.path = None
+        self.thread = None
+        self.samples = []      # (time, sm_mhz, reason_bits)
+        self.max_mhz = None
+        self._stop = False
+
+    def _nvml_loop(self, nv, handle):
+        while not self._stop:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                try:
+                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                except Exception:
+                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append((time.time(), float(mhz), int(bits)))
+            except Exception:
+                pass
+            time.sleep(0.004)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            handle = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle),
+                                           daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -97,6 +150,23 @@ class ClockSampler:
         (epoch seconds; all samples when not given)."""
         import datetime
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+            picked = [x for x in self.samples
+                      if t_begin is None or t_begin - 0.005 <= x[0] <= t_end + 0.005]
+            if not picked:          # a window shorter than one sampling period
+                picked = self.samples[-3:]
+            if picked:
+                out["sm_mhz"] = float(np.median([x[1] for x in picked]))
+                out["sm_max_mhz"] = self.max_mhz
+                out["samples"] = len(picked)
+                bits = 0
+                for x in picked:
+                    bits |= x[2]
+                out["reasons"] = sorted(name for bit, name in self.REASONS if bits & bit)
+            out["source"] = "nvml"
+            return out
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -132,6 +202,7 @@ class ClockSampler:
             out["sm_max_mhz"] = float(max(mx))
             out["samples"] = len(sm)
         out["reasons"] = sorted(reasons)
+        out["source"] = "nvidia-smi"
         return out
 
 
@@ -269,6 +340,19 @@ def run_ours(args):
         finish(torch, dist, world)
         return
 
+    parity = None
+    if world > 1:
+        parity = check_multi_gpu_parity(torch, dist, world, rank, dev, exchange,
+                                        dist.group.WORLD)
+        if rank == 0 and not (parity[0] and parity[1] in (True, None)):
+            print(json.dumps({"error": "multi-GPU parity check failed", "sync_parity": parity[0],
+                              "adam_shard_parity": parity[1], "detail": parity[2]}), flush=True)
+        if not (parity[0] and parity[1] in (True, None)):
+            torch.cuda.synchronize()
+            dist.barrier()
+            sys.stdout.flush()
+            os._exit(4)
+
     # Warm up eagerly, then capture the step in a CUDA graph (the launchers
     # neither allocate nor synchronise, so a step is a pure launch sequence).
     for _ in range(2):
@@ -346,14 +430,9 @@ def run_ours(args):
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers": n_layers, "batch_per_gpu": BATCH,
-                       "layout": "NHWC", "stats_dtype": "f32",
-                       "elements_per_step_per_gpu": elems_per_step,
-                       "algorithmic_bytes_per_step_per_gpu": algo_bytes_step,
-                       "sync": sync_kind,
-                       "l2": "every layer has its own x and dy (10.8 GB per GPU), "
-                             "so inputs exceed L2 between reuses",
-                       "launch": "cuda graph replay" if graph is not None else "eager"},
+            "config": workload_config(),
+            "run": {"sync": sync_kind,
+                    "launch": "cuda graph replay" if graph is not None else "eager"},
             "step_algorithmic_gbs_per_gpu": round(algo_bytes_step / (ms_per_step * 1e-3) / 1e9, 1),
             "step_frac_of_peak": round(algo_bytes_step / (ms_per_step * 1e-3) / 1e9 / peak, 4),
             "gpu_launches": launches_per_step * args.steps,
@@ -366,6 +445,12 @@ def run_ours(args):
         torch.cuda.empty_cache()
         ops, roof = (None, None) if args.skip_ops else \
             measure_ops(torch, lib, raw_ops, dev, args)
+        if roof is not None:
+            # The whole step beside the kernel: fraction of peak by algorithmic
+            # bytes, and the DRAM bytes a step really moves (ncu, per step).
+            roof["step_frac"] = result["step_frac_of_peak"]
+            roof["traffic_step"] = NCU_TRAFFIC_BYTES.get("resnet50_bn_step")
+            roof["algorithmic_bytes_step"] = algo_bytes_step
         result["roofline"] = roof
         result["ops"] = ops
         result["cpu_baseline"] = None if args.skip_cpu else \
@@ -377,6 +462,9 @@ def run_ours(args):
             result["roofline"] = None
             result["cpu_baseline"] = None
             result["adam_sharded"] = adam
+            result["sync_parity"] = parity[0]
+            result["adam_shard_parity"] = parity[1]
+            result["parity_detail"] = parity[2]
     if rank == 0:
         print(json.dumps(result), flush=True)
     finish(torch, dist, world)
@@ -492,6 +580,113 @@ def measure_e2e(torch, dist, raw_ops, layers, world, rank, dev, args):
     return out
 
 
+def _gather_rows(torch, dist, t, world):
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t.contiguous())
+    return torch.cat(parts, 0)
+
+
+def check_multi_gpu_parity(torch, dist, world, rank, dev, exchange, group):
+    """Before anything is timed at N > 1: one small cross-replica BatchNorm
+    layer (forward + gradient, bf16 and fp32) and three steps of the
+    range-sharded Adam, each compared with the CPU oracle on the WHOLE problem
+    (the concatenated batch; the unsharded vector) at the tolerances of the
+    single-GPU parity tests.  The oracle is the checker here, never the thing
+    measured.  Returns (sync_ok, adam_ok, details); every rank gets the same
+    verdict."""
+    from oracle import np_ref
+    from tensorflow_musa_extension_b200 import cross_replica as cr
+    import ml_dtypes
+    details = {}
+    rows, c = 4096, 256
+
+    def host_block(r, np_dt):
+        rng = np.random.default_rng(9000 + r)
+        x = (rng.standard_normal((rows, c), dtype=np.float32) * 2.0 + 0.5).astype(np_dt)
+        dy = (rng.standard_normal((rows, c), dtype=np.float32) * 1e-2).astype(np_dt)
+        return x, dy
+
+    def to_dev(a):
+        if a.dtype == ml_dtypes.bfloat16:
+            return torch.from_numpy(a.view(np.int16)).view(torch.bfloat16).to(dev)
+        return torch.from_numpy(a).to(dev)
+
+    def rms(a):
+        a = np.asarray(a, np.float64)
+        return float(np.sqrt(np.mean(a * a))) or 1.0
+
+    def worst(got, want, rtol):
+        """Largest |got - want| / (rtol * (|want| + rms(want))): <= 1 passes."""
+        g = got.detach().float().cpu().numpy().astype(np.float64)
+        w = np.asarray(want).astype(np.float64)
+        return float(np.max(np.abs(g - w) / (rtol * (np.abs(w) + rms(w)))))
+
+    sync_ok = True
+    prng = np.random.default_rng(77)
+    scale = prng.uniform(0.5, 1.5, c).astype(np.float32)
+    offset = prng.normal(0, 0.1, c).astype(np.float32)
+    for name, t_dt, np_dt, rtol in (("bf16", torch.bfloat16, ml_dtypes.bfloat16, 2e-2),
+                                    ("f32", torch.float32, np.float32, 1e-4)):
+        x, dy = host_block(rank, np_dt)
+        bn = cr.SyncBatchNorm(c, eps=EPS, dtype=t_dt, device=dev, max_rows=rows, group=group,
+                              exchange=exchange)
+        tx, tdy = to_dev(x), to_dev(dy)
+        y, dx = torch.empty_like(tx), torch.empty_like(tx)
+        ts, to = torch.from_numpy(scale).to(dev), torch.from_numpy(offset).to(dev)
+        bn.forward(tx, ts, to, y)
+        bn.backward(tdy, tx, ts, dx)
+        torch.cuda.synchronize()
+        all_y = _gather_rows(torch, dist, y, world)
+        all_dx = _gather_rows(torch, dist, dx, world)
+        blocks = [host_block(r, np_dt) for r in range(world)]
+        gx = np.concatenate([b[0] for b in blocks], 0)
+        gdy = np.concatenate([b[1] for b in blocks], 0)
+        want = np_ref.fused_batch_norm(gx, scale, offset, epsilon=EPS)
+        wg = np_ref.fused_batch_norm_grad(gdy, gx, scale, want[3], want[4], EPS)
+        errs = {"y": worst(all_y, want[0], rtol),
+                "batch_mean": worst(bn.batch_mean, want[1], 1e-4),
+                "batch_var": worst(bn.batch_var, want[2], 1e-4),
+                "saved_mean": worst(bn.saved_mean, want[3], 1e-4),
+                "saved_var": worst(bn.saved_var, want[4], 1e-4),
+                "dx": worst(all_dx, wg[0], rtol),
+                "dscale": worst(bn.dscale, wg[1], 1e-4),
+                "doffset": worst(bn.doffset, wg[2], 1e-4)}
+        details["syncbn_" + name] = {k: round(v, 4) for k, v in errs.items()}
+        sync_ok = sync_ok and all(v <= 1.0 for v in errs.values())
+        del bn
+
+    adam_ok = None
+    if exchange is not None:
+        n = 1_000_003
+        arng = np.random.default_rng(31)
+        var0 = arng.normal(0, 0.05, n).astype(np.float32)
+        pv = cr.PeerVector(group, n, dev)
+        pv.tensor.copy_(torch.from_numpy(var0).to(dev))
+        torch.cuda.synchronize()
+        dist.barrier()
+        opt = cr.FusedShardedAdam(pv, exchange)
+        ev, em, evv = var0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+        for step in range(1, 4):
+            g = arng.normal(0, 1e-3, n).astype(np.float32)
+            ev, em, evv = np_ref.apply_adam(ev, em, evv, 0.9 ** step, 0.999 ** step, 1e-3,
+                                            0.9, 0.999, 1e-7, g)
+            opt.step(torch.from_numpy(g).to(dev), 1e-3, 0.9 ** step, 0.999 ** step)
+        torch.cuda.synchronize()
+        got = pv.tensor.cpu().numpy().astype(np.float64)
+        err = float(np.max(np.abs(got - ev) / (1e-8 + 1e-5 * np.abs(ev))))
+        details["adam_shard_worst_over_tolerance"] = round(err, 4)
+        adam_ok = err <= 1.0
+        dist.barrier()
+        pv.close()
+    flags = torch.tensor([1.0 if sync_ok else 0.0, 1.0 if adam_ok in (True, None) else 0.0],
+                         device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    sync_ok = bool(flags[0].item() > 0.5)
+    if adam_ok is not None:
+        adam_ok = bool(flags[1].item() > 0.5)
+    return sync_ok, adam_ok, details
+
+
 def measure_adam_sharded(torch, dist, world, rank, dev, exchange, args):
     """ResourceApplyAdam over the 25,557,032-parameter vector, sharded by
     contiguous range over the replicas, two ways: update + NCCL all-gather of
@@ -500,7 +695,9 @@ def measure_adam_sharded(torch, dist, world, rank, dev, exchange, args):
     from tensorflow_musa_extension_b200 import cross_replica as cr
     n = 25_557_032
     peak, _ = measured_peak()
-    nvlink_gbs = 770.0   # measured peer-copy bandwidth per direction on this pool
+    # Peer-copy rate per direction and GPU (profiles/peer_copy_bandwidth.md has the
+    # command that measures it: `bench.py --probe peer_copy`).
+    nvlink_gbs = PEER_COPY_GBS
     hyper = dict(lr=1e-3, b1p=0.9 ** 10, b2p=0.999 ** 10)
     gen = torch.Generator(device=dev)
     gen.manual_seed(3)
@@ -544,35 +741,62 @@ def measure_adam_sharded(torch, dist, world, rank, dev, exchange, args):
     timed(step_nccl, "update_then_nccl_all_gather")
     del opt, var
 
-    # (b) fused update + broadcast over peer memory
+    # (b) fused forms over peer memory: the update kernel stores into every
+    # replica ("stores"), or copy engines carry finished chunks to the peers
+    # while the next chunk updates ("copies").  Each is replayed from a CUDA
+    # graph (the step is a fixed launch sequence), eager when capture fails.
     if exchange is not None:
-        try:
-            pv = cr.PeerVector(dist.group.WORLD, n, dev)
-            pv.tensor.normal_(0, 0.05, generator=gen)
-            fopt = cr.FusedShardedAdam(pv, exchange)
-            fshard = fopt.hi - fopt.lo
-            fgrads = [torch.empty(max(fshard, 1), device=dev).normal_(0, 1e-3, generator=gen)
-                      for _ in range(4)]
+        for label, transport, chunks in (
+                ("fused_update_and_peer_broadcast", "stores", 1),
+                ("update_and_copy_engine_broadcast_2_chunks", "copies", 2),
+                ("update_and_copy_engine_broadcast_4_chunks", "copies", 4)):
+            pv = fopt = None
+            try:
+                pv = cr.PeerVector(dist.group.WORLD, n, dev)
+                pv.tensor.normal_(0, 0.05, generator=gen)
+                fopt = cr.FusedShardedAdam(pv, exchange, transport=transport, chunks=chunks)
+                fshard = fopt.hi - fopt.lo
+                fgrad = torch.empty(max(fshard, 1), device=dev).normal_(0, 1e-3, generator=gen)
 
-            def step_peer():
-                k[0] += 1
-                fopt.step(fgrads[k[0] % 4][:fshard], hyper["lr"], hyper["b1p"], hyper["b2p"])
+                def step_peer():
+                    fopt.step(fgrad[:fshard], hyper["lr"], hyper["b1p"], hyper["b2p"])
 
-            timed(step_peer, "fused_update_and_peer_broadcast")
-            st = exchange.status()
-            if st != 0:
-                out["fused_update_and_peer_broadcast"]["error"] = "wait for replica %d ran out" % (st - 1)
-            # every replica must hold the same vector
-            check = pv.tensor[::4099].double().sum().reshape(1)
-            lo_hi = check.clone()
-            dist.all_reduce(lo_hi, op=dist.ReduceOp.MAX)
-            out["fused_update_and_peer_broadcast"]["replicas_identical"] = bool(
-                (lo_hi == check).all().item())
+                runner = step_peer
+                launch = "eager"
+                try:
+                    g = torch.cuda.CUDAGraph()
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side):
+                        step_peer()
+                        with torch.cuda.graph(g, stream=side):
+                            step_peer()
+                    torch.cuda.current_stream().wait_stream(side)
+                    torch.cuda.synchronize()
+                    runner = g.replay
+                    launch = "cuda graph replay"
+                except Exception as e:  # noqa: BLE001
+                    if rank == 0:
+                        print("adam graph capture failed (%s): %r" % (label, e), file=sys.stderr)
+                timed(runner, label)
+                out[label]["launch"] = launch
+                out[label]["transport"] = transport
+                st = exchange.status()
+                if st != 0:
+                    out[label]["error"] = "wait for replica %d ran out" % (st - 1)
+                # every replica must hold the same vector
+                check = pv.tensor[::4099].double().sum().reshape(1)
+                lo_hi = check.clone()
+                dist.all_reduce(lo_hi, op=dist.ReduceOp.MAX)
+                out[label]["replicas_identical"] = bool((lo_hi == check).all().item())
+            except Exception as e:  # noqa: BLE001
+                out[label] = {"unavailable": repr(e)}
             torch.cuda.synchronize()
             dist.barrier()
-            pv.close()
-        except Exception as e:  # noqa: BLE001
-            out["fused_update_and_peer_broadcast"] = {"unavailable": repr(e)}
+            if fopt is not None:
+                fopt.close()
+            if pv is not None:
+                pv.close()
     out["config"] = "ResourceApplyAdam fp32, 25,557,032 parameters, contiguous ranges, strong scaling"
     return out
 
@@ -782,6 +1006,32 @@ def measure_ops(torch, lib, raw_ops, dev, args):
         entry("bn_grad_" + name, ms, 3 * s_bytes, x.numel(), "L2 flushed before each launch")
         del x, dy, y
 
+    # The nine layer shapes of the headline workload, one launch each (bf16,
+    # batch 256): whole-op time, forward and gradient.
+    for (_, h, w, c) in RESNET50_BN:
+        rows = BATCH * h * w
+        x = torch.randn(rows, c, device=dev).to(torch.bfloat16)
+        dy = (torch.randn(rows, c, device=dev) * 1e-2).to(torch.bfloat16)
+        y = torch.empty_like(x)
+        sc = torch.rand(c, device=dev) + 0.5
+        of = torch.randn(c, device=dev) * 0.1
+        stats = [torch.empty(c, device=dev) for _ in range(6)]
+        need = lib.BnWorkspaceBytes(rows, c, 1)
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        s_bytes = x.numel() * 2
+        tag = "r50_%dx%dx%d_bf16" % (h, w, c)
+        ms = time_launch(torch, lambda: lib.LaunchBnFwdTrain_BF16(
+            x.data_ptr(), sc.data_ptr(), of.data_ptr(), None, None, y.data_ptr(),
+            stats[0].data_ptr(), stats[1].data_ptr(), stats[2].data_ptr(),
+            stats[3].data_ptr(), rows, c, 1, EPS, 1.0, ws.data_ptr(), need, st), iters, flush)
+        entry("bn_fwd_" + tag, ms, 2 * s_bytes, x.numel(), "L2 flushed before each launch")
+        ms = time_launch(torch, lambda: lib.LaunchBnGrad_BF16(
+            dy.data_ptr(), x.data_ptr(), sc.data_ptr(), stats[2].data_ptr(),
+            stats[3].data_ptr(), y.data_ptr(), stats[4].data_ptr(), stats[5].data_ptr(),
+            rows, c, 1, EPS, True, ws.data_ptr(), need, st), iters, flush)
+        entry("bn_grad_" + tag, ms, 3 * s_bytes, x.numel(), "L2 flushed before each launch")
+        del x, dy, y
+
     # Dominant kernel of the headline workload: the gradient element-wise pass
     # (reads dy and x, writes dx: 3 * S per launch), timed alone on the largest
     # ResNet-50 layer, [256, 56, 56, 256] bf16 (S = 411 MB).
@@ -806,6 +1056,9 @@ def measure_ops(torch, lib, raw_ops, dev, args):
             "traffic": None}
     roof["ms_back_to_back"] = round(ms_stream, 4)
     roof["frac_back_to_back"] = round(3 * s_bytes / (ms_stream * 1e-3) / 1e9 / peak, 4)
+    # The whole op this kernel belongs to (statistics + element-wise pass).
+    roof["op"] = "bn_grad_r50_56x56x256_bf16"
+    roof["op_frac"] = ops["bn_grad_r50_56x56x256_bf16"]["frac_of_peak"]
     roof["traffic"] = NCU_TRAFFIC_BYTES["bn_grad_apply_bf16_256x56x56x256"]
     roof["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
                               "kernel and case (profiles/bn_grad_apply_bf16_256x56x56x256_ncu_full.md)")
@@ -849,10 +1102,10 @@ def cpu_workload(batch, seed=4):
 
 
 def cpu_baseline(budget_s=15.0):
-    """The CPU oracle (C, all host threads) on a bounded sample of the workload:
-    the same 53 layers forward + gradient at batch 8 per layer."""
-    batch = 8
-    step, elems, cores = cpu_workload(batch)
+    """The CPU oracle (C, all host threads) on the stated workload: the same 53
+    layers forward + gradient at batch 256, as many whole passes as fit the
+    time budget (at least one)."""
+    step, elems, cores = cpu_workload(BATCH)
     step()
     t0 = time.perf_counter()
     n = 0
@@ -864,16 +1117,17 @@ def cpu_baseline(budget_s=15.0):
     dt = time.perf_counter() - t0
     return {"value": round(elems * n / dt / 1e9, 4), "unit": UNIT, "cores": cores,
             "kind": "port",
-            "sample": "same 53 layers fwd+grad at batch %d instead of %d, %d passes" % (batch, BATCH, n)}
+            "sample": "the whole step (53 layers fwd+grad at batch %d), %d passes after one "
+                      "warm-up pass" % (BATCH, n)}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    batch = 8
-    step, elems, cores = cpu_workload(batch)
-    for _ in range(max(1, min(args.warmup, 3))):
+    step, elems, cores = cpu_workload(BATCH)
+    warm = max(1, min(args.warmup, 3))
+    for _ in range(warm):
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -881,14 +1135,15 @@ def run_reference(args):
     dt = time.perf_counter() - t0
     ms = dt / args.steps * 1e3
     val = round(elems * args.steps / dt / 1e9, 4)
-    sample = "same 53 layers fwd+grad at batch %d per layer instead of %d" % (batch, BATCH)
+    sample = "the whole step (53 layers fwd+grad at batch %d), %d timed passes" % (
+        BATCH, args.steps)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT,
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": warm,
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": 53, "batch_per_gpu": BATCH,
-                   "layout": "NHWC", "stats_dtype": "f32"},
+        "config": workload_config(),
+        "run": {"sync": "none (host cores)", "launch": "one process, %d OpenMP threads" % cores},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -13,7 +13,9 @@
  *   - pointers are borrowed DEVICE pointers, valid until the stream work ends;
  *   - host scalars are passed by value; nothing is read back from the device;
  *   - a launcher enqueues work on `stream` and returns without synchronising;
- *   - a launcher allocates nothing and keeps no global state; scratch memory is
+ *   - a launcher allocates nothing and keeps no state between calls beyond
+ *     per-device launch constants (SM count, occupancy) cached on first use
+ *     and the test knobs at the end of this file; scratch memory is
  *     passed in by the caller (TF: `OpKernelContext::allocate_temp`) after a
  *     `*WorkspaceBytes()` query;
  *   - a launcher is re-entrant (TF calls Compute() from several threads);
@@ -95,6 +97,21 @@ void LaunchApplyAdamMixed_BFloat16(float* var, float* m, float* v,
                                    const void* grad, float lr_t, float beta1,
                                    float beta2, float epsilon, int64_t n,
                                    bool use_nesterov, cudaStream_t stream);
+
+/* ResourceApplyAdam / ApplyAdam for double tensors, one streaming pass
+ * (56 B/element).  No launcher of this name exists in the reference: it serves
+ * T = double with a chain of thirteen element-wise library calls
+ * (musa_ext/kernels/training/musa_applyadam_op.cc:297-415, registrations
+ * :672-687), each storing a double tensor.  This launcher performs the same
+ * operations in the same order with one IEEE rounding each:
+ *   m = m*b1 + g*(1-b1);  v = v*b2 + (g*g)*(1-b2);
+ *   var = var - (m / (sqrt(v) + eps)) * alpha
+ * (`alpha`: the bias-corrected step the op computes on the host, :236-246).
+ * With use_nesterov the numerator is m*b1 + g*(1-b1), as in TensorFlow's CPU
+ * kernel (the chain itself ignores the attribute). */
+void LaunchApplyAdam_F64(double* var, double* m, double* v, const double* grad,
+                         double alpha, double beta1, double beta2, double epsilon,
+                         int64_t n, bool use_nesterov, cudaStream_t stream);
 
 /* ------------------------- Nadam, RMSProp, gradient descent (same shape) -- */
 
@@ -426,20 +443,9 @@ void LaunchRmsNormGradDxBFloat16(const void* x, const void* inv_rms, const void*
 
 /* Bytes of scratch that the BatchNorm launchers below need for this geometry
  * (the per-CTA partial sums of the two-level reduction).  The same figure
- * serves forward and gradient.  16-byte aligned memory is expected. */
+ * serves forward and gradient.  16-byte
+ * aligned memory is expected; its contents may be arbitrary. */
 size_t BnWorkspaceBytes(int64_t outer, int64_t channels, int64_t inner);
-
-/* When the geometry allows it (channels-last, 128-bit packs, at most 256 packs
- * per row) LaunchBnFwdTrain_* and LaunchBnGrad_* run as ONE cooperative launch
- * whose CTAs meet at a barrier kept in the workspace.  Every wait in it is
- * bounded; if one ran out (the outputs of that call are then invalid) the
- * workspace's status word says so.  The word is reset by every such launch, so
- * this reports on the latest one that used `workspace`; it reads and clears the
- * word and synchronises the device (for tests and post-mortems, not for the hot
- * path).  0 = fine.  The result is meaningless for a workspace that no
- * single-launch op has used since it was allocated. */
-int BnWorkspaceStatus(void* workspace, int64_t outer, int64_t channels,
-                      int64_t inner);
 
 /* Training-mode forward.  Outputs follow TensorFlow's CPU kernel:
  *   y = (x - mean) * rsqrt(var + eps) * scale + offset, mean/var of the batch;
@@ -579,6 +585,30 @@ int LaunchBnStatsSums(int dtype, const void* x, float* sums, int64_t outer,
 int LaunchBnStatsSumsCount(int dtype, const void* x, float* sums, int64_t outer,
                            int64_t channels, int64_t inner, void* workspace,
                            size_t workspace_bytes, cudaStream_t stream);
+/* The cancellation-safe form of the same exchange: moments[0:C] = mean,
+ * moments[C:2C] = sum((x - mean)^2), moments[2C] = the row count, all of this
+ * replica's rows (2C + 1 floats).  Raw sums lose the variance when
+ * |mean| >> std (sum(x*x) and mean^2 agree in all fp32 digits); moments of
+ * replicas are merged, not added: LaunchExchangeMoments over peer memory, or
+ * an all-gather followed by LaunchBnMergeMoments. */
+int LaunchBnStatsMoments(int dtype, const void* x, float* moments, int64_t outer,
+                         int64_t channels, int64_t inner, void* workspace,
+                         size_t workspace_bytes, cudaStream_t stream);
+/* gathered = `world` moment vectors of 2C + 1 floats back to back, in rank
+ * order; merged (2C + 1 floats) = the moments of all rows together, in fp64
+ * and rank order (every replica computes the same bits). */
+int LaunchBnMergeMoments(const float* gathered, int world, int64_t channels,
+                         float* merged, cudaStream_t stream);
+/* LaunchBnApplyFromSums for merged moments (mean and sum of squared
+ * deviations over `total_count` values per channel). */
+int LaunchBnApplyFromMoments(int dtype, const void* x, const float* scale,
+                             const float* offset, const float* moments,
+                             double total_count, const float* est_mean,
+                             const float* est_var, float exp_avg_factor, void* y,
+                             float* batch_mean, float* batch_var,
+                             float* saved_mean, float* saved_var, int64_t outer,
+                             int64_t channels, int64_t inner, float epsilon,
+                             cudaStream_t stream);
 /* From all-reduced sums over `total_count` values per channel to the four
  * statistic outputs of the forward op. */
 int LaunchBnFinalizeFromSums(const float* sums, double total_count,
@@ -631,12 +661,19 @@ int LaunchBnGradApplyFromSums(int dtype, const void* dy, const void* x,
  * Per exchange: LaunchExchangeSums(handle, vector, n, stream) - in place, no
  * host synchronisation, works inside CUDA graph capture (the epoch counter
  * lives on the device).  MusaExchangeStatus (synchronises; call between steps)
- * returns 1 + q if a wait for replica q ever ran out, which leaves that
- * exchange's totals incomplete instead of hanging the GPU. */
+ * returns 1 + q if a wait for replica q ever ran out (after about a second),
+ * which leaves that exchange's totals incomplete instead of hanging the GPU;
+ * until the host has read the status, later exchanges do not wait for that
+ * replica again. */
 void* MusaExchangeCreate(int rank, int world, int64_t max_floats);
 int MusaExchangeIpcHandle(void* handle, void* out64);
 int MusaExchangeOpenPeers(void* handle, const void* handles);
 int LaunchExchangeSums(void* handle, float* vector, int64_t n, cudaStream_t stream);
+/* The same exchange with the merge of LaunchBnMergeMoments as its combine
+ * step: `moments` (2 * channels + 1 floats, see LaunchBnStatsMoments) becomes
+ * the moments of the rows of all replicas, bit-identical everywhere. */
+int LaunchExchangeMoments(void* handle, float* moments, int64_t channels,
+                          cudaStream_t stream);
 int MusaExchangeStatus(void* handle);
 void MusaExchangeDestroy(void* handle);
 /* Peer-visible device memory for the set-up of the two peer-memory paths: a
@@ -663,12 +700,62 @@ int LaunchAdamShardBroadcastFloat(float* const* var_replicas, int world, int ran
                                   float beta1, float beta2, float epsilon, float alpha,
                                   int64_t n, cudaStream_t stream);
 
+/* The same step with the copy engines as the all-gather, for four replicas
+ * and more, where the step is bound by the bytes that leave the GPU over
+ * NVLink and copy engines move them faster than SM stores: the local range is
+ * updated in `chunks` (1..8) pieces with LaunchResourceApplyAdamFloat's kernel
+ * on `stream`, and every finished piece goes to each peer with one
+ * cudaMemcpyAsync on a side stream of the pipe while the next piece updates;
+ * `stream` joins the side streams before the call returns, so the call is one
+ * asynchronous operation on `stream` (capturable in a CUDA graph).  Same
+ * results, bit for bit, and the same completion rule as
+ * LaunchAdamShardBroadcastFloat.  MusaShardPipeCreate (set-up: world - 1
+ * streams and the events) with the device current.  No counterpart in the
+ * reference. */
+void* MusaShardPipeCreate(int world, int rank);
+void MusaShardPipeDestroy(void* pipe);
+int LaunchAdamShardCopyFloat(void* pipe, float* const* var_replicas, int64_t lo, float* m,
+                             float* v, const float* grad, float beta1, float beta2,
+                             float epsilon, float alpha, int64_t n, int chunks,
+                             cudaStream_t stream);
+
 /* Test hook: `world` (<= 8) replicas emulated on one GPU by one cooperative
  * launch of `world` CTAs; `vectors` is a device array of `world` device
  * pointers to n floats each.  missing_rank = world - 1 leaves that replica out
  * to check that the others' waits run out (returns 1000 + world). */
 int MusaExchangeSelfTest(int world, int64_t n, float* const* vectors, int rounds,
-                         int missing_rank, cudaStream_t stream);
+                         int missing_rank, int mode, cudaStream_t stream);
+/* `mode`: 0 sums, 1 moments (n = 2 * channels + 1). */
+
+/* ---- Tracing of the launcher layer (off by default).  With
+ * MUSA_B200_TRACE=1 in the environment, or after MusaKernelsTraceEnable(1),
+ * every launcher call sits inside an NVTX range named after the launcher (a
+ * profiler that injects NVTX shows them; without one the range calls are
+ * no-ops) and adds to per-launcher counters: calls, algorithmic bytes (the
+ * bytes the op has to move, as in the roofline figures) and host nanoseconds
+ * spent inside the call.  The reference traces its allocator and copy paths
+ * only (musa_ext/mu/device/musa_telemetry.h:47-199); no counterpart there. */
+typedef struct MusaLaunchCounter {
+  const char* name;   /* launcher family, a static string */
+  long long calls;
+  long long bytes;
+  long long host_ns;
+} MusaLaunchCounter;
+/* Returns the previous state (0 / 1). */
+int MusaKernelsTraceEnable(int on);
+/* Copies up to max_entries counters; returns how many (out == NULL: how many
+ * exist). */
+int MusaKernelsTraceSnapshot(MusaLaunchCounter* out, int max_entries);
+void MusaKernelsTraceReset(void);
+
+/* Test and sweep hooks, not part of the reference boundary: launch-shape
+ * knobs (grid sizes, pipeline depths, cache hints; csrc/tuning.h lists the
+ * keys) that let a sweep compare variants without rebuilding.  They change
+ * HOW a launcher runs, never what it computes.  The table is process-wide and
+ * is read by every launcher at every call: set a knob only while no other
+ * thread is launching.  Set returns the previous value (-1: unknown key). */
+int MusaKernelsSetTuning(int key, int value);
+int MusaKernelsGetTuning(int key);
 
 #ifdef __cplusplus
 } /* extern "C" */

@@ -155,6 +155,15 @@ def adam_alpha(lr, beta1_power, beta2_power):
     return np.float32(float(lr) * np.sqrt(1.0 - float(beta2_power)) / one_minus)
 
 
+def adam_alpha64(lr, beta1_power, beta2_power):
+    """The same step size kept in float64 (T = double: `static_cast<T>(alpha_val)`,
+    musa_ext/kernels/training/musa_applyadam_op.cc:317)."""
+    one_minus = 1.0 - float(beta1_power)
+    if abs(one_minus) < 1e-10:
+        return np.float64(lr)
+    return np.float64(float(lr) * np.sqrt(1.0 - float(beta2_power)) / one_minus)
+
+
 def apply_adam(var, m, v, beta1_power, beta2_power, lr, beta1, beta2, epsilon,
                grad, use_nesterov=False):
     """One Adam step.  State arrays of float32, float16 or bfloat16; grad of
@@ -177,6 +186,32 @@ def apply_adam(var, m, v, beta1_power, beta2_power, lr, beta1, beta2, epsilon,
     numer = (b1 * m_new + omb1 * g) if use_nesterov else m_new
     var_new = var32 - alpha * numer / (np.sqrt(v_new) + eps)
     return var_new.astype(dt), m_new.astype(dt), v_new.astype(dt)
+
+
+def apply_adam_op_chain(var, m, v, beta1_power, beta2_power, lr, beta1, beta2, epsilon,
+                        grad, use_nesterov=False):
+    """One Adam step for float64 tensors the way the reference serves that
+    dtype: a chain of element-wise ops that each store a tensor of type T
+    (musa_ext/kernels/training/musa_applyadam_op.cc:297-415): MUL, MUL, ADD for
+    m; MUL, MUL, MUL, ADD for v; SQRT, ADD epsilon, DIV, MUL alpha, SUB.  NumPy
+    rounds every one of these float64 operations once, as the chain does.  The
+    scalars are read as T, alpha comes from `adam_alpha` in float64 (:236-246),
+    1 - beta is formed in T (:309-314).  With use_nesterov the numerator is
+    TensorFlow's m * beta1 + g * (1 - beta1) (the chain ignores the attr).
+    Returns new (var, m, v)."""
+    f64 = np.float64
+    var = np.asarray(var, f64)
+    m = np.asarray(m, f64)
+    v = np.asarray(v, f64)
+    g = np.asarray(grad, f64)
+    b1, b2, eps = f64(beta1), f64(beta2), f64(epsilon)
+    alpha = adam_alpha64(f64(lr), f64(beta1_power), f64(beta2_power))
+    omb1, omb2 = f64(1.0) - b1, f64(1.0) - b2
+    m_new = m * b1 + g * omb1
+    v_new = v * b2 + (g * g) * omb2
+    numer = (m_new * b1 + g * omb1) if use_nesterov else m_new
+    var_new = var - (numer / (np.sqrt(v_new) + eps)) * alpha
+    return var_new, m_new, v_new
 
 
 # --------------------------------------------------------------------------

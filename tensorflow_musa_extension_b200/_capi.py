@@ -41,6 +41,8 @@ PROTOTYPES = {
     "LaunchApplyAdamMixed_Float": (None, _ADAM_SAME),
     "LaunchApplyAdamMixed_Half": (None, _ADAM_SAME),
     "LaunchApplyAdamMixed_BFloat16": (None, _ADAM_SAME),
+    "LaunchApplyAdam_F64": (None, [c_vp, c_vp, c_vp, c_vp, c_f64, c_f64, c_f64, c_f64,
+                                   c_i64, ctypes.c_bool, c_vp]),
     "LaunchBiasAct_F32": (c_int, _BIAS_ACT),
     "LaunchBiasAct_F16": (c_int, _BIAS_ACT),
     "LaunchBiasAct_BF16": (c_int, _BIAS_ACT),
@@ -96,7 +98,6 @@ PROTOTYPES = {
     "LaunchBiasAddReluGrad_F16": (c_int, _BIAS_RELU_GRAD),
     "LaunchBiasAddReluGrad_BF16": (c_int, _BIAS_RELU_GRAD),
     "BnWorkspaceBytes": (c_size, [c_i64, c_i64, c_i64]),
-    "BnWorkspaceStatus": (c_int, [c_vp, c_i64, c_i64, c_i64]),
     "LaunchBnFwdTrain_F32": (c_int, _BN_TRAIN),
     "LaunchBnFwdTrain_F16": (c_int, _BN_TRAIN),
     "LaunchBnFwdTrain_BF16": (c_int, _BN_TRAIN),
@@ -118,6 +119,12 @@ PROTOTYPES = {
     "LaunchBnApplyFromSums":
         (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_f64, c_vp, c_vp, c_f32, c_vp,
                  c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_f32, c_vp]),
+    "LaunchBnStatsMoments":
+        (c_int, [c_int, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp]),
+    "LaunchBnMergeMoments": (c_int, [c_vp, c_int, c_i64, c_vp, c_vp]),
+    "LaunchBnApplyFromMoments":
+        (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_f64, c_vp, c_vp, c_f32, c_vp,
+                 c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_f32, c_vp]),
     "LaunchBnFinalizeFromSums":
         (c_int, [c_vp, c_f64] + [c_vp] * 6 + [c_i64, c_f32, c_vp]),
     "LaunchBnApply":
@@ -136,7 +143,8 @@ PROTOTYPES.update({
     "LaunchExchangeSums": (c_int, [c_vp, c_vp, c_i64, c_vp]),
     "MusaExchangeStatus": (c_int, [c_vp]),
     "MusaExchangeDestroy": (None, [c_vp]),
-    "MusaExchangeSelfTest": (c_int, [c_int, c_i64, c_vp, c_int, c_int, c_vp]),
+    "LaunchExchangeMoments": (c_int, [c_vp, c_vp, c_i64, c_vp]),
+    "MusaExchangeSelfTest": (c_int, [c_int, c_i64, c_vp, c_int, c_int, c_int, c_vp]),
     "MusaPeerAlloc": (c_vp, [c_i64]),
     "MusaPeerFree": (c_int, [c_vp]),
     "MusaPeerIpcHandle": (c_int, [c_vp, c_vp]),
@@ -145,13 +153,36 @@ PROTOTYPES.update({
     "LaunchAdamShardBroadcastFloat":
         (c_int, [c_vp, c_int, c_int, c_i64, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32,
                  c_i64, c_vp]),
+    "MusaShardPipeCreate": (c_vp, [c_int, c_int]),
+    "MusaShardPipeDestroy": (None, [c_vp]),
+    "LaunchAdamShardCopyFloat":
+        (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_i64,
+                 c_int, c_vp]),
 })
 
-# Hooks outside the reference boundary (launch-shape sweeps).
-EXTRA_PROTOTYPES = {
+# Hooks outside the reference boundary: launch-shape sweeps and tracing.
+class MusaLaunchCounter(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char_p), ("calls", ctypes.c_longlong),
+                ("bytes", ctypes.c_longlong), ("host_ns", ctypes.c_longlong)]
+
+
+PROTOTYPES.update({
     "MusaKernelsSetTuning": (c_int, [c_int, c_int]),
     "MusaKernelsGetTuning": (c_int, [c_int]),
-}
+    "MusaKernelsTraceEnable": (c_int, [c_int]),
+    "MusaKernelsTraceSnapshot": (c_int, [ctypes.POINTER(MusaLaunchCounter), c_int]),
+    "MusaKernelsTraceReset": (None, []),
+})
+EXTRA_PROTOTYPES = {}
+
+
+def trace_snapshot(lib):
+    """{launcher: {"calls", "bytes", "host_ns"}} of the tracing counters."""
+    n = lib.MusaKernelsTraceSnapshot(None, 0)
+    buf = (MusaLaunchCounter * max(n, 1))()
+    n = lib.MusaKernelsTraceSnapshot(buf, n)
+    return {buf[i].name.decode(): {"calls": buf[i].calls, "bytes": buf[i].bytes,
+                                   "host_ns": buf[i].host_ns} for i in range(n)}
 
 # Entry points of include/musa_plugin_runtime.h that the staging pipeline
 # drives (streams, events, asynchronous copies, the pinned pool).

@@ -1,10 +1,13 @@
 """Multi-GPU forms of the path, one process per GPU over torch.distributed.
 
 * Cross-replica BatchNorm (SyncBN): the batch is sharded over the replicas;
-  each pass exchanges 2*C fp32 per-channel sums with ONE all-reduce placed
-  between the statistics kernel and the element-wise kernel:
-      forward : [sum x, sum x^2]            -> mean, variance over all replicas
-      gradient: [sum dy, sum dy*(x - mean)] -> dscale, doffset, dx
+  each pass exchanges 2*C (+1) fp32 per-channel values with ONE collective
+  placed between the statistics kernel and the element-wise kernel:
+      forward : [mean, sum (x - mean)^2, rows] of the local rows, MERGED over
+                the replicas (count-weighted mean, Chan's formula for the
+                squared deviations) -> mean, variance over all replicas.  Raw
+                [sum x, sum x^2] would lose the variance when |mean| >> std.
+      gradient: [sum dy, sum dy*(x - mean)], ADDED -> dscale, doffset, dx
   The Bessel factor of batch_variance uses the global count.
 * Range-sharded Adam: every replica holds the whole `var` but only its
   contiguous range of m, v (and reads only that range of grad); after the
@@ -55,22 +58,29 @@ class _DeviceKernels:
     def workspace_bytes(self, rows, c):
         return self.lib.BnWorkspaceBytes(rows, c, 1)
 
-    def stats_sums(self, x, sums, ws):
-        """sums[0:2C] = local sums, sums[2C] = local row count."""
+    def stats_moments(self, x, moments, ws):
+        """moments[0:C] = local mean, [C:2C] = local sum of squared deviations,
+        moments[2C] = local row count."""
         rows, c = x.shape
-        raw_ops._check(self.lib.LaunchBnStatsSumsCount(
-            _DT_CODE[x.dtype], x.data_ptr(), sums.data_ptr(), rows, c, 1,
-            ws.data_ptr(), ws.numel(), self._st()), "LaunchBnStatsSumsCount")
+        raw_ops._check(self.lib.LaunchBnStatsMoments(
+            _DT_CODE[x.dtype], x.data_ptr(), moments.data_ptr(), rows, c, 1,
+            ws.data_ptr(), ws.numel(), self._st()), "LaunchBnStatsMoments")
 
-    def apply_from_sums(self, x, scale, offset, sums, count, stats, y, eps):
-        """Statistics from the all-reduced sums and the element-wise pass, one
+    def merge_moments(self, gathered, world, c, merged):
+        """`gathered`: the replicas' moment vectors in rank order -> `merged`."""
+        raw_ops._check(self.lib.LaunchBnMergeMoments(
+            gathered.data_ptr(), world, c, merged.data_ptr(), self._st()),
+            "LaunchBnMergeMoments")
+
+    def apply_from_moments(self, x, scale, offset, moments, count, stats, y, eps):
+        """Statistics from the merged moments and the element-wise pass, one
         launch."""
         rows, c = x.shape
-        raw_ops._check(self.lib.LaunchBnApplyFromSums(
+        raw_ops._check(self.lib.LaunchBnApplyFromMoments(
             _DT_CODE[x.dtype], x.data_ptr(), scale.data_ptr(), offset.data_ptr(),
-            sums.data_ptr(), float(count), None, None, 1.0, y.data_ptr(),
+            moments.data_ptr(), float(count), None, None, 1.0, y.data_ptr(),
             stats[0].data_ptr(), stats[1].data_ptr(), stats[2].data_ptr(),
-            stats[3].data_ptr(), rows, c, 1, eps, self._st()), "LaunchBnApplyFromSums")
+            stats[3].data_ptr(), rows, c, 1, eps, self._st()), "LaunchBnApplyFromMoments")
 
     def grad_stats_sums(self, dy, x, mean, sums, ws):
         rows, c = x.shape
@@ -157,6 +167,14 @@ class PeerExchange:
             "LaunchExchangeSums")
         return vector
 
+    def merge_moments_(self, moments, channels):
+        """In place: `moments` = [mean[C], M2[C], count] of this replica's rows
+        becomes the moments of the rows of all replicas."""
+        raw_ops._check(self.lib.LaunchExchangeMoments(
+            self.handle, moments.data_ptr(), int(channels),
+            torch.cuda.current_stream().cuda_stream), "LaunchExchangeMoments")
+        return moments
+
     def status(self):
         """0, or 1 + q if a wait for replica q ran out since the last call."""
         return int(self.lib.MusaExchangeStatus(self.handle))
@@ -196,8 +214,9 @@ class SyncBatchNorm:
         self.saved_var = torch.empty(self.c, **f32)
         self.dscale = torch.empty(self.c, **f32)
         self.doffset = torch.empty(self.c, **f32)
-        # [sum, sumsq | count]: the row count rides in the same all-reduce.
+        # [mean, squared deviations | count]: the row count rides along.
         self.sums = torch.zeros(2 * self.c + 1, **f32)
+        self._gathered = None   # all-gather target of the collective-library path
         self.gsums = torch.zeros(2 * self.c, **f32)
         nbytes = max(16, int(self.k.workspace_bytes(max(int(max_rows), 1), self.c)))
         self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
@@ -225,17 +244,23 @@ class SyncBatchNorm:
             self.k.fwd_local(x, scale, offset, y, self._stats(), self.ws, self.eps)
             self.global_count = float(rows)
             return y
-        self.k.stats_sums(x, self.sums, self.ws)
+        self.k.stats_moments(x, self.sums, self.ws)
         if self.exchange is not None:
-            self.exchange.sum_(self.sums)
+            self.exchange.merge_moments_(self.sums, self.c)
         elif self.world > 1:
-            dist.all_reduce(self.sums, op=dist.ReduceOp.SUM, group=self.group)
+            # Moments are merged, not added: gather every replica's vector and
+            # merge them (in rank order, so all replicas get the same bits).
+            if self._gathered is None:
+                self._gathered = torch.empty(self.world * (2 * self.c + 1),
+                                             dtype=torch.float32, device=self.sums.device)
+            dist.all_gather_into_tensor(self._gathered, self.sums, group=self.group)
+            self.k.merge_moments(self._gathered, self.world, self.c, self.sums)
         # Static shapes: the global count is rows * world unless a replica is
         # ragged; read it on the host only in that case.
         self.global_count = float(rows) * self.world if self._uniform_rows else \
             float(self.sums[2 * self.c].item())
-        self.k.apply_from_sums(x, scale, offset, self.sums, self.global_count,
-                               self._stats(), y, self.eps)
+        self.k.apply_from_moments(x, scale, offset, self.sums, self.global_count,
+                                  self._stats(), y, self.eps)
         return y
 
     _uniform_rows = True
@@ -448,9 +473,29 @@ class FusedShardedAdam:
     that range of every replica's vector over NVLink
     (LaunchAdamShardBroadcastFloat), then the replicas exchange one float with
     the peer-memory kernel, after which every copy is complete.  `var` is a
-    PeerVector; m and v exist only for the local range."""
+    PeerVector; m and v exist only for the local range.
 
-    def __init__(self, var, exchange, beta1=0.9, beta2=0.999, epsilon=1e-7):
+    Ordering between steps.  The closing exchange orders the peers' WRITES of
+    step t before anybody's reads of the new weights.  The other direction -
+    no replica may overwrite a peer's copy for step t + 1 while that peer
+    still reads it for its forward / backward pass of step t + 1 - needs every
+    replica to have finished reading `var` before any replica starts the next
+    update.  With `fence_before=True` (the default) step() opens with the same
+    one-float exchange, which gives exactly that as long as each replica
+    enqueues its reads of `var` on the stream before calling step().  A
+    training loop whose gradient all-reduce or reduce-scatter already sits
+    between the last read of `var` and step() may pass fence_before=False."""
+
+    def __init__(self, var, exchange, beta1=0.9, beta2=0.999, epsilon=1e-7,
+                 fence_before=True, transport="auto", chunks=2):
+        """`transport`: "stores" - the update kernel stores every new weight
+        into all replicas (one kernel; best for two replicas, where the step
+        is bound by HBM); "copies" - the local range is updated in `chunks`
+        pieces and the copy engines carry each finished piece to the peers
+        while the next updates (LaunchAdamShardCopyFloat; best from four
+        replicas on, where the step is bound by NVLink egress and copy engines
+        reach the peer-copy rate that SM stores do not); "auto" picks by the
+        number of replicas."""
         import ctypes
         self.var = var
         self.exchange = exchange
@@ -462,7 +507,20 @@ class FusedShardedAdam:
         self.beta1, self.beta2, self.epsilon = beta1, beta2, epsilon
         self._ptrs = (ctypes.c_void_p * self.world)(*var.replica_ptrs)
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.fence_before = bool(fence_before)
         self.lib = raw_ops._lib()
+        if transport == "auto":
+            transport = "copies" if self.world >= 4 else "stores"
+        if transport not in ("stores", "copies"):
+            raise InvalidArgumentError("FusedShardedAdam: unknown transport %r" % (transport,))
+        self.transport = transport
+        self.chunks = max(1, min(8, int(chunks)))
+        self._pipe = None
+        if transport == "copies" and self.world > 1:
+            with torch.cuda.device(dev):
+                self._pipe = self.lib.MusaShardPipeCreate(self.world, self.rank)
+            if self._pipe is None:
+                raise RuntimeError("FusedShardedAdam: could not create the copy pipe")
 
     def step(self, grad, lr, beta1_power, beta2_power):
         """`grad`: the full gradient vector or this replica's range of it."""
@@ -476,11 +534,26 @@ class FusedShardedAdam:
         alpha = raw_ops._adam_alpha(float(f32(lr)), float(f32(beta1_power)),
                                     float(f32(beta2_power)))
         st = torch.cuda.current_stream().cuda_stream
-        raw_ops._check(self.lib.LaunchAdamShardBroadcastFloat(
-            self._ptrs, self.world, self.rank, self.lo, self.m.data_ptr(), self.v.data_ptr(),
-            grad.data_ptr(), float(f32(self.beta1)), float(f32(self.beta2)),
-            float(f32(self.epsilon)), alpha, self.hi - self.lo, st),
-            "LaunchAdamShardBroadcastFloat")
+        if self.fence_before and self.exchange is not None and self.world > 1:
+            self.exchange.sum_(self._token)  # every replica is done reading var
+        if self._pipe is not None:
+            raw_ops._check(self.lib.LaunchAdamShardCopyFloat(
+                self._pipe, self._ptrs, self.lo, self.m.data_ptr(), self.v.data_ptr(),
+                grad.data_ptr(), float(f32(self.beta1)), float(f32(self.beta2)),
+                float(f32(self.epsilon)), alpha, self.hi - self.lo, self.chunks, st),
+                "LaunchAdamShardCopyFloat")
+        else:
+            raw_ops._check(self.lib.LaunchAdamShardBroadcastFloat(
+                self._ptrs, self.world, self.rank, self.lo, self.m.data_ptr(),
+                self.v.data_ptr(), grad.data_ptr(), float(f32(self.beta1)),
+                float(f32(self.beta2)), float(f32(self.epsilon)), alpha, self.hi - self.lo,
+                st), "LaunchAdamShardBroadcastFloat")
         if self.exchange is not None and self.world > 1:
             self.exchange.sum_(self._token)  # all ranges have landed everywhere
         return self.var.tensor
+
+    def close(self):
+        if getattr(self, "_pipe", None) is not None:
+            torch.cuda.synchronize()
+            self.lib.MusaShardPipeDestroy(self._pipe)
+            self._pipe = None

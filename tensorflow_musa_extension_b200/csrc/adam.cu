@@ -6,7 +6,10 @@
 // (musa_ext/kernels/training/musa_apply_sparse_adam_kernel.mu:140-157,
 //  musa_ext/kernels/training/musa_applyadam_bf16_kernel.mu:82-112,
 //  musa_ext/kernels/training/musa_applyadam_mixed_kernel.mu:55-86).
+#include <new>
+
 #include "common.cuh"
+#include "trace.h"
 #include "tuning.h"
 #include "../../include/musa_plugin_kernels.h"
 
@@ -147,6 +150,8 @@ template <typename StateT, typename GradT>
 void LaunchAdam(StateT* var, StateT* m, StateT* v, const GradT* grad,
                 float lr_t, float beta1, float beta2, float epsilon, int64_t n,
                 bool nesterov, cudaStream_t stream) {
+  MUSA_TRACE("LaunchApplyAdam",
+             n > 0 ? (6 * sizeof(StateT) + sizeof(GradT)) * n : 0);
   if (n <= 0) return;
   AdamParams p;
   p.lr_t = lr_t;
@@ -291,6 +296,7 @@ int LaunchAdamShardBroadcastFloat(float* const* var_replicas, int world, int ran
       lo < 0 || n < 0) {
     return MUSA_KERNELS_EINVAL;
   }
+  MUSA_TRACE("LaunchAdamShardBroadcast", 28 * n);
   if (n == 0) return MUSA_KERNELS_OK;
   if (m == nullptr || v == nullptr || grad == nullptr) return MUSA_KERNELS_EINVAL;
   Replicas r{};
@@ -319,6 +325,113 @@ int LaunchAdamShardBroadcastFloat(float* const* var_replicas, int world, int ran
   } else {
     LaunchChained(true, AdamShardBroadcastKernel<1>, dim3(static_cast<unsigned>(blocks)),
                   dim3(256), 0, stream, r, lo, m, v, grad, p, n);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---- Range-sharded Adam with the copy engines as the all-gather.  From four
+// replicas on, the step is bound by the bytes that leave the GPU over NVLink
+// ((world - 1) / world of the vector), and the copy engines move them at the
+// peer-copy rate, which stores issued by SMs do not reach.  The local range is
+// updated chunk by chunk on the caller's stream; as soon as a chunk is done
+// (an event), one cudaMemcpyAsync per peer carries it out on that peer's side
+// stream while the next chunk updates.  The caller's stream joins all side
+// streams at the end, so the call behaves like one asynchronous operation on
+// `stream` and can be captured in a CUDA graph.
+struct ShardPipe {
+  int world;
+  int rank;
+  int device;
+  cudaStream_t side[16];
+  cudaEvent_t done[16];
+  cudaEvent_t chunk[8];
+};
+
+void* MusaShardPipeCreate(int world, int rank) {
+  if (world < 1 || world > 16 || rank < 0 || rank >= world) return nullptr;
+  auto* p = new (std::nothrow) ShardPipe();
+  if (p == nullptr) return nullptr;
+  p->world = world;
+  p->rank = rank;
+  bool ok = cudaGetDevice(&p->device) == cudaSuccess;
+  for (int k = 0; k < world - 1 && ok; ++k) {
+    ok = cudaStreamCreateWithFlags(&p->side[k], cudaStreamNonBlocking) == cudaSuccess &&
+         cudaEventCreateWithFlags(&p->done[k], cudaEventDisableTiming) == cudaSuccess;
+  }
+  for (int c = 0; c < 8 && ok; ++c) {
+    ok = cudaEventCreateWithFlags(&p->chunk[c], cudaEventDisableTiming) == cudaSuccess;
+  }
+  if (!ok) {
+    cudaGetLastError();
+    MusaShardPipeDestroy(p);
+    return nullptr;
+  }
+  return p;
+}
+
+void MusaShardPipeDestroy(void* pipe) {
+  auto* p = static_cast<ShardPipe*>(pipe);
+  if (p == nullptr) return;
+  for (int k = 0; k < 16; ++k) {
+    if (p->side[k] != nullptr) cudaStreamDestroy(p->side[k]);
+    if (p->done[k] != nullptr) cudaEventDestroy(p->done[k]);
+  }
+  for (int c = 0; c < 8; ++c) {
+    if (p->chunk[c] != nullptr) cudaEventDestroy(p->chunk[c]);
+  }
+  delete p;
+}
+
+int LaunchAdamShardCopyFloat(void* pipe, float* const* var_replicas, int64_t lo, float* m,
+                             float* v, const float* grad, float beta1, float beta2,
+                             float epsilon, float alpha, int64_t n, int chunks,
+                             cudaStream_t stream) {
+  auto* p = static_cast<ShardPipe*>(pipe);
+  if (p == nullptr || var_replicas == nullptr || lo < 0 || n < 0) return MUSA_KERNELS_EINVAL;
+  MUSA_TRACE("LaunchAdamShardCopy", 28 * n);
+  if (n == 0) return MUSA_KERNELS_OK;
+  if (m == nullptr || v == nullptr || grad == nullptr) return MUSA_KERNELS_EINVAL;
+  for (int q = 0; q < p->world; ++q) {
+    if (var_replicas[q] == nullptr) return MUSA_KERNELS_EINVAL;
+  }
+  if (chunks < 1) chunks = 1;
+  if (chunks > 8) chunks = 8;
+  // Chunk boundaries on multiples of 1024 elements (whole 128-bit packs, whole
+  // CTAs' tiles), the last chunk taking the remainder.
+  int64_t per = (n / chunks + 1023) / 1024 * 1024;
+  if (per < 1024) per = 1024;
+  float* local = var_replicas[p->rank] + lo;
+  int used = 0;
+  for (int64_t off = 0; off < n && used < 8; off += per, ++used) {
+    const int64_t len = used == 7 || off + per > n ? n - off : per;
+    LaunchAdam<float, float>(local + off, m + off, v + off, grad + off, alpha, beta1, beta2,
+                             epsilon, len, /*nesterov=*/false, stream);
+    cudaError_t err = cudaEventRecord(p->chunk[used], stream);
+    for (int k = 1; k < p->world && err == cudaSuccess; ++k) {
+      const int q = (p->rank + k) % p->world;   // every replica starts at another peer
+      err = cudaStreamWaitEvent(p->side[k - 1], p->chunk[used], 0);
+      if (err == cudaSuccess) {
+        err = cudaMemcpyAsync(var_replicas[q] + lo + off, local + off,
+                              sizeof(float) * static_cast<size_t>(len),
+                              cudaMemcpyDeviceToDevice, p->side[k - 1]);
+      }
+    }
+    if (err != cudaSuccess) {
+      cudaGetLastError();
+      return static_cast<int>(err);
+    }
+    if (len == n - off) {
+      ++used;
+      break;
+    }
+  }
+  for (int k = 1; k < p->world; ++k) {
+    cudaError_t err = cudaEventRecord(p->done[k - 1], p->side[k - 1]);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(stream, p->done[k - 1], 0);
+    if (err != cudaSuccess) {
+      cudaGetLastError();
+      return static_cast<int>(err);
+    }
   }
   return static_cast<int>(cudaGetLastError());
 }

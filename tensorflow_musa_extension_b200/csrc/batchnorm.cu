@@ -26,9 +26,11 @@
 // Bessel-corrected, saved_var is the population variance, no correction when
 // there is one value per channel; :265-277: the gradient receives a variance
 // and turns it into 1/sqrt(var + eps)).
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
+#include "trace.h"
 #include "tuning.h"
 #include "../../include/musa_plugin_kernels.h"
 
@@ -70,9 +72,10 @@ struct Plan {
 // `resident`: CTAs of this kernel that fit on one SM; the grid is one full
 // wave of them (a second, partly filled wave would idle SMs at the end).
 inline Plan PlanLast(int64_t rows, int64_t channels, int64_t cv, int unroll,
-                     bool cap_by_workspace, int resident) {
+                     bool cap_by_workspace, int resident, int max_tx = kThreads) {
   Plan p;
   p.tx = Pow2Ceil(cv);
+  if (p.tx > max_tx) p.tx = max_tx;
   p.ty = kThreads / p.tx;
   p.gx = static_cast<int>(CeilDiv(cv, p.tx));
   int per_sm = GetTuning(kTuneBnCtasPerSm);
@@ -224,6 +227,77 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// ---- Per-channel epilogues shared by the finalize kernel and the in-kernel
+// finalize of the pipelined statistics kernel.
+struct FinalizeArgs {
+  const float* partial;  // [splits, 2, C] level-1 output (or NULL with sums)
+  int splits;
+  int64_t channels;
+  double count;          // values per channel behind the sums (all replicas)
+  double inv_count;      // 1 / count
+  double bessel;         // count / (count - 1), or 1 when count <= 1
+  // forward
+  const void* x_first;   // tensor base: the shift K is re-read from it
+  int x_dtype;
+  int64_t shift_stride;  // elements between consecutive channels' K
+  const float* est_mean;
+  const float* est_var;
+  float* batch_mean;
+  float* batch_var;
+  float* saved_mean;
+  float* saved_var;
+  float exp_avg_factor;
+  // gradient
+  const float* variance;
+  float* dscale;
+  float* doffset;
+  float epsilon;
+  // both: totals for the apply pass / the all-reduce
+  float* sums;           // [2, C] or NULL
+  float* count_out;      // optional: receives `count` (rides in the all-reduce)
+};
+
+__device__ __forceinline__ float LoadAsF32(const void* base, int dtype,
+                                           int64_t i) {
+  if (dtype == MUSA_DT_F32) return static_cast<const float*>(base)[i];
+  if (dtype == MUSA_DT_F16) return __half2float(static_cast<const __half*>(base)[i]);
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]);
+}
+
+__device__ __forceinline__ void WriteFwdStats(const FinalizeArgs& a, int64_t c,
+                                              double mean, double var) {
+  if (var < 0.0) var = 0.0;
+  // bessel = R / (R - 1), or 1 when there is one value per channel; taken on
+  // the host (an fp64 divide per thread is not free on the device).
+  const double unbiased = var * a.bessel;
+  if (a.saved_mean) a.saved_mean[c] = static_cast<float>(mean);
+  if (a.saved_var) a.saved_var[c] = static_cast<float>(var);
+  const double f = static_cast<double>(a.exp_avg_factor);
+  double bm = mean, bv = unbiased;
+  if (a.exp_avg_factor != 1.0f && a.est_mean != nullptr &&
+      a.est_var != nullptr) {
+    bm = (1.0 - f) * static_cast<double>(a.est_mean[c]) + f * mean;
+    bv = (1.0 - f) * static_cast<double>(a.est_var[c]) + f * unbiased;
+  }
+  if (a.batch_mean) a.batch_mean[c] = static_cast<float>(bm);
+  if (a.batch_var) a.batch_var[c] = static_cast<float>(bv);
+}
+
+inline void SetCount(FinalizeArgs* f, double count) {
+  f->count = count;
+  f->inv_count = 1.0 / count;
+  f->bessel = count > 1.0 ? count / (count - 1.0) : 1.0;
+}
+
+
+// What the second level of the reduction writes.
+enum TailKind {
+  kTailFwdStats = 0,    // mean / variance outputs of the training forward
+  kTailFwdSums = 1,     // raw [sum x, sum x^2] (+ count)
+  kTailGrad = 2,        // [sum dy, sum dy (x - mean)], dscale, doffset
+  kTailFwdMoments = 3,  // [mean, sum (x - mean)^2] (+ count) of the local rows
+};
+
 // ---- Pipelined channels-last stats (128-bit packs only).
 //
 // Same mapping as BnStatsLastKernel, but the row stream is staged through
@@ -246,6 +320,11 @@ __device__ __forceinline__ void CpAsync16(void* smem_dst, const void* gmem_src) 
 __device__ __forceinline__ uint64_t PolicyEvictLast() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t PolicyEvictNormal() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
 __device__ __forceinline__ uint64_t PolicyEvictFirst() {
@@ -288,18 +367,27 @@ struct StatsPipe {
   static constexpr int kSmemBytes = kSlots * 256 * 16;
 };
 
+// The loop is written for instruction count: measured, the forward form needs
+// about 2.7 instructions per clock and SM to keep up with HBM, so every
+// instruction per 16-byte pack beyond the arithmetic (convert, shift, two
+// accumulations) costs bandwidth.  Whole stages run without bounds checks
+// (the stage loop is not unrolled over the ring: the slot is a run-time
+// offset), source pointers advance by additions, and the rows that do not
+// fill a stage are read with plain loads at the end.
 template <typename T, int kMode, int kStagesT>
 __global__ void __launch_bounds__(kThreads)
     BnStatsPipeKernel(const T* __restrict__ x, const T* __restrict__ dy,
                       const float* __restrict__ mean,
                       float* __restrict__ partial, int64_t rows, int64_t cv,
-                      int64_t channels, int64_t rows_per_cta, bool keep_in_l2) {
+                      int64_t channels, int64_t rows_per_cta, float keep_fraction,
+                      bool drop_rest) {
   constexpr int kVec = VecWidth<T>::value;
   using P = Pack<T, kVec>;
   GridDepWait();
   GridDepLaunch();
   using Cfg = StatsPipe<kMode, kStagesT>;
   constexpr int kStages = Cfg::kStages, kU = Cfg::kU, kStreams = Cfg::kStreams;
+  constexpr int kStageSlots = kStreams * kU;           // 16-byte slots per thread and stage
   extern __shared__ uint4 pipe_smem[];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
@@ -320,6 +408,23 @@ __global__ void __launch_bounds__(kThreads)
     nshift[q] = make_float2(0.0f, 0.0f);
   }
 
+  auto accumulate = [&](const uint4& rx, const uint4& rd) {
+    float2 xv[kPairs], gv[kPairs];
+    WidenPack<kVec>(*reinterpret_cast<const P*>(&rx), xv);
+    if constexpr (kMode == kGrad) WidenPack<kVec>(*reinterpret_cast<const P*>(&rd), gv);
+#pragma unroll
+    for (int q = 0; q < kPairs; ++q) {
+      const float2 d = Add2(xv[q], nshift[q]);
+      if constexpr (kMode == kFwd) {
+        a1[q] = Add2(a1[q], d);
+        a2[q] = Fma2(d, d, a2[q]);
+      } else {
+        a1[q] = Add2(a1[q], gv[q]);
+        a2[q] = Fma2(gv[q], d, a2[q]);
+      }
+    }
+  };
+
   if (active) {
     if constexpr (kMode == kFwd) {
       const P first = LoadKeep(reinterpret_cast<const P*>(x) + col);
@@ -334,74 +439,102 @@ __global__ void __launch_bounds__(kThreads)
       }
     }
     // This thread's rows: r0 + ty + j * TY, j = 0 .. n_j - 1 (32-bit counters:
-    // a CTA never owns 2^31 rows).
+    // a CTA never owns 2^31 rows), in n_full whole stages of kU rows and a
+    // remainder.
     const int n_rows = static_cast<int>(r1 - r0);
     const int n_j = n_rows > ty ? (n_rows - ty + TY - 1) / TY : 0;
-    const int n_it = (n_j + kU - 1) / kU;
-    const int64_t row_stride = static_cast<int64_t>(TY) * cv;  // packs per row step
-    const P* xi = reinterpret_cast<const P*>(x) + col + (r0 + ty) * cv;
-    const P* di = reinterpret_cast<const P*>(dy) + col + (r0 + ty) * cv;
-    uint4* const my = pipe_smem + tid;
-    int j_issue = 0;
-    // Slot (stage, stream, u) of this thread: my + index * kThreads, with a
-    // compile-time index once the stage loop below is unrolled.
+    const int n_full = n_j / kU;
+    const int64_t row_bytes = static_cast<int64_t>(TY) * cv * 16;   // one row step
+    const int64_t stage_bytes = row_bytes * kU;
+    const char* xi = reinterpret_cast<const char*>(
+        reinterpret_cast<const P*>(x) + col + (r0 + ty) * cv);
+    const char* di = reinterpret_cast<const char*>(
+        reinterpret_cast<const P*>(dy) + col + (r0 + ty) * cv);
+    const unsigned my = static_cast<unsigned>(__cvta_generic_to_shared(pipe_smem + tid));
+    constexpr unsigned kSlotBytes = kThreads * 16;                  // between a thread's slots
+    constexpr unsigned kStageBytes = kStageSlots * kSlotBytes;
+    // L2 retention for the element-wise pass that follows: the LAST
+    // keep_fraction of this thread's stages is read with the evict-last
+    // priority, everything before it with evict-first (or the default), so
+    // that what stays in L2 is chosen by this kernel (about as much as L2 can
+    // hold back) instead of whatever the replacement policy happens to keep of
+    // a tensor that is larger than the cache.
     const uint64_t keep_policy = PolicyEvictLast();
-    auto issue = [&](int stage) {
+    const uint64_t drop_policy = drop_rest ? PolicyEvictFirst() : PolicyEvictNormal();
+    const int s_keep =
+        keep_fraction >= 1.0f ? 0
+        : keep_fraction <= 0.0f
+            ? n_full + 1
+            : n_full - static_cast<int>(static_cast<float>(n_full) * keep_fraction);
+    auto issue = [&](unsigned dst, uint64_t policy) {
 #pragma unroll
       for (int u = 0; u < kU; ++u) {
-        if (j_issue + u < n_j) {
-          uint4* sx = my + ((stage * kStreams + 0) * kU + u) * kThreads;
-          uint4* sd = my + ((stage * kStreams + 1) * kU + u) * kThreads;
-          if (keep_in_l2) {
-            CpAsync16Hint(sx, xi + u * row_stride, keep_policy);
-            if constexpr (kMode == kGrad) {
-              CpAsync16Hint(sd, di + u * row_stride, keep_policy);
-            }
-          } else {
-            CpAsync16(sx, xi + u * row_stride);
-            if constexpr (kMode == kGrad) CpAsync16(sd, di + u * row_stride);
-          }
+        asm volatile(
+            "cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(
+                dst + u * kSlotBytes),
+            "l"(xi + u * row_bytes), "l"(policy)
+            : "memory");
+        if constexpr (kMode == kGrad) {
+          asm volatile(
+              "cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(
+                  dst + (kU + u) * kSlotBytes),
+              "l"(di + u * row_bytes), "l"(policy)
+              : "memory");
         }
       }
-      xi += kU * row_stride;
-      di += kU * row_stride;
-      j_issue += kU;
-      CpAsyncCommit();
+      xi += stage_bytes;
+      di += stage_bytes;
     };
+    // Prologue: kStages - 1 stages in flight (empty groups keep the count
+    // uniform when the thread has fewer).
+    int s_issue = 0;
 #pragma unroll
-    for (int st = 0; st < kStages - 1; ++st) issue(st);
-    int j_done = 0;
-    for (int it = 0; it < n_it; it += kStages) {
+    for (int st = 0; st < kStages - 1; ++st) {
+      if (s_issue < n_full) {
+        issue(my + st * kStageBytes, s_issue >= s_keep ? keep_policy : drop_policy);
+        ++s_issue;
+      }
+      CpAsyncCommit();
+    }
+    unsigned fill = (kStages - 1) * kStageBytes;   // ring offset of the next stage to fill
+    unsigned drain = 0;                            // ring offset of the next stage to read
+    for (int s = 0; s < n_full; ++s) {
+      if (s_issue < n_full) {
+        issue(my + fill, s_issue >= s_keep ? keep_policy : drop_policy);
+        ++s_issue;
+      }
+      CpAsyncCommit();
+      fill = fill + kStageBytes == kStages * kStageBytes ? 0u : fill + kStageBytes;
+      CpAsyncWait<kStages - 1>();
 #pragma unroll
-      for (int sg = 0; sg < kStages; ++sg) {
-        if (it + sg < n_it) {
-          issue((sg + kStages - 1) % kStages);
-          CpAsyncWait<kStages - 1>();
-#pragma unroll
-          for (int u = 0; u < kU; ++u) {
-            if (j_done + u < n_j) {
-              const uint4 rx = my[((sg * kStreams + 0) * kU + u) * kThreads];
-              float2 xv[kPairs], gv[kPairs];
-              WidenPack<kVec>(*reinterpret_cast<const P*>(&rx), xv);
-              if constexpr (kMode == kGrad) {
-                const uint4 rd = my[((sg * kStreams + 1) * kU + u) * kThreads];
-                WidenPack<kVec>(*reinterpret_cast<const P*>(&rd), gv);
-              }
-#pragma unroll
-              for (int q = 0; q < kPairs; ++q) {
-                const float2 d = Add2(xv[q], nshift[q]);
-                if constexpr (kMode == kFwd) {
-                  a1[q] = Add2(a1[q], d);
-                  a2[q] = Fma2(d, d, a2[q]);
-                } else {
-                  a1[q] = Add2(a1[q], gv[q]);
-                  a2[q] = Fma2(gv[q], d, a2[q]);
-                }
-              }
-            }
-          }
-          j_done += kU;
+      for (int u = 0; u < kU; ++u) {
+        uint4 rx, rd;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(rx.x), "=r"(rx.y), "=r"(rx.z), "=r"(rx.w)
+                     : "r"(my + drain + u * kSlotBytes));
+        if constexpr (kMode == kGrad) {
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(rd.x), "=r"(rd.y), "=r"(rd.z), "=r"(rd.w)
+                       : "r"(my + drain + (kU + u) * kSlotBytes));
+        } else {
+          rd = rx;
         }
+        accumulate(rx, rd);
+      }
+      drain = drain + kStageBytes == kStages * kStageBytes ? 0u : drain + kStageBytes;
+    }
+    // Remainder rows (fewer than kU): plain loads; xi / di stand at the first
+    // of them.
+    const int rem = n_j - n_full * kU;
+#pragma unroll
+    for (int u = 0; u < kU - 1; ++u) {
+      if (u < rem) {
+        const P px = LoadKeep(reinterpret_cast<const P*>(xi + u * row_bytes));
+        P pd = px;
+        if constexpr (kMode == kGrad) {
+          pd = LoadKeep(reinterpret_cast<const P*>(di + u * row_bytes));
+        }
+        accumulate(*reinterpret_cast<const uint4*>(&px), *reinterpret_cast<const uint4*>(&pd));
       }
     }
   }
@@ -680,75 +813,22 @@ __global__ void __launch_bounds__(kThreads)
 
 // ------------------------------------------------------------ level 2 ----
 
-struct FinalizeArgs {
-  const float* partial;  // [splits, 2, C] level-1 output (or NULL with sums)
-  int splits;
-  int64_t channels;
-  double count;          // values per channel behind the sums (all replicas)
-  double inv_count;      // 1 / count
-  double bessel;         // count / (count - 1), or 1 when count <= 1
-  // forward
-  const void* x_first;   // tensor base: the shift K is re-read from it
-  int x_dtype;
-  int64_t shift_stride;  // elements between consecutive channels' K
-  const float* est_mean;
-  const float* est_var;
-  float* batch_mean;
-  float* batch_var;
-  float* saved_mean;
-  float* saved_var;
-  float exp_avg_factor;
-  // gradient
-  const float* variance;
-  float* dscale;
-  float* doffset;
-  float epsilon;
-  // both: totals for the apply pass / the all-reduce
-  float* sums;           // [2, C] or NULL
-  float* count_out;      // optional: receives `count` (rides in the all-reduce)
-};
-
-__device__ __forceinline__ float LoadAsF32(const void* base, int dtype,
-                                           int64_t i) {
-  if (dtype == MUSA_DT_F32) return static_cast<const float*>(base)[i];
-  if (dtype == MUSA_DT_F16) return __half2float(static_cast<const __half*>(base)[i]);
-  return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]);
-}
-
-__device__ __forceinline__ void WriteFwdStats(const FinalizeArgs& a, int64_t c,
-                                              double mean, double var) {
-  if (var < 0.0) var = 0.0;
-  // bessel = R / (R - 1), or 1 when there is one value per channel; taken on
-  // the host (an fp64 divide per thread is not free on the device).
-  const double unbiased = var * a.bessel;
-  if (a.saved_mean) a.saved_mean[c] = static_cast<float>(mean);
-  if (a.saved_var) a.saved_var[c] = static_cast<float>(var);
-  const double f = static_cast<double>(a.exp_avg_factor);
-  double bm = mean, bv = unbiased;
-  if (a.exp_avg_factor != 1.0f && a.est_mean != nullptr &&
-      a.est_var != nullptr) {
-    bm = (1.0 - f) * static_cast<double>(a.est_mean[c]) + f * mean;
-    bv = (1.0 - f) * static_cast<double>(a.est_var[c]) + f * unbiased;
-  }
-  if (a.batch_mean) a.batch_mean[c] = static_cast<float>(bm);
-  if (a.batch_var) a.batch_var[c] = static_cast<float>(bv);
-}
-
-inline void SetCount(FinalizeArgs* f, double count) {
-  f->count = count;
-  f->inv_count = 1.0 / count;
-  f->bessel = count > 1.0 ? count / (count - 1.0) : 1.0;
-}
-
-// kOut: 0 forward statistics, 1 forward raw sums (sum x, sum x^2) for the
-// cross-replica all-reduce, 2 gradient (dscale, doffset and/or sums).
-// Block (8 channels, 128 partial lanes).
-template <int kOut>
-__global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
-  GridDepWait();
+// kOut (a TailKind): forward statistics, forward raw sums (sum x, sum x^2),
+// gradient (dscale, doffset and/or sums), or the local moments (mean,
+// sum (x - mean)^2) for the cross-replica merge.
+// Block (8 channels, kLanes partial lanes): 32 lanes make a 256-thread CTA
+// that fits beside the draining statistics CTAs, so that a programmatic
+// launch can place it before they are gone; 128 lanes is the older shape.
+template <int kOut, int kLanes>
+__global__ void __launch_bounds__(8 * kLanes) BnFinalizeKernel(FinalizeArgs a) {
+  // Dependents first: the element-wise kernel that follows may take its place
+  // on the SMs (and request its first rows of x, which do not depend on this
+  // kernel) while the statistics kernel drains.  Its own wait still covers this
+  // kernel, and this kernel's wait covers the statistics kernel.
   GridDepLaunch();
+  GridDepWait();
   const int cx = threadIdx.x;  // 0..7
-  const int py = threadIdx.y;  // 0..127
+  const int py = threadIdx.y;  // 0..kLanes-1
   const int tid = py * 8 + cx;
   const int64_t c = static_cast<int64_t>(blockIdx.x) * 8 + cx;
   // The threads that finish a channel (first 8 of the CTA) fetch the shift
@@ -759,34 +839,37 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
   }
   double t1 = 0.0, t2 = 0.0;
   if (c < a.channels) {
-    // Four independent loads per sum in flight: the loop is a chain of L2
-    // round trips otherwise.
+    // kU independent loads per sum in flight: the loop is a chain of L2 round
+    // trips otherwise.
+    constexpr int kU = 8;
     int p = py;
-    for (; p + 3 * 128 < a.splits; p += 4 * 128) {
-      float u1[4], u2[4];
+    for (; p + (kU - 1) * kLanes < a.splits; p += kU * kLanes) {
+      float u1[kU], u2[kU];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int64_t row = static_cast<int64_t>(p + q * 128) * 2;
+      for (int q = 0; q < kU; ++q) {
+        const int64_t row = static_cast<int64_t>(p + q * kLanes) * 2;
         u1[q] = a.partial[(row + 0) * a.channels + c];
         u2[q] = a.partial[(row + 1) * a.channels + c];
       }
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < kU; ++q) {
         t1 += static_cast<double>(u1[q]);
         t2 += static_cast<double>(u2[q]);
       }
     }
-    float v1[3] = {0.0f, 0.0f, 0.0f}, v2[3] = {0.0f, 0.0f, 0.0f};
+    float v1[kU - 1], v2[kU - 1];
 #pragma unroll
-    for (int q = 0; q < 3; ++q) {
-      if (p + q * 128 < a.splits) {
-        const int64_t row = static_cast<int64_t>(p + q * 128) * 2;
+    for (int q = 0; q < kU - 1; ++q) {
+      v1[q] = 0.0f;
+      v2[q] = 0.0f;
+      if (p + q * kLanes < a.splits) {
+        const int64_t row = static_cast<int64_t>(p + q * kLanes) * 2;
         v1[q] = a.partial[(row + 0) * a.channels + c];
         v2[q] = a.partial[(row + 1) * a.channels + c];
       }
     }
 #pragma unroll
-    for (int q = 0; q < 3; ++q) {
+    for (int q = 0; q < kU - 1; ++q) {
       t1 += static_cast<double>(v1[q]);
       t2 += static_cast<double>(v2[q]);
     }
@@ -796,7 +879,8 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
   t2 += __shfl_xor_sync(0xffffffffu, t2, 8);
   t1 += __shfl_xor_sync(0xffffffffu, t1, 16);
   t2 += __shfl_xor_sync(0xffffffffu, t2, 16);
-  __shared__ double red[2][32][8];
+  constexpr int kWarps = kLanes / 4;
+  __shared__ double red[2][kWarps][8];
   const int warp = tid >> 5, lane = tid & 31;
   if (lane < 8) {
     red[0][warp][lane] = t1;
@@ -810,7 +894,7 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
     const int ch = lane & 7, grp = lane >> 3;
     double S1 = 0.0, S2 = 0.0;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {
+    for (int w = 0; w < kWarps / 4; ++w) {
       S1 += red[0][grp + 4 * w][ch];
       S2 += red[1][grp + 4 * w][ch];
     }
@@ -833,6 +917,15 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
         a.sums[c] = static_cast<float>(S1 + a.count * K);
         a.sums[a.channels + c] =
             static_cast<float>(S2 + 2.0 * K * S1 + a.count * K * K);
+      } else if constexpr (kOut == kTailFwdMoments) {
+        if (a.count_out != nullptr && c == 0) {
+          *a.count_out = static_cast<float>(a.count);
+        }
+        const double md = S1 * inv_count;
+        double m2 = S2 - md * S1;
+        if (m2 < 0.0) m2 = 0.0;
+        a.sums[c] = static_cast<float>(static_cast<double>(shift_k) + md);
+        a.sums[a.channels + c] = static_cast<float>(m2);
       } else {
         if (a.sums) {
           a.sums[c] = static_cast<float>(S1);
@@ -849,15 +942,55 @@ __global__ void __launch_bounds__(1024) BnFinalizeKernel(FinalizeArgs a) {
 }
 
 // Per-channel epilogues when the sums already exist (after an all-reduce).
-__global__ void BnFinalizeFromSumsKernel(FinalizeArgs a, const float* sums) {
+// `moments`: sums = [mean, sum (x - mean)^2] instead of [sum x, sum x^2].
+__global__ void BnFinalizeFromSumsKernel(FinalizeArgs a, const float* sums,
+                                         bool moments) {
   GridDepWait();
   GridDepLaunch();
   const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (c >= a.channels) return;
-  const double mean = static_cast<double>(sums[c]) * a.inv_count;
-  const double var =
-      static_cast<double>(sums[a.channels + c]) * a.inv_count - mean * mean;
+  double mean, var;
+  if (moments) {
+    mean = static_cast<double>(sums[c]);
+    var = static_cast<double>(sums[a.channels + c]) * a.inv_count;
+  } else {
+    mean = static_cast<double>(sums[c]) * a.inv_count;
+    var = static_cast<double>(sums[a.channels + c]) * a.inv_count - mean * mean;
+  }
   WriteFwdStats(a, c, mean, var);
+}
+
+// Merge of `world` per-replica moment vectors [mean[C], M2[C], count]
+// (gathered back to back) into the moments of all rows together, in rank
+// order and fp64: N = sum n_q, mean = sum n_q mean_q / N,
+// M2 = sum M2_q + sum n_q (mean_q - mean)^2.
+__global__ void BnMergeMomentsKernel(const float* gathered, int world,
+                                     int64_t channels, float* out) {
+  GridDepWait();
+  GridDepLaunch();
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int64_t stride = 2 * channels + 1;
+  double total = 0.0;
+  for (int q = 0; q < world; ++q) {
+    total += static_cast<double>(gathered[q * stride + 2 * channels]);
+  }
+  const double inv_total = total > 0.0 ? 1.0 / total : 0.0;
+  double mean = 0.0;
+  for (int q = 0; q < world; ++q) {
+    mean += static_cast<double>(gathered[q * stride + 2 * channels]) *
+            static_cast<double>(gathered[q * stride + c]);
+  }
+  mean *= inv_total;
+  double m2 = 0.0;
+  for (int q = 0; q < world; ++q) {
+    const double d = static_cast<double>(gathered[q * stride + c]) - mean;
+    m2 += static_cast<double>(gathered[q * stride + channels + c]) +
+          static_cast<double>(gathered[q * stride + 2 * channels]) * d * d;
+  }
+  out[c] = static_cast<float>(mean);
+  out[channels + c] = static_cast<float>(m2);
+  if (c == 0) out[2 * channels] = static_cast<float>(total);
 }
 
 __global__ void BnGradScalesFromSumsKernel(const float* sums,
@@ -902,6 +1035,7 @@ struct ApplyArgs {
   // derived from [sum x, sum x^2] over `count` values in the kernel prologue
   // and the first row of CTAs writes the four statistic outputs.
   const float* stat_sums;
+  bool stat_moments;      // stat_sums = [mean, sum (x - mean)^2] (merged moments)
   double count;
   FinalizeArgs stat_out;  // est_*, batch_*, saved_*, exp_avg_factor
   // Gradient: the first row of CTAs writes dscale / doffset when set.
@@ -914,19 +1048,60 @@ __global__ void __launch_bounds__(kThreads)
     BnApplyLastKernel(const T* __restrict__ x, const T* __restrict__ dy,
                       T* __restrict__ out, ApplyArgs a, int64_t rows,
                       int64_t cv, int64_t channels, int64_t rows_per_cta,
-                      bool reverse, bool last_use) {
+                      bool reverse, bool last_use, bool early_loads) {
   using P = Pack<T, kVec>;
-  GridDepWait();
-  GridDepLaunch();
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
   const int64_t col = static_cast<int64_t>(blockIdx.x) * TX + tx;
-  if (col >= cv) return;
   const int64_t chunk =
       reverse ? (gridDim.y - 1 - blockIdx.y) : blockIdx.y;
   const int64_t r0 = chunk * rows_per_cta;
   int64_t r1 = r0 + rows_per_cta;
   if (r1 > rows) r1 = rows;
+  const P* xp = reinterpret_cast<const P*>(x) + col;
+  const P* dp = reinterpret_cast<const P*>(dy) + col;
+  const int64_t n_rows = r1 - r0;
+  const int64_t step = static_cast<int64_t>(TY) * kUnroll;
+  const uint64_t drop_policy = PolicyEvictFirst();
+  P px[kUnroll];
+  P pd[kUnroll];
+  int64_t off[kUnroll];
+  // Loads of one batch of rows (local row l and the kUnroll - 1 after it).
+  auto load_batch = [&](int64_t l) {
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t li = l + static_cast<int64_t>(u) * TY;
+      const bool ok = li < n_rows;
+      const int64_t r = reverse ? (r1 - 1 - li) : (r0 + li);
+      off[u] = ok ? r * cv : -1;
+      if (ok) {
+        if constexpr (sizeof(P) == 16) {
+          if (last_use) {
+            px[u] = LoadHint16(xp + off[u], drop_policy);
+            if constexpr (kMode == kGrad) pd[u] = LoadHint16(dp + off[u], drop_policy);
+          } else {
+            px[u] = LoadKeep(xp + off[u]);
+            if constexpr (kMode == kGrad) pd[u] = LoadKeep(dp + off[u]);
+          }
+        } else {
+          px[u] = LoadKeep(xp + off[u]);
+          if constexpr (kMode == kGrad) pd[u] = LoadKeep(dp + off[u]);
+        }
+      }
+    }
+  };
+  // `early_loads`: x and dy are inputs of the whole op, final before the
+  // statistics kernel of the same launcher call started, and only the
+  // per-channel statistics come from the kernel this one depends on.  The
+  // first batch of rows is then requested BEFORE the wait for that kernel, so
+  // its latency (and the tail of the reduction) is hidden behind it.  A
+  // stand-alone element-wise launch cannot know who produced x and waits
+  // first.
+  const bool active = col < cv;
+  if (early_loads && active) load_batch(ty);
+  GridDepWait();
+  GridDepLaunch();
+  if (!active) return;
 
   // 16-bit outputs round to 8 or 11 bits, so the per-channel affine forms are
   // folded to two (forward) or three (gradient) coefficients and one or two
@@ -939,9 +1114,14 @@ __global__ void __launch_bounds__(kThreads)
     const int64_t c = col * kVec + e;
     float var_c;
     if (kMode == kFwd && a.stat_sums != nullptr) {
-      const double m = static_cast<double>(a.stat_sums[c]) * a.stat_out.inv_count;
-      double v =
-          static_cast<double>(a.stat_sums[channels + c]) * a.stat_out.inv_count - m * m;
+      double m, v;
+      if (a.stat_moments) {
+        m = static_cast<double>(a.stat_sums[c]);
+        v = static_cast<double>(a.stat_sums[channels + c]) * a.stat_out.inv_count;
+      } else {
+        m = static_cast<double>(a.stat_sums[c]) * a.stat_out.inv_count;
+        v = static_cast<double>(a.stat_sums[channels + c]) * a.stat_out.inv_count - m * m;
+      }
       if (v < 0.0) v = 0.0;
       mean[e] = static_cast<float>(m);
       var_c = static_cast<float>(v);
@@ -982,39 +1162,11 @@ __global__ void __launch_bounds__(kThreads)
     }
   }
 
-  const P* xp = reinterpret_cast<const P*>(x) + col;
-  const P* dp = reinterpret_cast<const P*>(dy) + col;
   P* op = reinterpret_cast<P*>(out) + col;
-  const int64_t n_rows = r1 - r0;
   // Row lane ty visits local rows ty, ty + TY, ...; in reverse mode the local
   // index is mirrored.
-  const int64_t step = static_cast<int64_t>(TY) * kUnroll;
-  const uint64_t drop_policy = PolicyEvictFirst();
   for (int64_t l = ty; l < n_rows; l += step) {
-    P px[kUnroll];
-    P pd[kUnroll];
-    int64_t off[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t li = l + static_cast<int64_t>(u) * TY;
-      const bool ok = li < n_rows;
-      const int64_t r = reverse ? (r1 - 1 - li) : (r0 + li);
-      off[u] = ok ? r * cv : -1;
-      if (ok) {
-        if constexpr (sizeof(P) == 16) {
-          if (last_use) {
-            px[u] = LoadHint16(xp + off[u], drop_policy);
-            if constexpr (kMode == kGrad) pd[u] = LoadHint16(dp + off[u], drop_policy);
-          } else {
-            px[u] = LoadKeep(xp + off[u]);
-            if constexpr (kMode == kGrad) pd[u] = LoadKeep(dp + off[u]);
-          }
-        } else {
-          px[u] = LoadKeep(xp + off[u]);
-          if constexpr (kMode == kGrad) pd[u] = LoadKeep(dp + off[u]);
-        }
-      }
-    }
+    if (!(early_loads && l == ty)) load_batch(l);
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (off[u] >= 0) {
@@ -1237,387 +1389,6 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
-// ------------------------------------------------- fused (one launch) -----
-//
-// The whole op in ONE cooperative launch: statistics, grid-wide reduction and
-// element-wise pass, with the tail of every CTA's row range kept in shared
-// memory between the two passes.
-//
-//   A  every thread streams its rows through a ring of kRing row slots per
-//      input stream (cp.async, kAhead batches in flight) and accumulates the
-//      two sums; when the stream ends, the last kRing rows of the thread are
-//      still in the ring;
-//   B  the CTA folds its row lanes and writes one partial row [2, C];
-//   -- grid barrier --
-//   C  CTA b reduces channels b, b + G, ... over all partial rows (fp64) and
-//      writes the statistics outputs / totals;
-//   -- grid barrier --
-//   D  every thread takes the coefficients of its channels;
-//   E  element-wise pass: first the rows still in the ring (no global read),
-//      then the remaining rows newest-first from L2 / HBM.
-// Against the three-kernel chain this saves two kernel boundaries and the
-// finalize launch, and the re-read of up to 16 rows * 16 B * resident threads
-// per SM (about 29 MB over the GPU): everything for the small layers.
-//
-// MEASURED (B200, bf16): it is slower than the programmatically chained three
-// kernels at every size - 38.9 vs 25.5 us forward at S = 25.7 MB, 79.9 vs 57.4
-// at 102.8 MB, 235 vs 213 at 411 MB - a fixed 13-25 us that the cooperative
-// launch (no overlap with the previous kernel's tail, plus the counter memset)
-// and the two grid barriers cost.  It is therefore OFF by default
-// (MusaKernelsSetTuning(5, 1) turns it on) and kept, tested, as the starting
-// point for a version with a cheaper barrier.
-//
-// The grid barrier is a counter in the workspace (zeroed by the launcher),
-// entered once per phase; the cooperative launch guarantees that all CTAs are
-// resident, and every wait is bounded all the same: when a wait runs out the
-// CTA sets the status word and returns.
-constexpr long long kBarrierSpinLimit = 1LL << 24;
-
-__device__ __forceinline__ bool GridBarrier(unsigned* counter, unsigned target,
-                                            int* status) {
-  __shared__ int s_ok;
-  __syncthreads();
-  if (threadIdx.x == 0 && threadIdx.y == 0) {
-    __threadfence();
-    atomicAdd(counter, 1u);
-    long long polls = 0;
-    int ok = 1;
-    while (true) {
-      unsigned seen;
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter));
-      if (seen >= target) break;
-      if (++polls > kBarrierSpinLimit) {
-        atomicCAS(status, 0, 1);
-        ok = 0;
-        break;
-      }
-      __nanosleep(32);
-    }
-    s_ok = ok;
-    __threadfence();
-  }
-  __syncthreads();
-  return s_ok != 0;
-}
-
-struct FusedArgs {
-  const void* x;
-  const void* dy;
-  void* out;
-  int64_t rows;
-  int64_t cv;
-  int64_t channels;
-  int64_t rows_per_cta;
-  float* partial;     // [gridDim.y, 2, C]
-  unsigned* barrier;  // zeroed before the launch
-  int* status;
-  FinalizeArgs fin;
-  ApplyArgs app;
-  bool is_training;   // gradient: inference mode skips the batch terms
-};
-
-template <int kMode>
-struct FusedCfg {
-  static constexpr int kStreams = kMode == 0 ? 1 : 2;
-  static constexpr int kU = kMode == 0 ? 4 : 2;   // rows per batch and stream
-  static constexpr int kRingBatches = 4;
-  static constexpr int kAhead = 3;                // batches in flight
-  static constexpr int kRingBytes = kRingBatches * kStreams * kU * kThreads * 16;
-  static constexpr int kScratchBytes = 8 * kThreads * 4;  // fold scratch
-  static constexpr int kSmemBytes = kRingBytes + kScratchBytes;
-};
-
-template <typename T, int kMode>
-__global__ void __launch_bounds__(kThreads) BnFusedKernel(FusedArgs a) {
-  constexpr int kVec = VecWidth<T>::value;
-  constexpr int kPairs = kVec / 2;
-  using P = Pack<T, kVec>;
-  using Cfg = FusedCfg<kMode>;
-  constexpr int kU = Cfg::kU, kStreams = Cfg::kStreams, kRB = Cfg::kRingBatches,
-                kAhead = Cfg::kAhead;
-  extern __shared__ uint4 fused_smem[];
-  float* scratch = reinterpret_cast<float*>(
-      reinterpret_cast<char*>(fused_smem) + Cfg::kRingBytes);
-
-  const int tx = threadIdx.x, ty = threadIdx.y;
-  const int TX = blockDim.x, TY = blockDim.y;
-  const int tid = ty * TX + tx;
-  const int64_t col = tx;  // one column block: cv <= TX
-  const bool active = col < a.cv;
-  const int64_t cv = a.cv, channels = a.channels;
-  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * a.rows_per_cta;
-  int64_t r1 = r0 + a.rows_per_cta;
-  if (r1 > a.rows) r1 = a.rows;
-  const int n_rows = r1 > r0 ? static_cast<int>(r1 - r0) : 0;
-  const int n_j = n_rows > ty ? (n_rows - ty + TY - 1) / TY : 0;
-  const int n_b = (n_j + kU - 1) / kU;
-  const int64_t row_stride = static_cast<int64_t>(TY) * cv;
-  const P* xbase = static_cast<const P*>(a.x) + col + (r0 + ty) * cv;
-  const P* dbase = static_cast<const P*>(a.dy) + col + (r0 + ty) * cv;
-  P* obase = static_cast<P*>(a.out) + col + (r0 + ty) * cv;
-  uint4* const my = fused_smem + tid;
-
-  // ---- A: statistics over the thread's rows, ring-staged.
-  float2 nshift[kPairs], a1[kPairs], a2[kPairs];
-#pragma unroll
-  for (int q = 0; q < kPairs; ++q) {
-    a1[q] = make_float2(0.0f, 0.0f);
-    a2[q] = make_float2(0.0f, 0.0f);
-    nshift[q] = make_float2(0.0f, 0.0f);
-  }
-  if (active) {
-    if constexpr (kMode == kFwd) {
-      const P first = LoadKeep(static_cast<const P*>(a.x) + col);
-      WidenPack<kVec>(first, nshift);
-#pragma unroll
-      for (int q = 0; q < kPairs; ++q) nshift[q] = Neg2(nshift[q]);
-    } else {
-#pragma unroll
-      for (int q = 0; q < kPairs; ++q) {
-        nshift[q] = make_float2(-a.app.mean[col * kVec + 2 * q],
-                                -a.app.mean[col * kVec + 2 * q + 1]);
-      }
-    }
-    const P* xi = xbase;
-    const P* di = dbase;
-    int j_issue = 0;
-    auto issue = [&](int ring_batch) {
-#pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        if (j_issue + u < n_j) {
-          CpAsync16(my + ((ring_batch * kStreams + 0) * kU + u) * kThreads,
-                    xi + u * row_stride);
-          if constexpr (kMode == kGrad) {
-            CpAsync16(my + ((ring_batch * kStreams + 1) * kU + u) * kThreads,
-                      di + u * row_stride);
-          }
-        }
-      }
-      xi += kU * row_stride;
-      di += kU * row_stride;
-      j_issue += kU;
-      CpAsyncCommit();
-    };
-#pragma unroll
-    for (int b = 0; b < kAhead; ++b) issue(b);
-    int j_done = 0;
-    for (int bi = 0; bi < n_b; bi += kRB) {
-#pragma unroll
-      for (int sg = 0; sg < kRB; ++sg) {
-        if (bi + sg < n_b) {
-          issue((sg + kAhead) % kRB);
-          CpAsyncWait<kAhead>();
-#pragma unroll
-          for (int u = 0; u < kU; ++u) {
-            if (j_done + u < n_j) {
-              const uint4 rx = my[((sg * kStreams + 0) * kU + u) * kThreads];
-              float2 xv[kPairs], gv[kPairs];
-              WidenPack<kVec>(*reinterpret_cast<const P*>(&rx), xv);
-              if constexpr (kMode == kGrad) {
-                const uint4 rd = my[((sg * kStreams + 1) * kU + u) * kThreads];
-                WidenPack<kVec>(*reinterpret_cast<const P*>(&rd), gv);
-              }
-#pragma unroll
-              for (int q = 0; q < kPairs; ++q) {
-                const float2 d = Add2(xv[q], nshift[q]);
-                if constexpr (kMode == kFwd) {
-                  a1[q] = Add2(a1[q], d);
-                  a2[q] = Fma2(d, d, a2[q]);
-                } else {
-                  a1[q] = Add2(a1[q], gv[q]);
-                  a2[q] = Fma2(gv[q], d, a2[q]);
-                }
-              }
-            }
-          }
-          j_done += kU;
-        }
-      }
-    }
-  }
-  CpAsyncWait<0>();
-
-  // ---- B: fold the row lanes, one sum at a time (8 KB of scratch).
-#pragma unroll
-  for (int which = 0; which < 2; ++which) {
-    __syncthreads();
-#pragma unroll
-    for (int q = 0; q < kPairs; ++q) {
-      const float2 v = which == 0 ? a1[q] : a2[q];
-      scratch[((2 * q) * TY + ty) * TX + tx] = v.x;
-      scratch[((2 * q + 1) * TY + ty) * TX + tx] = v.y;
-    }
-    __syncthreads();
-    for (int o = tid; o < kVec * TX; o += kThreads) {
-      const int otx = o % TX, e = o / TX;
-      float acc = 0.0f;
-      for (int j = 0; j < TY; ++j) acc += scratch[(e * TY + j) * TX + otx];
-      if (otx < cv) {
-        a.partial[(static_cast<int64_t>(blockIdx.y) * 2 + which) * channels +
-                  static_cast<int64_t>(otx) * kVec + e] = acc;
-      }
-    }
-  }
-
-  const unsigned G = gridDim.y;
-  if (!GridBarrier(a.barrier, G, a.status)) return;
-
-  // ---- C: CTA b owns channels b, b + G, ...: all partial rows, fp64.
-  {
-    double* red = reinterpret_cast<double*>(scratch);  // [2][8 warps]
-    for (int64_t c = blockIdx.y; c < channels; c += G) {
-      double t1 = 0.0, t2 = 0.0;
-      for (unsigned p = tid; p < G; p += kThreads) {
-        t1 += static_cast<double>(__ldcg(a.partial + (static_cast<int64_t>(p) * 2 + 0) * channels + c));
-        t2 += static_cast<double>(__ldcg(a.partial + (static_cast<int64_t>(p) * 2 + 1) * channels + c));
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        t1 += __shfl_xor_sync(0xffffffffu, t1, o);
-        t2 += __shfl_xor_sync(0xffffffffu, t2, o);
-      }
-      __syncthreads();
-      if ((tid & 31) == 0) {
-        red[tid >> 5] = t1;
-        red[8 + (tid >> 5)] = t2;
-      }
-      __syncthreads();
-      if (tid == 0) {
-        double S1 = 0.0, S2 = 0.0;
-#pragma unroll
-        for (int w = 0; w < kThreads / 32; ++w) {
-          S1 += red[w];
-          S2 += red[8 + w];
-        }
-        if constexpr (kMode == kFwd) {
-          const double K = static_cast<double>(
-              LoadAsF32(a.fin.x_first, a.fin.x_dtype, c * a.fin.shift_stride));
-          const double md = S1 * a.fin.inv_count;
-          WriteFwdStats(a.fin, c, K + md, S2 * a.fin.inv_count - md * md);
-        } else {
-          a.fin.sums[c] = static_cast<float>(S1);
-          a.fin.sums[channels + c] = static_cast<float>(S2);
-          a.fin.doffset[c] = static_cast<float>(S1);
-          const float inv = 1.0f / sqrtf(a.fin.variance[c] + a.fin.epsilon);
-          a.fin.dscale[c] = static_cast<float>(S2) * inv;
-        }
-      }
-    }
-  }
-
-  if (!GridBarrier(a.barrier, 2 * G, a.status)) return;
-  if (!active) return;
-
-  // ---- D: per-channel coefficients (values written by other CTAs during this
-  // launch are read past L1).
-  float mean[kVec], ca[kVec], cb[kVec], cc[kVec];
-  constexpr bool kFold = sizeof(T) == 2;
-#pragma unroll
-  for (int e = 0; e < kVec; ++e) {
-    const int64_t c = col * kVec + e;
-    float var_c;
-    if constexpr (kMode == kFwd) {
-      mean[e] = __ldcg(a.fin.saved_mean + c);
-      var_c = __ldcg(a.fin.saved_var + c);
-    } else {
-      mean[e] = a.app.mean[c];
-      var_c = a.app.variance[c];
-    }
-    const float inv = 1.0f / sqrtf(var_c + a.app.epsilon);
-    ca[e] = a.app.scale[c] * inv;
-    if constexpr (kMode == kFwd) {
-      cb[e] = a.app.offset[c];
-      cc[e] = 0.0f;
-    } else if (a.is_training) {
-      cb[e] = __ldcg(a.fin.sums + c) * a.app.inv_count;
-      cc[e] = __ldcg(a.fin.sums + channels + c) * inv * inv * a.app.inv_count;
-    } else {
-      cb[e] = 0.0f;
-      cc[e] = 0.0f;
-    }
-    if constexpr (kFold) {
-      if constexpr (kMode == kFwd) {
-        cb[e] = fmaf(-mean[e], ca[e], cb[e]);
-      } else {
-        const float fb = -ca[e] * cc[e];
-        const float fc = ca[e] * fmaf(cc[e], mean[e], -cb[e]);
-        cb[e] = fb;
-        cc[e] = fc;
-      }
-    }
-  }
-  auto transform = [&](const P& px, const P& pd) -> P {
-    float2 xv[kPairs], gv[kPairs], rv[kPairs];
-    WidenPack<kVec>(px, xv);
-    if constexpr (kMode == kGrad) WidenPack<kVec>(pd, gv);
-#pragma unroll
-    for (int q = 0; q < kPairs; ++q) {
-      const float2 A = make_float2(ca[2 * q], ca[2 * q + 1]);
-      const float2 B = make_float2(cb[2 * q], cb[2 * q + 1]);
-      const float2 C = make_float2(cc[2 * q], cc[2 * q + 1]);
-      if constexpr (kFold) {
-        if constexpr (kMode == kFwd) {
-          rv[q] = Fma2(xv[q], A, B);
-        } else {
-          rv[q] = Fma2(gv[q], A, Fma2(xv[q], B, C));
-        }
-      } else {
-        const float2 d = Add2(xv[q], make_float2(-mean[2 * q], -mean[2 * q + 1]));
-        if constexpr (kMode == kFwd) {
-          rv[q] = Fma2(d, A, B);
-        } else {
-          rv[q] = Mul2(A, Fma2(Neg2(d), C, Add2(gv[q], Neg2(B))));
-        }
-      }
-    }
-    P o;
-    NarrowPack<kVec>(rv, o);
-    return o;
-  };
-
-  // ---- E1: the rows still in the ring (batch bi sits in ring slot bi % kRB).
-  const int first_resident_b = n_b > kRB ? n_b - kRB : 0;
-  for (int bi = n_b - 1; bi >= first_resident_b; --bi) {
-    const int rb = bi % kRB;
-#pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const int j = bi * kU + u;
-      if (j < n_j) {
-        const uint4 rx = my[((rb * kStreams + 0) * kU + u) * kThreads];
-        uint4 rd = rx;
-        if constexpr (kMode == kGrad) rd = my[((rb * kStreams + 1) * kU + u) * kThreads];
-        const P o = transform(*reinterpret_cast<const P*>(&rx),
-                              *reinterpret_cast<const P*>(&rd));
-        StoreStream(obase + static_cast<int64_t>(j) * row_stride, o);
-      }
-    }
-  }
-  // ---- E2: the older rows, newest first, four loads per stream in flight.
-  constexpr int kUnroll = 4;
-  for (int j0 = first_resident_b * kU - 1; j0 >= 0; j0 -= kUnroll) {
-    P px[kUnroll], pd[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int j = j0 - u;
-      if (j >= 0) {
-        px[u] = LoadKeep(xbase + static_cast<int64_t>(j) * row_stride);
-        if constexpr (kMode == kGrad) {
-          pd[u] = LoadKeep(dbase + static_cast<int64_t>(j) * row_stride);
-        } else {
-          pd[u] = px[u];
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int j = j0 - u;
-      if (j >= 0) {
-        StoreStream(obase + static_cast<int64_t>(j) * row_stride, transform(px[u], pd[u]));
-      }
-    }
-  }
-}
-
 // ------------------------------------------------------------ host side --
 
 template <typename T>
@@ -1650,117 +1421,67 @@ inline bool IsEmpty(const Geom& g) {
 }
 
 // Workspace layout: [partial rows: MaxSplits * 2 * C floats][totals: 2 * C
-// floats][control block: grid-barrier counter, status word; 256 bytes].
-constexpr size_t kControlBytes = 256;
-
-inline int64_t ControlOffsetFloats(const Geom& g) {
-  const int64_t floats =
-      MaxSplits(g.outer, g.channels) * 2 * g.channels + 2 * g.channels;
-  return (floats + 63) / 64 * 64;  // 256-byte aligned
-}
-
+// floats], rounded up to 256 bytes.
 inline size_t WorkspaceBytes(const Geom& g) {
   if (IsEmpty(g)) return 0;
-  return static_cast<size_t>(ControlOffsetFloats(g)) * sizeof(float) + kControlBytes;
+  const int64_t floats =
+      MaxSplits(g.outer, g.channels) * 2 * g.channels + 2 * g.channels;
+  return static_cast<size_t>((floats + 63) / 64 * 64) * sizeof(float);
 }
 
-// The whole op in one cooperative launch, when the geometry allows it:
-// channels-last, 128-bit packs, one column block.  Returns false when the
-// caller should take the three-kernel chain instead.
-template <typename T, int kMode>
-bool LaunchFused(const T* x, const T* dy, T* out, const FinalizeArgs& fin,
-                 const ApplyArgs& app, bool is_training, float* workspace,
-                 const Geom& g, cudaStream_t stream) {
-  constexpr int kVec = VecWidth<T>::value;
-  using Cfg = FusedCfg<kMode>;
-  if (GetTuning(kTuneBnFused) == 0 || g.inner != 1 || g.channels % kVec != 0) {
-    return false;
-  }
-  const int64_t cv = g.channels / kVec;
-  if (cv > kThreads) return false;
-  if (!Aligned16(x) || !Aligned16(out) || (kMode == kGrad && !Aligned16(dy))) {
-    return false;
-  }
-  auto kernel = BnFusedKernel<T, kMode>;
-  static const int resident = [&] {
-    int dev = 0, coop = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
-    if (coop == 0) return 0;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::kSmemBytes) != cudaSuccess) {
-      cudaGetLastError();
-      return 0;
-    }
-    int n = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, Cfg::kSmemBytes);
-    return n;
-  }();
-  if (resident <= 0) return false;
-  const Plan p = PlanLast(g.outer, g.channels, cv, Cfg::kU, true, resident);
-  if (p.gx != 1 || p.gy > SmCount() * resident) return false;
-  FusedArgs a{};
-  a.x = x;
-  a.dy = dy;
-  a.out = out;
-  a.rows = g.outer;
-  a.cv = cv;
-  a.channels = g.channels;
-  a.rows_per_cta = p.rows_per_cta;
-  a.partial = workspace;
-  char* control = reinterpret_cast<char*>(workspace + ControlOffsetFloats(g));
-  a.barrier = reinterpret_cast<unsigned*>(control);
-  a.status = reinterpret_cast<int*>(control + 64);
-  a.fin = fin;
-  a.app = app;
-  a.is_training = is_training;
-  // Counter and status word start every launch at zero (the workspace arrives
-  // with arbitrary contents); BnWorkspaceStatus reports on the latest
-  // single-launch op that used this workspace.
-  if (cudaMemsetAsync(control, 0, 128, stream) != cudaSuccess) {
-    cudaGetLastError();
-    return false;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(1, p.gy);
-  cfg.blockDim = dim3(p.tx, p.ty);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, a) != cudaSuccess) {
-    cudaGetLastError();
-    return false;  // e.g. the grid does not fit beside other resident work
-  }
-  return true;
-}
+// Launch errors travel as -(1000 + cudaError_t) beside the negative
+// MUSA_KERNELS_E* codes and come back out as the positive cudaError_t.
+inline int EncodeCuda(cudaError_t e) { return -(1000 + static_cast<int>(e)); }
+inline int DecodeError(int rc) { return rc <= -1000 ? -rc - 1000 : rc; }
 
+// Pipelined channels-last statistics.  Returns the number of partial rows
+// written, or a negative error.
 template <typename T, int kMode, int kStagesT>
-int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* partial,
+int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* workspace,
                     const Geom& g, int64_t cv, cudaStream_t stream) {
   using Cfg = StatsPipe<kMode, kStagesT>;
   auto kernel = BnStatsPipeKernel<T, kMode, kStagesT>;
-  static const int resident = [&] {
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         Cfg::kSmemBytes);
+  static std::atomic<int> resident_by_device[kMaxDevices];
+  const int resident = PerDevice(resident_by_device, [&] {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
     int n = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads,
-                                                  Cfg::kSmemBytes);
-    return n > 0 ? n : 1;
-  }();
-  const Plan p = PlanLast(g.outer, g.channels, cv, Cfg::kU, true, resident);
-  // Ask L2 to hold on to what this pass reads when the element-wise pass that
-  // follows can find it there: all streams together within the budget.
-  const int64_t bytes = g.outer * g.channels * static_cast<int64_t>(sizeof(T)) *
-                        (kMode == kFwd ? 1 : 2);
-  const int64_t budget = static_cast<int64_t>(GetTuning(kTuneBnL2KeepMb)) << 20;
-  const bool keep_in_l2 = bytes <= budget;
-  LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
-                dim3(p.tx, p.ty), Cfg::kSmemBytes, stream, x, dy, mean, partial,
-                g.outer, cv, g.channels, p.rows_per_cta, keep_in_l2);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads,
+                                                      Cfg::kSmemBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    return n > 0 ? n : -1;
+  });
+  if (resident < 0) return EncodeCuda(cudaErrorInvalidValue);
+  // Column blocks of at most 32 packs (512-byte row segments, one warp wide):
+  // measured 1.5-3 % faster over the ResNet-50 step than blocks as wide as the
+  // row, which leave one row lane per CTA for the wide layers.
+  int max_tx = GetTuning(kTuneBnStatsMaxTx);
+  if (max_tx <= 0) max_tx = kThreads;
+  const Plan p = PlanLast(g.outer, g.channels, cv, Cfg::kU, true, resident, max_tx);
+  // What the element-wise pass that follows can find in L2: the budget over
+  // the bytes this pass reads (all streams), as the fraction of every
+  // thread's rows that is read with the evict-last priority.
+  const double bytes = static_cast<double>(g.outer) * static_cast<double>(g.channels) *
+                       sizeof(T) * (kMode == kFwd ? 1 : 2);
+  const double budget = static_cast<double>(GetTuning(kTuneBnL2KeepMb)) * 1048576.0;
+  float keep_fraction = 0.0f;
+  if (budget > 0.0) {
+    keep_fraction = budget >= bytes ? 1.0f : static_cast<float>(budget / bytes);
+    if (GetTuning(kTuneBnL2KeepPartial) == 0 && keep_fraction < 1.0f) keep_fraction = 0.0f;
+  }
+  const cudaError_t err = LaunchChained(
+      GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy), dim3(p.tx, p.ty),
+      Cfg::kSmemBytes, stream, x, dy, mean, workspace, g.outer, cv, g.channels,
+      p.rows_per_cta, keep_fraction, GetTuning(kTuneBnStatsDropRest) != 0);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return EncodeCuda(err);
+  }
   return p.gy;
 }
 
@@ -1830,7 +1551,8 @@ inline GroupPlan PlanGroups(const Geom& g) {
   return p;
 }
 
-// Stats launch: fills partial[splits][2][C]; returns splits (<0: error).
+// Stats launch: fills partial[splits][2][C]; returns splits or a negative
+// error.
 template <typename T, int kMode>
 int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
                 const Geom& g, cudaStream_t stream) {
@@ -1896,16 +1618,53 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
   return static_cast<int>(pp.gy);
 }
 
-template <int kOut>
-void LaunchFinalize(const FinalizeArgs& a, cudaStream_t stream) {
+template <int kLanes>
+void LaunchFinalizeAs(int kind, const FinalizeArgs& a, cudaStream_t stream) {
   const int grid = static_cast<int>(CeilDiv(a.channels, 8));
-  LaunchChained(GetTuning(kTuneBnPdl) != 0, BnFinalizeKernel<kOut>, dim3(grid),
-                dim3(8, 128), 0, stream, a);
+  const bool pdl = GetTuning(kTuneBnPdl) != 0;
+  const dim3 block(8, kLanes);
+  switch (kind) {
+    case kTailFwdStats:
+      LaunchChained(pdl, BnFinalizeKernel<kTailFwdStats, kLanes>, dim3(grid), block, 0, stream, a);
+      break;
+    case kTailFwdSums:
+      LaunchChained(pdl, BnFinalizeKernel<kTailFwdSums, kLanes>, dim3(grid), block, 0, stream, a);
+      break;
+    case kTailFwdMoments:
+      LaunchChained(pdl, BnFinalizeKernel<kTailFwdMoments, kLanes>, dim3(grid), block, 0, stream,
+                    a);
+      break;
+    default:
+      LaunchChained(pdl, BnFinalizeKernel<kTailGrad, kLanes>, dim3(grid), block, 0, stream, a);
+  }
 }
 
+void LaunchFinalize(int kind, const FinalizeArgs& a, cudaStream_t stream) {
+  if (GetTuning(kTuneBnFinalizeLanes) == 128) {
+    LaunchFinalizeAs<128>(kind, a, stream);
+  } else {
+    LaunchFinalizeAs<32>(kind, a, stream);
+  }
+}
+
+// Both levels of the reduction: the statistics kernel, then the finalize
+// kernel.  `f.partial` / `f.splits` are filled in here.  0 or an error code.
+template <typename T, int kMode>
+int RunStats(const T* x, const T* dy, const float* mean, float* workspace,
+             const Geom& g, FinalizeArgs f, int kind, cudaStream_t stream) {
+  f.partial = workspace;
+  const int splits = LaunchStats<T, kMode>(x, dy, mean, workspace, g, stream);
+  if (splits < 0) return DecodeError(splits);
+  f.splits = splits;
+  LaunchFinalize(kind, f, stream);
+  return MUSA_KERNELS_OK;
+}
+
+// `early_loads`: the caller launched the statistics kernel of the same op on
+// `stream` just before (see BnApplyLastKernel).
 template <typename T, int kMode>
 void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
-                 const Geom& g, cudaStream_t stream) {
+                 const Geom& g, cudaStream_t stream, bool early_loads = false) {
   constexpr int kVec = VecWidth<T>::value;
   constexpr int kUnroll = 4;
   const bool reverse = GetTuning(kTuneBnApplyReverse) != 0;
@@ -1915,6 +1674,7 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
                            static_cast<int64_t>(sizeof(T)) *
                            (kMode == kFwd ? 1 : 2);
   const bool last_use =
+      GetTuning(kTuneBnApplyDropAll) != 0 ||
       in_bytes <= (static_cast<int64_t>(GetTuning(kTuneBnL2KeepMb)) << 21);
   const bool aligned =
       Aligned16(x) && Aligned16(out) && (kMode == kFwd || Aligned16(dy));
@@ -1926,27 +1686,37 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
       if (deep) {
         constexpr int kDeep = kMode == kFwd ? 8 : kUnroll;
         auto kernel = BnApplyLastKernel<T, kVec, kDeep, kMode>;
-        static const int resident = [&] {
+        static std::atomic<int> resident_by_device[kMaxDevices];
+        const int resident = PerDevice(resident_by_device, [&] {
           int n = 0;
-          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0);
+          if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0) !=
+              cudaSuccess) {
+            cudaGetLastError();
+          }
           return n > 0 ? n : 1;
-        }();
+        });
         const Plan p = PlanLast(g.outer, g.channels, cv, kDeep, false, resident);
         LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
                       dim3(p.tx, p.ty), 0, stream, x, dy, out, a, g.outer, cv,
-                      g.channels, p.rows_per_cta, reverse, last_use);
+                      g.channels, p.rows_per_cta, reverse, last_use,
+                      early_loads && GetTuning(kTuneBnApplyEarlyLoads) != 0);
       } else {
         auto kernel = BnApplyLastKernel<T, kVec, kUnroll, kMode>;
-        static const int resident = [&] {
+        static std::atomic<int> resident_by_device[kMaxDevices];
+        const int resident = PerDevice(resident_by_device, [&] {
           int n = 0;
-          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0);
+          if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0) !=
+              cudaSuccess) {
+            cudaGetLastError();
+          }
           return n > 0 ? n : 1;
-        }();
+        });
         const Plan p =
             PlanLast(g.outer, g.channels, cv, kUnroll, false, resident);
         LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
                       dim3(p.tx, p.ty), 0, stream, x, dy, out, a, g.outer, cv,
-                      g.channels, p.rows_per_cta, reverse, last_use);
+                      g.channels, p.rows_per_cta, reverse, last_use,
+                      early_loads && GetTuning(kTuneBnApplyEarlyLoads) != 0);
       }
     } else {
       const Plan p =
@@ -1954,7 +1724,7 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
       BnApplyLastKernel<T, 1, kUnroll, kMode>
           <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
               x, dy, out, a, g.outer, g.channels, g.channels, p.rows_per_cta,
-              reverse, false);
+              reverse, false, false);
     }
     return;
   }
@@ -2002,6 +1772,7 @@ int FwdTrain(const void* x, const float* scale, const float* offset,
              size_t workspace_bytes, cudaStream_t stream) {
   const Geom g{outer, channels, inner};
   if (int rc = CheckGeom(g)) return rc;
+  MUSA_TRACE("LaunchBnFwdTrain", 2 * sizeof(T) * outer * channels * inner);
   if (IsEmpty(g)) return MUSA_KERNELS_OK;
   if (!x || !y || !scale || !offset || !saved_mean || !saved_var) {
     return MUSA_KERNELS_EINVAL;
@@ -2035,15 +1806,11 @@ int FwdTrain(const void* x, const float* scale, const float* offset,
   a.mean = saved_mean;
   a.variance = saved_var;
   a.epsilon = epsilon;
-  if (LaunchFused<T, kFwd>(xt, nullptr, static_cast<T*>(y), f, a, true, partial, g,
-                           stream)) {
-    return LastError();
+  if (int rc = RunStats<T, kFwd>(xt, nullptr, nullptr, partial, g, f, kTailFwdStats,
+                                 stream)) {
+    return rc;
   }
-  const int splits = LaunchStats<T, kFwd>(xt, nullptr, nullptr, partial, g, stream);
-  if (splits < 0) return splits;
-  f.splits = splits;
-  LaunchFinalize<0>(f, stream);
-  LaunchApply<T, kFwd>(xt, nullptr, static_cast<T*>(y), a, g, stream);
+  LaunchApply<T, kFwd>(xt, nullptr, static_cast<T*>(y), a, g, stream, true);
   return LastError();
 }
 
@@ -2054,6 +1821,7 @@ int FwdInfer(const void* x, const float* scale, const float* offset,
              cudaStream_t stream) {
   const Geom g{outer, channels, inner};
   if (int rc = CheckGeom(g)) return rc;
+  MUSA_TRACE("LaunchBnApply", 2 * sizeof(T) * outer * channels * inner);
   if (IsEmpty(g)) return MUSA_KERNELS_OK;
   if (!x || !y || !scale || !offset || !est_mean || !est_var) {
     return MUSA_KERNELS_EINVAL;
@@ -2077,6 +1845,7 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
          cudaStream_t stream) {
   const Geom g{outer, channels, inner};
   if (int rc = CheckGeom(g)) return rc;
+  MUSA_TRACE("LaunchBnGrad", 3 * sizeof(T) * outer * channels * inner);
   if (IsEmpty(g)) return MUSA_KERNELS_OK;
   if (!dy || !x || !scale || !mean || !variance || !dx || !dscale || !doffset) {
     return MUSA_KERNELS_EINVAL;
@@ -2105,33 +1874,25 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
   a.epsilon = epsilon;
   a.sums = is_training ? sums : nullptr;
   a.inv_count = static_cast<float>(1.0 / static_cast<double>(g.rows()));
-  if (LaunchFused<T, kGrad>(xt, dyt, static_cast<T*>(dx), f, a, is_training, partial,
-                            g, stream)) {
-    return LastError();
+  if (int rc = RunStats<T, kGrad>(xt, dyt, mean, partial, g, f, kTailGrad, stream)) {
+    return rc;
   }
-  const int splits = LaunchStats<T, kGrad>(xt, dyt, mean, partial, g, stream);
-  if (splits < 0) return splits;
-  f.splits = splits;
-  LaunchFinalize<2>(f, stream);
-  LaunchApply<T, kGrad>(xt, dyt, static_cast<T*>(dx), a, g, stream);
+  LaunchApply<T, kGrad>(xt, dyt, static_cast<T*>(dx), a, g, stream, true);
   return LastError();
 }
 
 template <typename T>
 int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
-              void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+              void* workspace, size_t workspace_bytes, int kind,
+              cudaStream_t stream) {
+  MUSA_TRACE("LaunchBnStats", sizeof(T) * g.outer * g.channels * g.inner);
   if (!x || !sums) return MUSA_KERNELS_EINVAL;
   if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
       !Aligned16(workspace)) {
     return MUSA_KERNELS_EWORKSPACE;
   }
   float* partial = static_cast<float*>(workspace);
-  const int splits = LaunchStats<T, kFwd>(static_cast<const T*>(x), nullptr,
-                                          nullptr, partial, g, stream);
-  if (splits < 0) return splits;
   FinalizeArgs f{};
-  f.partial = partial;
-  f.splits = splits;
   f.channels = g.channels;
   SetCount(&f, static_cast<double>(g.rows()));
   f.x_first = x;
@@ -2139,7 +1900,10 @@ int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
   f.shift_stride = g.inner == 1 ? 1 : g.inner;
   f.sums = sums;
   f.count_out = count_out;
-  LaunchFinalize<1>(f, stream);
+  if (int rc = RunStats<T, kFwd>(static_cast<const T*>(x), nullptr, nullptr, partial, g,
+                                 f, kind, stream)) {
+    return rc;
+  }
   return LastError();
 }
 
@@ -2147,23 +1911,21 @@ template <typename T>
 int GradStatsSums(const void* dy, const void* x, const float* mean, float* sums,
                   const Geom& g, void* workspace, size_t workspace_bytes,
                   cudaStream_t stream) {
+  MUSA_TRACE("LaunchBnGradStats", 2 * sizeof(T) * g.outer * g.channels * g.inner);
   if (!dy || !x || !mean || !sums) return MUSA_KERNELS_EINVAL;
   if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
       !Aligned16(workspace)) {
     return MUSA_KERNELS_EWORKSPACE;
   }
   float* partial = static_cast<float*>(workspace);
-  const int splits =
-      LaunchStats<T, kGrad>(static_cast<const T*>(x), static_cast<const T*>(dy),
-                            mean, partial, g, stream);
-  if (splits < 0) return splits;
   FinalizeArgs f{};
-  f.partial = partial;
-  f.splits = splits;
   f.channels = g.channels;
   SetCount(&f, static_cast<double>(g.rows()));
   f.sums = sums;
-  LaunchFinalize<2>(f, stream);
+  if (int rc = RunStats<T, kGrad>(static_cast<const T*>(x), static_cast<const T*>(dy),
+                                  mean, partial, g, f, kTailGrad, stream)) {
+    return rc;
+  }
   return LastError();
 }
 
@@ -2173,6 +1935,7 @@ int GradApplyFromSums(const void* dy, const void* x, const float* scale,
                       const float* sums, double total_count, void* dx,
                       float* dscale, float* doffset, const Geom& g,
                       float epsilon, cudaStream_t stream) {
+  MUSA_TRACE("LaunchBnGradApply", 3 * sizeof(T) * g.outer * g.channels * g.inner);
   if (!dy || !x || !scale || !mean || !variance || !sums || !dx) {
     return MUSA_KERNELS_EINVAL;
   }
@@ -2212,7 +1975,7 @@ constexpr size_t kStaticScratchBytes =
 static __device__ __align__(256) unsigned char
     g_bn_static_scratch[kStaticScratchBytes];
 
-constexpr int kScratchMaxDevices = 64;
+constexpr int kScratchMaxDevices = kMaxDevices;
 std::mutex g_scratch_mutex;
 void* g_scratch_addr[kScratchMaxDevices] = {};
 
@@ -2303,24 +2066,6 @@ MUSA_DEFINE_BN(F16, __half)
 MUSA_DEFINE_BN(BF16, __nv_bfloat16)
 #undef MUSA_DEFINE_BN
 
-int BnWorkspaceStatus(void* workspace, int64_t outer, int64_t channels,
-                      int64_t inner) {
-  const Geom g{outer, channels, inner};
-  if (workspace == nullptr || CheckGeom(g) != MUSA_KERNELS_OK || IsEmpty(g)) {
-    return MUSA_KERNELS_EINVAL;
-  }
-  char* control = reinterpret_cast<char*>(static_cast<float*>(workspace) +
-                                          ControlOffsetFloats(g));
-  int status = 0;
-  if (cudaMemcpy(&status, control + 64, sizeof(int), cudaMemcpyDeviceToHost) !=
-      cudaSuccess) {
-    cudaGetLastError();
-    return -100;
-  }
-  if (status != 0) cudaMemset(control + 64, 0, sizeof(int));
-  return status;
-}
-
 size_t BnNoAllocMaxChannels(void) {
   return static_cast<size_t>(kStaticScratchMaxChannels);
 }
@@ -2374,7 +2119,7 @@ int LaunchBnStatsSums(int dtype, const void* x, float* sums, int64_t outer,
         cudaMemsetAsync(sums, 0, sizeof(float) * 2 * channels, stream));
   }
   MUSA_BY_DTYPE(dtype, StatsSums<T>(x, sums, nullptr, g, workspace,
-                                    workspace_bytes, stream));
+                                    workspace_bytes, kTailFwdSums, stream));
 }
 
 int LaunchBnStatsSumsCount(int dtype, const void* x, float* sums, int64_t outer,
@@ -2389,67 +2134,14 @@ int LaunchBnStatsSumsCount(int dtype, const void* x, float* sums, int64_t outer,
         cudaMemsetAsync(sums, 0, sizeof(float) * (2 * channels + 1), stream));
   }
   MUSA_BY_DTYPE(dtype, StatsSums<T>(x, sums, sums + 2 * channels, g, workspace,
-                                    workspace_bytes, stream));
+                                    workspace_bytes, kTailFwdSums, stream));
 }
 
-int LaunchBnApplyFromSums(int dtype, const void* x, const float* scale,
-                          const float* offset, const float* sums,
-                          double total_count, const float* est_mean,
-                          const float* est_var, float exp_avg_factor, void* y,
-                          float* batch_mean, float* batch_var,
-                          float* saved_mean, float* saved_var, int64_t outer,
-                          int64_t channels, int64_t inner, float epsilon,
-                          cudaStream_t stream) {
-  const Geom g{outer, channels, inner};
-  if (int rc = CheckGeom(g)) return rc;
-  if (!(total_count > 0.0)) return MUSA_KERNELS_EINVAL;
-  if (channels == 0) return MUSA_KERNELS_OK;
-  if (!sums || !scale || !offset || !saved_mean || !saved_var) {
-    return MUSA_KERNELS_EINVAL;
-  }
-  if (exp_avg_factor != 1.0f && (!est_mean || !est_var)) {
-    return MUSA_KERNELS_EINVAL;
-  }
-  if (g.inner != 1 || IsEmpty(g)) {
-    // General layout (or a replica without rows): statistics first, then the
-    // element-wise pass.
-    if (int rc = LaunchBnFinalizeFromSums(sums, total_count, est_mean, est_var,
-                                          batch_mean, batch_var, saved_mean,
-                                          saved_var, channels, exp_avg_factor,
-                                          stream)) {
-      return rc;
-    }
-    if (IsEmpty(g)) return MUSA_KERNELS_OK;
-    return LaunchBnApply(dtype, x, scale, offset, saved_mean, saved_var, y,
-                         outer, channels, inner, epsilon, stream);
-  }
-  if (!x || !y) return MUSA_KERNELS_EINVAL;
-  ApplyArgs a{};
-  a.scale = scale;
-  a.offset = offset;
-  a.epsilon = epsilon;
-  a.stat_sums = sums;
-  a.count = total_count;
-  a.stat_out.channels = channels;
-  SetCount(&a.stat_out, total_count);
-  a.stat_out.est_mean = est_mean;
-  a.stat_out.est_var = est_var;
-  a.stat_out.batch_mean = batch_mean;
-  a.stat_out.batch_var = batch_var;
-  a.stat_out.saved_mean = saved_mean;
-  a.stat_out.saved_var = saved_var;
-  a.stat_out.exp_avg_factor = exp_avg_factor;
-  MUSA_BY_DTYPE(dtype, (LaunchApply<T, kFwd>(static_cast<const T*>(x), nullptr,
-                                             static_cast<T*>(y), a, g, stream),
-                        LastError()));
-}
-
-int LaunchBnFinalizeFromSums(const float* sums, double total_count,
-                             const float* est_mean, const float* est_var,
-                             float* batch_mean, float* batch_var,
-                             float* saved_mean, float* saved_var,
-                             int64_t channels, float exp_avg_factor,
-                             cudaStream_t stream) {
+namespace {
+int FinalizeFromSums(const float* sums, bool moments, double total_count,
+                     const float* est_mean, const float* est_var, float* batch_mean,
+                     float* batch_var, float* saved_mean, float* saved_var,
+                     int64_t channels, float exp_avg_factor, cudaStream_t stream) {
   if (channels < 0 || !(total_count > 0.0)) return MUSA_KERNELS_EINVAL;
   if (channels == 0) return MUSA_KERNELS_OK;
   if (!sums || !saved_mean || !saved_var) return MUSA_KERNELS_EINVAL;
@@ -2467,8 +2159,122 @@ int LaunchBnFinalizeFromSums(const float* sums, double total_count,
   f.saved_var = saved_var;
   f.exp_avg_factor = exp_avg_factor;
   const int grid = static_cast<int>(CeilDiv(channels, 256));
-  BnFinalizeFromSumsKernel<<<grid, 256, 0, stream>>>(f, sums);
+  BnFinalizeFromSumsKernel<<<grid, 256, 0, stream>>>(f, sums, moments);
   return LastError();
+}
+
+int ApplyFromSums(int dtype, const void* x, const float* scale, const float* offset,
+                  const float* sums, bool moments, double total_count,
+                  const float* est_mean, const float* est_var, float exp_avg_factor,
+                  void* y, float* batch_mean, float* batch_var, float* saved_mean,
+                  float* saved_var, int64_t outer, int64_t channels, int64_t inner,
+                  float epsilon, cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (!(total_count > 0.0)) return MUSA_KERNELS_EINVAL;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!sums || !scale || !offset || !saved_mean || !saved_var) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  if (exp_avg_factor != 1.0f && (!est_mean || !est_var)) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  if (g.inner != 1 || IsEmpty(g)) {
+    // General layout (or a replica without rows): statistics first, then the
+    // element-wise pass.
+    if (int rc = FinalizeFromSums(sums, moments, total_count, est_mean, est_var,
+                                  batch_mean, batch_var, saved_mean, saved_var, channels,
+                                  exp_avg_factor, stream)) {
+      return rc;
+    }
+    if (IsEmpty(g)) return MUSA_KERNELS_OK;
+    return LaunchBnApply(dtype, x, scale, offset, saved_mean, saved_var, y,
+                         outer, channels, inner, epsilon, stream);
+  }
+  if (!x || !y) return MUSA_KERNELS_EINVAL;
+  ApplyArgs a{};
+  a.scale = scale;
+  a.offset = offset;
+  a.epsilon = epsilon;
+  a.stat_sums = sums;
+  a.stat_moments = moments;
+  a.count = total_count;
+  a.stat_out.channels = channels;
+  SetCount(&a.stat_out, total_count);
+  a.stat_out.est_mean = est_mean;
+  a.stat_out.est_var = est_var;
+  a.stat_out.batch_mean = batch_mean;
+  a.stat_out.batch_var = batch_var;
+  a.stat_out.saved_mean = saved_mean;
+  a.stat_out.saved_var = saved_var;
+  a.stat_out.exp_avg_factor = exp_avg_factor;
+  MUSA_BY_DTYPE(dtype, (LaunchApply<T, kFwd>(static_cast<const T*>(x), nullptr,
+                                             static_cast<T*>(y), a, g, stream),
+                        LastError()));
+}
+}  // namespace
+
+int LaunchBnApplyFromSums(int dtype, const void* x, const float* scale,
+                          const float* offset, const float* sums,
+                          double total_count, const float* est_mean,
+                          const float* est_var, float exp_avg_factor, void* y,
+                          float* batch_mean, float* batch_var,
+                          float* saved_mean, float* saved_var, int64_t outer,
+                          int64_t channels, int64_t inner, float epsilon,
+                          cudaStream_t stream) {
+  return ApplyFromSums(dtype, x, scale, offset, sums, false, total_count, est_mean,
+                       est_var, exp_avg_factor, y, batch_mean, batch_var, saved_mean,
+                       saved_var, outer, channels, inner, epsilon, stream);
+}
+
+int LaunchBnApplyFromMoments(int dtype, const void* x, const float* scale,
+                             const float* offset, const float* moments,
+                             double total_count, const float* est_mean,
+                             const float* est_var, float exp_avg_factor, void* y,
+                             float* batch_mean, float* batch_var,
+                             float* saved_mean, float* saved_var, int64_t outer,
+                             int64_t channels, int64_t inner, float epsilon,
+                             cudaStream_t stream) {
+  return ApplyFromSums(dtype, x, scale, offset, moments, true, total_count, est_mean,
+                       est_var, exp_avg_factor, y, batch_mean, batch_var, saved_mean,
+                       saved_var, outer, channels, inner, epsilon, stream);
+}
+
+int LaunchBnStatsMoments(int dtype, const void* x, float* moments, int64_t outer,
+                         int64_t channels, int64_t inner, void* workspace,
+                         size_t workspace_bytes, cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!moments) return MUSA_KERNELS_EINVAL;
+  if (IsEmpty(g)) {
+    // A replica with no rows: count 0, nothing to merge.
+    return static_cast<int>(
+        cudaMemsetAsync(moments, 0, sizeof(float) * (2 * channels + 1), stream));
+  }
+  MUSA_BY_DTYPE(dtype, StatsSums<T>(x, moments, moments + 2 * channels, g, workspace,
+                                    workspace_bytes, kTailFwdMoments, stream));
+}
+
+int LaunchBnMergeMoments(const float* gathered, int world, int64_t channels,
+                         float* merged, cudaStream_t stream) {
+  if (world < 1 || channels < 0) return MUSA_KERNELS_EINVAL;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!gathered || !merged) return MUSA_KERNELS_EINVAL;
+  const int grid = static_cast<int>(CeilDiv(channels, 256));
+  BnMergeMomentsKernel<<<grid, 256, 0, stream>>>(gathered, world, channels, merged);
+  return LastError();
+}
+
+int LaunchBnFinalizeFromSums(const float* sums, double total_count,
+                             const float* est_mean, const float* est_var,
+                             float* batch_mean, float* batch_var,
+                             float* saved_mean, float* saved_var,
+                             int64_t channels, float exp_avg_factor,
+                             cudaStream_t stream) {
+  return FinalizeFromSums(sums, false, total_count, est_mean, est_var, batch_mean,
+                          batch_var, saved_mean, saved_var, channels, exp_avg_factor,
+                          stream);
 }
 
 int LaunchBnApply(int dtype, const void* x, const float* scale,

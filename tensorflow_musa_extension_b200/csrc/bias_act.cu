@@ -11,6 +11,7 @@
 // (musa_ext/kernels/nn/musa_relu_op.cc:19-57), Sigmoid
 // (musa_ext/kernels/nn/musa_sigmoid_op.cc:18-35).
 #include "common.cuh"
+#include "trace.h"
 #include "tuning.h"
 #include "../../include/musa_plugin_kernels.h"
 
@@ -411,6 +412,7 @@ int LaunchBiasAct(const void* x, const void* bias, void* y, int64_t outer,
                   int64_t channels, int64_t inner, int act,
                   cudaStream_t stream) {
   if (outer < 0 || channels < 0 || inner < 0) return MUSA_KERNELS_EINVAL;
+  MUSA_TRACE("LaunchBiasAct", 2 * sizeof(T) * outer * channels * inner);
   if (outer == 0 || channels == 0 || inner == 0) return MUSA_KERNELS_OK;
   if (x == nullptr || y == nullptr) return MUSA_KERNELS_EINVAL;
   const T* xt = static_cast<const T*>(x);

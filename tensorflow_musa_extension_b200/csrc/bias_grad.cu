@@ -15,6 +15,7 @@
 // partial rows in a wider type and rounds once to the output type.  The two
 // kernels are chained with programmatic dependent launch.
 #include "common.cuh"
+#include "trace.h"
 #include "tuning.h"
 #include "../../include/musa_plugin_kernels.h"
 
@@ -472,12 +473,15 @@ int LaunchLast(const T* dy, const T* feat, T* dx,
   lg.lanes = kThreads / lg.cols;
   const int grid_x = static_cast<int>(CeilDiv(lg.cv, lg.cols));
 
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads,
-                                                    0) != cudaSuccess ||
-      per_sm < 1) {
-    per_sm = 1;
-  }
+  static std::atomic<int> per_sm_by_device[kMaxDevices];
+  int per_sm = PerDevice(per_sm_by_device, [&] {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0) !=
+        cudaSuccess) {
+      cudaGetLastError();
+    }
+    return n > 0 ? n : 1;
+  });
   if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
   int64_t want = static_cast<int64_t>(SmCount()) * per_sm / grid_x;
   const int64_t by_rows = CeilDiv(g.outer, static_cast<int64_t>(lg.lanes) * 4);
@@ -531,6 +535,8 @@ int BiasGrad(const void* dy_v, const void* feat_v, void* dx_v, void* out_v,
              cudaStream_t stream) {
   using A = typename AccOf<T>::type;
   if (BadGeom(g)) return MUSA_KERNELS_EINVAL;
+  MUSA_TRACE(kFused ? "LaunchBiasAddReluGrad" : "LaunchBiasAddGrad",
+             (kFused ? 3 : 1) * sizeof(T) * g.outer * g.channels * g.inner);
   if (g.channels == 0) return MUSA_KERNELS_OK;
   if (out_v == nullptr) return MUSA_KERNELS_EINVAL;
   T* out = static_cast<T*>(out_v);
@@ -601,6 +607,7 @@ template <typename T>
 int ReluGrad(const void* dy_v, const void* feat_v, void* dx_v, int64_t n,
              cudaStream_t stream) {
   if (n < 0) return MUSA_KERNELS_EINVAL;
+  MUSA_TRACE("LaunchReluGrad", 3 * sizeof(T) * n);
   if (n == 0) return MUSA_KERNELS_OK;
   if (dy_v == nullptr || feat_v == nullptr || dx_v == nullptr) {
     return MUSA_KERNELS_EINVAL;
@@ -613,12 +620,15 @@ int ReluGrad(const void* dy_v, const void* feat_v, void* dx_v, int64_t n,
   if (aligned) {
     const int64_t packs = n / kFull;
     auto kernel = ReluGradKernel<T, kFull>;
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads,
-                                                      0) != cudaSuccess ||
-        per_sm < 1) {
-      per_sm = 1;
-    }
+    static std::atomic<int> per_sm_by_device[kMaxDevices];
+    const int per_sm = PerDevice(per_sm_by_device, [&] {
+      int n = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0) !=
+          cudaSuccess) {
+        cudaGetLastError();
+      }
+      return n > 0 ? n : 1;
+    });
     int64_t grid = static_cast<int64_t>(SmCount()) * per_sm;
     const int64_t need = CeilDiv(packs > 0 ? packs : 1, kThreads);
     if (grid > need) grid = need;

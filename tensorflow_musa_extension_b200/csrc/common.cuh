@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace musa_b200 {
 
 // B200: 148 SMs.  Grids of streaming kernels are sized as a multiple of the SM
@@ -188,6 +190,27 @@ inline cudaError_t LaunchChained(bool programmatic, void (*kernel)(KArgs...),
   cfg.attrs = attr;
   cfg.numAttrs = programmatic ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// One value per device and call site, computed on the first use on that
+// device with that device current (function attributes and occupancy are
+// per-device state, and one process may drive several GPUs).  The table is a
+// zero-initialised static of the call site; 0 means "not computed yet", so
+// `init` returns non-zero values.
+constexpr int kMaxDevices = 64;
+template <typename Init>
+inline int PerDevice(std::atomic<int>* table, Init init) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return init();
+  }
+  int v = table[dev].load(std::memory_order_acquire);
+  if (v == 0) {
+    v = init();
+    table[dev].store(v, std::memory_order_release);
+  }
+  return v;
 }
 
 inline bool Aligned16(const void* p) {

@@ -3,12 +3,13 @@
 // (2*C + 1 floats per layer and pass) without a collective-library launch.
 //
 // Every replica owns one buffer in its OWN memory:
-//     cell[2 slots][world][slot_floats]    8-byte cells {value bits, epoch}
-// written by the peers (and by itself).  A cell is stored with one aligned
-// 8-byte store, so a reader sees either the old cell or the new one, never a
-// mix: the epoch inside the cell says whether the value is the one it waits
-// for.  No separate flag and no memory fence are needed (the latency of one
-// exchange is one NVLink store plus a poll).
+//     cell[2 slots][world][slot_floats]    8-byte cells (epoch << 32 | value bits)
+// written by the peers (and by itself).  A cell is ONE 64-bit scalar, stored
+// and loaded with single relaxed system-scope accesses, which the PTX memory
+// model makes single-copy atomic: a reader sees either the old cell or the
+// new one, never a mix, and the epoch inside the cell says whether the value
+// is the one it waits for.  No separate flag and no memory fence are needed
+// (the latency of one exchange is one NVLink store plus a poll).
 // One exchange = one single-CTA kernel per replica:
 //   1. epoch = local counter + 1 (a device-side counter, so a captured CUDA
 //      graph replays correctly); slot = epoch & 1;
@@ -16,10 +17,15 @@
 //      (plain stores to peer-mapped addresses);
 //   3. gather, in its own memory: for each i, read cell[slot][q][i] for every
 //      q and poll the ones whose epoch is still old.  The poll is bounded:
-//      after kSpinLimit tries the kernel records which replica was missing in
-//      a status word and goes on, so a lost peer never hangs a GPU;
-//   4. total[i] = sum over q = 0..world-1, in rank order, so every replica
-//      gets bit-identical totals; written over the input vector.
+//      after kSpinLimit tries (about a second) the kernel records which
+//      replica was missing in a status word and stops waiting for that replica
+//      - for the rest of this exchange and, while the host has not read the
+//      status word, in every later exchange - so a lost peer costs one wait,
+//      not one per cell, and never hangs a GPU;
+//   4. combine over q = 0..world-1, in rank order, so every replica gets
+//      bit-identical results, written over the input vector: the plain sum,
+//      or (moments mode, the forward of cross-replica BatchNorm) the merge of
+//      per-replica [mean[C], M2[C], count] into the moments of the union.
 // Two slots suffice: a replica can publish epoch e+2 only after it consumed
 // e+1, which needs every replica to have published e+1, which each does only
 // after consuming e.
@@ -36,6 +42,7 @@
 #include <new>
 
 #include "common.cuh"
+#include "trace.h"
 #include "../../include/musa_plugin_kernels.h"
 
 namespace musa_b200 {
@@ -43,15 +50,15 @@ namespace {
 
 constexpr int kMaxWorld = 16;
 constexpr int kExchangeThreads = 512;
-// Polls of one cell before a wait gives up (each poll is a volatile load plus
-// a short sleep: of the order of a second in total).
-constexpr long long kSpinLimit = 4LL << 20;
+// Polls of one cell before a wait gives up (each poll is a load from local
+// memory plus a short sleep, about a microsecond: a second in total).
+constexpr long long kSpinLimit = 1LL << 20;
 
 struct ExchangeDev {
   int rank;
   int world;
   long long slot_floats;
-  uint2* cells[kMaxWorld];  // cell buffer of every replica (peer-mapped)
+  unsigned long long* cells[kMaxWorld];  // cell buffer of every replica (peer-mapped)
   unsigned* epoch;          // local
   int* status;              // local: 0 ok, 1 + q when replica q never arrived
 };
@@ -67,22 +74,52 @@ struct ExchangeHost {
 
 size_t Align256(size_t n) { return (n + 255) / 256 * 256; }
 
-__device__ __forceinline__ uint2 LoadCell(const uint2* p) {
-  uint2 v;
-  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
-               : "=r"(v.x), "=r"(v.y)
-               : "l"(p));
+__device__ __forceinline__ unsigned long long LoadCell(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
 
-__device__ __forceinline__ void StoreCell(uint2* p, uint2 v) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y)
-               : "memory");
+__device__ __forceinline__ void StoreCell(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long MakeCell(float value, unsigned epoch) {
+  return (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(value);
+}
+__device__ __forceinline__ unsigned CellEpoch(unsigned long long cell) {
+  return static_cast<unsigned>(cell >> 32);
+}
+__device__ __forceinline__ float CellValue(unsigned long long cell) {
+  return __uint_as_float(static_cast<unsigned>(cell & 0xffffffffULL));
+}
+
+enum ExchangeMode { kExchangeSum = 0, kExchangeMoments = 1 };
+
+// Waits (bounded) until the cell of replica q carries `epoch`.  `dead` is the
+// CTA's shared mask of replicas nobody waits for any more.
+__device__ __forceinline__ unsigned long long AwaitCell(const unsigned long long* cell,
+                                                        unsigned epoch, int q, unsigned* dead,
+                                                        int* status) {
+  unsigned long long got = LoadCell(cell);
+  long long polls = 0;
+  while (CellEpoch(got) != epoch) {
+    if ((*reinterpret_cast<volatile unsigned*>(dead) >> q) & 1u) break;
+    if (++polls > kSpinLimit) {
+      atomicOr(dead, 1u << q);
+      atomicCAS(status, 0, 1 + q);
+      break;
+    }
+    __nanosleep(40);
+    got = LoadCell(cell);
+  }
+  return got;
 }
 
 template <int kWorld>  // 0: run-time world size
 __device__ __forceinline__ void ExchangeBody(const ExchangeDev& c, float* vec, int n,
-                                             unsigned epoch) {
+                                             unsigned epoch, int mode, unsigned* dead) {
+  constexpr int kW = kWorld > 0 ? kWorld : kMaxWorld;
   const int world = kWorld > 0 ? kWorld : c.world;
   const int slot = static_cast<int>(epoch & 1u);
   const long long slot_base = static_cast<long long>(slot) * world * c.slot_floats;
@@ -90,55 +127,118 @@ __device__ __forceinline__ void ExchangeBody(const ExchangeDev& c, float* vec, i
 
   // 2. push the local vector into every replica's memory.
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const uint2 cell = make_uint2(__float_as_uint(vec[i]), epoch);
+    const unsigned long long cell = MakeCell(vec[i], epoch);
 #pragma unroll
-    for (int p = 0; p < (kWorld > 0 ? kWorld : kMaxWorld); ++p) {
+    for (int p = 0; p < kW; ++p) {
       if (p < world) StoreCell(c.cells[p] + mine + i, cell);
     }
   }
 
-  // 3. + 4. gather from local memory and sum in rank order.
-  const uint2* local = c.cells[c.rank] + slot_base;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    uint2 got[kWorld > 0 ? kWorld : kMaxWorld];
+  // The combine step overwrites `vec`; in moments mode a thread's outputs are
+  // not the elements it pushed, so every push has to be issued first.
+  __syncthreads();
+
+  // 3. + 4. gather from local memory and combine in rank order.
+  const unsigned long long* local = c.cells[c.rank] + slot_base;
+  if (mode == kExchangeSum) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      unsigned long long got[kW];
 #pragma unroll
-    for (int q = 0; q < (kWorld > 0 ? kWorld : kMaxWorld); ++q) {
-      if (q < world) got[q] = LoadCell(local + static_cast<long long>(q) * c.slot_floats + i);
-    }
-    float total = 0.0f;
+      for (int q = 0; q < kW; ++q) {
+        if (q < world) got[q] = LoadCell(local + static_cast<long long>(q) * c.slot_floats + i);
+      }
+      float total = 0.0f;
 #pragma unroll
-    for (int q = 0; q < (kWorld > 0 ? kWorld : kMaxWorld); ++q) {
-      if (q < world) {
-        long long polls = 0;
-        while (got[q].y != epoch) {
-          if (++polls > kSpinLimit) {
-            atomicCAS(c.status, 0, 1 + q);
-            break;
+      for (int q = 0; q < kW; ++q) {
+        if (q < world) {
+          if (CellEpoch(got[q]) != epoch) {
+            got[q] = AwaitCell(local + static_cast<long long>(q) * c.slot_floats + i, epoch, q,
+                               dead, c.status);
           }
-          __nanosleep(40);
-          got[q] = LoadCell(local + static_cast<long long>(q) * c.slot_floats + i);
+          total += CellValue(got[q]);
         }
-        total += __uint_as_float(got[q].x);
+      }
+      vec[i] = total;
+    }
+    return;
+  }
+  // Moments: vec = [mean[C], M2[C], count], n = 2 * C + 1.  The union of the
+  // replicas' rows has  N = sum n_q,  mean = sum n_q mean_q / N,
+  // M2 = sum M2_q + sum n_q (mean_q - mean)^2  (fp64, rank order).
+  const int channels = (n - 1) / 2;
+  double counts[kW];
+  double total_count = 0.0;
+#pragma unroll
+  for (int q = 0; q < kW; ++q) {
+    if (q < world) {
+      const unsigned long long got =
+          AwaitCell(local + static_cast<long long>(q) * c.slot_floats + 2 * channels, epoch, q,
+                    dead, c.status);
+      counts[q] = static_cast<double>(CellValue(got));
+      total_count += counts[q];
+    }
+  }
+  const double inv_total = total_count > 0.0 ? 1.0 / total_count : 0.0;
+  for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) {
+    unsigned long long gm[kW], gs[kW];
+#pragma unroll
+    for (int q = 0; q < kW; ++q) {
+      if (q < world) {
+        const unsigned long long* base = local + static_cast<long long>(q) * c.slot_floats;
+        gm[q] = LoadCell(base + ch);
+        gs[q] = LoadCell(base + channels + ch);
       }
     }
-    vec[i] = total;
+    double mean = 0.0;
+#pragma unroll
+    for (int q = 0; q < kW; ++q) {
+      if (q < world) {
+        const unsigned long long* base = local + static_cast<long long>(q) * c.slot_floats;
+        if (CellEpoch(gm[q]) != epoch) gm[q] = AwaitCell(base + ch, epoch, q, dead, c.status);
+        if (CellEpoch(gs[q]) != epoch) {
+          gs[q] = AwaitCell(base + channels + ch, epoch, q, dead, c.status);
+        }
+        mean += counts[q] * static_cast<double>(CellValue(gm[q]));
+      }
+    }
+    mean *= inv_total;
+    double m2 = 0.0;
+#pragma unroll
+    for (int q = 0; q < kW; ++q) {
+      if (q < world) {
+        const double d = static_cast<double>(CellValue(gm[q])) - mean;
+        m2 += static_cast<double>(CellValue(gs[q])) + counts[q] * d * d;
+      }
+    }
+    vec[ch] = static_cast<float>(mean);
+    vec[channels + ch] = static_cast<float>(m2);
   }
+  __syncthreads();  // every thread has read its own count input by now
+  if (threadIdx.x == 0) vec[2 * channels] = static_cast<float>(total_count);
 }
 
 __global__ void __launch_bounds__(kExchangeThreads)
     ExchangeSumsKernel(const ExchangeDev* ctxs, float* const* vectors,
-                       float* single_vector, int n) {
+                       float* single_vector, int n, int mode) {
   GridDepWait();
   GridDepLaunch();
   const ExchangeDev& c = ctxs[blockIdx.x];
   float* vec = vectors != nullptr ? vectors[blockIdx.x] : single_vector;
   const unsigned epoch = *c.epoch + 1u;  // nobody writes it before the barrier below
+  // A replica that an earlier exchange gave up on (the host has not read the
+  // status word yet) is not waited for again.
+  __shared__ unsigned dead;
+  if (threadIdx.x == 0) {
+    const int st = *reinterpret_cast<volatile int*>(c.status);
+    dead = st > 0 && st <= kMaxWorld ? 1u << (st - 1) : 0u;
+  }
+  __syncthreads();
   switch (c.world) {
-    case 1: ExchangeBody<1>(c, vec, n, epoch); break;
-    case 2: ExchangeBody<2>(c, vec, n, epoch); break;
-    case 4: ExchangeBody<4>(c, vec, n, epoch); break;
-    case 8: ExchangeBody<8>(c, vec, n, epoch); break;
-    default: ExchangeBody<0>(c, vec, n, epoch); break;
+    case 1: ExchangeBody<1>(c, vec, n, epoch, mode, &dead); break;
+    case 2: ExchangeBody<2>(c, vec, n, epoch, mode, &dead); break;
+    case 4: ExchangeBody<4>(c, vec, n, epoch, mode, &dead); break;
+    case 8: ExchangeBody<8>(c, vec, n, epoch, mode, &dead); break;
+    default: ExchangeBody<0>(c, vec, n, epoch, mode, &dead); break;
   }
   __syncthreads();
   if (threadIdx.x == 0) *c.epoch = epoch;
@@ -163,7 +263,7 @@ void* MusaExchangeCreate(int rank, int world, int64_t max_floats) {
     return nullptr;
   }
   const long long slot_floats = static_cast<long long>(Align256(max_floats * 4) / 4);
-  const size_t cell_bytes = Align256(sizeof(uint2) * 2 * world * slot_floats);
+  const size_t cell_bytes = Align256(sizeof(unsigned long long) * 2 * world * slot_floats);
   h->bytes = cell_bytes + 256 /*epoch*/ + 256 /*status*/ + Align256(sizeof(ExchangeDev));
   if (cudaMalloc(&h->base, h->bytes) != cudaSuccess ||
       cudaMemset(h->base, 0, h->bytes) != cudaSuccess) {
@@ -176,7 +276,7 @@ void* MusaExchangeCreate(int rank, int world, int64_t max_floats) {
   h->dev.rank = rank;
   h->dev.world = world;
   h->dev.slot_floats = slot_floats;
-  h->dev.cells[rank] = reinterpret_cast<uint2*>(p);
+  h->dev.cells[rank] = reinterpret_cast<unsigned long long*>(p);
   h->dev.epoch = reinterpret_cast<unsigned*>(p + cell_bytes);
   h->dev.status = reinterpret_cast<int*>(p + cell_bytes + 256);
   h->dev_copy = reinterpret_cast<ExchangeDev*>(p + cell_bytes + 512);
@@ -209,7 +309,7 @@ int MusaExchangeOpenPeers(void* handle, const void* handles) {
         cudaIpcOpenMemHandle(&mapped, ipc, cudaIpcMemLazyEnablePeerAccess);
     if (err != cudaSuccess) return static_cast<int>(err);
     h->opened[q] = mapped;
-    h->dev.cells[q] = static_cast<uint2*>(mapped);
+    h->dev.cells[q] = static_cast<unsigned long long*>(mapped);
   }
   return static_cast<int>(
       cudaMemcpy(h->dev_copy, &h->dev, sizeof(ExchangeDev), cudaMemcpyHostToDevice));
@@ -217,15 +317,37 @@ int MusaExchangeOpenPeers(void* handle, const void* handles) {
 
 // In place: `vector` (n floats, local device memory) becomes the sum over all
 // replicas.  One single-CTA kernel on `stream`; no host synchronisation.
-int LaunchExchangeSums(void* handle, float* vector, int64_t n, cudaStream_t stream) {
+namespace {
+int LaunchExchange(void* handle, float* vector, int64_t n, int mode, cudaStream_t stream) {
   auto* h = static_cast<ExchangeHost*>(handle);
   if (h == nullptr || vector == nullptr || n < 0) return MUSA_KERNELS_EINVAL;
   if (n > h->dev.slot_floats) return MUSA_KERNELS_ETOOLARGE;
+  MUSA_TRACE("LaunchExchange", 4 * n);
   if (n == 0) return MUSA_KERNELS_OK;
-  LaunchChained(true, ExchangeSumsKernel, dim3(1), dim3(kExchangeThreads), 0, stream,
-                static_cast<const ExchangeDev*>(h->dev_copy),
-                static_cast<float* const*>(nullptr), vector, static_cast<int>(n));
-  return static_cast<int>(cudaGetLastError());
+  const cudaError_t err = LaunchChained(
+      true, ExchangeSumsKernel, dim3(1), dim3(kExchangeThreads), 0, stream,
+      static_cast<const ExchangeDev*>(h->dev_copy), static_cast<float* const*>(nullptr),
+      vector, static_cast<int>(n), mode);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return static_cast<int>(err);
+  }
+  return MUSA_KERNELS_OK;
+}
+}  // namespace
+
+int LaunchExchangeSums(void* handle, float* vector, int64_t n, cudaStream_t stream) {
+  return LaunchExchange(handle, vector, n, kExchangeSum, stream);
+}
+
+// In place: `moments` = [mean[C], M2[C], count] of the local rows (fp32,
+// 2 * C + 1 floats) becomes the same three quantities of the rows of all
+// replicas together (M2 = sum of squared deviations from the mean).
+int LaunchExchangeMoments(void* handle, float* moments, int64_t channels,
+                          cudaStream_t stream) {
+  if (channels < 0) return MUSA_KERNELS_EINVAL;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  return LaunchExchange(handle, moments, 2 * channels + 1, kExchangeMoments, stream);
 }
 
 // 0, or 1 + q if a wait for replica q ran out; clears the word.  Synchronises
@@ -303,7 +425,7 @@ int MusaPeerClose(void* mapped) {
 // `missing_rank`: -1, or world - 1 to leave the last replica out (one round):
 // the others' waits must then run out and report it (return 1000 + world).
 int MusaExchangeSelfTest(int world, int64_t n, float* const* vectors, int rounds,
-                         int missing_rank, cudaStream_t stream) {
+                         int missing_rank, int mode, cudaStream_t stream) {
   if (world < 1 || world > 8 || n < 1 || vectors == nullptr) return MUSA_KERNELS_EINVAL;
   ExchangeHost* hs[8] = {};
   int rc = 0;
@@ -326,7 +448,7 @@ int MusaExchangeSelfTest(int world, int64_t n, float* const* vectors, int rounds
     for (int round = 0; round < rounds && rc == 0; ++round) {
       float* none = nullptr;
       int n32 = static_cast<int>(n);
-      void* args[] = {&table, const_cast<float* const**>(&vectors), &none, &n32};
+      void* args[] = {&table, const_cast<float* const**>(&vectors), &none, &n32, &mode};
       rc = static_cast<int>(cudaLaunchCooperativeKernel(
           reinterpret_cast<void*>(ExchangeSumsKernel), dim3(ctas), dim3(kExchangeThreads),
           args, 0, stream));

@@ -8,12 +8,14 @@
 //   centered RMSProp musa_ext/kernels/training/musa_applyrmsprop_kernel.mu:101-133
 //   gradient descent musa_ext/kernels/training/musa_applygradientdescent_kernel.mu:14-96
 //   Adagrad (V2)     musa_ext/kernels/training/musa_applyadagrad_kernel.mu:55-79
+//   Adam, double     the op chain of musa_ext/kernels/training/musa_applyadam_op.cc:297-415
 //
 // Arithmetic: fp32 for float / half / bfloat16 tensors with one round-to-
 // nearest-even on store, fp64 for double tensors.  Every rounding is spelled
 // out so that the vector path, the element path and a range-sharded run give
 // the same bits.
 #include "common.cuh"
+#include "trace.h"
 #include "tuning.h"
 #include "../../include/musa_plugin_kernels.h"
 
@@ -125,6 +127,34 @@ struct CenteredRmsPropRule {
     s[1] = mg;
     s[2] = ms;
     s[3] = mom;
+  }
+};
+
+// Adam for double tensors.  The reference serves this dtype with a chain of
+// thirteen element-wise library calls, every one of which stores a double
+// tensor (musa_applyadam_op.cc:297-415): multiply, multiply, add for each
+// moment, then sqrt, add epsilon, divide, multiply by alpha, subtract.  This
+// rule performs the same operations in the same order with one IEEE rounding
+// each (no contraction into fused multiply-adds), in one pass.
+template <bool kNesterov>
+struct AdamChainRule {
+  using StateT = double;
+  using GradT = double;
+  using C = double;
+  static constexpr int kStates = 3;  // var, m, v
+  struct Params {
+    double alpha, beta1, one_minus_b1, beta2, one_minus_b2, epsilon;
+  };
+  static __device__ __forceinline__ void Step(C (&s)[kStates], C g,
+                                              const Params& p) {
+    const C m = Add(Mul(s[1], p.beta1), Mul(g, p.one_minus_b1));
+    const C v = Add(Mul(s[2], p.beta2), Mul(Mul(g, g), p.one_minus_b2));
+    // The chain has no Nesterov branch; with the attribute set the numerator
+    // is TensorFlow's m * beta1 + g * (1 - beta1), built the same way.
+    const C numer = kNesterov ? Add(Mul(m, p.beta1), Mul(g, p.one_minus_b1)) : m;
+    s[0] = Sub(s[0], Mul(Div(numer, Add(Sqrt(v), p.epsilon)), p.alpha));
+    s[1] = m;
+    s[2] = v;
   }
 };
 
@@ -264,6 +294,10 @@ void LaunchStream(const UpdateArgs<Rule>& a, int64_t n, cudaStream_t stream) {
 // same element count), element accesses otherwise.
 template <typename Rule>
 void LaunchUpdate(const UpdateArgs<Rule>& a, int64_t n, cudaStream_t stream) {
+  MUSA_TRACE("LaunchStreamUpdate",
+             n > 0 ? (2 * Rule::kStates * sizeof(typename Rule::StateT) +
+                      sizeof(typename Rule::GradT)) * n
+                   : 0);
   if (n <= 0) return;
   constexpr int kEpt = VecWidth<typename Rule::StateT>::value;
   constexpr size_t kGradPackBytes = sizeof(typename Rule::GradT) * kEpt;
@@ -567,6 +601,31 @@ MUSA_DEFINE_STATEFUL(Half, __half)
 MUSA_DEFINE_STATEFUL(BFloat16, __nv_bfloat16)
 MUSA_DEFINE_STATEFUL(Double, double)
 #undef MUSA_DEFINE_STATEFUL
+
+void LaunchApplyAdam_F64(double* var, double* m, double* v, const double* grad,
+                         double alpha, double beta1, double beta2, double epsilon,
+                         int64_t n, bool use_nesterov, cudaStream_t stream) {
+  auto run = [&](auto rule) {
+    using Rule = decltype(rule);
+    UpdateArgs<Rule> a;
+    a.state[0] = var;
+    a.state[1] = m;
+    a.state[2] = v;
+    a.grad = grad;
+    a.p.alpha = alpha;
+    a.p.beta1 = beta1;
+    a.p.one_minus_b1 = 1.0 - beta1;
+    a.p.beta2 = beta2;
+    a.p.one_minus_b2 = 1.0 - beta2;
+    a.p.epsilon = epsilon;
+    LaunchUpdate<Rule>(a, n, stream);
+  };
+  if (use_nesterov) {
+    run(AdamChainRule<true>());
+  } else {
+    run(AdamChainRule<false>());
+  }
+}
 
 void LaunchResourceApplyGradientDescentFloat(float* var, const float* grad,
                                              float alpha, int64_t n,

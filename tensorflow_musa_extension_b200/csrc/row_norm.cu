@@ -19,6 +19,7 @@
 // cancel.  Rows that do not fit the register form (very long, or not a whole
 // number of aligned packs) take a CTA-per-row kernel with element accesses.
 #include "common.cuh"
+#include "trace.h"
 #include "tuning.h"
 #include "../../include/musa_plugin_kernels.h"
 
@@ -696,21 +697,48 @@ int LaunchGroupAs(const RowArgs& a, int* ctas_out, cudaStream_t stream) {
   constexpr int kRows = kThreads / kGroup;
   auto kernel = RowNormKernel<T, kGroup, kMaxPacks, kOp, kFull>;
   size_t smem = RowSmemBytes<kOp>(kGroup, sizeof(T), kThreads, kMaxPacks, a.row_size);
-  if (smem > 40 * 1024) {
+  // Function attributes and occupancy are per-device state; both are cached
+  // per device for this instantiation.  The shared-memory size depends on the
+  // row length, so the attribute is raised when a longer row arrives and the
+  // occupancy is remembered for the latest size (a model repeats its shapes).
+  static std::atomic<int> carveout_by_device[kMaxDevices];
+  static std::atomic<int> smem_limit_by_device[kMaxDevices];
+  static std::atomic<long long> occupancy_by_device[kMaxDevices];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return static_cast<int>(cudaErrorInvalidDevice);
+  }
+  // Ask for the largest shared-memory carve-out: the ring, not L1, is what
+  // these kernels live on, and the default carve-out fits fewer CTAs.
+  PerDevice(carveout_by_device, [&] {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaGetLastError();
+    return 1;
+  });
+  if (smem > 40 * 1024 &&
+      static_cast<int>(smem) > smem_limit_by_device[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess) {
       return static_cast<int>(cudaGetLastError());
     }
+    smem_limit_by_device[dev].store(static_cast<int>(smem), std::memory_order_release);
   }
-  // Ask for the largest shared-memory carve-out: the ring, not L1, is what
-  // these kernels live on, and the default carve-out fits fewer CTAs.
-  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                       cudaSharedmemCarveoutMaxShared);
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) !=
-          cudaSuccess ||
-      per_sm < 1) {
-    per_sm = 1;
+  const long long cached = occupancy_by_device[dev].load(std::memory_order_acquire);
+  if (cached != 0 && (cached >> 8) == static_cast<long long>(smem)) {
+    per_sm = static_cast<int>(cached & 0xff);
+  } else {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) !=
+            cudaSuccess ||
+        per_sm < 1) {
+      cudaGetLastError();
+      per_sm = 1;
+    }
+    if (per_sm > 255) per_sm = 255;
+    occupancy_by_device[dev].store((static_cast<long long>(smem) << 8) | per_sm,
+                                   std::memory_order_release);
   }
   constexpr int kCap = kOp == kOpLnGrad ? kMaxGradCtasPerSm : kMaxCtasPerSm;
   if (per_sm > kCap) per_sm = kCap;
@@ -821,6 +849,7 @@ int LayerNormFwd(const void* x, const void* gamma, const void* beta, void* y,
                  float* mean_out, float* inv_std_out, int64_t rows,
                  int64_t row_size, float epsilon, cudaStream_t stream) {
   if (BadRows(rows, row_size)) return MUSA_KERNELS_EINVAL;
+  MUSA_TRACE("LaunchLayerNorm", 2 * sizeof(T) * rows * row_size);
   if (rows == 0 || row_size == 0) return MUSA_KERNELS_OK;
   if (x == nullptr || gamma == nullptr || beta == nullptr || y == nullptr) {
     return MUSA_KERNELS_EINVAL;
@@ -847,6 +876,7 @@ int LayerNormGrad(const void* dy, const void* x, const void* gamma, void* dx,
                   float epsilon, void* workspace, size_t workspace_bytes,
                   cudaStream_t stream) {
   if (BadRows(rows, row_size)) return MUSA_KERNELS_EINVAL;
+  MUSA_TRACE("LaunchLayerNormGrad", 3 * sizeof(T) * rows * row_size);
   if (row_size == 0) return MUSA_KERNELS_OK;
   if (dgamma == nullptr || dbeta == nullptr) return MUSA_KERNELS_EINVAL;
   if (rows == 0) {
@@ -887,6 +917,7 @@ template <typename T>
 void RmsNormFwd(const void* x, const void* gamma, void* y, void* normalized,
                 void* inv_rms, int64_t rows, int64_t row_size, float epsilon,
                 cudaStream_t stream) {
+  MUSA_TRACE("LaunchRmsNorm", rows > 0 && row_size > 0 ? 3 * sizeof(T) * rows * row_size : 0);
   if (rows <= 0 || row_size <= 0 || row_size > (int64_t(1) << 24)) return;
   RowArgs a = {};
   a.x = x;
@@ -907,6 +938,8 @@ template <typename T>
 void RmsNormGradDx(const void* x, const void* inv_rms, const void* gamma,
                    const void* dy, void* dx, int64_t rows, int64_t row_size,
                    cudaStream_t stream) {
+  MUSA_TRACE("LaunchRmsNormGradDx",
+             rows > 0 && row_size > 0 ? 3 * sizeof(T) * rows * row_size : 0);
   if (rows <= 0 || row_size <= 0 || row_size > (int64_t(1) << 24)) return;
   RowArgs a = {};
   a.x = x;

@@ -9,7 +9,6 @@
 namespace musa_b200 {
 
 namespace {
-constexpr int kMaxDevices = 64;
 std::atomic<int> g_sm_count[kMaxDevices];
 std::atomic<int> g_tuning[kTuneCount];
 std::once_flag g_tuning_once;
@@ -20,7 +19,10 @@ void InitTuningOnce() {
         /*AdamCtasPerSm*/ 0, /*AdamUnroll*/ 2, /*BiasActCtasPerSm*/ 0,
         /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 0, /*BnFused*/ 0,
         /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1, /*BnStatsPipe*/ 4,
-        /*BnApplyDeep*/ 0, /*BnPdl*/ 1, /*BnL2KeepMb*/ 64};
+        /*BnApplyDeep*/ 0, /*BnPdl*/ 1, /*BnL2KeepMb*/ 64, /*RowNormPacks*/ 0,
+        /*reserved*/ 0, /*BnStatsMaxTx*/ 32, /*BnL2KeepPartial*/ 1,
+        /*BnStatsDropRest*/ 1, /*BnApplyDropAll*/ 1, /*BnApplyEarlyLoads*/ 1,
+        /*BnFinalizeLanes*/ 32};
     for (int i = 0; i < kTuneCount; ++i) g_tuning[i].store(defaults[i]);
   });
 }

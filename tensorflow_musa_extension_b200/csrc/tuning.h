@@ -11,15 +11,22 @@ enum TuningKey {
   kTuneBiasActCtasPerSm = 2,
   kTuneBiasActUnroll = 3,
   kTuneBnCtasPerSm = 4,     // CTAs per SM of the BatchNorm grids; 0: what fits
-  kTuneBnFused = 5,         // 1: one cooperative launch per op (measured slower: off)
+  kTuneReserved5 = 5,
   kTuneBnApplyReverse = 6,  // 1: apply pass walks rows in reverse (L2 reuse)
   kTuneBnStatsKeep = 7,     // 1: stats pass loads with the default L2 policy
   kTuneBnStatsPipe = 8,     // cp.async stages of the stats kernel (3 or 4); 0: register loads
   kTuneBnApplyDeep = 9,     // 1: forward element-wise pass keeps 8 rows in flight
   kTuneBnPdl = 10,          // 1: BatchNorm kernels use programmatic dependent launch
-  kTuneBnL2KeepMb = 11,     // stats pass pins its reads in L2 up to this many MB (0: off)
+  kTuneBnL2KeepMb = 11,     // MB of its reads that the stats pass asks L2 to hold back (0: off)
   kTuneRowNormPacks = 12,   // packs per thread of the row kernels: 1 .. 4; 0: chosen per op and row
-  kTuneCount = 16
+  kTuneReserved13 = 13,
+  kTuneBnStatsMaxTx = 14,   // channel packs per column block of the stats kernel; 0: by rule
+  kTuneBnL2KeepPartial = 15,  // 1: tensors beyond the budget keep the budget's share
+  kTuneBnStatsDropRest = 16,  // 1: rows outside the kept share are read evict-first
+  kTuneBnApplyDropAll = 17,   // 1: the element-wise pass reads evict-first at every size
+  kTuneBnApplyEarlyLoads = 18,  // 1: first rows of the element-wise pass are loaded before its wait
+  kTuneBnFinalizeLanes = 19,  // partial lanes per CTA of the finalize kernel: 32 or 128
+  kTuneCount = 24
 };
 
 int GetTuning(int key);

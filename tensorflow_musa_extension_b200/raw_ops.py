@@ -488,10 +488,24 @@ def _adam_impl(opname, var, m, v, beta1_power, beta2_power, lr, beta1, beta2,
                 raise InvalidArgumentError(
                     "%s: grad dtype %s does not match var dtype %s"
                     % (opname, grad.dtype, T))
-            if T not in _BN_DTYPES:
+            if T in (torch.int32, torch.int64):
+                # Registered by the reference for ResourceApplyAdam only
+                # (musa_applyadam_op.cc:676-677) and served by its op chain
+                # (:297-415), whose integer results hang on what a closed
+                # library does for integer sqrt and divide (beta1 = beta2 = 0
+                # after the cast to T, a divide by sqrt(g*g) + 0); TensorFlow's
+                # own CPU kernel, the parity oracle of this op, is not
+                # registered for integer T at all.  There is nothing to match.
                 raise UnimplementedError(
-                    "%s: T=%s takes the reference's muDNN op chain, which this "
-                    "build does not provide (float, half, bfloat16 only)" % (opname, T))
+                    "%s: T=%s is not supported: TensorFlow's CPU kernel has no integer "
+                    "ApplyAdam to compare with, and the reference's element-wise op chain "
+                    "for it (musa_applyadam_op.cc:297-415) is defined only by a closed "
+                    "library's integer sqrt/divide; float, double, half and bfloat16 are "
+                    "served" % (opname, T))
+            if T not in _BN_DTYPES and T != torch.float64:
+                raise InvalidArgumentError(
+                    "%s: T must be one of float, double, half, bfloat16; got %s"
+                    % (opname, T))
             scalar_t = T
         b1p = _scalar_in(beta1_power, scalar_t)
         b2p = _scalar_in(beta2_power, scalar_t)
@@ -506,7 +520,12 @@ def _adam_impl(opname, var, m, v, beta1_power, beta2_power, lr, beta1, beta2,
             L = _lib()
             with torch.cuda.device(var_t.device):
                 st = _stream()
-                if mixed or (T == torch.float32 and use_nesterov):
+                if T == torch.float64:
+                    # One pass with the operations, order and roundings of the
+                    # reference's op chain for this dtype (:297-415).
+                    L.LaunchApplyAdam_F64(_ptr(var_t), _ptr(m_t), _ptr(v_t), _ptr(grad),
+                                          alpha, b1, b2, eps, n, bool(use_nesterov), st)
+                elif mixed or (T == torch.float32 and use_nesterov):
                     fn = {torch.float32: L.LaunchApplyAdamMixed_Float,
                           torch.float16: L.LaunchApplyAdamMixed_Half,
                           torch.bfloat16: L.LaunchApplyAdamMixed_BFloat16}[grad.dtype]
@@ -532,7 +551,8 @@ def ResourceApplyAdam(var, m, v, beta1_power, beta2_power, lr, beta1, beta2,
                       name=None):
     """ResourceApplyAdam: in-place Adam step on var, m, v
     (musa_ext/kernels/training/musa_applyadam_op.cc:130-416; registered for
-    float, half, bfloat16 among others, :645-677).  var/m/v are `Variable`s or
+    float, double, half, bfloat16, int64 and int32, :672-677; the two integer
+    types raise Unimplemented here, with the reason in the message).  var/m/v are `Variable`s or
     device tensors.  The six scalars are host values read as T; alpha is taken
     in float64.  float + use_nesterov runs the Nesterov numerator (TensorFlow's
     CPU kernel honours the attr; the reference's float fast path is taken only

@@ -22,20 +22,31 @@ class CpuStages:
     def workspace_bytes(self, rows, c):
         return 16
 
-    def stats_sums(self, x, sums, ws):
+    def stats_moments(self, x, moments, ws):
         c = x.shape[1]
         xf = x.double()
-        sums[:c] = xf.sum(0).float()
-        sums[c:2 * c] = (xf * xf).sum(0).float()
-        sums[2 * c] = float(x.shape[0])
+        mean = xf.mean(0) if x.shape[0] else torch.zeros(c, dtype=torch.float64)
+        moments[:c] = mean.float()
+        moments[c:2 * c] = ((xf - mean) ** 2).sum(0).float()
+        moments[2 * c] = float(x.shape[0])
 
-    def apply_from_sums(self, x, scale, offset, sums, count, stats, y, eps):
-        self.finalize(sums, count, stats, x.shape[1])
+    def merge_moments(self, gathered, world, c, merged):
+        g = gathered.double().reshape(world, 2 * c + 1)
+        n = g[:, 2 * c]
+        total = n.sum()
+        mean = (n[:, None] * g[:, :c]).sum(0) / total
+        m2 = (g[:, c:2 * c] + n[:, None] * (g[:, :c] - mean) ** 2).sum(0)
+        merged[:c] = mean.float()
+        merged[c:2 * c] = m2.float()
+        merged[2 * c] = float(total)
+
+    def apply_from_moments(self, x, scale, offset, moments, count, stats, y, eps):
+        self._finalize_moments(moments, count, stats, x.shape[1])
         self.apply(x, scale, offset, stats[2], stats[3], y, eps)
 
-    def finalize(self, sums, count, stats, c):
-        mean = sums[:c].double() / count
-        var = (sums[c:2 * c].double() / count - mean * mean).clamp_min(0)
+    def _finalize_moments(self, moments, count, stats, c):
+        mean = moments[:c].double()
+        var = (moments[c:2 * c].double() / count).clamp_min(0)
         stats[0].copy_(mean.float())
         stats[1].copy_((var * (count / (count - 1.0)) if count > 1 else var).float())
         stats[2].copy_(mean.float())
@@ -71,11 +82,14 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     mode = sys.argv[1]
     rng = np.random.default_rng(123)
-    if mode in ("syncbn", "syncbn_ragged"):
+    if mode in ("syncbn", "syncbn_ragged", "syncbn_large_mean"):
         c = 24
-        rows = [40, 40] if mode == "syncbn" else [40, 13]
+        rows = [40, 13] if mode == "syncbn_ragged" else [40, 40]
         total = sum(rows)
-        x = (rng.standard_normal((total, c)) * 2 + 0.5).astype(np.float32)
+        # |mean| / std = 1000: raw [sum x, sum x^2] exchanged in fp32 would
+        # lose the variance here; the merged moments keep it.
+        loc, std = (1e3, 1.0) if mode == "syncbn_large_mean" else (0.5, 2.0)
+        x = (rng.standard_normal((total, c)) * std + loc).astype(np.float32)
         dy = rng.standard_normal((total, c)).astype(np.float32)
         s = rng.uniform(0.5, 1.5, c).astype(np.float32)
         o = rng.normal(0, 0.1, c).astype(np.float32)
@@ -92,12 +106,17 @@ def main():
         want = np_ref.fused_batch_norm(x, s, o, epsilon=1e-3)
         wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], 1e-3)
         assert bn.global_count == total, (bn.global_count, total)
-        np.testing.assert_allclose(y.numpy(), want[0][lo:hi], rtol=1e-4, atol=1e-5)
+        # The op's mean output is fp32: at |mean| = 1000 its half-ulp (3e-5) is
+        # the floor of x - mean, whoever computes it.
+        y_atol = 2e-4 if mode == "syncbn_large_mean" else 1e-5
+        np.testing.assert_allclose(y.numpy(), want[0][lo:hi], rtol=1e-4, atol=y_atol)
         np.testing.assert_allclose(bn.batch_mean.numpy(), want[1], rtol=1e-4, atol=1e-6)
         np.testing.assert_allclose(bn.batch_var.numpy(), want[2], rtol=1e-4)
         np.testing.assert_allclose(bn.saved_var.numpy(), want[4], rtol=1e-4)
-        np.testing.assert_allclose(dx.numpy(), wg[0][lo:hi], rtol=1e-3, atol=1e-5)
-        np.testing.assert_allclose(bn.dscale.numpy(), wg[1], rtol=1e-4, atol=1e-4)
+        np.testing.assert_allclose(dx.numpy(), wg[0][lo:hi], rtol=1e-3,
+                                   atol=2e-4 if mode == "syncbn_large_mean" else 1e-5)
+        np.testing.assert_allclose(bn.dscale.numpy(), wg[1], rtol=1e-4,
+                                   atol=5e-3 if mode == "syncbn_large_mean" else 1e-4)
         np.testing.assert_allclose(bn.doffset.numpy(), wg[2], rtol=1e-4, atol=1e-4)
     elif mode in ("adam_even", "adam_padded"):
         n = 1000 if mode == "adam_even" else 1001

@@ -241,31 +241,71 @@ def test_host_buffers_round_trip(kernel_lib):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("rows,c", [(2, 8), (33, 64), (5000, 256), (70000, 128)])
-def test_single_launch_variant(kernel_lib, dtype, rows, c):
-    """The one-cooperative-launch form of the two ops (off by default) returns
-    what the kernel chain returns, and none of its bounded waits runs out."""
+@pytest.mark.parametrize("rows,c", [(2, 8), (33, 64), (5000, 256), (70000, 128), (3000, 2048),
+                                    (9000, 520), (1200, 4104)])
+def test_dirty_workspace_and_launch_shapes(kernel_lib, dtype, rows, c):
+    """The workspace arrives with arbitrary contents (a framework hands out
+    temporary memory as it finds it); the same call twice gives the same bits;
+    column blocks as wide as the row, or 8 packs wide, and the older
+    1024-thread finalize kernel agree with the default shapes to rounding."""
     x, s, o, dy = bn_inputs(300 + rows, (rows, c), dtype, 1.0, 3.0)
     want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
     wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS)
-    old = kernel_lib.MusaKernelsSetTuning(5, 1)
-    try:
-        fwd, grad = run_both(x, s, o, dy, "NHWC")
-        torch.cuda.synchronize()
-        ws = raw_ops._workspace(kernel_lib.BnWorkspaceBytes(rows, c, 1), torch.device("cuda", 0))
-        assert kernel_lib.BnWorkspaceStatus(ws.data_ptr(), rows, c, 1) == 0
-    finally:
-        kernel_lib.MusaKernelsSetTuning(5, old)
+    need = kernel_lib.BnWorkspaceBytes(rows, c, 1)
+    ws = raw_ops._workspace(need, torch.device("cuda", 0))
+    ws.fill_(0xA5)
+    fwd, grad = run_both(x, s, o, dy, "NHWC")
+    fwd2, grad2 = run_both(x, s, o, dy, "NHWC")
+    torch.cuda.synchronize()
+    for a, b in zip(list(fwd)[:5] + list(grad)[:3], list(fwd2)[:5] + list(grad2)[:3]):
+        assert torch.equal(a, b)
     check_forward(fwd, want, dtype)
     terms = _rms(dy) * float(np.max(s / np.sqrt(want[4] + EPS)))
     check_grad(grad, wg, dtype, dx_scale=terms)
+    for key, value in ((14, 256), (14, 8), (19, 128)):
+        old = kernel_lib.MusaKernelsSetTuning(key, value)
+        try:
+            fwd3, grad3 = run_both(x, s, o, dy, "NHWC")
+            torch.cuda.synchronize()
+        finally:
+            kernel_lib.MusaKernelsSetTuning(key, old)
+        check_forward(fwd3, want, dtype)
+        check_grad(grad3, wg, dtype, dx_scale=terms)
+        assert_close(to_numpy(fwd.batch_mean), to_numpy(fwd3.batch_mean), 1e-5, 1e-6)
+        assert_close(to_numpy(fwd.reserve_space_2), to_numpy(fwd3.reserve_space_2), 1e-5, 1e-7)
+
+
+def test_bessel_and_inv_std_launchers(kernel_lib):
+    """The two fix-up launchers kept from the reference boundary
+    (musa_ext/kernels/nn/musa_fused_batchnorm_kernel.mu:38-56)."""
+    rng = np.random.default_rng(5)
+    st = torch.cuda.current_stream().cuda_stream
+    for count in (1, 7, 256, 1000):
+        var = rng.uniform(0.0, 4.0, count).astype(np.float32)
+        data = to_torch(var.copy())
+        factor = np.float32(50176.0 / 50175.0)
+        kernel_lib.LaunchBesselCorrection(data.data_ptr(), float(factor), count, st)
+        assert np.array_equal(to_numpy(data), var * factor)          # one fp32 multiply
+        inv = torch.empty(count, device="cuda")
+        kernel_lib.LaunchVarianceToInvStd(to_torch(var).data_ptr(), inv.data_ptr(), EPS,
+                                          count, st)
+        want = 1.0 / np.sqrt(var.astype(np.float64) + np.float64(np.float32(EPS)))
+        assert_close(to_numpy(inv), want, 1e-6, 0)
+    keep = torch.full((4,), 3.0, device="cuda")
+    kernel_lib.LaunchBesselCorrection(keep.data_ptr(), 2.0, 0, st)      # empty: untouched
+    torch.cuda.synchronize()
+    assert float(keep.sum()) == 12.0
 
 
 # ------------------------------------------------ cross-replica (split) API --
 
 def _split_forward_and_grad(lib, x, dy, scale, offset, parts, fused=False):
     """Runs the SyncBN halves on `parts` row blocks as if they were replicas
-    and sums the per-replica sums on the host side of the all-reduce."""
+    and sums the per-replica sums on the host side of the all-reduce.
+    fused="moments": the replicas' [mean, M2, count] vectors are gathered and
+    merged instead (LaunchBnStatsMoments / MergeMoments / ApplyFromMoments)."""
+    if fused == "moments":
+        return _split_with_moments(lib, x, dy, scale, offset, parts)
     dt = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[x.dtype]
     rows, c = x.shape
     st = torch.cuda.current_stream().cuda_stream
@@ -315,9 +355,81 @@ def _split_forward_and_grad(lib, x, dy, scale, offset, parts, fused=False):
     return y, bm, bv, sm, sv, dx, dscale, doffset
 
 
+def _split_with_moments(lib, x, dy, scale, offset, parts):
+    dt = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[x.dtype]
+    rows, c = x.shape
+    st = torch.cuda.current_stream().cuda_stream
+    bounds = np.linspace(0, rows, parts + 1).astype(int)
+    need = lib.BnWorkspaceBytes(rows, c, 1)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    gathered = torch.zeros(parts, 2 * c + 1, device="cuda")
+    for q, (lo, hi) in enumerate(zip(bounds[:-1], bounds[1:])):
+        assert lib.LaunchBnStatsMoments(dt, x[lo:hi].data_ptr(), gathered[q].data_ptr(),
+                                        int(hi - lo), c, 1, ws.data_ptr(), ws.numel(), st) == 0
+    merged = torch.empty(2 * c + 1, device="cuda")
+    assert lib.LaunchBnMergeMoments(gathered.data_ptr(), parts, c, merged.data_ptr(), st) == 0
+    assert float(merged[2 * c]) == float(rows)
+    bm, bv, sm, sv = (torch.empty(c, device="cuda") for _ in range(4))
+    y = torch.empty_like(x)
+    gtotal = torch.zeros(2 * c, device="cuda")
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        assert lib.LaunchBnApplyFromMoments(
+            dt, x[lo:hi].data_ptr(), scale.data_ptr(), offset.data_ptr(), merged.data_ptr(),
+            float(rows), None, None, 1.0, y[lo:hi].data_ptr(), bm.data_ptr(), bv.data_ptr(),
+            sm.data_ptr(), sv.data_ptr(), int(hi - lo), c, 1, EPS, st) == 0
+        sums = torch.empty(2 * c, device="cuda")
+        assert lib.LaunchBnGradStatsSums(dt, dy[lo:hi].data_ptr(), x[lo:hi].data_ptr(),
+                                         sm.data_ptr(), sums.data_ptr(), int(hi - lo), c, 1,
+                                         ws.data_ptr(), ws.numel(), st) == 0
+        gtotal += sums
+    dx = torch.empty_like(x)
+    dscale, doffset = torch.empty(c, device="cuda"), torch.empty(c, device="cuda")
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        assert lib.LaunchBnGradApplyFromSums(
+            dt, dy[lo:hi].data_ptr(), x[lo:hi].data_ptr(), scale.data_ptr(), sm.data_ptr(),
+            sv.data_ptr(), gtotal.data_ptr(), float(rows), dx[lo:hi].data_ptr(),
+            dscale.data_ptr(), doffset.data_ptr(), int(hi - lo), c, 1, EPS, st) == 0
+    return y, bm, bv, sm, sv, dx, dscale, doffset
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+def test_merged_moments_keep_the_variance_when_the_mean_is_large(kernel_lib, layout):
+    """|mean| / std = 1000, four replicas: the statistics of the merged
+    moments meet the tolerance of the single-GPU op (raw fp32 [sum x, sum x^2]
+    would have no correct digit left in the variance)."""
+    rng = np.random.default_rng(77)
+    rows, c = 4096, 64
+    x = (rng.standard_normal((rows, c)) + 1e3).astype(np.float32)
+    want = np_ref.fused_batch_norm(x, np.ones(c, np.float32), np.zeros(c, np.float32),
+                                   epsilon=EPS)
+    st = torch.cuda.current_stream().cuda_stream
+    parts = 4
+    gathered = torch.zeros(parts, 2 * c + 1, device="cuda")
+    per = rows // parts
+    for q in range(parts):
+        blk = x[q * per:(q + 1) * per]
+        if layout == "NCHW":     # [n, C, 4] view of the same values per channel
+            t = to_torch(np.ascontiguousarray(blk.reshape(per // 4, 4, c).transpose(0, 2, 1)))
+            outer, inner = per // 4, 4
+        else:
+            t = to_torch(blk)
+            outer, inner = per, 1
+        need = kernel_lib.BnWorkspaceBytes(outer, c, inner)
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+        assert kernel_lib.LaunchBnStatsMoments(0, t.data_ptr(), gathered[q].data_ptr(), outer,
+                                               c, inner, ws.data_ptr(), ws.numel(), st) == 0
+    merged = torch.empty(2 * c + 1, device="cuda")
+    assert kernel_lib.LaunchBnMergeMoments(gathered.data_ptr(), parts, c, merged.data_ptr(),
+                                           st) == 0
+    m = to_numpy(merged)
+    assert m[2 * c] == rows
+    assert_close(m[:c], want[3], 1e-6, 0, "mean")
+    assert_close(m[c:2 * c] / rows, want[4], 1e-4, 0, "variance")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("parts", [1, 2, 8])
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "moments"])
 def test_split_api_equals_global_batchnorm(kernel_lib, dtype, parts, fused):
     x, s, o, dy = bn_inputs(16, (4096, 64), dtype, 0.0, 1.0)
     got = _split_forward_and_grad(kernel_lib, to_torch(x), to_torch(dy), to_torch(s),

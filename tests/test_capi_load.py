@@ -102,3 +102,28 @@ def test_loader_finds_library_on_ld_library_path(monkeypatch, tmp_path):
     monkeypatch.setattr(_loader, "PLUGIN_LIBRARY", "libfake_plugin.so")
     monkeypatch.setenv("LD_LIBRARY_PATH", str(tmp_path))
     assert _loader._find_plugin_library() == str(fake)
+
+
+def test_launcher_tracing_counts_calls_and_bytes(kernel_lib):
+    """Tracing is off unless asked for; switched on, every launcher call adds
+    to its counters (calls, algorithmic bytes).  Calls that return before any
+    CUDA work (empty inputs) are enough to see that without a device."""
+    from tensorflow_musa_extension_b200 import _capi
+    was = kernel_lib.MusaKernelsTraceEnable(0)
+    kernel_lib.MusaKernelsTraceReset()
+    assert kernel_lib.LaunchBiasAct_F32(None, None, None, 0, 4, 1, 0, None) == 0
+    before = _capi.trace_snapshot(kernel_lib)
+    assert all(v["calls"] == 0 for v in before.values())        # off: nothing counted
+    kernel_lib.MusaKernelsTraceEnable(1)
+    try:
+        for _ in range(3):
+            assert kernel_lib.LaunchBiasAct_F32(None, None, None, 0, 4, 1, 0, None) == 0
+        kernel_lib.LaunchRmsNormFloat(None, None, None, None, None, 0, 128, 1e-5, None)
+        snap = _capi.trace_snapshot(kernel_lib)
+        assert snap["LaunchBiasAct"]["calls"] == 3 and snap["LaunchBiasAct"]["bytes"] == 0
+        assert snap["LaunchRmsNorm"]["calls"] == 1
+        assert snap["LaunchBiasAct"]["host_ns"] >= 0
+        kernel_lib.MusaKernelsTraceReset()
+        assert _capi.trace_snapshot(kernel_lib)["LaunchBiasAct"]["calls"] == 0
+    finally:
+        kernel_lib.MusaKernelsTraceEnable(was)

@@ -43,7 +43,7 @@ def _run(mode, world=2):
         assert "rank %d ok" % rank in out
 
 
-@pytest.mark.parametrize("mode", ["syncbn", "syncbn_ragged", "adam_even", "adam_padded"])
+@pytest.mark.parametrize("mode", ["syncbn", "syncbn_ragged", "syncbn_large_mean", "adam_even", "adam_padded"])
 def test_two_ranks(mode):
     _run(mode)
 

@@ -23,7 +23,7 @@ def _vectors(world, n, seed):
 def test_every_replica_gets_the_rank_ordered_sum(kernel_lib, world, n):
     host, dev, table = _vectors(world, n, world * 1000 + n)
     st = torch.cuda.current_stream().cuda_stream
-    assert kernel_lib.MusaExchangeSelfTest(world, n, table.data_ptr(), 1, -1, st) == 0
+    assert kernel_lib.MusaExchangeSelfTest(world, n, table.data_ptr(), 1, -1, 0, st) == 0
     want = np.zeros(n, np.float32)
     for h in host:                          # rank order, fp32: bit-exact
         want = want + h
@@ -35,7 +35,7 @@ def test_back_to_back_rounds_reuse_the_two_slots(kernel_lib):
     world, n, rounds = 4, 513, 5
     host, dev, table = _vectors(world, n, 7)
     st = torch.cuda.current_stream().cuda_stream
-    assert kernel_lib.MusaExchangeSelfTest(world, n, table.data_ptr(), rounds, -1, st) == 0
+    assert kernel_lib.MusaExchangeSelfTest(world, n, table.data_ptr(), rounds, -1, 0, st) == 0
     # every round replaces each vector by the sum of all: total * world^(rounds-1)
     total = np.zeros(n, np.float32)
     for h in host:
@@ -46,14 +46,52 @@ def test_back_to_back_rounds_reuse_the_two_slots(kernel_lib):
         assert torch.equal(d, dev[0])       # identical on every replica
 
 
-def test_a_missing_replica_is_reported_not_waited_for_forever(kernel_lib):
-    world, n = 3, 64
+@pytest.mark.parametrize("n", [64, 4097])
+def test_a_missing_replica_is_reported_not_waited_for_forever(kernel_lib, n):
+    """One wait (about a second) runs out, the kernel reports the replica and
+    stops waiting for it: the other cells of that replica cost nothing more."""
+    import time
+    world = 3
     _, dev, table = _vectors(world, n, 9)
     st = torch.cuda.current_stream().cuda_stream
-    rc = kernel_lib.MusaExchangeSelfTest(world, n, table.data_ptr(), 1, world - 1, st)
-    assert rc == 1000 + world               # 1000 + 1 + q with q = world - 1
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rc = kernel_lib.MusaExchangeSelfTest(world, n, table.data_ptr(), 1, world - 1, 0, st)
     torch.cuda.synchronize()                # the context is still usable
+    elapsed = time.perf_counter() - t0
+    assert rc == 1000 + world               # 1000 + 1 + q with q = world - 1
+    assert elapsed < 4.0, elapsed
     assert torch.isfinite(dev[0]).all()
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("channels", [1, 64, 2048])
+def test_moments_mode_merges_in_rank_order(kernel_lib, world, channels):
+    """Every replica ends with the moments of the union of all replicas' rows:
+    count-weighted mean, M2 by Chan's formula (fp64 reference)."""
+    rng = np.random.default_rng(world * 100 + channels)
+    n = 2 * channels + 1
+    host = []
+    for q in range(world):
+        rows = float(rng.integers(1, 5000))
+        v = np.concatenate([rng.normal(1e3, 1.0, channels), rng.uniform(0, 1e4, channels),
+                            [rows]]).astype(np.float32)
+        host.append(v)
+    dev = [torch.from_numpy(h).cuda() for h in host]
+    table = torch.tensor([d.data_ptr() for d in dev], dtype=torch.int64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert kernel_lib.MusaExchangeSelfTest(world, n, table.data_ptr(), 1, -1, 1, st) == 0
+    g = np.stack(host).astype(np.float64)
+    cnt = g[:, 2 * channels]
+    total = cnt.sum()
+    mean = (cnt[:, None] * g[:, :channels]).sum(0) / total
+    m2 = (g[:, channels:2 * channels] + cnt[:, None] * (g[:, :channels] - mean) ** 2).sum(0)
+    for d in dev:
+        got = d.cpu().numpy().astype(np.float64)
+        assert got[2 * channels] == total
+        np.testing.assert_allclose(got[:channels], mean, rtol=1e-6)
+        np.testing.assert_allclose(got[channels:2 * channels], m2, rtol=1e-5, atol=1e-3)
+        assert torch.equal(d, dev[0])       # bit-identical on every replica
 
 
 def test_single_replica_handle_round_trip(kernel_lib):

@@ -18,6 +18,28 @@ def test_adam_matches_reference_numpy_statement(golden, case):
     assert_close(var, g[case + "/expected_var"], 1e-6, what="var")
 
 
+@pytest.mark.parametrize("case", ["step10", "first_step_guard", "step1"])
+def test_adam_double_op_chain_matches_reference_numpy_statement(golden, case):
+    """The float64 restatement of the reference's op chain (T = double) against
+    the reference's own NumPy statement of the update: the same inputs widened
+    to double agree with its float32 answers to float32 rounding."""
+    g = golden["adam_reference_numpy"]
+    s = [float(x) for x in g[case + "/scalars"]]
+    var, m, v = np_ref.apply_adam_op_chain(g[case + "/var"], g[case + "/m"], g[case + "/v"],
+                                           s[0], s[1], s[2], s[3], s[4], s[5],
+                                           g[case + "/grad"])
+    assert var.dtype == np.float64
+    # (absolute floors: the float32 roundings of the golden's own terms)
+    assert_close(m, g[case + "/expected_m"], 2e-7, 1e-10, what="m")
+    assert_close(v, g[case + "/expected_v"], 2e-7, 1e-14, what="v")
+    assert_close(var, g[case + "/expected_var"], 1e-6, 1e-8, what="var")
+    # Nesterov numerator: m * beta1 + g * (1 - beta1) (TensorFlow's CPU kernel).
+    nv, nm, _ = np_ref.apply_adam_op_chain(g[case + "/var"], g[case + "/m"], g[case + "/v"],
+                                           s[0], s[1], s[2], s[3], s[4], s[5],
+                                           g[case + "/grad"], use_nesterov=True)
+    assert np.array_equal(nm, m) and not np.array_equal(nv, var)
+
+
 def test_adam_first_step_guard_uses_lr():
     assert np_ref.adam_alpha(1e-3, 1.0, 1.0) == np.float32(1e-3)
     a = np_ref.adam_alpha(1e-3, 0.9, 0.999)

@@ -16,6 +16,7 @@ import pytest
 import torch
 
 from helpers import RTOL, assert_close, bn_inputs, to_numpy, to_torch
+from oracle import np_ref
 
 pytestmark = pytest.mark.gpu
 
@@ -63,6 +64,12 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point(kernel_lib, dtype):
             scale_ = float(np.sqrt(np.mean(w_np.astype(np.float64) ** 2))) or 1.0
             assert_close(to_numpy(g), w_np, rt if name == "y" else RTOL["f32_bn"],
                          1e-6 * scale_, "%s seed %d" % (name, seed))
+        # ... and what the CPU oracle returns for the same inputs.
+        oracle = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
+        for name, g, w in zip(names, got, oracle):
+            rms = float(np.sqrt(np.mean(np.asarray(w, np.float64) ** 2))) or 1.0
+            r = rt if name == "y" else RTOL["f32_bn"]
+            assert_close(to_numpy(g), w, r, r * rms, "oracle %s seed %d" % (name, seed))
 
 
 def test_sizes_beyond_the_scratch_are_refused(kernel_lib):
