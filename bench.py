@@ -300,13 +300,14 @@ def run_ours(args):
     sync_kind = "none (1 GPU)"
     if world > 1:
         sync_kind = "nccl all-reduce of 2*C(+1) fp32 per layer and pass"
-        if args.sync == "peer":
+        if args.sync in ("peer", "peer_kernel"):
             from tensorflow_musa_extension_b200.cross_replica import PeerExchange
             try:
                 exchange = PeerExchange(dist.group.WORLD, 2 * max(c for (_, _, c) in layers) + 1,
                                         dev)
-                sync_kind = ("peer-memory exchange kernel (NVLink stores into every replica, "
-                             "bounded wait, rank-ordered sum) of 2*C(+1) fp32 per layer and pass")
+                sync_kind = ("peer-memory exchange inside the finalize kernel (NVLink stores "
+                             "into every replica, bounded wait, rank-ordered merge) of "
+                             "2*C(+1) fp32 per layer and pass")
             except Exception as e:  # not one node / no peer access
                 if rank == 0:
                     print("peer exchange unavailable (%r): using NCCL" % (e,), file=sys.stderr)
@@ -314,6 +315,12 @@ def run_ours(args):
                          max_rows=BATCH * h * w, group=(dist.group.WORLD if world > 1 else None),
                          exchange=exchange)
            for (h, w, c) in layers]
+    if args.sync == "peer_kernel":
+        for b in bns:
+            b.fuse_exchange = False
+        if exchange is not None:
+            sync_kind = ("peer-memory exchange kernel (NVLink stores into every replica, bounded "
+                         "wait, rank-ordered merge) of 2*C(+1) fp32 per layer and pass")
 
     def step():
         for i in range(n_layers):
@@ -331,8 +338,9 @@ def run_ours(args):
             b.force_split = True
             b.exchange = exchange
         sync_kind = "split launch chain on one replica (%s)" % args.force_split
-    launches_per_step = sum(b.launches_per_step for b in bns) + \
-        (2 * n_layers if exchange is not None else 0)
+    # Three kernels per pass (statistics, finalize, element-wise); with the
+    # peer exchange the finalize kernel runs the exchange itself.
+    launches_per_step = sum(b.launches_per_step for b in bns)
 
     if args.profile_step:
         # One eager pass and nothing else: the target of an ncu launch list.
@@ -343,7 +351,7 @@ def run_ours(args):
     parity = None
     if world > 1:
         parity = check_multi_gpu_parity(torch, dist, world, rank, dev, exchange,
-                                        dist.group.WORLD)
+                                        dist.group.WORLD, args.adam_multicast)
         if rank == 0 and not (parity[0] and parity[1] in (True, None)):
             print(json.dumps({"error": "multi-GPU parity check failed", "sync_parity": parity[0],
                               "adam_shard_parity": parity[1], "detail": parity[2]}), flush=True)
@@ -586,7 +594,8 @@ def _gather_rows(torch, dist, t, world):
     return torch.cat(parts, 0)
 
 
-def check_multi_gpu_parity(torch, dist, world, rank, dev, exchange, group):
+def check_multi_gpu_parity(torch, dist, world, rank, dev, exchange, group,
+                           with_multicast=False):
     """Before anything is timed at N > 1: one small cross-replica BatchNorm
     layer (forward + gradient, bf16 and fp32) and three steps of the
     range-sharded Adam, each compared with the CPU oracle on the WHOLE problem
@@ -657,27 +666,36 @@ def check_multi_gpu_parity(torch, dist, world, rank, dev, exchange, group):
 
     adam_ok = None
     if exchange is not None:
+        adam_ok = True
         n = 1_000_003
-        arng = np.random.default_rng(31)
-        var0 = arng.normal(0, 0.05, n).astype(np.float32)
-        pv = cr.PeerVector(group, n, dev)
-        pv.tensor.copy_(torch.from_numpy(var0).to(dev))
-        torch.cuda.synchronize()
-        dist.barrier()
-        opt = cr.FusedShardedAdam(pv, exchange)
-        ev, em, evv = var0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
-        for step in range(1, 4):
-            g = arng.normal(0, 1e-3, n).astype(np.float32)
-            ev, em, evv = np_ref.apply_adam(ev, em, evv, 0.9 ** step, 0.999 ** step, 1e-3,
-                                            0.9, 0.999, 1e-7, g)
-            opt.step(torch.from_numpy(g).to(dev), 1e-3, 0.9 ** step, 0.999 ** step)
-        torch.cuda.synchronize()
-        got = pv.tensor.cpu().numpy().astype(np.float64)
-        err = float(np.max(np.abs(got - ev) / (1e-8 + 1e-5 * np.abs(ev))))
-        details["adam_shard_worst_over_tolerance"] = round(err, 4)
-        adam_ok = err <= 1.0
-        dist.barrier()
-        pv.close()
+        for want_multicast in ((True, False) if with_multicast else (False,)):
+            arng = np.random.default_rng(31)
+            var0 = arng.normal(0, 0.05, n).astype(np.float32)
+            pv = cr.PeerVector(group, n, dev, multicast=want_multicast)
+            if want_multicast and not pv.multicast_ptr:
+                details["adam_shard_multicast"] = "no multicast mapping on this node"
+                pv.close()
+                continue
+            pv.tensor.copy_(torch.from_numpy(var0).to(dev))
+            torch.cuda.synchronize()
+            dist.barrier()
+            opt = cr.FusedShardedAdam(pv, exchange,
+                                      transport="multicast" if want_multicast else "stores")
+            ev, em, evv = var0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+            for step in range(1, 4):
+                g = arng.normal(0, 1e-3, n).astype(np.float32)
+                ev, em, evv = np_ref.apply_adam(ev, em, evv, 0.9 ** step, 0.999 ** step, 1e-3,
+                                                0.9, 0.999, 1e-7, g)
+                opt.step(torch.from_numpy(g).to(dev), 1e-3, 0.9 ** step, 0.999 ** step)
+            torch.cuda.synchronize()
+            dist.barrier()
+            got = pv.tensor.cpu().numpy().astype(np.float64)
+            err = float(np.max(np.abs(got - ev) / (1e-8 + 1e-5 * np.abs(ev))))
+            details["adam_shard_%s_worst_over_tolerance" % opt.transport] = round(err, 4)
+            adam_ok = adam_ok and err <= 1.0
+            opt.close()
+            dist.barrier()
+            pv.close()
     flags = torch.tensor([1.0 if sync_ok else 0.0, 1.0 if adam_ok in (True, None) else 0.0],
                          device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
@@ -720,10 +738,13 @@ def measure_adam_sharded(torch, dist, world, rank, dev, exchange, args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
         hbm = 28.0 * n / world
+        # Bytes every GPU has to RECEIVE over NVLink (the other replicas'
+        # ranges) - with unicast stores also what it sends; a multicast store
+        # sends less but cannot receive less.
         link = 4.0 * n / world * (world - 1)
         bound_ms = max(hbm / (peak * 1e9), link / (nvlink_gbs * 1e9)) * 1e3
         out[label] = {"ms_per_step": round(ms, 4), "gelem_per_s": round(n / (ms * 1e-3) / 1e9, 2),
-                      "hbm_bytes_per_gpu": int(hbm), "nvlink_bytes_out_per_gpu": int(link),
+                      "hbm_bytes_per_gpu": int(hbm), "nvlink_bytes_in_per_gpu": int(link),
                       "bound_ms": round(bound_ms, 4), "frac_of_bound": round(bound_ms / ms, 3)}
 
     # (a) update, then NCCL all-gather in place
@@ -746,13 +767,19 @@ def measure_adam_sharded(torch, dist, world, rank, dev, exchange, args):
     # while the next chunk updates ("copies").  Each is replayed from a CUDA
     # graph (the step is a fixed launch sequence), eager when capture fails.
     if exchange is not None:
-        for label, transport, chunks in (
-                ("fused_update_and_peer_broadcast", "stores", 1),
-                ("update_and_copy_engine_broadcast_2_chunks", "copies", 2),
-                ("update_and_copy_engine_broadcast_4_chunks", "copies", 4)):
+        variants = [("fused_update_and_peer_broadcast", "stores", 1),
+                    ("update_and_copy_engine_broadcast_2_chunks", "copies", 2)]
+        if args.adam_multicast:
+            variants.append(("fused_update_and_multicast_store", "multicast", 1))
+        for label, transport, chunks in variants:
             pv = fopt = None
             try:
-                pv = cr.PeerVector(dist.group.WORLD, n, dev)
+                pv = cr.PeerVector(dist.group.WORLD, n, dev, multicast=(transport == "multicast"))
+                if transport == "multicast" and not pv.multicast_ptr:
+                    out[label] = {"unavailable": "no multicast mapping on this node"}
+                    pv.close()
+                    pv = None
+                    continue
                 pv.tensor.normal_(0, 0.05, generator=gen)
                 fopt = cr.FusedShardedAdam(pv, exchange, transport=transport, chunks=chunks)
                 fshard = fopt.hi - fopt.lo
@@ -1154,6 +1181,135 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_probe(args):
+    """Measurements of the machine that the bounds quoted beside the results
+    rest on (not part of the timed benchmark):
+      peer_copy  one-directional cudaMemcpyAsync rate between two GPUs, and the
+                 rate per GPU when every GPU sends a block to every other GPU at
+                 once (the traffic pattern of the range-sharded Adam); N >= 2
+      pcie       pinned host <-> device copy rates per GPU, one direction at a
+                 time and both at once, with all N ranks copying simultaneously
+                 (the bound of the end-to-end leg)"""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    arm_watchdog(args.watchdog)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+    import tensorflow_musa_extension_b200 as pkg
+    from tensorflow_musa_extension_b200 import raw_ops
+    from tensorflow_musa_extension_b200 import cross_replica as cr
+    pkg.load_plugin()
+    lib = raw_ops._lib()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed_ms(fn, iters):
+        """Max over ranks of the device time of `iters` calls of fn()."""
+        for _ in range(2):
+            fn()
+        sync_all()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = {"probe": args.probe, "n_gpus": world}
+    if args.probe == "peer_copy":
+        if world < 2:
+            raise SystemExit("--probe peer_copy needs at least two ranks")
+        n = 64 << 20                               # floats: 256 MB per replica
+        pv = cr.PeerVector(dist.group.WORLD, n, dev, multicast=False)
+        src = torch.empty(n, device=dev).normal_()
+        main = torch.cuda.current_stream()
+        # (a) one pair, one direction: rank 0 -> rank 1, everybody else idle.
+        nbytes = n * 4
+
+        def one_way():
+            if rank == 0:
+                raw_ops._check(lib.MusaPeerCopyAsync(pv.replica_ptrs[1], src.data_ptr(), nbytes,
+                                                     main.cuda_stream), "MusaPeerCopyAsync")
+
+        ms = timed_ms(one_way, 10)
+        out["one_pair_one_direction_gbs"] = round(nbytes / (ms * 1e-3) / 1e9, 1)
+        # (b) every GPU sends a block to every other GPU at once, one copy per
+        # peer on its own stream (block = 1 / world of the buffer).
+        block = n // world
+        sides = [torch.cuda.Stream() for _ in range(world - 1)]
+
+        def all_to_all():
+            ev = torch.cuda.Event()
+            ev.record(main)
+            for k in range(1, world):
+                q = (rank + k) % world
+                st = sides[k - 1]
+                st.wait_event(ev)
+                dst = pv.replica_ptrs[q] + rank * block * 4
+                raw_ops._check(lib.MusaPeerCopyAsync(dst, src.data_ptr() + rank * block * 4,
+                                                     block * 4, st.cuda_stream),
+                               "MusaPeerCopyAsync")
+            for st in sides:
+                main.wait_stream(st)
+
+        ms = timed_ms(all_to_all, 10)
+        out["all_to_all_block_mb"] = round(block * 4 / 1e6, 1)
+        out["all_to_all_egress_gbs_per_gpu"] = round((world - 1) * block * 4 / (ms * 1e-3) / 1e9, 1)
+        sync_all()
+        pv.close()
+    elif args.probe == "pcie":
+        nbytes = 1 << 30
+        h_up = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+        h_down = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+        d_up = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        d_down = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+        main = torch.cuda.current_stream()
+
+        def up():
+            d_up.copy_(h_up, non_blocking=True)
+
+        def down():
+            h_down.copy_(d_down, non_blocking=True)
+
+        def both():
+            s_up.wait_stream(main)
+            s_down.wait_stream(main)
+            with torch.cuda.stream(s_up):
+                d_up.copy_(h_up, non_blocking=True)
+            with torch.cuda.stream(s_down):
+                h_down.copy_(d_down, non_blocking=True)
+            main.wait_stream(s_up)
+            main.wait_stream(s_down)
+
+        for name, fn in (("h2d", up), ("d2h", down), ("both_each_way", both)):
+            ms = timed_ms(fn, 5)
+            out[name + "_gbs_per_gpu"] = round(nbytes / (ms * 1e-3) / 1e9, 1)
+        out["note"] = ("all %d ranks copy at the same time; rates are per GPU and direction, "
+                       "from the slowest rank" % world)
+        out["host_cores"] = len(os.sched_getaffinity(0))
+    else:
+        raise SystemExit("unknown --probe " + args.probe)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    finish(torch, dist, world)
+
+
 def run_profile_case(args):
     """Small fixed launch sequences for `ncu` captures (one kernel family per
     case, inputs beyond L2, a few hundred MB on the device):
@@ -1290,14 +1446,24 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--watchdog", type=int, default=600,
                     help="seconds after which a run that has not finished is ended")
-    ap.add_argument("--sync", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: how the per-channel sums cross the replicas")
+    ap.add_argument("--sync", default="peer", choices=["peer", "peer_kernel", "nccl"],
+                    help="N > 1: how the per-channel values cross the replicas: peer-memory "
+                         "exchange run by the finalize kernel (peer), by its own kernel "
+                         "(peer_kernel), or an NCCL collective")
+    ap.add_argument("--adam-multicast", action="store_true",
+                    help="N > 1: also check and time the NVSwitch-multicast transport of the "
+                         "sharded Adam step (torch symmetric memory)")
     ap.add_argument("--force-split", default="off", choices=["off", "bare", "exchange"],
                     help="N = 1 diagnostic: run the cross-replica launch chain anyway")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed launch sequence and exit (ncu target): "
                          "bn | bnsmall | bnbig | adam | bias | biasgrad | optim | rownorm")
+    ap.add_argument("--probe", default=None, choices=["peer_copy", "pcie"],
+                    help="measure a machine rate that a quoted bound rests on, and exit")
     args = ap.parse_args()
+    if args.probe:
+        run_probe(args)
+        return
     if args.profile_case:
         run_profile_case(args)
         return

@@ -624,7 +624,12 @@ int LaunchBnApply(int dtype, const void* x, const float* scale,
                   float epsilon, cudaStream_t stream);
 /* LaunchBnFinalizeFromSums and LaunchBnApply as one launch: the element-wise
  * kernel derives mean and variance from the all-reduced sums in its prologue
- * and writes the four statistic outputs itself. */
+ * and writes the four statistic outputs itself.  `x` must be the tensor whose
+ * statistics the LaunchBnStats* call before it on `stream` took, unchanged
+ * since: the kernel requests its first rows of x while it still waits for the
+ * kernel that delivers `sums` (the same holds for LaunchBnApplyFromMoments,
+ * and for dy and x of LaunchBnGradApplyFromSums after
+ * LaunchBnGradStatsSums*). */
 int LaunchBnApplyFromSums(int dtype, const void* x, const float* scale,
                           const float* offset, const float* sums,
                           double total_count, const float* est_mean,
@@ -675,6 +680,23 @@ int LaunchExchangeSums(void* handle, float* vector, int64_t n, cudaStream_t stre
 int LaunchExchangeMoments(void* handle, float* moments, int64_t channels,
                           cudaStream_t stream);
 int MusaExchangeStatus(void* handle);
+/* LaunchBnStatsMoments + LaunchExchangeMoments, and LaunchBnGradStatsSums +
+ * LaunchExchangeSums, without the exchange kernel: the finalize kernel of the
+ * statistics pass pushes the values of its own channels to the replicas, waits
+ * (bounded, same status word) for theirs and writes the result over ALL
+ * replicas into `moments` (2C + 1 floats) / `sums` (2C floats).  One kernel and
+ * two kernel boundaries less in every cross-replica BatchNorm pass.  Every
+ * replica must call with the same `channels`, in the same order as its other
+ * exchanges on `exchange`. */
+int LaunchBnStatsMomentsExchange(int dtype, const void* x, float* moments, int64_t outer,
+                                 int64_t channels, int64_t inner, void* workspace,
+                                 size_t workspace_bytes, void* exchange,
+                                 cudaStream_t stream);
+int LaunchBnGradStatsSumsExchange(int dtype, const void* dy, const void* x,
+                                  const float* mean, float* sums, int64_t outer,
+                                  int64_t channels, int64_t inner, void* workspace,
+                                  size_t workspace_bytes, void* exchange,
+                                  cudaStream_t stream);
 void MusaExchangeDestroy(void* handle);
 /* Peer-visible device memory for the set-up of the two peer-memory paths: a
  * cudaMalloc block, its 64-byte CUDA IPC handle, and the mapping of another
@@ -684,6 +706,8 @@ int MusaPeerFree(void* ptr);
 int MusaPeerIpcHandle(void* ptr, void* out64);
 void* MusaPeerOpen(const void* handle64);
 int MusaPeerClose(void* mapped);
+/* One cudaMemcpyAsync (device to device, local or peer-mapped addresses). */
+int MusaPeerCopyAsync(void* dst, const void* src, int64_t bytes, cudaStream_t stream);
 
 /* Range-sharded ResourceApplyAdam (fp32) fused with the all-gather of the
  * updated weights: updates var[lo, lo + n) from this replica's m, v (n
@@ -699,6 +723,19 @@ int LaunchAdamShardBroadcastFloat(float* const* var_replicas, int world, int ran
                                   int64_t lo, float* m, float* v, const float* grad,
                                   float beta1, float beta2, float epsilon, float alpha,
                                   int64_t n, cudaStream_t stream);
+
+/* The same step over an NVSwitch multicast mapping of the replicas' copies
+ * (`var_multicast`: the multicast address of the vector's base, e.g. from
+ * torch.distributed._symmetric_memory; `var_local`: this replica's own copy):
+ * one multimem.st per 128-bit pack writes the new weights into every replica,
+ * so the shard leaves the GPU once instead of world - 1 times and the step is
+ * bound by HBM again.  Needs lo % 4 == 0 and 16-byte aligned pointers
+ * (MUSA_KERNELS_EINVAL otherwise).  Same results and completion rule as
+ * LaunchAdamShardBroadcastFloat.  No counterpart in the reference. */
+int LaunchAdamShardMulticastFloat(float* var_local, float* var_multicast, int64_t lo,
+                                  float* m, float* v, const float* grad, float beta1,
+                                  float beta2, float epsilon, float alpha, int64_t n,
+                                  cudaStream_t stream);
 
 /* The same step with the copy engines as the all-gather, for four replicas
  * and more, where the step is bound by the bytes that leave the GPU over

@@ -144,15 +144,23 @@ PROTOTYPES.update({
     "MusaExchangeStatus": (c_int, [c_vp]),
     "MusaExchangeDestroy": (None, [c_vp]),
     "LaunchExchangeMoments": (c_int, [c_vp, c_vp, c_i64, c_vp]),
+    "LaunchBnStatsMomentsExchange":
+        (c_int, [c_int, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp, c_vp]),
+    "LaunchBnGradStatsSumsExchange":
+        (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_size, c_vp,
+                 c_vp]),
     "MusaExchangeSelfTest": (c_int, [c_int, c_i64, c_vp, c_int, c_int, c_int, c_vp]),
     "MusaPeerAlloc": (c_vp, [c_i64]),
     "MusaPeerFree": (c_int, [c_vp]),
     "MusaPeerIpcHandle": (c_int, [c_vp, c_vp]),
     "MusaPeerOpen": (c_vp, [c_vp]),
     "MusaPeerClose": (c_int, [c_vp]),
+    "MusaPeerCopyAsync": (c_int, [c_vp, c_vp, c_i64, c_vp]),
     "LaunchAdamShardBroadcastFloat":
         (c_int, [c_vp, c_int, c_int, c_i64, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32,
                  c_i64, c_vp]),
+    "LaunchAdamShardMulticastFloat":
+        (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_i64, c_vp]),
     "MusaShardPipeCreate": (c_vp, [c_int, c_int]),
     "MusaShardPipeDestroy": (None, [c_vp]),
     "LaunchAdamShardCopyFloat":

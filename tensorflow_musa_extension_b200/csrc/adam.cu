@@ -253,6 +253,73 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// ---- The same step through an NVSwitch multicast mapping: one `multimem.st`
+// per pack writes the new weights into the copy of EVERY replica (the switch
+// replicates the store), so the shard leaves the GPU once instead of once per
+// peer, and the step is no longer bound by NVLink egress.
+__device__ __forceinline__ void MulticastStore4(float* mc, const Pack<float, 4>& p) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc),
+               "f"(p.v[0]), "f"(p.v[1]), "f"(p.v[2]), "f"(p.v[3])
+               : "memory");
+}
+__device__ __forceinline__ void MulticastStore1(float* mc, float v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc), "f"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(256)
+    AdamShardMulticastKernel(const float* __restrict__ var_local, float* __restrict__ var_mc,
+                             float* __restrict__ m, float* __restrict__ v,
+                             const float* __restrict__ grad, AdamParams p, int64_t n) {
+  GridDepWait();
+  GridDepLaunch();
+  using SPack = Pack<float, 4>;
+  constexpr int kUnroll = 2;
+  const int64_t n_packs = n / 4;
+  const int64_t tile = static_cast<int64_t>(blockDim.x) * kUnroll;
+  const int64_t n_tiles = (n_packs + tile - 1) / tile;
+  const SPack* var_p = reinterpret_cast<const SPack*>(var_local);
+  SPack* m_p = reinterpret_cast<SPack*>(m);
+  SPack* v_p = reinterpret_cast<SPack*>(v);
+  const SPack* g_p = reinterpret_cast<const SPack*>(grad);
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int64_t base = t * tile + threadIdx.x;
+    SPack pv[kUnroll], pm[kUnroll], pvv[kUnroll], pg[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+      if (i < n_packs) {
+        pg[u] = LoadStream(g_p + i);
+        pm[u] = LoadStream(m_p + i);
+        pvv[u] = LoadStream(v_p + i);
+        pv[u] = LoadStream(var_p + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+      if (i < n_packs) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          AdamStep<false>(pv[u].v[e], pm[u].v[e], pvv[u].v[e], pg[u].v[e], p);
+        }
+        StoreStream(m_p + i, pm[u]);
+        StoreStream(v_p + i, pvv[u]);
+        MulticastStore4(var_mc + i * 4, pv[u]);   // all replicas, this one included
+      }
+    }
+  }
+  if (blockIdx.x == 0) {
+    const int64_t i = n_packs * 4 + threadIdx.x;
+    if (threadIdx.x < 4 && i < n) {
+      float fvar = var_local[i], fm = m[i], fv = v[i];
+      AdamStep<false>(fvar, fm, fv, grad[i], p);
+      m[i] = fm;
+      v[i] = fv;
+      MulticastStore1(var_mc + i, fvar);
+    }
+  }
+}
+
 }  // namespace
 }  // namespace musa_b200
 
@@ -327,6 +394,42 @@ int LaunchAdamShardBroadcastFloat(float* const* var_replicas, int world, int ran
                   dim3(256), 0, stream, r, lo, m, v, grad, p, n);
   }
   return static_cast<int>(cudaGetLastError());
+}
+
+int LaunchAdamShardMulticastFloat(float* var_local, float* var_multicast, int64_t lo,
+                                  float* m, float* v, const float* grad, float beta1,
+                                  float beta2, float epsilon, float alpha, int64_t n,
+                                  cudaStream_t stream) {
+  if (var_local == nullptr || var_multicast == nullptr || lo < 0 || n < 0) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  MUSA_TRACE("LaunchAdamShardMulticast", 28 * n);
+  if (n == 0) return MUSA_KERNELS_OK;
+  if (m == nullptr || v == nullptr || grad == nullptr) return MUSA_KERNELS_EINVAL;
+  // 128-bit packs throughout: the range starts on a pack and every pointer is
+  // 16-byte aligned (the multicast store has no element-wise form here).
+  if (lo % 4 != 0 || !Aligned16(var_local) || !Aligned16(var_multicast) || !Aligned16(m) ||
+      !Aligned16(v) || !Aligned16(grad)) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  AdamParams p;
+  p.lr_t = alpha;
+  p.beta1 = beta1;
+  p.one_minus_b1 = 1.0f - beta1;
+  p.beta2 = beta2;
+  p.one_minus_b2 = 1.0f - beta2;
+  p.epsilon = epsilon;
+  int64_t blocks = CeilDiv(n / 4, 256 * 2);
+  if (blocks < 1) blocks = 1;
+  if (blocks > 0x7fffffffLL) blocks = 0x7fffffffLL;
+  const cudaError_t err = LaunchChained(
+      true, AdamShardMulticastKernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream,
+      static_cast<const float*>(var_local + lo), var_multicast + lo, m, v, grad, p, n);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return static_cast<int>(err);
+  }
+  return MUSA_KERNELS_OK;
 }
 
 // ---- Range-sharded Adam with the copy engines as the all-gather.  From four

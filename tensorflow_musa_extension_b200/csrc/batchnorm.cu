@@ -30,6 +30,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "exchange_dev.cuh"
 #include "trace.h"
 #include "tuning.h"
 #include "../../include/musa_plugin_kernels.h"
@@ -78,7 +79,7 @@ inline Plan PlanLast(int64_t rows, int64_t channels, int64_t cv, int unroll,
   if (p.tx > max_tx) p.tx = max_tx;
   p.ty = kThreads / p.tx;
   p.gx = static_cast<int>(CeilDiv(cv, p.tx));
-  int per_sm = GetTuning(kTuneBnCtasPerSm);
+  int per_sm = GetTuning(cap_by_workspace ? kTuneBnCtasPerSm : kTuneBnApplyCtasPerSm);
   if (per_sm < 1) per_sm = resident > 0 ? resident : 4;
   int64_t target = static_cast<int64_t>(SmCount()) * per_sm / p.gx;
   if (target < 1) target = 1;
@@ -255,6 +256,10 @@ struct FinalizeArgs {
   // both: totals for the apply pass / the all-reduce
   float* sums;           // [2, C] or NULL
   float* count_out;      // optional: receives `count` (rides in the all-reduce)
+  // Cross-replica: when set, the finalize kernel exchanges its channels' pair
+  // with the other replicas itself (moments are merged, gradient sums added)
+  // and everything it writes is the result over all replicas.
+  const ExchangeDev* xchg;
 };
 
 __device__ __forceinline__ float LoadAsF32(const void* base, int dtype,
@@ -816,9 +821,9 @@ __global__ void __launch_bounds__(kThreads)
 // kOut (a TailKind): forward statistics, forward raw sums (sum x, sum x^2),
 // gradient (dscale, doffset and/or sums), or the local moments (mean,
 // sum (x - mean)^2) for the cross-replica merge.
-// Block (8 channels, kLanes partial lanes): 32 lanes make a 256-thread CTA
-// that fits beside the draining statistics CTAs, so that a programmatic
-// launch can place it before they are gone; 128 lanes is the older shape.
+// Block (8 channels, kLanes partial lanes): 128 lanes (1024 threads) by
+// default; 32 lanes make a 256-thread CTA that fits beside the draining
+// statistics CTAs (measured the same to 1 % slower over the ResNet-50 step).
 template <int kOut, int kLanes>
 __global__ void __launch_bounds__(8 * kLanes) BnFinalizeKernel(FinalizeArgs a) {
   // Dependents first: the element-wise kernel that follows may take its place
@@ -836,6 +841,17 @@ __global__ void __launch_bounds__(8 * kLanes) BnFinalizeKernel(FinalizeArgs a) {
   float shift_k = 0.0f;
   if (kOut != 2 && tid < 8 && c < a.channels) {
     shift_k = LoadAsF32(a.x_first, a.x_dtype, c * a.shift_stride);
+  }
+  // In-kernel exchange: the epoch of this exchange, and the replicas an
+  // earlier exchange gave up on (not waited for again).
+  __shared__ unsigned dead;
+  unsigned epoch = 0;
+  if (a.xchg != nullptr && tid < 32) {
+    epoch = *a.xchg->epoch + 1u;
+    if (tid == 0) {
+      const int st = *reinterpret_cast<volatile int*>(a.xchg->status);
+      dead = st > 0 && st <= kMaxWorld ? 1u << (st - 1) : 0u;
+    }
   }
   double t1 = 0.0, t2 = 0.0;
   if (c < a.channels) {
@@ -918,25 +934,42 @@ __global__ void __launch_bounds__(8 * kLanes) BnFinalizeKernel(FinalizeArgs a) {
         a.sums[a.channels + c] =
             static_cast<float>(S2 + 2.0 * K * S1 + a.count * K * K);
       } else if constexpr (kOut == kTailFwdMoments) {
-        if (a.count_out != nullptr && c == 0) {
-          *a.count_out = static_cast<float>(a.count);
-        }
         const double md = S1 * inv_count;
         double m2 = S2 - md * S1;
         if (m2 < 0.0) m2 = 0.0;
-        a.sums[c] = static_cast<float>(static_cast<double>(shift_k) + md);
-        a.sums[a.channels + c] = static_cast<float>(m2);
-      } else {
-        if (a.sums) {
-          a.sums[c] = static_cast<float>(S1);
-          a.sums[a.channels + c] = static_cast<float>(S2);
+        float mean_f = static_cast<float>(static_cast<double>(shift_k) + md);
+        float m2_f = static_cast<float>(m2);
+        float count_f = static_cast<float>(a.count);
+        if (a.xchg != nullptr) {
+          ExchangeChannelPair<true>(*a.xchg, epoch, static_cast<int>(a.channels),
+                                    static_cast<int>(c), mean_f, m2_f, count_f, &dead, &mean_f,
+                                    &m2_f, &count_f);
         }
-        if (a.doffset) a.doffset[c] = static_cast<float>(S1);
+        if (a.count_out != nullptr && c == 0) *a.count_out = count_f;
+        a.sums[c] = mean_f;
+        a.sums[a.channels + c] = m2_f;
+      } else {
+        float s1_f = static_cast<float>(S1), s2_f = static_cast<float>(S2);
+        if (a.xchg != nullptr) {
+          float unused;
+          ExchangeChannelPair<false>(*a.xchg, epoch, static_cast<int>(a.channels),
+                                     static_cast<int>(c), s1_f, s2_f, 0.0f, &dead, &s1_f, &s2_f,
+                                     &unused);
+        }
+        if (a.sums) {
+          a.sums[c] = s1_f;
+          a.sums[a.channels + c] = s2_f;
+        }
+        if (a.doffset) a.doffset[c] = s1_f;
         if (a.dscale) {
           const float inv = 1.0f / sqrtf(a.variance[c] + a.epsilon);
-          a.dscale[c] = static_cast<float>(S2) * inv;
+          a.dscale[c] = s2_f * inv;
         }
       }
+    }
+    if (a.xchg != nullptr) {
+      __syncwarp();
+      if (lane == 0) ExchangeCloseInKernel(*a.xchg, epoch, gridDim.x);
     }
   }
 }
@@ -1457,9 +1490,10 @@ int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* workspace
     return n > 0 ? n : -1;
   });
   if (resident < 0) return EncodeCuda(cudaErrorInvalidValue);
-  // Column blocks of at most 32 packs (512-byte row segments, one warp wide):
-  // measured 1.5-3 % faster over the ResNet-50 step than blocks as wide as the
-  // row, which leave one row lane per CTA for the wide layers.
+  // Column blocks of at most 16 packs (256-byte row segments; the tuning
+  // table holds the width): measured 3 % faster over the ResNet-50 step than
+  // blocks as wide as the row, which leave one row lane per CTA for the wide
+  // layers.
   int max_tx = GetTuning(kTuneBnStatsMaxTx);
   if (max_tx <= 0) max_tx = kThreads;
   const Plan p = PlanLast(g.outer, g.channels, cv, Cfg::kU, true, resident, max_tx);
@@ -1884,7 +1918,7 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
 template <typename T>
 int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
               void* workspace, size_t workspace_bytes, int kind,
-              cudaStream_t stream) {
+              cudaStream_t stream, const ExchangeDev* xchg = nullptr) {
   MUSA_TRACE("LaunchBnStats", sizeof(T) * g.outer * g.channels * g.inner);
   if (!x || !sums) return MUSA_KERNELS_EINVAL;
   if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
@@ -1900,6 +1934,7 @@ int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
   f.shift_stride = g.inner == 1 ? 1 : g.inner;
   f.sums = sums;
   f.count_out = count_out;
+  f.xchg = xchg;
   if (int rc = RunStats<T, kFwd>(static_cast<const T*>(x), nullptr, nullptr, partial, g,
                                  f, kind, stream)) {
     return rc;
@@ -1910,7 +1945,7 @@ int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
 template <typename T>
 int GradStatsSums(const void* dy, const void* x, const float* mean, float* sums,
                   const Geom& g, void* workspace, size_t workspace_bytes,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const ExchangeDev* xchg = nullptr) {
   MUSA_TRACE("LaunchBnGradStats", 2 * sizeof(T) * g.outer * g.channels * g.inner);
   if (!dy || !x || !mean || !sums) return MUSA_KERNELS_EINVAL;
   if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
@@ -1922,6 +1957,7 @@ int GradStatsSums(const void* dy, const void* x, const float* mean, float* sums,
   f.channels = g.channels;
   SetCount(&f, static_cast<double>(g.rows()));
   f.sums = sums;
+  f.xchg = xchg;
   if (int rc = RunStats<T, kGrad>(static_cast<const T*>(x), static_cast<const T*>(dy),
                                   mean, partial, g, f, kTailGrad, stream)) {
     return rc;
@@ -1956,8 +1992,10 @@ int GradApplyFromSums(const void* dy, const void* x, const float* scale,
   a.epsilon = epsilon;
   a.sums = sums;
   a.inv_count = static_cast<float>(1.0 / total_count);
+  // dy and x were read by the preceding LaunchBnGradStatsSums* call on this
+  // stream: final before it (see ApplyFromSums).
   LaunchApply<T, kGrad>(static_cast<const T*>(x), static_cast<const T*>(dy),
-                        static_cast<T*>(dx), a, g, stream);
+                        static_cast<T*>(dx), a, g, stream, true);
   return LastError();
 }
 
@@ -2208,8 +2246,11 @@ int ApplyFromSums(int dtype, const void* x, const float* scale, const float* off
   a.stat_out.saved_mean = saved_mean;
   a.stat_out.saved_var = saved_var;
   a.stat_out.exp_avg_factor = exp_avg_factor;
+  // x is the tensor whose statistics the preceding launcher call on this
+  // stream took: it was final before that call, so the first rows may be
+  // requested before the wait for the kernel that delivers the statistics.
   MUSA_BY_DTYPE(dtype, (LaunchApply<T, kFwd>(static_cast<const T*>(x), nullptr,
-                                             static_cast<T*>(y), a, g, stream),
+                                             static_cast<T*>(y), a, g, stream, true),
                         LastError()));
 }
 }  // namespace
@@ -2254,6 +2295,54 @@ int LaunchBnStatsMoments(int dtype, const void* x, float* moments, int64_t outer
   }
   MUSA_BY_DTYPE(dtype, StatsSums<T>(x, moments, moments + 2 * channels, g, workspace,
                                     workspace_bytes, kTailFwdMoments, stream));
+}
+
+// The cross-replica forms: statistics kernel, then a finalize kernel that
+// also runs the peer-memory exchange for its own channels, so that `moments`
+// / `sums` hold the result over all replicas when the call's work is done and
+// no separate exchange kernel sits in the chain.
+int LaunchBnStatsMomentsExchange(int dtype, const void* x, float* moments, int64_t outer,
+                                 int64_t channels, int64_t inner, void* workspace,
+                                 size_t workspace_bytes, void* exchange,
+                                 cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!moments || !exchange) return MUSA_KERNELS_EINVAL;
+  long long slot_floats = 0;
+  const ExchangeDev* xchg = ExchangeDeviceContext(exchange, &slot_floats);
+  if (2 * channels + 1 > slot_floats) return MUSA_KERNELS_ETOOLARGE;
+  if (IsEmpty(g)) {
+    // A replica with no rows still takes part: zeros through the stand-alone
+    // exchange kernel.
+    const cudaError_t err =
+        cudaMemsetAsync(moments, 0, sizeof(float) * (2 * channels + 1), stream);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    return LaunchExchangeMoments(exchange, moments, channels, stream);
+  }
+  MUSA_BY_DTYPE(dtype, StatsSums<T>(x, moments, moments + 2 * channels, g, workspace,
+                                    workspace_bytes, kTailFwdMoments, stream, xchg));
+}
+
+int LaunchBnGradStatsSumsExchange(int dtype, const void* dy, const void* x,
+                                  const float* mean, float* sums, int64_t outer,
+                                  int64_t channels, int64_t inner, void* workspace,
+                                  size_t workspace_bytes, void* exchange,
+                                  cudaStream_t stream) {
+  const Geom g{outer, channels, inner};
+  if (int rc = CheckGeom(g)) return rc;
+  if (channels == 0) return MUSA_KERNELS_OK;
+  if (!sums || !exchange) return MUSA_KERNELS_EINVAL;
+  long long slot_floats = 0;
+  const ExchangeDev* xchg = ExchangeDeviceContext(exchange, &slot_floats);
+  if (2 * channels + 1 > slot_floats) return MUSA_KERNELS_ETOOLARGE;
+  if (IsEmpty(g)) {
+    const cudaError_t err = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * channels, stream);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    return LaunchExchangeSums(exchange, sums, 2 * channels, stream);
+  }
+  MUSA_BY_DTYPE(dtype, GradStatsSums<T>(dy, x, mean, sums, g, workspace, workspace_bytes,
+                                        stream, xchg));
 }
 
 int LaunchBnMergeMoments(const float* gathered, int world, int64_t channels,

@@ -42,26 +42,12 @@
 #include <new>
 
 #include "common.cuh"
+#include "exchange_dev.cuh"
 #include "trace.h"
 #include "../../include/musa_plugin_kernels.h"
 
 namespace musa_b200 {
 namespace {
-
-constexpr int kMaxWorld = 16;
-constexpr int kExchangeThreads = 512;
-// Polls of one cell before a wait gives up (each poll is a load from local
-// memory plus a short sleep, about a microsecond: a second in total).
-constexpr long long kSpinLimit = 1LL << 20;
-
-struct ExchangeDev {
-  int rank;
-  int world;
-  long long slot_floats;
-  unsigned long long* cells[kMaxWorld];  // cell buffer of every replica (peer-mapped)
-  unsigned* epoch;          // local
-  int* status;              // local: 0 ok, 1 + q when replica q never arrived
-};
 
 struct ExchangeHost {
   ExchangeDev dev;
@@ -73,48 +59,6 @@ struct ExchangeHost {
 };
 
 size_t Align256(size_t n) { return (n + 255) / 256 * 256; }
-
-__device__ __forceinline__ unsigned long long LoadCell(const unsigned long long* p) {
-  unsigned long long v;
-  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-
-__device__ __forceinline__ void StoreCell(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-
-__device__ __forceinline__ unsigned long long MakeCell(float value, unsigned epoch) {
-  return (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(value);
-}
-__device__ __forceinline__ unsigned CellEpoch(unsigned long long cell) {
-  return static_cast<unsigned>(cell >> 32);
-}
-__device__ __forceinline__ float CellValue(unsigned long long cell) {
-  return __uint_as_float(static_cast<unsigned>(cell & 0xffffffffULL));
-}
-
-enum ExchangeMode { kExchangeSum = 0, kExchangeMoments = 1 };
-
-// Waits (bounded) until the cell of replica q carries `epoch`.  `dead` is the
-// CTA's shared mask of replicas nobody waits for any more.
-__device__ __forceinline__ unsigned long long AwaitCell(const unsigned long long* cell,
-                                                        unsigned epoch, int q, unsigned* dead,
-                                                        int* status) {
-  unsigned long long got = LoadCell(cell);
-  long long polls = 0;
-  while (CellEpoch(got) != epoch) {
-    if ((*reinterpret_cast<volatile unsigned*>(dead) >> q) & 1u) break;
-    if (++polls > kSpinLimit) {
-      atomicOr(dead, 1u << q);
-      atomicCAS(status, 0, 1 + q);
-      break;
-    }
-    __nanosleep(40);
-    got = LoadCell(cell);
-  }
-  return got;
-}
 
 template <int kWorld>  // 0: run-time world size
 __device__ __forceinline__ void ExchangeBody(const ExchangeDev& c, float* vec, int n,
@@ -245,6 +189,14 @@ __global__ void __launch_bounds__(kExchangeThreads)
 }
 
 }  // namespace
+
+const ExchangeDev* ExchangeDeviceContext(void* handle, long long* slot_floats) {
+  auto* h = static_cast<ExchangeHost*>(handle);
+  if (h == nullptr) return nullptr;
+  if (slot_floats != nullptr) *slot_floats = h->dev.slot_floats;
+  return h->dev_copy;
+}
+
 }  // namespace musa_b200
 
 using namespace musa_b200;
@@ -264,7 +216,8 @@ void* MusaExchangeCreate(int rank, int world, int64_t max_floats) {
   }
   const long long slot_floats = static_cast<long long>(Align256(max_floats * 4) / 4);
   const size_t cell_bytes = Align256(sizeof(unsigned long long) * 2 * world * slot_floats);
-  h->bytes = cell_bytes + 256 /*epoch*/ + 256 /*status*/ + Align256(sizeof(ExchangeDev));
+  h->bytes = cell_bytes + 256 /*epoch*/ + 256 /*status*/ + 256 /*ticket*/ +
+             Align256(sizeof(ExchangeDev));
   if (cudaMalloc(&h->base, h->bytes) != cudaSuccess ||
       cudaMemset(h->base, 0, h->bytes) != cudaSuccess) {
     cudaGetLastError();
@@ -279,7 +232,8 @@ void* MusaExchangeCreate(int rank, int world, int64_t max_floats) {
   h->dev.cells[rank] = reinterpret_cast<unsigned long long*>(p);
   h->dev.epoch = reinterpret_cast<unsigned*>(p + cell_bytes);
   h->dev.status = reinterpret_cast<int*>(p + cell_bytes + 256);
-  h->dev_copy = reinterpret_cast<ExchangeDev*>(p + cell_bytes + 512);
+  h->dev.ticket = reinterpret_cast<unsigned*>(p + cell_bytes + 512);
+  h->dev_copy = reinterpret_cast<ExchangeDev*>(p + cell_bytes + 768);
   return h;
 }
 
@@ -411,6 +365,17 @@ void* MusaPeerOpen(const void* handle64) {
     return nullptr;
   }
   return mapped;
+}
+
+// One asynchronous device-to-device copy (local or peer-mapped addresses) on
+// `stream`: a copy engine moves it.
+int MusaPeerCopyAsync(void* dst, const void* src, int64_t bytes, cudaStream_t stream) {
+  if (bytes < 0 || (bytes > 0 && (dst == nullptr || src == nullptr))) return MUSA_KERNELS_EINVAL;
+  if (bytes == 0) return MUSA_KERNELS_OK;
+  const cudaError_t err = cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes),
+                                          cudaMemcpyDeviceToDevice, stream);
+  if (err != cudaSuccess) cudaGetLastError();
+  return static_cast<int>(err);
 }
 
 int MusaPeerClose(void* mapped) {

@@ -20,9 +20,9 @@ void InitTuningOnce() {
         /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 0, /*BnFused*/ 0,
         /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1, /*BnStatsPipe*/ 4,
         /*BnApplyDeep*/ 0, /*BnPdl*/ 1, /*BnL2KeepMb*/ 64, /*RowNormPacks*/ 0,
-        /*reserved*/ 0, /*BnStatsMaxTx*/ 32, /*BnL2KeepPartial*/ 1,
+        /*reserved*/ 0, /*BnStatsMaxTx*/ 16, /*BnL2KeepPartial*/ 1,
         /*BnStatsDropRest*/ 1, /*BnApplyDropAll*/ 1, /*BnApplyEarlyLoads*/ 1,
-        /*BnFinalizeLanes*/ 32};
+        /*BnFinalizeLanes*/ 128};
     for (int i = 0; i < kTuneCount; ++i) g_tuning[i].store(defaults[i]);
   });
 }

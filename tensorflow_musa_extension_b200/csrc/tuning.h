@@ -10,7 +10,7 @@ enum TuningKey {
   kTuneAdamUnroll = 1,      // packs in flight per thread and stream: 1, 2, 4
   kTuneBiasActCtasPerSm = 2,
   kTuneBiasActUnroll = 3,
-  kTuneBnCtasPerSm = 4,     // CTAs per SM of the BatchNorm grids; 0: what fits
+  kTuneBnCtasPerSm = 4,     // CTAs per SM of the BatchNorm statistics grids; 0: what fits
   kTuneReserved5 = 5,
   kTuneBnApplyReverse = 6,  // 1: apply pass walks rows in reverse (L2 reuse)
   kTuneBnStatsKeep = 7,     // 1: stats pass loads with the default L2 policy
@@ -26,6 +26,7 @@ enum TuningKey {
   kTuneBnApplyDropAll = 17,   // 1: the element-wise pass reads evict-first at every size
   kTuneBnApplyEarlyLoads = 18,  // 1: first rows of the element-wise pass are loaded before its wait
   kTuneBnFinalizeLanes = 19,  // partial lanes per CTA of the finalize kernel: 32 or 128
+  kTuneBnApplyCtasPerSm = 20,  // CTAs per SM of the element-wise grids; 0: what fits
   kTuneCount = 24
 };
 

@@ -110,3 +110,49 @@ def test_single_replica_handle_round_trip(kernel_lib):
     assert kernel_lib.LaunchExchangeSums(h, v.data_ptr(), 5000, st) == -4
     kernel_lib.MusaExchangeDestroy(h)
     assert kernel_lib.MusaExchangeCreate(3, 2, 10) is None
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,c", [(4096, 64), (777, 520), (5000, 2048)])
+def test_finalize_kernel_runs_the_exchange_itself(kernel_lib, dtype, rows, c):
+    """LaunchBnStatsMomentsExchange / LaunchBnGradStatsSumsExchange with a
+    one-replica handle return what the two-step forms return, call after call
+    (epoch and ticket advance inside the finalize kernel), and leave the
+    handle usable by the stand-alone exchange kernel."""
+    h = kernel_lib.MusaExchangeCreate(0, 1, 2 * c + 1)
+    assert h and kernel_lib.MusaExchangeOpenPeers(h, None) == 0
+    st = torch.cuda.current_stream().cuda_stream
+    dt = {torch.float32: 0, torch.bfloat16: 2}[dtype]
+    need = kernel_lib.BnWorkspaceBytes(rows, c, 1)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(rows + c)
+    for _ in range(3):
+        x = (torch.randn(rows, c, device="cuda", generator=gen) * 2 + 5).to(dtype)
+        dy = torch.randn(rows, c, device="cuda", generator=gen).to(dtype)
+        want = torch.empty(2 * c + 1, device="cuda")
+        got = torch.empty(2 * c + 1, device="cuda")
+        assert kernel_lib.LaunchBnStatsMoments(dt, x.data_ptr(), want.data_ptr(), rows, c, 1,
+                                               ws.data_ptr(), ws.numel(), st) == 0
+        assert kernel_lib.LaunchBnStatsMomentsExchange(
+            dt, x.data_ptr(), got.data_ptr(), rows, c, 1, ws.data_ptr(), ws.numel(), h, st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+        mean = want[:c].clone()
+        gw, gg = torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda")
+        assert kernel_lib.LaunchBnGradStatsSums(dt, dy.data_ptr(), x.data_ptr(), mean.data_ptr(),
+                                                gw.data_ptr(), rows, c, 1, ws.data_ptr(),
+                                                ws.numel(), st) == 0
+        assert kernel_lib.LaunchBnGradStatsSumsExchange(
+            dt, dy.data_ptr(), x.data_ptr(), mean.data_ptr(), gg.data_ptr(), rows, c, 1,
+            ws.data_ptr(), ws.numel(), h, st) == 0
+        v = torch.arange(7, dtype=torch.float32, device="cuda")
+        assert kernel_lib.LaunchExchangeSums(h, v.data_ptr(), 7, st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(gg, gw)
+        assert torch.equal(v, torch.arange(7, dtype=torch.float32, device="cuda"))
+    assert kernel_lib.MusaExchangeStatus(h) == 0
+    small = kernel_lib.MusaExchangeCreate(0, 1, 8)
+    assert kernel_lib.LaunchBnStatsMomentsExchange(
+        dt, x.data_ptr(), got.data_ptr(), rows, c, 1, ws.data_ptr(), ws.numel(), small, st) == -4
+    kernel_lib.MusaExchangeDestroy(small)
+    kernel_lib.MusaExchangeDestroy(h)
