@@ -385,7 +385,7 @@ __global__ void __launch_bounds__(kThreads)
                       const float* __restrict__ mean,
                       float* __restrict__ partial, int64_t rows, int64_t cv,
                       int64_t channels, int64_t rows_per_cta, float keep_fraction,
-                      bool drop_rest) {
+                      bool drop_rest, bool interleave) {
   constexpr int kVec = VecWidth<T>::value;
   using P = Pack<T, kVec>;
   GridDepWait();
@@ -446,31 +446,70 @@ __global__ void __launch_bounds__(kThreads)
     // This thread's rows: r0 + ty + j * TY, j = 0 .. n_j - 1 (32-bit counters:
     // a CTA never owns 2^31 rows), in n_full whole stages of kU rows and a
     // remainder.
-    const int n_rows = static_cast<int>(r1 - r0);
-    const int n_j = n_rows > ty ? (n_rows - ty + TY - 1) / TY : 0;
-    const int n_full = n_j / kU;
+    // Two row maps.  Contiguous: CTA b owns rows [r0, r1).  Interleaved: the
+    // rows are cut into tiles of kU * TY rows (one stage of one CTA) and CTA b
+    // takes tiles b, b + G, b + 2G ...: at any moment all CTAs read inside one
+    // window of G tiles that moves through the tensor, instead of G streams
+    // spread over all of it (fewer DRAM pages open at once).
     const int64_t row_bytes = static_cast<int64_t>(TY) * cv * 16;   // one row step
-    const int64_t stage_bytes = row_bytes * kU;
-    const char* xi = reinterpret_cast<const char*>(
-        reinterpret_cast<const P*>(x) + col + (r0 + ty) * cv);
-    const char* di = reinterpret_cast<const char*>(
-        reinterpret_cast<const P*>(dy) + col + (r0 + ty) * cv);
+    int n_full, rem;
+    int64_t stage_bytes, first_row;
+    int keep_from_tile = 0, tile_step = 1, tile_first = 0;   // global tile of stage s: first + s * step
+    if (interleave) {
+      const int64_t tile_rows = static_cast<int64_t>(kU) * TY;
+      const int64_t tiles = (rows + tile_rows - 1) / tile_rows;
+      const int64_t G = gridDim.y, b = blockIdx.y;
+      const int64_t mine = b < tiles ? (tiles - 1 - b) / G + 1 : 0;
+      const bool owns_last = mine > 0 && b + (mine - 1) * G == tiles - 1;
+      const int64_t last_rows = rows - (tiles - 1) * tile_rows;     // rows of the last tile
+      if (owns_last && last_rows != tile_rows) {
+        n_full = static_cast<int>(mine - 1);
+        rem = last_rows > ty ? static_cast<int>((last_rows - ty + TY - 1) / TY) : 0;
+      } else {
+        n_full = static_cast<int>(mine);
+        rem = 0;
+      }
+      stage_bytes = row_bytes * kU * G;
+      first_row = b * tile_rows + ty;
+      tile_first = static_cast<int>(b);
+      tile_step = static_cast<int>(G);
+      keep_from_tile =
+          keep_fraction >= 1.0f ? 0
+          : keep_fraction <= 0.0f
+              ? static_cast<int>(tiles) + 1
+              : static_cast<int>(tiles) -
+                    static_cast<int>(static_cast<float>(tiles) * keep_fraction);
+    } else {
+      const int n_rows = static_cast<int>(r1 - r0);
+      const int n_j = n_rows > ty ? (n_rows - ty + TY - 1) / TY : 0;
+      n_full = n_j / kU;
+      rem = n_j - n_full * kU;
+      stage_bytes = row_bytes * kU;
+      first_row = r0 + ty;
+      keep_from_tile =
+          keep_fraction >= 1.0f ? 0
+          : keep_fraction <= 0.0f
+              ? n_full + 1
+              : n_full - static_cast<int>(static_cast<float>(n_full) * keep_fraction);
+    }
+    const char* xi =
+        reinterpret_cast<const char*>(reinterpret_cast<const P*>(x) + col + first_row * cv);
+    const char* di =
+        reinterpret_cast<const char*>(reinterpret_cast<const P*>(dy) + col + first_row * cv);
     const unsigned my = static_cast<unsigned>(__cvta_generic_to_shared(pipe_smem + tid));
     constexpr unsigned kSlotBytes = kThreads * 16;                  // between a thread's slots
     constexpr unsigned kStageBytes = kStageSlots * kSlotBytes;
     // L2 retention for the element-wise pass that follows: the LAST
-    // keep_fraction of this thread's stages is read with the evict-last
-    // priority, everything before it with evict-first (or the default), so
+    // keep_fraction of this thread's stages (contiguous map) or of the tensor's
+    // tiles (interleaved map) is read with the evict-last priority, everything before it with evict-first (or the default), so
     // that what stays in L2 is chosen by this kernel (about as much as L2 can
     // hold back) instead of whatever the replacement policy happens to keep of
     // a tensor that is larger than the cache.
     const uint64_t keep_policy = PolicyEvictLast();
     const uint64_t drop_policy = drop_rest ? PolicyEvictFirst() : PolicyEvictNormal();
-    const int s_keep =
-        keep_fraction >= 1.0f ? 0
-        : keep_fraction <= 0.0f
-            ? n_full + 1
-            : n_full - static_cast<int>(static_cast<float>(n_full) * keep_fraction);
+    auto policy_of = [&](int stage) {
+      return tile_first + stage * tile_step >= keep_from_tile ? keep_policy : drop_policy;
+    };
     auto issue = [&](unsigned dst, uint64_t policy) {
 #pragma unroll
       for (int u = 0; u < kU; ++u) {
@@ -496,7 +535,7 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
     for (int st = 0; st < kStages - 1; ++st) {
       if (s_issue < n_full) {
-        issue(my + st * kStageBytes, s_issue >= s_keep ? keep_policy : drop_policy);
+        issue(my + st * kStageBytes, policy_of(s_issue));
         ++s_issue;
       }
       CpAsyncCommit();
@@ -505,7 +544,7 @@ __global__ void __launch_bounds__(kThreads)
     unsigned drain = 0;                            // ring offset of the next stage to read
     for (int s = 0; s < n_full; ++s) {
       if (s_issue < n_full) {
-        issue(my + fill, s_issue >= s_keep ? keep_policy : drop_policy);
+        issue(my + fill, policy_of(s_issue));
         ++s_issue;
       }
       CpAsyncCommit();
@@ -528,11 +567,10 @@ __global__ void __launch_bounds__(kThreads)
       }
       drain = drain + kStageBytes == kStages * kStageBytes ? 0u : drain + kStageBytes;
     }
-    // Remainder rows (fewer than kU): plain loads; xi / di stand at the first
-    // of them.
-    const int rem = n_j - n_full * kU;
+    // Remainder rows (at most kU: a thread's share of a last, partial tile):
+    // plain loads; xi / di stand at the first of them.
 #pragma unroll
-    for (int u = 0; u < kU - 1; ++u) {
+    for (int u = 0; u < kU; ++u) {
       if (u < rem) {
         const P px = LoadKeep(reinterpret_cast<const P*>(xi + u * row_bytes));
         P pd = px;
@@ -1081,31 +1119,59 @@ __global__ void __launch_bounds__(kThreads)
     BnApplyLastKernel(const T* __restrict__ x, const T* __restrict__ dy,
                       T* __restrict__ out, ApplyArgs a, int64_t rows,
                       int64_t cv, int64_t channels, int64_t rows_per_cta,
-                      bool reverse, bool last_use, bool early_loads) {
+                      bool reverse, bool last_use, bool early_loads, bool interleave) {
   using P = Pack<T, kVec>;
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
   const int64_t col = static_cast<int64_t>(blockIdx.x) * TX + tx;
-  const int64_t chunk =
-      reverse ? (gridDim.y - 1 - blockIdx.y) : blockIdx.y;
-  const int64_t r0 = chunk * rows_per_cta;
-  int64_t r1 = r0 + rows_per_cta;
-  if (r1 > rows) r1 = rows;
+  const int64_t step = static_cast<int64_t>(TY) * kUnroll;
+  // Two row maps (see BnStatsPipeKernel).  Contiguous: CTA b owns one range of
+  // rows_per_cta rows, walked in batches of `step` rows.  Interleaved: the
+  // rows are cut into tiles of `step` rows and CTA b takes tiles b, b + G ...
+  // Either way the CTA sees "local rows" 0 .. n_rows - 1, batch k being local
+  // rows [k * step, (k + 1) * step), mapped to global rows below; `reverse`
+  // walks them from the end.
+  int64_t r0, r1, n_rows, batch_stride;
+  if (interleave) {
+    const int64_t tiles = (rows + step - 1) / step;
+    const int64_t G = gridDim.y, b = blockIdx.y;
+    const int64_t mine = b < tiles ? (tiles - 1 - b) / G + 1 : 0;
+    r0 = b * step;                 // global row of local row 0
+    batch_stride = G * step;       // global rows between consecutive batches
+    n_rows = mine * step;          // the last tile may stick out: checked per row
+    r1 = rows;
+  } else {
+    const int64_t chunk = reverse ? (gridDim.y - 1 - blockIdx.y) : blockIdx.y;
+    r0 = chunk * rows_per_cta;
+    r1 = r0 + rows_per_cta;
+    if (r1 > rows) r1 = rows;
+    n_rows = r1 > r0 ? r1 - r0 : 0;
+    batch_stride = step;
+  }
   const P* xp = reinterpret_cast<const P*>(x) + col;
   const P* dp = reinterpret_cast<const P*>(dy) + col;
-  const int64_t n_rows = r1 - r0;
-  const int64_t step = static_cast<int64_t>(TY) * kUnroll;
   const uint64_t drop_policy = PolicyEvictFirst();
   P px[kUnroll];
   P pd[kUnroll];
   int64_t off[kUnroll];
   // Loads of one batch of rows (local row l and the kUnroll - 1 after it).
-  auto load_batch = [&](int64_t l) {
+  const int64_t n_batches = interleave ? n_rows / step : 0;
+  // `k`: the batch, l = ty + k * step its first local row for this thread.
+  auto load_batch = [&](int64_t l, int64_t k) {
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t li = l + static_cast<int64_t>(u) * TY;
-      const bool ok = li < n_rows;
-      const int64_t r = reverse ? (r1 - 1 - li) : (r0 + li);
+      const int64_t in_batch = ty + static_cast<int64_t>(u) * TY;
+      const int64_t kk = reverse ? (n_batches - 1 - k) : k;
+      int64_t r;
+      bool ok;
+      if (interleave) {
+        r = r0 + kk * batch_stride + in_batch;
+        ok = li < n_rows && r < rows;
+      } else {
+        ok = li < n_rows;
+        r = reverse ? (r1 - 1 - li) : (r0 + li);
+      }
       off[u] = ok ? r * cv : -1;
       if (ok) {
         if constexpr (sizeof(P) == 16) {
@@ -1131,7 +1197,7 @@ __global__ void __launch_bounds__(kThreads)
   // stand-alone element-wise launch cannot know who produced x and waits
   // first.
   const bool active = col < cv;
-  if (early_loads && active) load_batch(ty);
+  if (early_loads && active) load_batch(ty, 0);
   GridDepWait();
   GridDepLaunch();
   if (!active) return;
@@ -1198,8 +1264,9 @@ __global__ void __launch_bounds__(kThreads)
   P* op = reinterpret_cast<P*>(out) + col;
   // Row lane ty visits local rows ty, ty + TY, ...; in reverse mode the local
   // index is mirrored.
-  for (int64_t l = ty; l < n_rows; l += step) {
-    if (!(early_loads && l == ty)) load_batch(l);
+  int64_t batch = 0;
+  for (int64_t l = ty; l < n_rows; l += step, ++batch) {
+    if (!(early_loads && batch == 0)) load_batch(l, batch);
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (off[u] >= 0) {
@@ -1511,7 +1578,8 @@ int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* workspace
   const cudaError_t err = LaunchChained(
       GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy), dim3(p.tx, p.ty),
       Cfg::kSmemBytes, stream, x, dy, mean, workspace, g.outer, cv, g.channels,
-      p.rows_per_cta, keep_fraction, GetTuning(kTuneBnStatsDropRest) != 0);
+      p.rows_per_cta, keep_fraction, GetTuning(kTuneBnStatsDropRest) != 0,
+      GetTuning(kTuneBnInterleave) != 0);
   if (err != cudaSuccess) {
     cudaGetLastError();
     return EncodeCuda(err);
@@ -1733,7 +1801,8 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
         LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
                       dim3(p.tx, p.ty), 0, stream, x, dy, out, a, g.outer, cv,
                       g.channels, p.rows_per_cta, reverse, last_use,
-                      early_loads && GetTuning(kTuneBnApplyEarlyLoads) != 0);
+                      early_loads && GetTuning(kTuneBnApplyEarlyLoads) != 0,
+                      GetTuning(kTuneBnInterleave) != 0);
       } else {
         auto kernel = BnApplyLastKernel<T, kVec, kUnroll, kMode>;
         static std::atomic<int> resident_by_device[kMaxDevices];
@@ -1750,7 +1819,8 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
         LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
                       dim3(p.tx, p.ty), 0, stream, x, dy, out, a, g.outer, cv,
                       g.channels, p.rows_per_cta, reverse, last_use,
-                      early_loads && GetTuning(kTuneBnApplyEarlyLoads) != 0);
+                      early_loads && GetTuning(kTuneBnApplyEarlyLoads) != 0,
+                      GetTuning(kTuneBnInterleave) != 0);
       }
     } else {
       const Plan p =
@@ -1758,7 +1828,7 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
       BnApplyLastKernel<T, 1, kUnroll, kMode>
           <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
               x, dy, out, a, g.outer, g.channels, g.channels, p.rows_per_cta,
-              reverse, false, false);
+              reverse, false, false, false);
     }
     return;
   }

@@ -19,10 +19,10 @@ void InitTuningOnce() {
         /*AdamCtasPerSm*/ 0, /*AdamUnroll*/ 2, /*BiasActCtasPerSm*/ 0,
         /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 0, /*BnFused*/ 0,
         /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1, /*BnStatsPipe*/ 4,
-        /*BnApplyDeep*/ 0, /*BnPdl*/ 1, /*BnL2KeepMb*/ 64, /*RowNormPacks*/ 0,
+        /*BnApplyDeep*/ 1, /*BnPdl*/ 1, /*BnL2KeepMb*/ 64, /*RowNormPacks*/ 0,
         /*reserved*/ 0, /*BnStatsMaxTx*/ 16, /*BnL2KeepPartial*/ 1,
         /*BnStatsDropRest*/ 1, /*BnApplyDropAll*/ 1, /*BnApplyEarlyLoads*/ 1,
-        /*BnFinalizeLanes*/ 128};
+        /*BnFinalizeLanes*/ 128, /*BnApplyCtasPerSm*/ 0, /*BnInterleave*/ 1};
     for (int i = 0; i < kTuneCount; ++i) g_tuning[i].store(defaults[i]);
   });
 }

@@ -27,6 +27,7 @@ enum TuningKey {
   kTuneBnApplyEarlyLoads = 18,  // 1: first rows of the element-wise pass are loaded before its wait
   kTuneBnFinalizeLanes = 19,  // partial lanes per CTA of the finalize kernel: 32 or 128
   kTuneBnApplyCtasPerSm = 20,  // CTAs per SM of the element-wise grids; 0: what fits
+  kTuneBnInterleave = 21,   // 1: CTAs take row tiles round-robin instead of one contiguous range
   kTuneCount = 24
 };
 
