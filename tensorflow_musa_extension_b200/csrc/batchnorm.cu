@@ -102,6 +102,17 @@ inline Plan PlanLast(int64_t rows, int64_t channels, int64_t cv, int unroll,
 
 // ------------------------------------------------------------ level 1 ----
 
+// Cross-replica passes: the finalize kernel that follows a statistics kernel
+// runs a peer-memory exchange whose cells are tagged with an epoch.  The
+// statistics kernel advances the device-side epoch counter (one thread, once
+// it may touch memory), so that every CTA of the finalize kernel reads the
+// same, already advanced value and nothing has to count CTAs afterwards.
+__device__ __forceinline__ void BumpEpoch(unsigned* epoch, int linear_tid) {
+  if (epoch != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && linear_tid == 0) {
+    *epoch = *epoch + 1u;
+  }
+}
+
 enum Mode { kFwd = 0, kGrad = 1 };
 
 // Channels-last stats.  Grid (gx, gy), block (tx, ty).
@@ -110,10 +121,12 @@ __global__ void __launch_bounds__(kThreads)
     BnStatsLastKernel(const T* __restrict__ x, const T* __restrict__ dy,
                       const float* __restrict__ mean,
                       float* __restrict__ partial, int64_t rows, int64_t cv,
-                      int64_t channels, int64_t rows_per_cta, bool keep) {
+                      int64_t channels, int64_t rows_per_cta, bool keep,
+                      unsigned* epoch_bump) {
   using P = Pack<T, kVec>;
   GridDepWait();
   GridDepLaunch();
+  BumpEpoch(epoch_bump, threadIdx.y * blockDim.x + threadIdx.x);
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
   const int64_t col = static_cast<int64_t>(blockIdx.x) * TX + tx;
@@ -260,6 +273,7 @@ struct FinalizeArgs {
   // with the other replicas itself (moments are merged, gradient sums added)
   // and everything it writes is the result over all replicas.
   const ExchangeDev* xchg;
+  unsigned* xchg_epoch;   // the exchange's epoch counter (advanced by the statistics kernel)
 };
 
 __device__ __forceinline__ float LoadAsF32(const void* base, int dtype,
@@ -385,11 +399,12 @@ __global__ void __launch_bounds__(kThreads)
                       const float* __restrict__ mean,
                       float* __restrict__ partial, int64_t rows, int64_t cv,
                       int64_t channels, int64_t rows_per_cta, float keep_fraction,
-                      bool drop_rest, bool interleave) {
+                      bool drop_rest, bool interleave, unsigned* epoch_bump) {
   constexpr int kVec = VecWidth<T>::value;
   using P = Pack<T, kVec>;
   GridDepWait();
   GridDepLaunch();
+  BumpEpoch(epoch_bump, threadIdx.y * blockDim.x + threadIdx.x);
   using Cfg = StatsPipe<kMode, kStagesT>;
   constexpr int kStages = Cfg::kStages, kU = Cfg::kU, kStreams = Cfg::kStreams;
   constexpr int kStageSlots = kStreams * kU;           // 16-byte slots per thread and stage
@@ -661,10 +676,12 @@ __global__ void __launch_bounds__(kThreads)
     BnStatsPlaneKernel(const T* __restrict__ x, const T* __restrict__ dy,
                        const float* __restrict__ mean,
                        float* __restrict__ partial, int64_t outer,
-                       int64_t channels, int64_t inner, int64_t outer_per_cta) {
+                       int64_t channels, int64_t inner, int64_t outer_per_cta,
+                       unsigned* epoch_bump) {
   using P = Pack<T, kVec>;
   GridDepWait();
   GridDepLaunch();
+  BumpEpoch(epoch_bump, threadIdx.x);
   const int lane = threadIdx.x & 31;
   const int64_t c = static_cast<int64_t>(blockIdx.x) * kPlaneWarps + (threadIdx.x >> 5);
   if (c >= channels) return;  // whole warp; nothing below synchronises the CTA
@@ -763,13 +780,15 @@ __global__ void __launch_bounds__(kThreads)
     BnStatsGroupKernel(const T* __restrict__ x, const T* __restrict__ dy,
                        const float* __restrict__ mean,
                        float* __restrict__ partial, int64_t outer,
-                       int64_t channels, int inner, int64_t outer_per_cta) {
+                       int64_t channels, int inner, int64_t outer_per_cta,
+                       unsigned* epoch_bump) {
   constexpr int kG = VecWidth<T>::value;
   using P = Pack<T, kG>;
   extern __shared__ float4 contrib[];  // [inner]: (s1, s2) of lo, (s1, s2) of lo + 1
   __shared__ float shift_s[kG + 1];
   GridDepWait();
   GridDepLaunch();
+  BumpEpoch(epoch_bump, threadIdx.x);
   const int64_t c0 = static_cast<int64_t>(blockIdx.x) * kG;
   const int64_t n0 = static_cast<int64_t>(blockIdx.y) * outer_per_cta;
   int64_t n1 = n0 + outer_per_cta;
@@ -885,7 +904,7 @@ __global__ void __launch_bounds__(8 * kLanes) BnFinalizeKernel(FinalizeArgs a) {
   __shared__ unsigned dead;
   unsigned epoch = 0;
   if (a.xchg != nullptr && tid < 32) {
-    epoch = *a.xchg->epoch + 1u;
+    epoch = *reinterpret_cast<volatile unsigned*>(a.xchg_epoch);   // advanced by the statistics kernel
     if (tid == 0) {
       const int st = *reinterpret_cast<volatile int*>(a.xchg->status);
       dead = st > 0 && st <= kMaxWorld ? 1u << (st - 1) : 0u;
@@ -1004,10 +1023,6 @@ __global__ void __launch_bounds__(8 * kLanes) BnFinalizeKernel(FinalizeArgs a) {
           a.dscale[c] = s2_f * inv;
         }
       }
-    }
-    if (a.xchg != nullptr) {
-      __syncwarp();
-      if (lane == 0) ExchangeCloseInKernel(*a.xchg, epoch, gridDim.x);
     }
   }
 }
@@ -1538,7 +1553,7 @@ inline int DecodeError(int rc) { return rc <= -1000 ? -rc - 1000 : rc; }
 // written, or a negative error.
 template <typename T, int kMode, int kStagesT>
 int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* workspace,
-                    const Geom& g, int64_t cv, cudaStream_t stream) {
+                    const Geom& g, int64_t cv, unsigned* epoch_bump, cudaStream_t stream) {
   using Cfg = StatsPipe<kMode, kStagesT>;
   auto kernel = BnStatsPipeKernel<T, kMode, kStagesT>;
   static std::atomic<int> resident_by_device[kMaxDevices];
@@ -1579,7 +1594,7 @@ int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* workspace
       GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy), dim3(p.tx, p.ty),
       Cfg::kSmemBytes, stream, x, dy, mean, workspace, g.outer, cv, g.channels,
       p.rows_per_cta, keep_fraction, GetTuning(kTuneBnStatsDropRest) != 0,
-      GetTuning(kTuneBnInterleave) != 0);
+      GetTuning(kTuneBnInterleave) != 0, epoch_bump);
   if (err != cudaSuccess) {
     cudaGetLastError();
     return EncodeCuda(err);
@@ -1657,7 +1672,7 @@ inline GroupPlan PlanGroups(const Geom& g) {
 // error.
 template <typename T, int kMode>
 int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
-                const Geom& g, cudaStream_t stream) {
+                const Geom& g, unsigned* epoch_bump, cudaStream_t stream) {
   constexpr int kVec = VecWidth<T>::value;
   constexpr int kUnroll = 4;
   const bool keep = GetTuning(kTuneBnStatsKeep) != 0;
@@ -1667,23 +1682,23 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
       const int64_t cv = g.channels / kVec;
       const int stages = GetTuning(kTuneBnStatsPipe);
       if (stages == 3) {
-        return LaunchStatsPipe<T, kMode, 3>(x, dy, mean, partial, g, cv, stream);
+        return LaunchStatsPipe<T, kMode, 3>(x, dy, mean, partial, g, cv, epoch_bump, stream);
       }
       if (stages != 0) {
-        return LaunchStatsPipe<T, kMode, 4>(x, dy, mean, partial, g, cv, stream);
+        return LaunchStatsPipe<T, kMode, 4>(x, dy, mean, partial, g, cv, epoch_bump, stream);
       }
       const Plan p = PlanLast(g.outer, g.channels, cv, kUnroll, true, 3);
       BnStatsLastKernel<T, kVec, kUnroll, kMode>
           <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
               x, dy, mean, partial, g.outer, cv, g.channels, p.rows_per_cta,
-              keep);
+              keep, epoch_bump);
       return p.gy;
     }
     const Plan p = PlanLast(g.outer, g.channels, g.channels, kUnroll, true, 4);
     BnStatsLastKernel<T, 1, kUnroll, kMode>
         <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
             x, dy, mean, partial, g.outer, g.channels, g.channels,
-            p.rows_per_cta, keep);
+            p.rows_per_cta, keep, epoch_bump);
     return p.gy;
   }
   if (UseChannelGroups<T>(g, aligned) && g.channels / kVec <= 0x7fffffffLL) {
@@ -1691,7 +1706,8 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
     BnStatsGroupKernel<T, kMode>
         <<<dim3(static_cast<unsigned>(gp.gx), static_cast<unsigned>(gp.gy)), gp.threads,
            static_cast<size_t>(g.inner) * sizeof(float4), stream>>>(
-            x, dy, mean, partial, g.outer, g.channels, static_cast<int>(g.inner), gp.per);
+            x, dy, mean, partial, g.outer, g.channels, static_cast<int>(g.inner), gp.per,
+            epoch_bump);
     return static_cast<int>(gp.gy);
   }
   // [outer, C, inner]: a warp per channel, the outer axis split over grid.y.
@@ -1702,20 +1718,20 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
     case 8:
       if constexpr (kVec >= 8) {
         BnStatsPlaneKernel<T, 8, kMode><<<grid, kThreads, 0, stream>>>(
-            x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per);
+            x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per, epoch_bump);
       }
       break;
     case 4:
       BnStatsPlaneKernel<T, 4, kMode><<<grid, kThreads, 0, stream>>>(
-          x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per);
+          x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per, epoch_bump);
       break;
     case 2:
       BnStatsPlaneKernel<T, 2, kMode><<<grid, kThreads, 0, stream>>>(
-          x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per);
+          x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per, epoch_bump);
       break;
     default:
       BnStatsPlaneKernel<T, 1, kMode><<<grid, kThreads, 0, stream>>>(
-          x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per);
+          x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per, epoch_bump);
   }
   return static_cast<int>(pp.gy);
 }
@@ -1755,7 +1771,7 @@ template <typename T, int kMode>
 int RunStats(const T* x, const T* dy, const float* mean, float* workspace,
              const Geom& g, FinalizeArgs f, int kind, cudaStream_t stream) {
   f.partial = workspace;
-  const int splits = LaunchStats<T, kMode>(x, dy, mean, workspace, g, stream);
+  const int splits = LaunchStats<T, kMode>(x, dy, mean, workspace, g, f.xchg_epoch, stream);
   if (splits < 0) return DecodeError(splits);
   f.splits = splits;
   LaunchFinalize(kind, f, stream);
@@ -1988,7 +2004,8 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
 template <typename T>
 int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
               void* workspace, size_t workspace_bytes, int kind,
-              cudaStream_t stream, const ExchangeDev* xchg = nullptr) {
+              cudaStream_t stream, const ExchangeDev* xchg = nullptr,
+              unsigned* xchg_epoch = nullptr) {
   MUSA_TRACE("LaunchBnStats", sizeof(T) * g.outer * g.channels * g.inner);
   if (!x || !sums) return MUSA_KERNELS_EINVAL;
   if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
@@ -2005,6 +2022,7 @@ int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
   f.sums = sums;
   f.count_out = count_out;
   f.xchg = xchg;
+  f.xchg_epoch = xchg_epoch;
   if (int rc = RunStats<T, kFwd>(static_cast<const T*>(x), nullptr, nullptr, partial, g,
                                  f, kind, stream)) {
     return rc;
@@ -2015,7 +2033,8 @@ int StatsSums(const void* x, float* sums, float* count_out, const Geom& g,
 template <typename T>
 int GradStatsSums(const void* dy, const void* x, const float* mean, float* sums,
                   const Geom& g, void* workspace, size_t workspace_bytes,
-                  cudaStream_t stream, const ExchangeDev* xchg = nullptr) {
+                  cudaStream_t stream, const ExchangeDev* xchg = nullptr,
+                  unsigned* xchg_epoch = nullptr) {
   MUSA_TRACE("LaunchBnGradStats", 2 * sizeof(T) * g.outer * g.channels * g.inner);
   if (!dy || !x || !mean || !sums) return MUSA_KERNELS_EINVAL;
   if (!workspace || workspace_bytes < WorkspaceBytes(g) ||
@@ -2028,6 +2047,7 @@ int GradStatsSums(const void* dy, const void* x, const float* mean, float* sums,
   SetCount(&f, static_cast<double>(g.rows()));
   f.sums = sums;
   f.xchg = xchg;
+  f.xchg_epoch = xchg_epoch;
   if (int rc = RunStats<T, kGrad>(static_cast<const T*>(x), static_cast<const T*>(dy),
                                   mean, partial, g, f, kTailGrad, stream)) {
     return rc;
@@ -2380,7 +2400,8 @@ int LaunchBnStatsMomentsExchange(int dtype, const void* x, float* moments, int64
   if (channels == 0) return MUSA_KERNELS_OK;
   if (!moments || !exchange) return MUSA_KERNELS_EINVAL;
   long long slot_floats = 0;
-  const ExchangeDev* xchg = ExchangeDeviceContext(exchange, &slot_floats);
+  unsigned* xchg_epoch = nullptr;
+  const ExchangeDev* xchg = ExchangeDeviceContext(exchange, &slot_floats, &xchg_epoch);
   if (2 * channels + 1 > slot_floats) return MUSA_KERNELS_ETOOLARGE;
   if (IsEmpty(g)) {
     // A replica with no rows still takes part: zeros through the stand-alone
@@ -2391,7 +2412,7 @@ int LaunchBnStatsMomentsExchange(int dtype, const void* x, float* moments, int64
     return LaunchExchangeMoments(exchange, moments, channels, stream);
   }
   MUSA_BY_DTYPE(dtype, StatsSums<T>(x, moments, moments + 2 * channels, g, workspace,
-                                    workspace_bytes, kTailFwdMoments, stream, xchg));
+                                    workspace_bytes, kTailFwdMoments, stream, xchg, xchg_epoch));
 }
 
 int LaunchBnGradStatsSumsExchange(int dtype, const void* dy, const void* x,
@@ -2404,7 +2425,8 @@ int LaunchBnGradStatsSumsExchange(int dtype, const void* dy, const void* x,
   if (channels == 0) return MUSA_KERNELS_OK;
   if (!sums || !exchange) return MUSA_KERNELS_EINVAL;
   long long slot_floats = 0;
-  const ExchangeDev* xchg = ExchangeDeviceContext(exchange, &slot_floats);
+  unsigned* xchg_epoch = nullptr;
+  const ExchangeDev* xchg = ExchangeDeviceContext(exchange, &slot_floats, &xchg_epoch);
   if (2 * channels + 1 > slot_floats) return MUSA_KERNELS_ETOOLARGE;
   if (IsEmpty(g)) {
     const cudaError_t err = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * channels, stream);
@@ -2412,7 +2434,7 @@ int LaunchBnGradStatsSumsExchange(int dtype, const void* dy, const void* x,
     return LaunchExchangeSums(exchange, sums, 2 * channels, stream);
   }
   MUSA_BY_DTYPE(dtype, GradStatsSums<T>(dy, x, mean, sums, g, workspace, workspace_bytes,
-                                        stream, xchg));
+                                        stream, xchg, xchg_epoch));
 }
 
 int LaunchBnMergeMoments(const float* gathered, int world, int64_t channels,

@@ -190,10 +190,12 @@ __global__ void __launch_bounds__(kExchangeThreads)
 
 }  // namespace
 
-const ExchangeDev* ExchangeDeviceContext(void* handle, long long* slot_floats) {
+const ExchangeDev* ExchangeDeviceContext(void* handle, long long* slot_floats,
+                                         unsigned** epoch) {
   auto* h = static_cast<ExchangeHost*>(handle);
   if (h == nullptr) return nullptr;
   if (slot_floats != nullptr) *slot_floats = h->dev.slot_floats;
+  if (epoch != nullptr) *epoch = h->dev.epoch;
   return h->dev_copy;
 }
 
@@ -216,8 +218,7 @@ void* MusaExchangeCreate(int rank, int world, int64_t max_floats) {
   }
   const long long slot_floats = static_cast<long long>(Align256(max_floats * 4) / 4);
   const size_t cell_bytes = Align256(sizeof(unsigned long long) * 2 * world * slot_floats);
-  h->bytes = cell_bytes + 256 /*epoch*/ + 256 /*status*/ + 256 /*ticket*/ +
-             Align256(sizeof(ExchangeDev));
+  h->bytes = cell_bytes + 256 /*epoch*/ + 256 /*status*/ + Align256(sizeof(ExchangeDev));
   if (cudaMalloc(&h->base, h->bytes) != cudaSuccess ||
       cudaMemset(h->base, 0, h->bytes) != cudaSuccess) {
     cudaGetLastError();
@@ -232,8 +233,7 @@ void* MusaExchangeCreate(int rank, int world, int64_t max_floats) {
   h->dev.cells[rank] = reinterpret_cast<unsigned long long*>(p);
   h->dev.epoch = reinterpret_cast<unsigned*>(p + cell_bytes);
   h->dev.status = reinterpret_cast<int*>(p + cell_bytes + 256);
-  h->dev.ticket = reinterpret_cast<unsigned*>(p + cell_bytes + 512);
-  h->dev_copy = reinterpret_cast<ExchangeDev*>(p + cell_bytes + 768);
+  h->dev_copy = reinterpret_cast<ExchangeDev*>(p + cell_bytes + 512);
   return h;
 }
 

@@ -23,7 +23,6 @@ struct ExchangeDev {
   unsigned long long* cells[kMaxWorld];  // cell buffer of every replica (peer-mapped)
   unsigned* epoch;          // local
   int* status;              // local: 0 ok, 1 + q when replica q never arrived
-  unsigned* ticket;         // local: CTAs that finished an in-kernel exchange (0 between uses)
 };
 
 __device__ __forceinline__ unsigned long long LoadCell(const unsigned long long* p) {
@@ -91,7 +90,7 @@ __device__ __forceinline__ void ExchangeChannelPairW(const ExchangeDev& x, unsig
   const unsigned long long c0 = MakeCell(v0, epoch), c1 = MakeCell(v1, epoch);
 #pragma unroll
   for (int p = 0; p < kW; ++p) {
-    if (p < world) {
+    if (p < world && p != x.rank) {   // the own contribution stays in registers
       unsigned long long* dst = x.cells[p] + mine;
       StoreCell(dst + c, c0);
       StoreCell(dst + channels + c, c1);
@@ -103,15 +102,21 @@ __device__ __forceinline__ void ExchangeChannelPairW(const ExchangeDev& x, unsig
 #pragma unroll
   for (int q = 0; q < kW; ++q) {
     if (q < world) {
-      const unsigned long long* base = local + static_cast<long long>(q) * x.slot_floats;
-      g0[q] = LoadCell(base + c);
-      g1[q] = LoadCell(base + channels + c);
-      gn[q] = kMoments ? LoadCell(base + 2 * channels) : 0ULL;
+      if (q == x.rank) {
+        g0[q] = c0;
+        g1[q] = c1;
+        gn[q] = MakeCell(count, epoch);
+      } else {
+        const unsigned long long* base = local + static_cast<long long>(q) * x.slot_floats;
+        g0[q] = LoadCell(base + c);
+        g1[q] = LoadCell(base + channels + c);
+        gn[q] = kMoments ? LoadCell(base + 2 * channels) : 0ULL;
+      }
     }
   }
 #pragma unroll
   for (int q = 0; q < kW; ++q) {
-    if (q < world) {
+    if (q < world && q != x.rank) {
       const unsigned long long* base = local + static_cast<long long>(q) * x.slot_floats;
       if (CellEpoch(g0[q]) != epoch) g0[q] = AwaitCell(base + c, epoch, q, dead, x.status);
       if (CellEpoch(g1[q]) != epoch) {
@@ -188,19 +193,10 @@ __device__ __forceinline__ void ExchangeChannelPair(const ExchangeDev& x, unsign
   }
 }
 
-// Closes an in-kernel exchange: the last CTA of the grid to get here advances
-// the epoch (every CTA has read it by then) and clears the ticket.
-__device__ __forceinline__ void ExchangeCloseInKernel(const ExchangeDev& x, unsigned epoch,
-                                                      unsigned ctas) {
-  __threadfence();
-  if (atomicAdd(x.ticket, 1u) == ctas - 1u) {
-    *x.ticket = 0u;
-    *x.epoch = epoch;
-  }
-}
-
 // Device context of an exchange handle (exchange.cu): the table that kernels
-// take, and the capacity of a slot in floats.
-const ExchangeDev* ExchangeDeviceContext(void* handle, long long* slot_floats);
+// take, the capacity of a slot in floats, and the device address of the epoch
+// counter (a kernel that precedes an in-kernel exchange advances it).
+const ExchangeDev* ExchangeDeviceContext(void* handle, long long* slot_floats,
+                                         unsigned** epoch);
 
 }  // namespace musa_b200
