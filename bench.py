@@ -303,7 +303,7 @@ def run_ours(args):
     sync_kind = "none (1 GPU)"
     if world > 1:
         sync_kind = "nccl all-reduce of 2*C(+1) fp32 per layer and pass"
-        if args.sync in ("peer", "peer_kernel"):
+        if args.sync in ("peer", "peer_fused", "peer_kernel"):
             from tensorflow_musa_extension_b200.cross_replica import PeerExchange
             try:
                 exchange = PeerExchange(dist.group.WORLD, 2 * max(c for (_, _, c) in layers) + 1,
@@ -321,9 +321,12 @@ def run_ours(args):
     if args.sync == "peer_kernel":
         for b in bns:
             b.fuse_exchange = False
-        if exchange is not None:
-            sync_kind = ("peer-memory exchange kernel (NVLink stores into every replica, bounded "
-                         "wait, rank-ordered merge) of 2*C(+1) fp32 per layer and pass")
+    elif args.sync == "peer_fused":
+        for b in bns:
+            b.fuse_exchange = True
+    if exchange is not None and not bns[0].fuse_exchange:
+        sync_kind = ("peer-memory exchange kernel (NVLink stores into every replica, bounded "
+                     "wait, rank-ordered merge) of 2*C(+1) fp32 per layer and pass")
 
     def step():
         for i in range(n_layers):
@@ -1449,10 +1452,11 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--watchdog", type=int, default=600,
                     help="seconds after which a run that has not finished is ended")
-    ap.add_argument("--sync", default="peer", choices=["peer", "peer_kernel", "nccl"],
+    ap.add_argument("--sync", default="peer", choices=["peer", "peer_fused", "peer_kernel", "nccl"],
                     help="N > 1: how the per-channel values cross the replicas: peer-memory "
-                         "exchange run by the finalize kernel (peer), by its own kernel "
-                         "(peer_kernel), or an NCCL collective")
+                         "exchange (peer: run by the finalize kernel up to 4 replicas, by its "
+                         "own kernel beyond; peer_fused / peer_kernel force one), or an NCCL "
+                         "collective")
     ap.add_argument("--adam-multicast", action="store_true",
                     help="N > 1: also check and time the NVSwitch-multicast transport of the "
                          "sharded Adam step (torch symmetric memory)")

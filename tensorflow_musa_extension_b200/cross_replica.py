@@ -225,7 +225,11 @@ class SyncBatchNorm:
         self.force_split = False  # run the split launch chain even with one replica
         # With a PeerExchange: True lets the finalize kernel of the statistics
         # pass run the exchange itself, False launches the exchange kernel.
-        self.fuse_exchange = True
+        # Measured on 8 x B200 (the ResNet-50 step, ms): 4 replicas 7.79 in the
+        # finalize kernel against 8.29 with the kernel; 8 replicas 8.48 against
+        # 8.28 - up to four replicas the saved kernel wins, at eight the one
+        # CTA that waits costs less than every finalize CTA waiting.
+        self.fuse_exchange = _world(group) <= 4
         self.world = _world(group)
         self.k = kernels if kernels is not None else _DeviceKernels()
         dev = torch.device(device)

@@ -112,14 +112,25 @@ __device__ __forceinline__ void ExchangeBody(const ExchangeDev& c, float* vec, i
   const int channels = (n - 1) / 2;
   double counts[kW];
   double total_count = 0.0;
+  {
+    // All count cells at once; only the ones that have not arrived are polled.
+    unsigned long long gn[kW];
 #pragma unroll
-  for (int q = 0; q < kW; ++q) {
-    if (q < world) {
-      const unsigned long long got =
-          AwaitCell(local + static_cast<long long>(q) * c.slot_floats + 2 * channels, epoch, q,
-                    dead, c.status);
-      counts[q] = static_cast<double>(CellValue(got));
-      total_count += counts[q];
+    for (int q = 0; q < kW; ++q) {
+      if (q < world) {
+        gn[q] = LoadCell(local + static_cast<long long>(q) * c.slot_floats + 2 * channels);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < kW; ++q) {
+      if (q < world) {
+        if (CellEpoch(gn[q]) != epoch) {
+          gn[q] = AwaitCell(local + static_cast<long long>(q) * c.slot_floats + 2 * channels,
+                            epoch, q, dead, c.status);
+        }
+        counts[q] = static_cast<double>(CellValue(gn[q]));
+        total_count += counts[q];
+      }
     }
   }
   const double inv_total = total_count > 0.0 ? 1.0 / total_count : 0.0;

@@ -21,7 +21,7 @@ void InitTuningOnce() {
         /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1, /*BnStatsPipe*/ 4,
         /*BnApplyDeep*/ 1, /*BnPdl*/ 1, /*BnL2KeepMb*/ 64, /*RowNormPacks*/ 0,
         /*reserved*/ 0, /*BnStatsMaxTx*/ 16, /*BnL2KeepPartial*/ 1,
-        /*BnStatsDropRest*/ 1, /*BnApplyDropAll*/ 1, /*BnApplyEarlyLoads*/ 1,
+        /*BnStatsDropRest*/ 1, /*BnApplyDropAll*/ 0, /*BnApplyEarlyLoads*/ 1,
         /*BnFinalizeLanes*/ 128, /*BnApplyCtasPerSm*/ 0, /*BnInterleave*/ 1};
     for (int i = 0; i < kTuneCount; ++i) g_tuning[i].store(defaults[i]);
   });
