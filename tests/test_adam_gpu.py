@@ -315,3 +315,66 @@ def test_sharded_adam_takes_16bit_gradients(kernel_lib, gdtype):
                                            h["lr"], h["beta1"], h["beta2"], h["epsilon"],
                                            to_torch(grad)[lo:hi])
     assert torch.equal(a, wv)
+
+
+@pytest.mark.parametrize("chunks", [1, 2, 8])
+def test_sharded_copy_engine_transport_on_one_gpu(kernel_lib, chunks):
+    """LaunchAdamShardCopyFloat with 4 "replicas" that all live on this GPU:
+    the local range is updated chunk by chunk and copy engines carry every
+    finished chunk into the other copies; after the 4 shards' calls every copy
+    equals the un-sharded update, bit for bit, and the caller's stream has
+    joined the side streams (a plain synchronize of that stream is enough)."""
+    import ctypes
+    from tensorflow_musa_extension_b200.cross_replica import aligned_shard_range
+    n, world = 300_003, 4
+    rng, var, m, v = adam_inputs(22, n)
+    g = rng.normal(0, 1e-3, n).astype(np.float32)
+    want = [to_torch(t) for t in (var, m, v)]
+    raw_ops.ResourceApplyAdam(*want, *_step_args(), to_torch(g))
+    copies = [to_torch(var) for _ in range(world)]
+    tm, tvv, tg = to_torch(m), to_torch(v), to_torch(g)
+    ptrs = (ctypes.c_void_p * world)(*[c_.data_ptr() for c_ in copies])
+    alpha = raw_ops._adam_alpha(*[float(np.float32(H[k])) for k in
+                                  ("lr", "beta1_power", "beta2_power")])
+    stream = torch.cuda.Stream()
+    pipes = [kernel_lib.MusaShardPipeCreate(world, r) for r in range(world)]
+    assert all(pipes)
+    with torch.cuda.stream(stream):
+        stream.wait_stream(torch.cuda.default_stream())
+        for r in range(world):
+            lo, hi = aligned_shard_range(n, world, r)
+            rc = kernel_lib.LaunchAdamShardCopyFloat(
+                pipes[r], ptrs, lo, tm[lo:hi].data_ptr(), tvv[lo:hi].data_ptr(),
+                tg[lo:hi].data_ptr(), float(np.float32(H["beta1"])),
+                float(np.float32(H["beta2"])), float(np.float32(H["epsilon"])), alpha, hi - lo,
+                chunks, stream.cuda_stream)
+            assert rc == 0
+    stream.synchronize()
+    for c_ in copies:
+        assert torch.equal(c_, want[0])
+    assert torch.equal(tm, want[1]) and torch.equal(tvv, want[2])
+    for p in pipes:
+        kernel_lib.MusaShardPipeDestroy(p)
+    assert kernel_lib.MusaShardPipeCreate(0, 0) is None
+    assert kernel_lib.MusaShardPipeCreate(4, 4) is None
+
+
+def test_multicast_transport_refuses_what_it_cannot_run(kernel_lib):
+    """LaunchAdamShardMulticastFloat needs whole 128-bit packs (range start on
+    a pack, aligned pointers) and both addresses; anything else is refused
+    before a kernel is launched.  (The transport itself needs two GPUs behind
+    one NVSwitch: `bench.py --gpus N --adam-multicast` checks it against the
+    oracle.)"""
+    t = torch.zeros(64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    args = (0.9, 0.999, 1e-7, 1e-3)
+    f = kernel_lib.LaunchAdamShardMulticastFloat
+    assert f(t.data_ptr(), None, 0, t.data_ptr(), t.data_ptr(), t.data_ptr(), *args, 16, st) == -1
+    assert f(t.data_ptr(), t.data_ptr(), 2, t.data_ptr(), t.data_ptr(), t.data_ptr(), *args, 16,
+             st) == -1
+    assert f(t.data_ptr(), t.data_ptr(), 0, t.data_ptr() + 4, t.data_ptr(), t.data_ptr(), *args,
+             16, st) == -1
+    assert f(t.data_ptr(), t.data_ptr(), 0, t.data_ptr(), t.data_ptr(), t.data_ptr(), *args, 0,
+             st) == 0
+    torch.cuda.synchronize()
+    assert not t.any()
