@@ -17,12 +17,13 @@ void InitTuningOnce() {
   std::call_once(g_tuning_once, [] {
     static const int defaults[kTuneCount] = {
         /*AdamCtasPerSm*/ 0, /*AdamUnroll*/ 2, /*BiasActCtasPerSm*/ 0,
-        /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 0, /*BnFused*/ 0,
+        /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 0, /*reserved*/ 0,
         /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1, /*BnStatsPipe*/ 4,
         /*BnApplyDeep*/ 1, /*BnPdl*/ 1, /*BnL2KeepMb*/ 64, /*RowNormPacks*/ 0,
         /*reserved*/ 0, /*BnStatsMaxTx*/ 16, /*BnL2KeepPartial*/ 1,
         /*BnStatsDropRest*/ 1, /*BnApplyDropAll*/ 0, /*BnApplyEarlyLoads*/ 1,
-        /*BnFinalizeLanes*/ 128, /*BnApplyCtasPerSm*/ 0, /*BnInterleave*/ 1};
+        /*BnFinalizeLanes*/ 128, /*BnApplyCtasPerSm*/ 0, /*BnInterleave*/ 1,
+        /*BnApplyMaxTx*/ 16};
     for (int i = 0; i < kTuneCount; ++i) g_tuning[i].store(defaults[i]);
   });
 }

@@ -28,6 +28,7 @@ enum TuningKey {
   kTuneBnFinalizeLanes = 19,  // partial lanes per CTA of the finalize kernel: 32 or 128
   kTuneBnApplyCtasPerSm = 20,  // CTAs per SM of the element-wise grids; 0: what fits
   kTuneBnInterleave = 21,   // 1: CTAs take row tiles round-robin instead of one contiguous range
+  kTuneBnApplyMaxTx = 22,   // channel packs per column block of the element-wise kernel; 0: the row
   kTuneCount = 24
 };
 

@@ -246,7 +246,7 @@ def test_host_buffers_round_trip(kernel_lib):
 def test_dirty_workspace_and_launch_shapes(kernel_lib, dtype, rows, c):
     """The workspace arrives with arbitrary contents (a framework hands out
     temporary memory as it finds it); the same call twice gives the same bits;
-    column blocks as wide as the row, or 8 packs wide, the 256-thread finalize
+    column blocks as wide as the row, or 8 packs wide (both passes), the 256-thread finalize
     kernel and the other row map (contiguous ranges / interleaved tiles) agree
     with the default shapes to rounding."""
     x, s, o, dy = bn_inputs(300 + rows, (rows, c), dtype, 1.0, 3.0)
@@ -263,7 +263,8 @@ def test_dirty_workspace_and_launch_shapes(kernel_lib, dtype, rows, c):
     check_forward(fwd, want, dtype)
     terms = _rms(dy) * float(np.max(s / np.sqrt(want[4] + EPS)))
     check_grad(grad, wg, dtype, dx_scale=terms)
-    for key, value in ((14, 256), (14, 8), (19, 32), (21, 1 - kernel_lib.MusaKernelsGetTuning(21))):
+    for key, value in ((14, 256), (14, 8), (19, 32), (22, 0), (22, 8),
+                       (21, 1 - kernel_lib.MusaKernelsGetTuning(21))):
         old = kernel_lib.MusaKernelsSetTuning(key, value)
         try:
             fwd3, grad3 = run_both(x, s, o, dy, "NHWC")
