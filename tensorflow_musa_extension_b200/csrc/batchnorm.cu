@@ -399,7 +399,7 @@ __global__ void __launch_bounds__(kThreads)
                       const float* __restrict__ mean,
                       float* __restrict__ partial, int64_t rows, int64_t cv,
                       int64_t channels, int64_t rows_per_cta, float keep_fraction,
-                      bool drop_rest, bool interleave, unsigned* epoch_bump) {
+                      bool drop_rest, bool interleave, unsigned* epoch_bump, int fold) {
   constexpr int kVec = VecWidth<T>::value;
   using P = Pack<T, kVec>;
   GridDepWait();
@@ -616,17 +616,54 @@ __global__ void __launch_bounds__(kThreads)
     }
     __syncthreads();
     const int n_out = 2 * kVec * TX;
-    for (int o = tid; o < n_out; o += kThreads) {
-      const int otx = o % TX;
-      const int se = o / TX;
-      float acc = 0.0f;
-      for (int j = 0; j < TY; ++j) acc += red[(se * TY + j) * TX + otx];
-      const int64_t ocol = static_cast<int64_t>(blockIdx.x) * TX + otx;
-      if (ocol < cv) {
-        const int sidx = se / kVec, e = se % kVec;
-        partial[(static_cast<int64_t>(blockIdx.y) * 2 + sidx) * channels +
-                ocol * kVec + e] = acc;
+    if (fold <= 1) {
+      for (int o = tid; o < n_out; o += kThreads) {
+        const int otx = o % TX;
+        const int se = o / TX;
+        float acc = 0.0f;
+        for (int j = 0; j < TY; ++j) acc += red[(se * TY + j) * TX + otx];
+        const int64_t ocol = static_cast<int64_t>(blockIdx.x) * TX + otx;
+        if (ocol < cv) {
+          const int sidx = se / kVec, e = se % kVec;
+          partial[(static_cast<int64_t>(blockIdx.y) * 2 + sidx) * channels +
+                  ocol * kVec + e] = acc;
+        }
       }
+    } else {
+      // The launch put `fold` CTAs that are neighbours along y into one
+      // cluster: their partial rows are added through distributed shared
+      // memory (CTA r of the cluster adds its share of the columns, in CTA
+      // order) and ONE row per cluster goes to memory, so few enough rows are
+      // left for the element-wise kernel to add them itself.
+      float* crow = red + 2 * kVec * kThreads;
+      for (int o = tid; o < n_out; o += kThreads) {
+        const int otx = o % TX;
+        const int se = o / TX;
+        float acc = 0.0f;
+        for (int j = 0; j < TY; ++j) acc += red[(se * TY + j) * TX + otx];
+        crow[o] = acc;
+      }
+      ClusterSync();
+      const int rank = static_cast<int>(ClusterCtaRank());
+      const int chunk = (n_out + fold - 1) / fold;
+      for (int t = tid; t < chunk; t += kThreads) {
+        const int o = rank * chunk + t;
+        if (o < n_out) {
+          double acc = 0.0;
+          for (int q = 0; q < fold; ++q) {
+            acc += static_cast<double>(LoadClusterF32(crow + o, static_cast<unsigned>(q)));
+          }
+          const int otx = o % TX;
+          const int se = o / TX;
+          const int64_t ocol = static_cast<int64_t>(blockIdx.x) * TX + otx;
+          if (ocol < cv) {
+            const int sidx = se / kVec, e = se % kVec;
+            partial[(static_cast<int64_t>(blockIdx.y / fold) * 2 + sidx) * channels +
+                    ocol * kVec + e] = static_cast<float>(acc);
+          }
+        }
+      }
+      ClusterSync();   // nobody leaves while a neighbour still reads its row
     }
   } else if (active) {
 #pragma unroll
@@ -1127,6 +1164,16 @@ struct ApplyArgs {
   // Gradient: the first row of CTAs writes dscale / doffset when set.
   float* dscale;
   float* doffset;
+  // The statistics kernel of the same op left `fold_n` partial rows
+  // ([fold_n, 2, C], folded on chip per cluster): every CTA adds the rows of
+  // its own channels in its prologue (fp64, row order) and there is no
+  // finalize kernel.  Forward: shifted sums (shift = first row of x), the
+  // first row of CTAs writes the statistics outputs (stat_out); gradient:
+  // [sum dy, sum dy (x - mean)], `fold_use` tells whether dx uses them
+  // (training) or only dscale / doffset are written.
+  const float* fold_rows;
+  int fold_n;
+  bool fold_use;
 };
 
 template <typename T, int kVec, int kUnroll, int kMode>
@@ -1213,8 +1260,46 @@ __global__ void __launch_bounds__(kThreads)
   // first.
   const bool active = col < cv;
   if (early_loads && active) load_batch(ty, 0);
+  // The shift of the shifted sums (first row of x: an input of the op, like
+  // the early rows).
+  P first_row;
+  if (kMode == kFwd && a.fold_rows != nullptr && active) first_row = LoadKeep(xp);
   GridDepWait();
   GridDepLaunch();
+  // Second level of the reduction when no finalize kernel ran (fold_rows):
+  // the CTA fetches the partial rows of its own channels into shared memory
+  // with one round of 16-byte copies and adds them in fp64, in row order.
+  extern __shared__ __align__(16) float fold_smem[];   // [fold_n][2][TX * kVec]
+  __shared__ double s_tot[2][kThreads];     // TX * kVec <= kThreads (the launcher sees to it)
+  if (a.fold_rows != nullptr) {
+    const int tid = ty * TX + tx;
+    const int nch = TX * kVec;
+    const int64_t c0 = static_cast<int64_t>(blockIdx.x) * nch;
+    const int seg = channels - c0 < nch ? static_cast<int>(channels - c0) : nch;
+    if constexpr (kVec >= 4) {
+      const int per_seg = seg / 4;                       // 16-byte copies per row segment
+      const int copies = a.fold_n * 2 * per_seg;
+      for (int i = tid; i < copies; i += kThreads) {
+        const int r2 = i / per_seg, j = i - r2 * per_seg;
+        CpAsync16(fold_smem + r2 * nch + j * 4,
+                  a.fold_rows + static_cast<int64_t>(r2) * channels + c0 + j * 4);
+      }
+      CpAsyncCommit();
+      CpAsyncWait<0>();
+    }
+    __syncthreads();
+    for (int o = tid; o < 2 * nch; o += kThreads) {
+      const int which = o / nch, ch = o - which * nch;
+      double acc = 0.0;
+      if (ch < seg) {
+        for (int r = 0; r < a.fold_n; ++r) {
+          acc += static_cast<double>(fold_smem[(r * 2 + which) * nch + ch]);
+        }
+      }
+      s_tot[which][ch] = acc;
+    }
+    __syncthreads();
+  }
   if (!active) return;
 
   // 16-bit outputs round to 8 or 11 bits, so the per-channel affine forms are
@@ -1227,7 +1312,17 @@ __global__ void __launch_bounds__(kThreads)
   for (int e = 0; e < kVec; ++e) {
     const int64_t c = col * kVec + e;
     float var_c;
-    if (kMode == kFwd && a.stat_sums != nullptr) {
+    if (kMode == kFwd && a.fold_rows != nullptr) {
+      // Shifted sums (the statistics kernel subtracted the first row).
+      const double K = static_cast<double>(ToF32(first_row.v[e]));
+      const double md = s_tot[0][tx * kVec + e] * a.stat_out.inv_count;
+      const double m = K + md;
+      double v = s_tot[1][tx * kVec + e] * a.stat_out.inv_count - md * md;
+      if (v < 0.0) v = 0.0;
+      mean[e] = static_cast<float>(m);
+      var_c = static_cast<float>(v);
+      if (writer) WriteFwdStats(a.stat_out, c, m, v);
+    } else if (kMode == kFwd && a.stat_sums != nullptr) {
       double m, v;
       if (a.stat_moments) {
         m = static_cast<double>(a.stat_sums[c]);
@@ -1250,7 +1345,16 @@ __global__ void __launch_bounds__(kThreads)
       cb[e] = a.offset[c];
       cc[e] = 0.0f;
     } else {
-      if (a.sums != nullptr) {
+      if (a.fold_rows != nullptr) {
+        const float t1 = static_cast<float>(s_tot[0][tx * kVec + e]);
+        const float t2 = static_cast<float>(s_tot[1][tx * kVec + e]);
+        cb[e] = a.fold_use ? t1 * a.inv_count : 0.0f;
+        cc[e] = a.fold_use ? t2 * inv * inv * a.inv_count : 0.0f;
+        if (writer && a.dscale != nullptr) {
+          a.doffset[c] = t1;
+          a.dscale[c] = t2 * inv;
+        }
+      } else if (a.sums != nullptr) {
         cb[e] = a.sums[c] * a.inv_count;
         cc[e] = a.sums[channels + c] * inv * inv * a.inv_count;
       } else {
@@ -1553,7 +1657,8 @@ inline int DecodeError(int rc) { return rc <= -1000 ? -rc - 1000 : rc; }
 // written, or a negative error.
 template <typename T, int kMode, int kStagesT>
 int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* workspace,
-                    const Geom& g, int64_t cv, unsigned* epoch_bump, cudaStream_t stream) {
+                    const Geom& g, int64_t cv, unsigned* epoch_bump, cudaStream_t stream,
+                    int* fold_io = nullptr) {
   using Cfg = StatsPipe<kMode, kStagesT>;
   auto kernel = BnStatsPipeKernel<T, kMode, kStagesT>;
   static std::atomic<int> resident_by_device[kMaxDevices];
@@ -1590,16 +1695,50 @@ int LaunchStatsPipe(const T* x, const T* dy, const float* mean, float* workspace
     keep_fraction = budget >= bytes ? 1.0f : static_cast<float>(budget / bytes);
     if (GetTuning(kTuneBnL2KeepPartial) == 0 && keep_fraction < 1.0f) keep_fraction = 0.0f;
   }
-  const cudaError_t err = LaunchChained(
-      GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy), dim3(p.tx, p.ty),
+  // Clusters of `fold` CTAs along y add their partial rows on chip (the
+  // caller asked for it and the block has row lanes to fold): grid.y becomes a
+  // multiple of `fold` within what is resident at once, and gy / fold rows are
+  // written.
+  int fold = fold_io != nullptr ? *fold_io : 1;
+  if (fold != 2 && fold != 4 && fold != 8) fold = 1;   // portable cluster sizes
+  if (p.ty == 1) fold = 1;
+  int gy = p.gy;
+  int64_t rows_per_cta = p.rows_per_cta;
+  if (fold > 1) {
+    static std::atomic<int> clusters_by_device[4][kMaxDevices];   // fold 2, 4, 8
+    const int max_clusters = PerDevice(clusters_by_device[fold == 2 ? 0 : fold == 4 ? 1 : 2], [&] {
+      cudaLaunchConfig_t cfg;
+      cudaLaunchAttribute attr[2];
+      ClusterConfig(&cfg, attr, false, fold, dim3(1, fold), dim3(kThreads), Cfg::kSmemBytes,
+                    nullptr);
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+      }
+      return n > 0 ? n : -1;
+    });
+    int64_t per_column = max_clusters > 0 ? max_clusters / p.gx : 0;
+    if (per_column < 1) {
+      fold = 1;
+    } else {
+      int64_t clusters = CeilDiv(static_cast<int64_t>(gy), static_cast<int64_t>(fold));
+      if (clusters > per_column) clusters = per_column;
+      gy = static_cast<int>(clusters) * fold;
+      rows_per_cta = CeilDiv(CeilDiv(g.outer, static_cast<int64_t>(gy)), p.ty) * p.ty;
+    }
+  }
+  if (fold_io != nullptr) *fold_io = fold;
+  const cudaError_t err = LaunchClustered(
+      GetTuning(kTuneBnPdl) != 0, fold, kernel, dim3(p.gx, gy), dim3(p.tx, p.ty),
       Cfg::kSmemBytes, stream, x, dy, mean, workspace, g.outer, cv, g.channels,
-      p.rows_per_cta, keep_fraction, GetTuning(kTuneBnStatsDropRest) != 0,
-      GetTuning(kTuneBnInterleave) != 0, epoch_bump);
+      rows_per_cta, keep_fraction, GetTuning(kTuneBnStatsDropRest) != 0,
+      GetTuning(kTuneBnInterleave) != 0, epoch_bump, fold);
   if (err != cudaSuccess) {
     cudaGetLastError();
     return EncodeCuda(err);
   }
-  return p.gy;
+  return gy / fold;
 }
 
 // Grid of the channel-major kernels: 8 channels per CTA along x, the outer
@@ -1672,9 +1811,15 @@ inline GroupPlan PlanGroups(const Geom& g) {
 // error.
 template <typename T, int kMode>
 int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
-                const Geom& g, unsigned* epoch_bump, cudaStream_t stream) {
+                const Geom& g, unsigned* epoch_bump, cudaStream_t stream,
+                int* fold_io = nullptr) {
   constexpr int kVec = VecWidth<T>::value;
   constexpr int kUnroll = 4;
+  // Only the pipelined channels-last kernel folds partial rows on chip.
+  int fold_none = 1;
+  int* const fold_pipe = fold_io != nullptr ? fold_io : &fold_none;
+  const int fold_wanted = *fold_pipe;
+  *fold_pipe = 1;
   const bool keep = GetTuning(kTuneBnStatsKeep) != 0;
   const bool aligned = Aligned16(x) && (kMode == kFwd || Aligned16(dy));
   if (g.inner == 1) {
@@ -1682,10 +1827,14 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
       const int64_t cv = g.channels / kVec;
       const int stages = GetTuning(kTuneBnStatsPipe);
       if (stages == 3) {
-        return LaunchStatsPipe<T, kMode, 3>(x, dy, mean, partial, g, cv, epoch_bump, stream);
+        *fold_pipe = fold_wanted;
+        return LaunchStatsPipe<T, kMode, 3>(x, dy, mean, partial, g, cv, epoch_bump, stream,
+                                            fold_pipe);
       }
       if (stages != 0) {
-        return LaunchStatsPipe<T, kMode, 4>(x, dy, mean, partial, g, cv, epoch_bump, stream);
+        *fold_pipe = fold_wanted;
+        return LaunchStatsPipe<T, kMode, 4>(x, dy, mean, partial, g, cv, epoch_bump, stream,
+                                            fold_pipe);
       }
       const Plan p = PlanLast(g.outer, g.channels, cv, kUnroll, true, 3);
       BnStatsLastKernel<T, kVec, kUnroll, kMode>
@@ -1785,6 +1934,50 @@ inline int ApplyMaxTx() {
   return t > 0 ? t : kThreads;
 }
 
+// Dynamic shared memory of an element-wise launch that adds `fold_n` partial
+// rows itself, or -1 when its column blocks are wider than a CTA has threads
+// (the prologue gives every channel of the block one thread).
+constexpr int64_t kApplyFoldSmemMax = 64 * 1024;
+template <typename T>
+inline int64_t ApplyFoldBytes(int64_t cv, int fold_n) {
+  constexpr int kVec = VecWidth<T>::value;
+  int tx = Pow2Ceil(cv);
+  if (tx > ApplyMaxTx()) tx = ApplyMaxTx();
+  if (tx * kVec > kThreads) return -1;
+  return static_cast<int64_t>(fold_n) * 2 * tx * kVec * static_cast<int64_t>(sizeof(float));
+}
+
+template <typename T, int kVec, int kU, int kMode>
+void LaunchApplyLast(const T* x, const T* dy, T* out, const ApplyArgs& a, const Geom& g,
+                     int64_t cv, bool reverse, bool last_use, bool early_loads,
+                     cudaStream_t stream) {
+  auto kernel = BnApplyLastKernel<T, kVec, kU, kMode>;
+  static std::atomic<int> resident_by_device[kMaxDevices];
+  int resident = PerDevice(resident_by_device, [&] {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kApplyFoldSmemMax)) != cudaSuccess) {
+      cudaGetLastError();
+    }
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0) !=
+        cudaSuccess) {
+      cudaGetLastError();
+    }
+    return n > 0 ? n : 1;
+  });
+  size_t smem = 0;
+  if (a.fold_rows != nullptr) {
+    smem = static_cast<size_t>(ApplyFoldBytes<T>(cv, a.fold_n));
+    // Shared memory of an SM over a CTA's dynamic + static + reserved bytes.
+    const int by_smem = static_cast<int>(233472 / (smem + 4096 + 1024));
+    if (by_smem < resident) resident = by_smem > 0 ? by_smem : 1;
+  }
+  const Plan p = PlanLast(g.outer, g.channels, cv, kU, false, resident, ApplyMaxTx());
+  LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy), dim3(p.tx, p.ty), smem,
+                stream, x, dy, out, a, g.outer, cv, g.channels, p.rows_per_cta, reverse,
+                last_use, early_loads, GetTuning(kTuneBnInterleave) != 0);
+}
+
 // `early_loads`: the caller launched the statistics kernel of the same op on
 // `stream` just before (see BnApplyLastKernel).
 template <typename T, int kMode>
@@ -1811,43 +2004,14 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
       const int64_t cv = g.channels / kVec;
       // The forward pass has one input stream: twice the rows in flight.
       const bool deep = kMode == kFwd && GetTuning(kTuneBnApplyDeep) != 0;
+      const bool early = early_loads && GetTuning(kTuneBnApplyEarlyLoads) != 0;
       if (deep) {
         constexpr int kDeep = kMode == kFwd ? 8 : kUnroll;
-        auto kernel = BnApplyLastKernel<T, kVec, kDeep, kMode>;
-        static std::atomic<int> resident_by_device[kMaxDevices];
-        const int resident = PerDevice(resident_by_device, [&] {
-          int n = 0;
-          if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0) !=
-              cudaSuccess) {
-            cudaGetLastError();
-          }
-          return n > 0 ? n : 1;
-        });
-        const Plan p = PlanLast(g.outer, g.channels, cv, kDeep, false, resident, ApplyMaxTx());
-        LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
-                      dim3(p.tx, p.ty), 0, stream, x, dy, out, a, g.outer, cv,
-                      g.channels, p.rows_per_cta, reverse, last_use,
-                      early_loads && GetTuning(kTuneBnApplyEarlyLoads) != 0,
-                      GetTuning(kTuneBnInterleave) != 0);
+        LaunchApplyLast<T, kVec, kDeep, kMode>(x, dy, out, a, g, cv, reverse, last_use, early,
+                                               stream);
       } else {
-        auto kernel = BnApplyLastKernel<T, kVec, kUnroll, kMode>;
-        static std::atomic<int> resident_by_device[kMaxDevices];
-        const int resident = PerDevice(resident_by_device, [&] {
-          int n = 0;
-          if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0) !=
-              cudaSuccess) {
-            cudaGetLastError();
-          }
-          return n > 0 ? n : 1;
-        });
-        const Plan p =
-            PlanLast(g.outer, g.channels, cv, kUnroll, false, resident,
-                     ApplyMaxTx());
-        LaunchChained(GetTuning(kTuneBnPdl) != 0, kernel, dim3(p.gx, p.gy),
-                      dim3(p.tx, p.ty), 0, stream, x, dy, out, a, g.outer, cv,
-                      g.channels, p.rows_per_cta, reverse, last_use,
-                      early_loads && GetTuning(kTuneBnApplyEarlyLoads) != 0,
-                      GetTuning(kTuneBnInterleave) != 0);
+        LaunchApplyLast<T, kVec, kUnroll, kMode>(x, dy, out, a, g, cv, reverse, last_use, early,
+                                                 stream);
       }
     } else {
       const Plan p =
@@ -1894,6 +2058,27 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
 
 inline int LastError() { return static_cast<int>(cudaGetLastError()); }
 
+// Whether the op has the geometry in which the element-wise kernel can add
+// the partial rows itself (channels-last whole packs, 16-byte aligned
+// tensors: the vector form of BnApplyLastKernel).
+template <typename T>
+inline bool VectorChain(const Geom& g, const void* x, const void* out, const void* dy) {
+  constexpr int kVec = VecWidth<T>::value;
+  return g.inner == 1 && g.channels % kVec == 0 && Aligned16(x) && Aligned16(out) &&
+         (dy == nullptr || Aligned16(dy));
+}
+// ... and whether it does, given the rows the statistics kernel left: few
+// enough (the tuning table holds the limit) and within the shared memory the
+// element-wise kernel may take.  The finalize kernel costs a kernel boundary
+// and, for wide layers, hundreds of CTAs; a few dozen rows are added faster by
+// every CTA for its own channels.
+template <typename T>
+inline bool ApplyAddsRows(const Geom& g, int rows) {
+  if (rows > GetTuning(kTuneBnApplyAddsRows)) return false;
+  const int64_t bytes = ApplyFoldBytes<T>(g.channels / VecWidth<T>::value, rows);
+  return bytes >= 0 && bytes <= kApplyFoldSmemMax;
+}
+
 template <typename T>
 int FwdTrain(const void* x, const float* scale, const float* offset,
              const float* est_mean, const float* est_var, void* y,
@@ -1937,9 +2122,20 @@ int FwdTrain(const void* x, const float* scale, const float* offset,
   a.mean = saved_mean;
   a.variance = saved_var;
   a.epsilon = epsilon;
-  if (int rc = RunStats<T, kFwd>(xt, nullptr, nullptr, partial, g, f, kTailFwdStats,
-                                 stream)) {
-    return rc;
+  const bool vector_chain = VectorChain<T>(g, x, y, nullptr);
+  int fold = vector_chain ? GetTuning(kTuneBnClusterFold) : 1;
+  const int splits = LaunchStats<T, kFwd>(xt, nullptr, nullptr, partial, g, nullptr, stream,
+                                          &fold);
+  if (splits < 0) return DecodeError(splits);
+  if (vector_chain && ApplyAddsRows<T>(g, splits)) {
+    // The element-wise kernel adds the few rows that are left and writes the
+    // statistics outputs: no finalize kernel.
+    a.fold_rows = partial;
+    a.fold_n = splits;
+    a.stat_out = f;
+  } else {
+    f.splits = splits;
+    LaunchFinalize(kTailFwdStats, f, stream);
   }
   LaunchApply<T, kFwd>(xt, nullptr, static_cast<T*>(y), a, g, stream, true);
   return LastError();
@@ -2005,8 +2201,20 @@ int Grad(const void* dy, const void* x, const float* scale, const float* mean,
   a.epsilon = epsilon;
   a.sums = is_training ? sums : nullptr;
   a.inv_count = static_cast<float>(1.0 / static_cast<double>(g.rows()));
-  if (int rc = RunStats<T, kGrad>(xt, dyt, mean, partial, g, f, kTailGrad, stream)) {
-    return rc;
+  const bool vector_chain = VectorChain<T>(g, x, dx, dy);
+  int fold = vector_chain ? GetTuning(kTuneBnClusterFold) : 1;
+  const int splits = LaunchStats<T, kGrad>(xt, dyt, mean, partial, g, nullptr, stream, &fold);
+  if (splits < 0) return DecodeError(splits);
+  if (vector_chain && ApplyAddsRows<T>(g, splits)) {
+    a.sums = nullptr;
+    a.fold_rows = partial;
+    a.fold_n = splits;
+    a.fold_use = is_training;
+    a.dscale = dscale;
+    a.doffset = doffset;
+  } else {
+    f.splits = splits;
+    LaunchFinalize(kTailGrad, f, stream);
   }
   LaunchApply<T, kGrad>(xt, dyt, static_cast<T*>(dx), a, g, stream, true);
   return LastError();

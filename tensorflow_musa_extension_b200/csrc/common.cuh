@@ -192,6 +192,67 @@ inline cudaError_t LaunchChained(bool programmatic, void (*kernel)(KArgs...),
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Thread-block clusters along grid.y (`cluster_y` CTAs share distributed
+// shared memory; grid.y is a multiple of it).  cluster_y == 1 is a plain
+// launch.
+inline void ClusterConfig(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, bool programmatic,
+                          int cluster_y, dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream) {
+  *cfg = cudaLaunchConfig_t{};
+  cfg->gridDim = grid;
+  cfg->blockDim = block;
+  cfg->dynamicSmemBytes = smem;
+  cfg->stream = stream;
+  int n = 0;
+  if (programmatic) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_y > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = static_cast<unsigned>(cluster_y);
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg->attrs = attr;
+  cfg->numAttrs = n;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t LaunchClustered(bool programmatic, int cluster_y, void (*kernel)(KArgs...),
+                                   dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                   Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[2];
+  ClusterConfig(&cfg, attr, programmatic, cluster_y, grid, block, smem, stream);
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Cluster-wide barrier (all threads of all CTAs of the cluster; a superset of
+// __syncthreads) and a 32-bit load from the shared memory of CTA `rank` of
+// the cluster at the address `local` has in this CTA's window.
+__device__ __forceinline__ void ClusterSync() {
+  asm volatile(
+      "barrier.cluster.arrive.release.aligned;\n"
+      "barrier.cluster.wait.acquire.aligned;" ::
+          : "memory");
+}
+__device__ __forceinline__ unsigned ClusterCtaRank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float LoadClusterF32(const float* local, unsigned rank) {
+  const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(local));
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // One value per device and call site, computed on the first use on that
 // device with that device current (function attributes and occupancy are
 // per-device state, and one process may drive several GPUs).  The table is a

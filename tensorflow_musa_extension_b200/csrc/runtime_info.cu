@@ -17,10 +17,10 @@ void InitTuningOnce() {
   std::call_once(g_tuning_once, [] {
     static const int defaults[kTuneCount] = {
         /*AdamCtasPerSm*/ 0, /*AdamUnroll*/ 2, /*BiasActCtasPerSm*/ 0,
-        /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 0, /*reserved*/ 0,
+        /*BiasActUnroll*/ 4, /*BnCtasPerSm*/ 0, /*BnClusterFold*/ 0,
         /*BnApplyReverse*/ 1, /*BnStatsKeep*/ 1, /*BnStatsPipe*/ 4,
         /*BnApplyDeep*/ 1, /*BnPdl*/ 1, /*BnL2KeepMb*/ 64, /*RowNormPacks*/ 0,
-        /*reserved*/ 0, /*BnStatsMaxTx*/ 16, /*BnL2KeepPartial*/ 1,
+        /*BnApplyAddsRows*/ 64, /*BnStatsMaxTx*/ 16, /*BnL2KeepPartial*/ 1,
         /*BnStatsDropRest*/ 1, /*BnApplyDropAll*/ 0, /*BnApplyEarlyLoads*/ 1,
         /*BnFinalizeLanes*/ 128, /*BnApplyCtasPerSm*/ 0, /*BnInterleave*/ 1,
         /*BnApplyMaxTx*/ 16};

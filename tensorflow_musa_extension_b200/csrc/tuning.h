@@ -11,7 +11,8 @@ enum TuningKey {
   kTuneBiasActCtasPerSm = 2,
   kTuneBiasActUnroll = 3,
   kTuneBnCtasPerSm = 4,     // CTAs per SM of the BatchNorm statistics grids; 0: what fits
-  kTuneReserved5 = 5,
+  kTuneBnClusterFold = 5,   // CTAs per cluster of the stats kernel that fold their partial rows on chip
+                            // (the element-wise kernel adds the rest: no finalize kernel); 0, 1: off
   kTuneBnApplyReverse = 6,  // 1: apply pass walks rows in reverse (L2 reuse)
   kTuneBnStatsKeep = 7,     // 1: stats pass loads with the default L2 policy
   kTuneBnStatsPipe = 8,     // cp.async stages of the stats kernel (3 or 4); 0: register loads
@@ -19,7 +20,8 @@ enum TuningKey {
   kTuneBnPdl = 10,          // 1: BatchNorm kernels use programmatic dependent launch
   kTuneBnL2KeepMb = 11,     // MB of its reads that the stats pass asks L2 to hold back (0: off)
   kTuneRowNormPacks = 12,   // packs per thread of the row kernels: 1 .. 4; 0: chosen per op and row
-  kTuneReserved13 = 13,
+  kTuneBnApplyAddsRows = 13,  // the element-wise kernel adds up to this many partial rows itself (no
+                              // finalize kernel); 0: never
   kTuneBnStatsMaxTx = 14,   // channel packs per column block of the stats kernel; 0: by rule
   kTuneBnL2KeepPartial = 15,  // 1: tensors beyond the budget keep the budget's share
   kTuneBnStatsDropRest = 16,  // 1: rows outside the kept share are read evict-first

@@ -487,3 +487,62 @@ def test_config2_16bit_full_size(kernel_lib, dtype):
     dxs = grad.x_backprop.double().reshape(-1, 256).sum(0).cpu().numpy()
     want_dxs = wg[0].astype(np.float64).sum(0)
     assert float(np.abs(dxs - want_dxs).max()) < 5e-2
+
+
+@pytest.mark.parametrize("fold", [0, 2, 4, 8])
+@pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
+@pytest.mark.parametrize("rows,c", [(2, 8), (33, 64), (1000, 520), (5000, 256), (70000, 128),
+                                    (3000, 2048), (20000, 64), (1200, 4104), (40000, 32)])
+def test_chain_without_finalize_kernel(kernel_lib, fold, dtype, rows, c):
+    """The element-wise kernel adds the partial rows itself when few enough are
+    left (tuning key 13: here any number that fits its shared memory), with
+    and without clusters of the statistics kernel adding theirs on chip first
+    (key 5) - no finalize kernel: training forward with running statistics,
+    training gradient and inference gradient against the oracle, from a
+    workspace with arbitrary contents, the same bits on a second call, and the
+    same numbers (to rounding) as the chain with the finalize kernel."""
+    x, s, o, dy = bn_inputs(900 + rows + c, (rows, c), dtype, 1.0, 3.0)
+    gen = np.random.default_rng(rows + c)
+    rm = gen.standard_normal(c).astype(np.float32)
+    rv = (gen.random(c) + 0.5).astype(np.float32)
+    want = np_ref.fused_batch_norm(x, s, o, rm, rv, epsilon=EPS, exponential_avg_factor=0.25)
+    wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS)
+    wi = np_ref.fused_batch_norm_grad(dy, x, s, rm, rv, EPS, is_training=False)
+    terms = _rms(dy) * float(np.max(s / np.sqrt(want[4] + EPS)))
+
+    def run():
+        tx = to_torch(x)
+        fwd = raw_ops.FusedBatchNormV3(tx, to_torch(s), to_torch(o), to_torch(rm), to_torch(rv),
+                                       epsilon=EPS, exponential_avg_factor=0.25)
+        grad = raw_ops.FusedBatchNormGradV3(to_torch(dy), tx, to_torch(s), fwd.reserve_space_1,
+                                            fwd.reserve_space_2, fwd.reserve_space_3,
+                                            epsilon=EPS)
+        infer = raw_ops.FusedBatchNormGradV3(to_torch(dy), tx, to_torch(s), to_torch(rm),
+                                             to_torch(rv), None, epsilon=EPS, is_training=False)
+        torch.cuda.synchronize()
+        return fwd, grad, infer
+
+    old_rows = kernel_lib.MusaKernelsSetTuning(13, 0)
+    try:
+        base = run()
+    finally:
+        kernel_lib.MusaKernelsSetTuning(13, old_rows)
+    old = kernel_lib.MusaKernelsSetTuning(5, fold)
+    kernel_lib.MusaKernelsSetTuning(13, 4096)
+    try:
+        need = kernel_lib.BnWorkspaceBytes(rows, c, 1)
+        raw_ops._workspace(need, torch.device("cuda", 0)).fill_(0x5A)
+        got = run()
+        again = run()
+    finally:
+        kernel_lib.MusaKernelsSetTuning(5, old)
+        kernel_lib.MusaKernelsSetTuning(13, old_rows)
+    check_forward(got[0], want, dtype)
+    check_grad(got[1], wg, dtype, dx_scale=terms)
+    check_grad(got[2], wi, dtype, dx_scale=terms)
+    for a, b in zip(list(got[0])[:5] + list(got[1])[:3] + list(got[2])[:3],
+                    list(again[0])[:5] + list(again[1])[:3] + list(again[2])[:3]):
+        assert torch.equal(a, b)
+    for a, b in zip(list(got[0])[1:5] + list(got[1])[1:3], list(base[0])[1:5] + list(base[1])[1:3]):
+        a, b = to_numpy(a).astype(np.float64), to_numpy(b).astype(np.float64)
+        assert np.all(np.abs(a - b) <= 1e-5 * np.abs(b) + 1e-5 * max(_rms(b), 1e-12))
