@@ -49,7 +49,7 @@ EPS = 1e-3
 # The whole step: sum over its 318 launches, one single-pass capture per metric with
 # L2 left as the previous kernel left it (profiles/resnet50_bn_step_launch_list.md).
 NCU_TRAFFIC_BYTES = {"bn_grad_apply_bf16_256x56x56x256": 1198591488,
-                     "resnet50_bn_step": 37311032576}
+                     "resnet50_bn_step": 37391728896}
 # One-directional rate of a cudaMemcpyAsync between two B200 of one NVSwitch
 # node, as measured by `bench.py --probe peer_copy` (nominal 900 GB/s).
 PEER_COPY_GBS = 770.0
