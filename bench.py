@@ -344,15 +344,22 @@ def run_ours(args):
             b.force_split = True
             b.exchange = exchange
         sync_kind = "split launch chain on one replica (%s)" % args.force_split
-    # Three kernels per pass (statistics, finalize, element-wise); with the
-    # peer exchange the finalize kernel runs the exchange itself.
-    launches_per_step = sum(b.launches_per_step for b in bns)
-
     if args.profile_step:
         # One eager pass and nothing else: the target of an ncu launch list.
         step()
         finish(torch, dist, world)
         return
+
+    # Kernels per step, counted by the library itself over one eager step
+    # (three per pass - statistics, finalize, element-wise - or two where the
+    # element-wise kernel adds the partial rows itself; a collective-library
+    # exchange adds launches that are not this library's and are not counted).
+    step()
+    torch.cuda.synchronize()
+    launched = lib.MusaKernelsLaunchCount()
+    step()
+    torch.cuda.synchronize()
+    launches_per_step = lib.MusaKernelsLaunchCount() - launched
 
     parity = None
     if world > 1:

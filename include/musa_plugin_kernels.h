@@ -769,14 +769,15 @@ int MusaExchangeSelfTest(int world, int64_t n, float* const* vectors, int rounds
  * every launcher call sits inside an NVTX range named after the launcher (a
  * profiler that injects NVTX shows them; without one the range calls are
  * no-ops) and adds to per-launcher counters: calls, algorithmic bytes (the
- * bytes the op has to move, as in the roofline figures) and host nanoseconds
- * spent inside the call.  The reference traces its allocator and copy paths
+ * bytes the op has to move, as in the roofline figures), host nanoseconds
+ * spent inside the call and the kernel launches it made.  The reference traces its allocator and copy paths
  * only (musa_ext/mu/device/musa_telemetry.h:47-199); no counterpart there. */
 typedef struct MusaLaunchCounter {
   const char* name;   /* launcher family, a static string */
   long long calls;
   long long bytes;
   long long host_ns;
+  long long kernels;  /* kernel launches made inside the calls */
 } MusaLaunchCounter;
 /* Returns the previous state (0 / 1). */
 int MusaKernelsTraceEnable(int on);
@@ -784,6 +785,10 @@ int MusaKernelsTraceEnable(int on);
  * exist). */
 int MusaKernelsTraceSnapshot(MusaLaunchCounter* out, int max_entries);
 void MusaKernelsTraceReset(void);
+/* Kernel launches this library has made since it was loaded (counted whether
+ * tracing is on or not: one relaxed add per launch); the difference around a
+ * region is the number of this library's kernels launched in it. */
+long long MusaKernelsLaunchCount(void);
 
 /* Test and sweep hooks, not part of the reference boundary: launch-shape
  * knobs (grid sizes, pipeline depths, cache hints; csrc/tuning.h lists the

@@ -171,7 +171,8 @@ PROTOTYPES.update({
 # Hooks outside the reference boundary: launch-shape sweeps and tracing.
 class MusaLaunchCounter(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("calls", ctypes.c_longlong),
-                ("bytes", ctypes.c_longlong), ("host_ns", ctypes.c_longlong)]
+                ("bytes", ctypes.c_longlong), ("host_ns", ctypes.c_longlong),
+                ("kernels", ctypes.c_longlong)]
 
 
 PROTOTYPES.update({
@@ -180,17 +181,19 @@ PROTOTYPES.update({
     "MusaKernelsTraceEnable": (c_int, [c_int]),
     "MusaKernelsTraceSnapshot": (c_int, [ctypes.POINTER(MusaLaunchCounter), c_int]),
     "MusaKernelsTraceReset": (None, []),
+    "MusaKernelsLaunchCount": (ctypes.c_longlong, []),
 })
 EXTRA_PROTOTYPES = {}
 
 
 def trace_snapshot(lib):
-    """{launcher: {"calls", "bytes", "host_ns"}} of the tracing counters."""
+    """{launcher: {"calls", "bytes", "host_ns", "kernels"}} of the tracing counters."""
     n = lib.MusaKernelsTraceSnapshot(None, 0)
     buf = (MusaLaunchCounter * max(n, 1))()
     n = lib.MusaKernelsTraceSnapshot(buf, n)
     return {buf[i].name.decode(): {"calls": buf[i].calls, "bytes": buf[i].bytes,
-                                   "host_ns": buf[i].host_ns} for i in range(n)}
+                                   "host_ns": buf[i].host_ns, "kernels": buf[i].kernels}
+            for i in range(n)}
 
 # Entry points of include/musa_plugin_runtime.h that the staging pipeline
 # drives (streams, events, asynchronous copies, the pinned pool).

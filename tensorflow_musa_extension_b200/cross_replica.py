@@ -248,7 +248,6 @@ class SyncBatchNorm:
         self.ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         self._ws_rows = int(max_rows)
         self.global_count = None
-        self.launches_per_step = 6
 
     def _stats(self):
         return (self.batch_mean, self.batch_var, self.saved_mean, self.saved_var)

@@ -136,10 +136,12 @@ void LaunchWithNesterov(StateT* var, StateT* m, StateT* v, const GradT* grad,
     AdamKernel<StateT, GradT, kEpt, kUnroll, true>
         <<<static_cast<unsigned>(blocks), threads, 0, stream>>>(var, m, v, grad,
                                                                p, n);
+    CountKernelLaunch();
   } else {
     AdamKernel<StateT, GradT, kEpt, kUnroll, false>
         <<<static_cast<unsigned>(blocks), threads, 0, stream>>>(var, m, v, grad,
                                                                p, n);
+    CountKernelLaunch();
   }
 }
 

@@ -1841,6 +1841,7 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
           <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
               x, dy, mean, partial, g.outer, cv, g.channels, p.rows_per_cta,
               keep, epoch_bump);
+      CountKernelLaunch();
       return p.gy;
     }
     const Plan p = PlanLast(g.outer, g.channels, g.channels, kUnroll, true, 4);
@@ -1848,6 +1849,7 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
         <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
             x, dy, mean, partial, g.outer, g.channels, g.channels,
             p.rows_per_cta, keep, epoch_bump);
+    CountKernelLaunch();
     return p.gy;
   }
   if (UseChannelGroups<T>(g, aligned) && g.channels / kVec <= 0x7fffffffLL) {
@@ -1857,6 +1859,7 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
            static_cast<size_t>(g.inner) * sizeof(float4), stream>>>(
             x, dy, mean, partial, g.outer, g.channels, static_cast<int>(g.inner), gp.per,
             epoch_bump);
+    CountKernelLaunch();
     return static_cast<int>(gp.gy);
   }
   // [outer, C, inner]: a warp per channel, the outer axis split over grid.y.
@@ -1868,19 +1871,23 @@ int LaunchStats(const T* x, const T* dy, const float* mean, float* partial,
       if constexpr (kVec >= 8) {
         BnStatsPlaneKernel<T, 8, kMode><<<grid, kThreads, 0, stream>>>(
             x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per, epoch_bump);
+        CountKernelLaunch();
       }
       break;
     case 4:
       BnStatsPlaneKernel<T, 4, kMode><<<grid, kThreads, 0, stream>>>(
           x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per, epoch_bump);
+      CountKernelLaunch();
       break;
     case 2:
       BnStatsPlaneKernel<T, 2, kMode><<<grid, kThreads, 0, stream>>>(
           x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per, epoch_bump);
+      CountKernelLaunch();
       break;
     default:
       BnStatsPlaneKernel<T, 1, kMode><<<grid, kThreads, 0, stream>>>(
           x, dy, mean, partial, g.outer, g.channels, g.inner, pp.per, epoch_bump);
+      CountKernelLaunch();
   }
   return static_cast<int>(pp.gy);
 }
@@ -2020,6 +2027,7 @@ void LaunchApply(const T* x, const T* dy, T* out, const ApplyArgs& a,
           <<<dim3(p.gx, p.gy), dim3(p.tx, p.ty), 0, stream>>>(
               x, dy, out, a, g.outer, g.channels, g.channels, p.rows_per_cta,
               reverse, false, false, false);
+      CountKernelLaunch();
     }
     return;
   }
@@ -2293,6 +2301,7 @@ int GradApplyFromSums(const void* dy, const void* x, const float* scale,
       const int grid = static_cast<int>(CeilDiv(g.channels, 256));
       BnGradScalesFromSumsKernel<<<grid, 256, 0, stream>>>(
           sums, variance, epsilon, dscale, doffset, g.channels);
+      CountKernelLaunch();
     }
   }
   a.scale = scale;
@@ -2444,6 +2453,7 @@ void LaunchBesselCorrection(float* data, float factor, int count,
                             cudaStream_t stream) {
   if (count <= 0) return;
   ScaleKernel<<<(count + 255) / 256, 256, 0, stream>>>(data, factor, count);
+  CountKernelLaunch();
 }
 
 void LaunchVarianceToInvStd(const float* variance, float* inv_std,
@@ -2451,6 +2461,7 @@ void LaunchVarianceToInvStd(const float* variance, float* inv_std,
   if (count <= 0) return;
   InvStdKernel<<<(count + 255) / 256, 256, 0, stream>>>(variance, inv_std,
                                                        epsilon, count);
+  CountKernelLaunch();
 }
 
 int LaunchBnStatsSums(int dtype, const void* x, float* sums, int64_t outer,
@@ -2507,6 +2518,7 @@ int FinalizeFromSums(const float* sums, bool moments, double total_count,
   f.exp_avg_factor = exp_avg_factor;
   const int grid = static_cast<int>(CeilDiv(channels, 256));
   BnFinalizeFromSumsKernel<<<grid, 256, 0, stream>>>(f, sums, moments);
+  CountKernelLaunch();
   return LastError();
 }
 
@@ -2663,6 +2675,7 @@ int LaunchBnMergeMoments(const float* gathered, int world, int64_t channels,
   if (!gathered || !merged) return MUSA_KERNELS_EINVAL;
   const int grid = static_cast<int>(CeilDiv(channels, 256));
   BnMergeMomentsKernel<<<grid, 256, 0, stream>>>(gathered, world, channels, merged);
+  CountKernelLaunch();
   return LastError();
 }
 

@@ -350,10 +350,12 @@ int LaunchTyped(const T* x, const T* bias, T* y, int64_t outer,
         GridFor(CeilDiv(n_packs, 256 * 4), GetTuning(kTuneBiasActCtasPerSm));
     BiasActLastKernel<T, kVec, 4, kAct, false>
         <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, 1);
+    CountKernelLaunch();
     const int64_t done = n_packs * kVec;
     if (done < n) {
       BiasActInnerKernel<T, 1, kAct, false><<<1, 256, 0, stream>>>(
           x + done, bias, y + done, n - done, 1, 1);
+      CountKernelLaunch();
     }
     return static_cast<int>(cudaGetLastError());
   }
@@ -368,6 +370,7 @@ int LaunchTyped(const T* x, const T* bias, T* y, int64_t outer,
         const int grid = GridFor(CeilDiv(n_packs, 1024), per_sm);
         BiasActFixedKernel<T, kVec, kAct>
             <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
+        CountKernelLaunch();
         return static_cast<int>(cudaGetLastError());
       }
     }
@@ -375,14 +378,17 @@ int LaunchTyped(const T* x, const T* bias, T* y, int64_t outer,
       const int grid = GridFor(CeilDiv(n_packs, 256 * 2), per_sm);
       BiasActLastKernel<T, kVec, 2, kAct, kHasBias>
           <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
+      CountKernelLaunch();
     } else if (unroll == 8) {
       const int grid = GridFor(CeilDiv(n_packs, 256 * 8), per_sm);
       BiasActLastKernel<T, kVec, 8, kAct, kHasBias>
           <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
+      CountKernelLaunch();
     } else {
       const int grid = GridFor(CeilDiv(n_packs, 256 * 4), per_sm);
       BiasActLastKernel<T, kVec, 4, kAct, kHasBias>
           <<<grid, 256, 0, stream>>>(x, bias, y, n_packs, cv);
+      CountKernelLaunch();
     }
   } else if (inner % kVec == 0 && aligned) {
     // Planes of whole packs: one bias value per pack.
@@ -390,6 +396,7 @@ int LaunchTyped(const T* x, const T* bias, T* y, int64_t outer,
     const int grid = GridFor(CeilDiv(n_packs, 256), 16);
     BiasActInnerKernel<T, kVec, kAct, kHasBias><<<grid, 256, 0, stream>>>(
         x, bias, y, n_packs, inner / kVec, channels);
+    CountKernelLaunch();
   } else if (kHasBias && aligned && inner >= kVec && n >= kVec) {
     // Any other plane length (14x14, 7x7, ...): flat packs that may cross into
     // the next plane once.
@@ -398,11 +405,13 @@ int LaunchTyped(const T* x, const T* bias, T* y, int64_t outer,
     if constexpr (kHasBias) {
       BiasActFlatKernel<T, kVec, kAct><<<grid, 256, 0, stream>>>(x, bias, y, n, inner,
                                                                channels);
+      CountKernelLaunch();
     }
   } else {
     const int grid = GridFor(CeilDiv(n, 256), 16);
     BiasActInnerKernel<T, 1, kAct, kHasBias>
         <<<grid, 256, 0, stream>>>(x, bias, y, n, inner, channels);
+    CountKernelLaunch();
   }
   return static_cast<int>(cudaGetLastError());
 }
@@ -452,10 +461,12 @@ int LaunchBiasAddExact(const void* x, const void* bias, void* y, int64_t outer,
     BiasAddExactKernel<T, true><<<grid, 256, 0, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(bias),
         static_cast<T*>(y), n, inner, channels);
+    CountKernelLaunch();
   } else {
     BiasAddExactKernel<T, false><<<grid, 256, 0, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(bias),
         static_cast<T*>(y), n, inner, channels);
+    CountKernelLaunch();
   }
   return static_cast<int>(cudaGetLastError());
 }

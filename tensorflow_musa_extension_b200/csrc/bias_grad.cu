@@ -634,12 +634,14 @@ int ReluGrad(const void* dy_v, const void* feat_v, void* dx_v, int64_t n,
     if (grid > need) grid = need;
     kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(dy, feat, dx,
                                                                  packs, n);
+    CountKernelLaunch();
   } else {
     int64_t grid = CeilDiv(n, kThreads);
     const int64_t cap = static_cast<int64_t>(SmCount()) * kMaxCtasPerSm;
     if (grid > cap) grid = cap;
     ReluGradKernel<T, 1><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
         dy, feat, dx, n, n);
+    CountKernelLaunch();
   }
   return LastError();
 }

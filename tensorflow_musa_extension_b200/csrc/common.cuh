@@ -9,6 +9,8 @@
 
 #include <atomic>
 
+#include "trace.h"
+
 namespace musa_b200 {
 
 // B200: 148 SMs.  Grids of streaming kernels are sized as a multiple of the SM
@@ -189,6 +191,7 @@ inline cudaError_t LaunchChained(bool programmatic, void (*kernel)(KArgs...),
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = programmatic ? 1 : 0;
+  CountKernelLaunch();
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
@@ -227,6 +230,7 @@ inline cudaError_t LaunchClustered(bool programmatic, int cluster_y, void (*kern
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
   ClusterConfig(&cfg, attr, programmatic, cluster_y, grid, block, smem, stream);
+  CountKernelLaunch();
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

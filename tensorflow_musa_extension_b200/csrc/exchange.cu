@@ -425,6 +425,7 @@ int MusaExchangeSelfTest(int world, int64_t n, float* const* vectors, int rounds
       float* none = nullptr;
       int n32 = static_cast<int>(n);
       void* args[] = {&table, const_cast<float* const**>(&vectors), &none, &n32, &mode};
+      CountKernelLaunch();
       rc = static_cast<int>(cudaLaunchCooperativeKernel(
           reinterpret_cast<void*>(ExchangeSumsKernel), dim3(ctas), dim3(kExchangeThreads),
           args, 0, stream));

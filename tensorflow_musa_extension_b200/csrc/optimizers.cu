@@ -288,6 +288,7 @@ void LaunchStream(const UpdateArgs<Rule>& a, int64_t n, cudaStream_t stream) {
   if (blocks > 0x7fffffffLL) blocks = 0x7fffffffLL;
   StreamUpdateKernel<Rule, kEpt, kUnroll>
       <<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a, n);
+  CountKernelLaunch();
 }
 
 // 128-bit state packs when every pointer allows it (the gradient pack has the
@@ -557,6 +558,7 @@ int GroupedSgdHost(void* const* var_ptrs, const void* const* delta_ptrs,
     g.tile_begin[g.count] = static_cast<int>(tiles);
     GroupedSgdParamKernel<DeltaT>
         <<<static_cast<unsigned>(tiles), kThreads, 0, stream>>>(g);
+    CountKernelLaunch();
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);
   }
@@ -655,6 +657,7 @@ void LaunchGroupedResourceApplyGradientDescentFloat(
   if (num_tensors <= 0 || total_blocks <= 0) return;
   GroupedSgdTableKernel<float><<<total_blocks, kThreads, 0, stream>>>(
       var_ptrs, grad_ptrs, alphas, sizes, block_offsets, num_tensors);
+  CountKernelLaunch();
 }
 void LaunchGroupedResourceApplyGradientDescentFloatBFloat16(
     const uint64_t* var_ptrs, const uint64_t* grad_ptrs, const float* alphas,
@@ -663,6 +666,7 @@ void LaunchGroupedResourceApplyGradientDescentFloatBFloat16(
   if (num_tensors <= 0 || total_blocks <= 0) return;
   GroupedSgdTableKernel<__nv_bfloat16><<<total_blocks, kThreads, 0, stream>>>(
       var_ptrs, grad_ptrs, alphas, sizes, block_offsets, num_tensors);
+  CountKernelLaunch();
 }
 
 int LaunchGroupedGradientDescentHostTable(void* const* var_ptrs,

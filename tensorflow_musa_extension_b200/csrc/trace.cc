@@ -13,12 +13,13 @@
 namespace musa_b200 {
 
 std::atomic<int> g_trace_state{-1};
+std::atomic<long long> g_kernel_launches{0};
 
 namespace {
 constexpr int kMaxSlots = 128;
 struct Slot {
   const char* name;  // string literal of the call site
-  std::atomic<long long> calls, bytes, host_ns;
+  std::atomic<long long> calls, bytes, host_ns, kernels;
 };
 Slot g_slots[kMaxSlots];
 std::atomic<int> g_used{0};
@@ -64,12 +65,16 @@ void LaunchScope::Begin(const char* name, int64_t bytes) {
   }
   g_slots[slot_].calls.fetch_add(1, std::memory_order_relaxed);
   g_slots[slot_].bytes.fetch_add(bytes, std::memory_order_relaxed);
+  launches0_ = g_kernel_launches.load(std::memory_order_relaxed);
   t0_ = NowNs();
 }
 
 void LaunchScope::End() {
   if (slot_ < kMaxSlots) {
     g_slots[slot_].host_ns.fetch_add(NowNs() - t0_, std::memory_order_relaxed);
+    g_slots[slot_].kernels.fetch_add(
+        g_kernel_launches.load(std::memory_order_relaxed) - launches0_,
+        std::memory_order_relaxed);
   }
   nvtxRangePop();
 }
@@ -94,8 +99,13 @@ int MusaKernelsTraceSnapshot(MusaLaunchCounter* out, int max_entries) {
     out[n].calls = g_slots[i].calls.load(std::memory_order_relaxed);
     out[n].bytes = g_slots[i].bytes.load(std::memory_order_relaxed);
     out[n].host_ns = g_slots[i].host_ns.load(std::memory_order_relaxed);
+    out[n].kernels = g_slots[i].kernels.load(std::memory_order_relaxed);
   }
   return n;
+}
+
+long long MusaKernelsLaunchCount(void) {
+  return g_kernel_launches.load(std::memory_order_relaxed);
 }
 
 void MusaKernelsTraceReset(void) {
@@ -104,6 +114,7 @@ void MusaKernelsTraceReset(void) {
     g_slots[i].calls.store(0, std::memory_order_relaxed);
     g_slots[i].bytes.store(0, std::memory_order_relaxed);
     g_slots[i].host_ns.store(0, std::memory_order_relaxed);
+    g_slots[i].kernels.store(0, std::memory_order_relaxed);
   }
 }
 

@@ -1,6 +1,6 @@
 // Optional tracing of the launcher layer: an NVTX range around every launcher
-// call and per-launcher counters (calls, algorithmic bytes, host time spent in
-// the call).  Off by default; MUSA_B200_TRACE=1 in the environment or
+// call and per-launcher counters (calls, kernel launches, algorithmic bytes,
+// host time spent in the call).  Off by default; MUSA_B200_TRACE=1 in the environment or
 // MusaKernelsTraceEnable(1) turns it on.  When it is off a launcher pays one
 // relaxed atomic load.
 //
@@ -22,6 +22,12 @@ inline bool TraceOn() {
   return s > 0 || (s < 0 && TraceInit());
 }
 
+// Kernel launches made by the library since it was loaded (every launch site
+// counts; one relaxed add).  A LaunchScope attributes the launches made while
+// it is open to its launcher (exact as long as one thread launches at a time).
+extern std::atomic<long long> g_kernel_launches;
+inline void CountKernelLaunch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
+
 class LaunchScope {
  public:
   LaunchScope(const char* name, int64_t bytes) : slot_(-1) {
@@ -38,6 +44,7 @@ class LaunchScope {
   void End();
   int slot_;
   int64_t t0_;
+  long long launches0_;
 };
 
 }  // namespace musa_b200

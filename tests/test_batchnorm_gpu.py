@@ -546,3 +546,29 @@ def test_chain_without_finalize_kernel(kernel_lib, fold, dtype, rows, c):
     for a, b in zip(list(got[0])[1:5] + list(got[1])[1:3], list(base[0])[1:5] + list(base[1])[1:3]):
         a, b = to_numpy(a).astype(np.float64), to_numpy(b).astype(np.float64)
         assert np.all(np.abs(a - b) <= 1e-5 * np.abs(b) + 1e-5 * max(_rms(b), 1e-12))
+
+
+def test_tracing_counts_the_kernels_of_a_chain(kernel_lib):
+    """The tracing counters tell how many kernels a launcher call made: three
+    for a BatchNorm pass (statistics, finalize, element-wise), two when the
+    element-wise kernel adds the partial rows itself (few rows are left: a
+    wide or a small layer)."""
+    from tensorflow_musa_extension_b200 import _capi
+    was = kernel_lib.MusaKernelsTraceEnable(1)
+    try:
+        for rows, c, want in ((200000, 64, 3), (4096, 2048, 2)):
+            x, s_, o, dy = bn_inputs(5, (rows, c), "bfloat16", 0.0, 1.0)
+            run_both(x, s_, o, dy, "NHWC")          # per-device set-up happens here
+            torch.cuda.synchronize()
+            kernel_lib.MusaKernelsTraceReset()
+            launched = kernel_lib.MusaKernelsLaunchCount()
+            run_both(x, s_, o, dy, "NHWC")
+            torch.cuda.synchronize()
+            assert kernel_lib.MusaKernelsLaunchCount() - launched == 2 * want
+            snap = _capi.trace_snapshot(kernel_lib)
+            assert snap["LaunchBnFwdTrain"]["calls"] == 1
+            assert snap["LaunchBnFwdTrain"]["kernels"] == want
+            assert snap["LaunchBnGrad"]["kernels"] == want
+    finally:
+        kernel_lib.MusaKernelsTraceEnable(was)
+        kernel_lib.MusaKernelsTraceReset()

@@ -123,6 +123,7 @@ def test_launcher_tracing_counts_calls_and_bytes(kernel_lib):
         assert snap["LaunchBiasAct"]["calls"] == 3 and snap["LaunchBiasAct"]["bytes"] == 0
         assert snap["LaunchRmsNorm"]["calls"] == 1
         assert snap["LaunchBiasAct"]["host_ns"] >= 0
+        assert snap["LaunchBiasAct"]["kernels"] == 0             # empty inputs launch nothing
         kernel_lib.MusaKernelsTraceReset()
         assert _capi.trace_snapshot(kernel_lib)["LaunchBiasAct"]["calls"] == 0
     finally:
