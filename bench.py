@@ -53,6 +53,9 @@ NCU_TRAFFIC_BYTES = {"bn_grad_apply_bf16_256x56x56x256": 1198591488,
 # One-directional rate of a cudaMemcpyAsync between two B200 of one NVSwitch
 # node, as measured by `bench.py --probe peer_copy` (nominal 900 GB/s).
 PEER_COPY_GBS = 770.0
+# HBM3e bandwidth NVIDIA quotes for the part (8 TB/s); fractions against it ride
+# along with the fractions against the measured copy bandwidth.
+NOMINAL_HBM_GBS = 8000.0
 WORKLOAD = "resnet50_bn_train_bf16_b256"
 METRIC = "bn_fwd_grad_throughput"
 UNIT = "Gelem/s"
@@ -681,7 +684,12 @@ def check_multi_gpu_parity(torch, dist, world, rank, dev, exchange, group,
     if exchange is not None:
         adam_ok = True
         n = 1_000_003
-        for want_multicast in ((True, False) if with_multicast else (False,)):
+        # (multicast transport?, gradient dtype): the fp32 op, and the mixed
+        # op (fp32 state, bf16 gradient) through the same fused kernel.
+        variants = [(False, torch.float32), (False, torch.bfloat16)]
+        if with_multicast:
+            variants.insert(0, (True, torch.float32))
+        for want_multicast, gdt in variants:
             arng = np.random.default_rng(31)
             var0 = arng.normal(0, 0.05, n).astype(np.float32)
             pv = cr.PeerVector(group, n, dev, multicast=want_multicast)
@@ -697,14 +705,17 @@ def check_multi_gpu_parity(torch, dist, world, rank, dev, exchange, group,
             ev, em, evv = var0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
             for step in range(1, 4):
                 g = arng.normal(0, 1e-3, n).astype(np.float32)
+                tg = torch.from_numpy(g).to(gdt)
+                g = tg.float().numpy()          # what the kernel sees, widened
                 ev, em, evv = np_ref.apply_adam(ev, em, evv, 0.9 ** step, 0.999 ** step, 1e-3,
                                                 0.9, 0.999, 1e-7, g)
-                opt.step(torch.from_numpy(g).to(dev), 1e-3, 0.9 ** step, 0.999 ** step)
+                opt.step(tg.to(dev), 1e-3, 0.9 ** step, 0.999 ** step)
             torch.cuda.synchronize()
             dist.barrier()
             got = pv.tensor.cpu().numpy().astype(np.float64)
             err = float(np.max(np.abs(got - ev) / (1e-8 + 1e-5 * np.abs(ev))))
-            details["adam_shard_%s_worst_over_tolerance" % opt.transport] = round(err, 4)
+            label = opt.transport + ("" if gdt == torch.float32 else "_bf16_grad")
+            details["adam_shard_%s_worst_over_tolerance" % label] = round(err, 4)
             adam_ok = adam_ok and err <= 1.0
             opt.close()
             dist.barrier()
@@ -910,6 +921,7 @@ def measure_ops(torch, lib, raw_ops, dev, args):
         gbs = algo_bytes / (ms * 1e-3) / 1e9
         ops[name] = {"ms": round(ms, 4), "algorithmic_bytes": algo_bytes,
                      "achieved_gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                     "frac_of_nominal": round(gbs / NOMINAL_HBM_GBS, 4),
                      "gelem_per_s": round(elems / (ms * 1e-3) / 1e9, 2), "note": note}
         if ms_stream is not None:
             # The same launch as one of a run of back-to-back launches (how it
@@ -1093,7 +1105,8 @@ def measure_ops(torch, lib, raw_ops, dev, args):
             "case": "[256,56,56,256] bf16, 3*S = %d bytes per launch" % (3 * s_bytes),
             "achieved": round(achieved, 1), "peak": peak, "peak_kind": peak_kind,
             "unit": "GB/s", "frac": round(achieved / peak, 4), "ms": round(ms, 4),
-            "traffic": None}
+            "frac_of_nominal": round(achieved / NOMINAL_HBM_GBS, 4),
+            "nominal_gbs": NOMINAL_HBM_GBS, "traffic": None}
     roof["ms_back_to_back"] = round(ms_stream, 4)
     roof["frac_back_to_back"] = round(3 * s_bytes / (ms_stream * 1e-3) / 1e9 / peak, 4)
     # The whole op this kernel belongs to (statistics + element-wise pass).

@@ -724,6 +724,18 @@ int LaunchAdamShardBroadcastFloat(float* const* var_replicas, int world, int ran
                                   float beta1, float beta2, float epsilon, float alpha,
                                   int64_t n, cudaStream_t stream);
 
+/* The same step with the gradient in fp32, fp16 or bf16 beside fp32 state:
+ * the range-sharded form of MusaResourceApplyAdamMixed
+ * (musa_ext/kernels/training/musa_applyadam_mixed_op.cc:125-258; arithmetic
+ * and use_nesterov as LaunchApplyAdamMixed_*).  `grad_dtype`: MUSA_DT_F32,
+ * MUSA_DT_F16 or MUSA_DT_BF16 (else MUSA_KERNELS_EUNSUPPORTED).  128-bit path
+ * when lo % 4 == 0, the state pointers are 16-byte aligned and grad is aligned
+ * to four of its elements.  No counterpart in the reference. */
+int LaunchAdamShardBroadcastMixed(int grad_dtype, float* const* var_replicas, int world,
+                                  int rank, int64_t lo, float* m, float* v, const void* grad,
+                                  float beta1, float beta2, float epsilon, float alpha,
+                                  int64_t n, bool use_nesterov, cudaStream_t stream);
+
 /* The same step over an NVSwitch multicast mapping of the replicas' copies
  * (`var_multicast`: the multicast address of the vector's base, e.g. from
  * torch.distributed._symmetric_memory; `var_local`: this replica's own copy):

@@ -159,6 +159,9 @@ PROTOTYPES.update({
     "LaunchAdamShardBroadcastFloat":
         (c_int, [c_vp, c_int, c_int, c_i64, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32,
                  c_i64, c_vp]),
+    "LaunchAdamShardBroadcastMixed":
+        (c_int, [c_int, c_vp, c_int, c_int, c_i64, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32,
+                 c_i64, c_bool, c_vp]),
     "LaunchAdamShardMulticastFloat":
         (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_f32, c_f32, c_f32, c_f32, c_i64, c_vp]),
     "MusaShardPipeCreate": (c_vp, [c_int, c_int]),

@@ -573,8 +573,12 @@ class FusedShardedAdam:
     between the last read of `var` and step() may pass fence_before=False."""
 
     def __init__(self, var, exchange, beta1=0.9, beta2=0.999, epsilon=1e-7,
-                 fence_before=True, transport="auto", chunks=2):
-        """`transport`: "multicast" - the update kernel writes every new weight
+                 fence_before=True, transport="auto", chunks=2, use_nesterov=False):
+        """A gradient of half or bfloat16 beside the float state, or
+        `use_nesterov`, makes it the range-sharded MusaResourceApplyAdamMixed
+        (LaunchAdamShardBroadcastMixed; the "stores" transport only).
+
+        `transport`: "multicast" - the update kernel writes every new weight
         with one multimem.st to the NVSwitch multicast address of the vector
         (needs a PeerVector with `multicast_ptr`; the shard leaves the GPU
         once); "stores" - the update kernel stores every new weight into each
@@ -612,6 +616,10 @@ class FusedShardedAdam:
                 "FusedShardedAdam: transport 'multicast' needs a PeerVector with a multicast "
                 "mapping")
         self.transport = transport
+        self.use_nesterov = bool(use_nesterov)
+        if self.use_nesterov and transport != "stores":
+            raise InvalidArgumentError(
+                "FusedShardedAdam: use_nesterov needs the 'stores' transport")
         self.chunks = max(1, min(8, int(chunks)))
         self._pipe = None
         if transport == "copies" and self.world > 1:
@@ -632,9 +640,22 @@ class FusedShardedAdam:
         alpha = raw_ops._adam_alpha(float(f32(lr)), float(f32(beta1_power)),
                                     float(f32(beta2_power)))
         st = torch.cuda.current_stream().cuda_stream
+        mixed = grad.dtype != torch.float32 or self.use_nesterov
+        if mixed and (grad.dtype not in _DT_CODE or self.transport != "stores"):
+            raise InvalidArgumentError(
+                "FusedShardedAdam: a %s gradient%s needs the 'stores' transport and a float, "
+                "half or bfloat16 gradient" % (grad.dtype, " with use_nesterov"
+                                               if self.use_nesterov else ""))
+        grad = grad.contiguous()
         if self.fence_before and self.exchange is not None and self.world > 1:
             self.exchange.sum_(self._token)  # every replica is done reading var
-        if self.transport == "multicast":
+        if mixed:
+            raw_ops._check(self.lib.LaunchAdamShardBroadcastMixed(
+                _DT_CODE[grad.dtype], self._ptrs, self.world, self.rank, self.lo,
+                self.m.data_ptr(), self.v.data_ptr(), grad.data_ptr(), float(f32(self.beta1)),
+                float(f32(self.beta2)), float(f32(self.epsilon)), alpha, self.hi - self.lo,
+                self.use_nesterov, st), "LaunchAdamShardBroadcastMixed")
+        elif self.transport == "multicast":
             raw_ops._check(self.lib.LaunchAdamShardMulticastFloat(
                 self.var.replica_ptrs[self.rank], self.var.multicast_ptr, self.lo,
                 self.m.data_ptr(), self.v.data_ptr(), grad.data_ptr(), float(f32(self.beta1)),

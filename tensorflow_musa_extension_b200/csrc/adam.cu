@@ -195,14 +195,17 @@ struct Replicas {
   int rank;
 };
 
-template <int kEpt>
+// GradT: the gradient's type (fp32 as ResourceApplyAdam, or fp16 / bf16 beside
+// fp32 state as MusaResourceApplyAdamMixed, which also honours use_nesterov).
+template <typename GradT, int kEpt, bool kNesterov>
 __global__ void __launch_bounds__(256)
     AdamShardBroadcastKernel(Replicas r, int64_t lo, float* __restrict__ m,
-                             float* __restrict__ v, const float* __restrict__ grad,
+                             float* __restrict__ v, const GradT* __restrict__ grad,
                              AdamParams p, int64_t n) {
   GridDepWait();
   GridDepLaunch();
   using SPack = Pack<float, kEpt>;
+  using GPack = Pack<GradT, kEpt>;
   constexpr int kUnroll = 2;
   const int64_t n_packs = n / kEpt;
   const int64_t tile = static_cast<int64_t>(blockDim.x) * kUnroll;
@@ -210,10 +213,11 @@ __global__ void __launch_bounds__(256)
   const SPack* var_p = reinterpret_cast<const SPack*>(r.var[r.rank] + lo);
   SPack* m_p = reinterpret_cast<SPack*>(m);
   SPack* v_p = reinterpret_cast<SPack*>(v);
-  const SPack* g_p = reinterpret_cast<const SPack*>(grad);
+  const GPack* g_p = reinterpret_cast<const GPack*>(grad);
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
     const int64_t base = t * tile + threadIdx.x;
-    SPack pv[kUnroll], pm[kUnroll], pvv[kUnroll], pg[kUnroll];
+    SPack pv[kUnroll], pm[kUnroll], pvv[kUnroll];
+    GPack pg[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
@@ -230,7 +234,7 @@ __global__ void __launch_bounds__(256)
       if (i < n_packs) {
 #pragma unroll
         for (int e = 0; e < kEpt; ++e) {
-          AdamStep<false>(pv[u].v[e], pm[u].v[e], pvv[u].v[e], pg[u].v[e], p);
+          AdamStep<kNesterov>(pv[u].v[e], pm[u].v[e], pvv[u].v[e], ToF32(pg[u].v[e]), p);
         }
         StoreStream(m_p + i, pm[u]);
         StoreStream(v_p + i, pvv[u]);
@@ -247,7 +251,7 @@ __global__ void __launch_bounds__(256)
     const int64_t i = n_packs * kEpt + threadIdx.x;
     if (threadIdx.x < kEpt && i < n) {
       float fvar = r.var[r.rank][lo + i], fm = m[i], fv = v[i];
-      AdamStep<false>(fvar, fm, fv, grad[i], p);
+      AdamStep<kNesterov>(fvar, fm, fv, ToF32(grad[i]), p);
       m[i] = fm;
       v[i] = fv;
       for (int q = 0; q < r.world; ++q) r.var[q][lo + i] = fvar;
@@ -322,6 +326,59 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+template <typename GradT>
+int AdamShardBroadcast(float* const* var_replicas, int world, int rank, int64_t lo, float* m,
+                       float* v, const GradT* grad, float beta1, float beta2, float epsilon,
+                       float alpha, int64_t n, bool nesterov, cudaStream_t stream) {
+  if (var_replicas == nullptr || world < 1 || world > 16 || rank < 0 || rank >= world ||
+      lo < 0 || n < 0) {
+    return MUSA_KERNELS_EINVAL;
+  }
+  MUSA_TRACE("LaunchAdamShardBroadcast", (24 + sizeof(GradT)) * n);
+  if (n == 0) return MUSA_KERNELS_OK;
+  if (m == nullptr || v == nullptr || grad == nullptr) return MUSA_KERNELS_EINVAL;
+  Replicas r{};
+  r.world = world;
+  r.rank = rank;
+  // 128-bit state packs beside a gradient pack of the same four elements.
+  bool vec = (lo % 4 == 0) && Aligned16(m) && Aligned16(v) &&
+             reinterpret_cast<uintptr_t>(grad) % (4 * sizeof(GradT)) == 0;
+  for (int q = 0; q < world; ++q) {
+    if (var_replicas[q] == nullptr) return MUSA_KERNELS_EINVAL;
+    r.var[q] = var_replicas[q];
+    vec = vec && Aligned16(var_replicas[q]);
+  }
+  AdamParams p;
+  p.lr_t = alpha;
+  p.beta1 = beta1;
+  p.one_minus_b1 = 1.0f - beta1;
+  p.beta2 = beta2;
+  p.one_minus_b2 = 1.0f - beta2;
+  p.epsilon = epsilon;
+  const int64_t packs = vec ? n / 4 : n;
+  int64_t blocks = CeilDiv(packs, 256 * 2);
+  if (blocks < 1) blocks = 1;
+  if (blocks > 0x7fffffffLL) blocks = 0x7fffffffLL;
+  const dim3 grid(static_cast<unsigned>(blocks));
+  cudaError_t err;
+  if (vec) {
+    err = nesterov ? LaunchChained(true, AdamShardBroadcastKernel<GradT, 4, true>, grid,
+                                   dim3(256), 0, stream, r, lo, m, v, grad, p, n)
+                   : LaunchChained(true, AdamShardBroadcastKernel<GradT, 4, false>, grid,
+                                   dim3(256), 0, stream, r, lo, m, v, grad, p, n);
+  } else {
+    err = nesterov ? LaunchChained(true, AdamShardBroadcastKernel<GradT, 1, true>, grid,
+                                   dim3(256), 0, stream, r, lo, m, v, grad, p, n)
+                   : LaunchChained(true, AdamShardBroadcastKernel<GradT, 1, false>, grid,
+                                   dim3(256), 0, stream, r, lo, m, v, grad, p, n);
+  }
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return static_cast<int>(err);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace
 }  // namespace musa_b200
 
@@ -361,41 +418,30 @@ int LaunchAdamShardBroadcastFloat(float* const* var_replicas, int world, int ran
                                   int64_t lo, float* m, float* v, const float* grad,
                                   float beta1, float beta2, float epsilon, float alpha,
                                   int64_t n, cudaStream_t stream) {
-  if (var_replicas == nullptr || world < 1 || world > 16 || rank < 0 || rank >= world ||
-      lo < 0 || n < 0) {
-    return MUSA_KERNELS_EINVAL;
+  return AdamShardBroadcast<float>(var_replicas, world, rank, lo, m, v, grad, beta1, beta2,
+                                   epsilon, alpha, n, false, stream);
+}
+
+int LaunchAdamShardBroadcastMixed(int grad_dtype, float* const* var_replicas, int world,
+                                  int rank, int64_t lo, float* m, float* v, const void* grad,
+                                  float beta1, float beta2, float epsilon, float alpha,
+                                  int64_t n, bool use_nesterov, cudaStream_t stream) {
+  switch (grad_dtype) {
+    case MUSA_DT_F32:
+      return AdamShardBroadcast<float>(var_replicas, world, rank, lo, m, v,
+                                       static_cast<const float*>(grad), beta1, beta2, epsilon,
+                                       alpha, n, use_nesterov, stream);
+    case MUSA_DT_F16:
+      return AdamShardBroadcast<__half>(var_replicas, world, rank, lo, m, v,
+                                        static_cast<const __half*>(grad), beta1, beta2, epsilon,
+                                        alpha, n, use_nesterov, stream);
+    case MUSA_DT_BF16:
+      return AdamShardBroadcast<__nv_bfloat16>(var_replicas, world, rank, lo, m, v,
+                                               static_cast<const __nv_bfloat16*>(grad), beta1,
+                                               beta2, epsilon, alpha, n, use_nesterov, stream);
+    default:
+      return MUSA_KERNELS_EUNSUPPORTED;
   }
-  MUSA_TRACE("LaunchAdamShardBroadcast", 28 * n);
-  if (n == 0) return MUSA_KERNELS_OK;
-  if (m == nullptr || v == nullptr || grad == nullptr) return MUSA_KERNELS_EINVAL;
-  Replicas r{};
-  r.world = world;
-  r.rank = rank;
-  bool vec = (lo % 4 == 0) && Aligned16(m) && Aligned16(v) && Aligned16(grad);
-  for (int q = 0; q < world; ++q) {
-    if (var_replicas[q] == nullptr) return MUSA_KERNELS_EINVAL;
-    r.var[q] = var_replicas[q];
-    vec = vec && Aligned16(var_replicas[q]);
-  }
-  AdamParams p;
-  p.lr_t = alpha;
-  p.beta1 = beta1;
-  p.one_minus_b1 = 1.0f - beta1;
-  p.beta2 = beta2;
-  p.one_minus_b2 = 1.0f - beta2;
-  p.epsilon = epsilon;
-  const int64_t packs = vec ? n / 4 : n;
-  int64_t blocks = CeilDiv(packs, 256 * 2);
-  if (blocks < 1) blocks = 1;
-  if (blocks > 0x7fffffffLL) blocks = 0x7fffffffLL;
-  if (vec) {
-    LaunchChained(true, AdamShardBroadcastKernel<4>, dim3(static_cast<unsigned>(blocks)),
-                  dim3(256), 0, stream, r, lo, m, v, grad, p, n);
-  } else {
-    LaunchChained(true, AdamShardBroadcastKernel<1>, dim3(static_cast<unsigned>(blocks)),
-                  dim3(256), 0, stream, r, lo, m, v, grad, p, n);
-  }
-  return static_cast<int>(cudaGetLastError());
 }
 
 int LaunchAdamShardMulticastFloat(float* var_local, float* var_multicast, int64_t lo,

@@ -317,6 +317,82 @@ def test_sharded_adam_takes_16bit_gradients(kernel_lib, gdtype):
     assert torch.equal(a, wv)
 
 
+@pytest.mark.parametrize("nesterov", [False, True])
+@pytest.mark.parametrize("gdtype", ["float32", "float16", "bfloat16"])
+def test_sharded_broadcast_kernel_with_mixed_gradients(kernel_lib, gdtype, nesterov):
+    """LaunchAdamShardBroadcastMixed, 4 "replicas" on this GPU: fp32 state, a
+    gradient of float / half / bfloat16, use_nesterov honoured - after the 4
+    launches every copy equals MusaResourceApplyAdamMixed on the whole vector,
+    bit for bit; an unaligned range start takes the element-wise form."""
+    import ctypes
+    from tensorflow_musa_extension_b200.cross_replica import aligned_shard_range
+    n, world = 400_003, 4
+    rng, var, m, v = adam_inputs(33, n)
+    g = rng.normal(0, 1e-3, n).astype(np_dtype(gdtype))
+    h = ADAM_HYPER
+    want = [to_torch(t) for t in (var, m, v)]
+    raw_ops.MusaResourceApplyAdamMixed(*want, h["beta1_power"], h["beta2_power"], h["lr"],
+                                       h["beta1"], h["beta2"], h["epsilon"], to_torch(g),
+                                       use_nesterov=nesterov)
+    code = {"float32": 0, "float16": 1, "bfloat16": 2}[gdtype]
+    alpha = raw_ops._adam_alpha(*[float(np.float32(h[k])) for k in
+                                  ("lr", "beta1_power", "beta2_power")])
+    st = torch.cuda.current_stream().cuda_stream
+    f32 = lambda k: float(np.float32(h[k]))
+    copies = [to_torch(var) for _ in range(world)]
+    tm, tvv, tg = to_torch(m), to_torch(v), to_torch(g)
+    ptrs = (ctypes.c_void_p * world)(*[c_.data_ptr() for c_ in copies])
+    for r in range(world):
+        lo, hi = aligned_shard_range(n, world, r)
+        assert kernel_lib.LaunchAdamShardBroadcastMixed(
+            code, ptrs, world, r, lo, tm[lo:hi].data_ptr(), tvv[lo:hi].data_ptr(),
+            tg[lo:hi].data_ptr(), f32("beta1"), f32("beta2"), f32("epsilon"), alpha, hi - lo,
+            nesterov, st) == 0
+    torch.cuda.synchronize()
+    for c_ in copies:
+        assert torch.equal(c_, want[0])
+    assert torch.equal(tm, want[1]) and torch.equal(tvv, want[2])
+    one = to_torch(var)
+    ptr1 = (ctypes.c_void_p * 1)(one.data_ptr())
+    tm2, tv2 = to_torch(m), to_torch(v)
+    assert kernel_lib.LaunchAdamShardBroadcastMixed(
+        code, ptr1, 1, 0, 3, tm2[3:1000].data_ptr(), tv2[3:1000].data_ptr(),
+        tg[3:1000].data_ptr(), f32("beta1"), f32("beta2"), f32("epsilon"), alpha, 997,
+        nesterov, st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(one[3:1000], want[0][3:1000]) and np.array_equal(to_numpy(one[:3]), var[:3])
+    assert kernel_lib.LaunchAdamShardBroadcastMixed(
+        7, ptr1, 1, 0, 0, tm2.data_ptr(), tv2.data_ptr(), tg.data_ptr(), 0.9, 0.999, 1e-7,
+        alpha, 16, False, st) == -3
+
+
+def test_fused_sharded_adam_runs_the_mixed_op(kernel_lib):
+    """FusedShardedAdam with a bfloat16 gradient and use_nesterov, one replica:
+    the same bits as MusaResourceApplyAdamMixed; transports that have no mixed
+    form refuse."""
+    from tensorflow_musa_extension_b200 import errors
+    from tensorflow_musa_extension_b200.cross_replica import FusedShardedAdam, PeerVector
+    n = 70_001
+    rng = np.random.default_rng(8)
+    var = rng.normal(0, 0.05, n).astype(np.float32)
+    grad = rng.normal(0, 1e-3, n).astype(NP_BF16)
+    h = ADAM_HYPER
+    pv = PeerVector(None, n, torch.device("cuda", 0))
+    pv.tensor.copy_(to_torch(var))
+    opt = FusedShardedAdam(pv, None, h["beta1"], h["beta2"], h["epsilon"], use_nesterov=True)
+    opt.step(to_torch(grad), h["lr"], h["beta1_power"], h["beta2_power"])
+    wv, wm, wvv = (to_torch(a) for a in (var, np.zeros(n, np.float32), np.zeros(n, np.float32)))
+    raw_ops.MusaResourceApplyAdamMixed(wv, wm, wvv, h["beta1_power"], h["beta2_power"], h["lr"],
+                                       h["beta1"], h["beta2"], h["epsilon"], to_torch(grad),
+                                       use_nesterov=True)
+    torch.cuda.synchronize()
+    assert torch.equal(pv.tensor, wv) and torch.equal(opt.m, wm) and torch.equal(opt.v, wvv)
+    copies = FusedShardedAdam(pv, None, transport="copies")
+    with pytest.raises(errors.InvalidArgumentError):
+        copies.step(to_torch(grad), h["lr"], h["beta1_power"], h["beta2_power"])
+    copies.close()
+
+
 @pytest.mark.parametrize("chunks", [1, 2, 8])
 def test_sharded_copy_engine_transport_on_one_gpu(kernel_lib, chunks):
     """LaunchAdamShardCopyFloat with 4 "replicas" that all live on this GPU:
