@@ -69,14 +69,19 @@ struct Plan {
   int64_t rows_per_cta;
 };
 
+// Channel packs per column block of a channels-last launch.
+inline int PlanTx(int64_t cv, int max_tx) {
+  const int tx = Pow2Ceil(cv);
+  return tx > max_tx ? max_tx : tx;
+}
+
 // Channels-last plan.  `cv` = channel packs per row.
 // `resident`: CTAs of this kernel that fit on one SM; the grid is one full
 // wave of them (a second, partly filled wave would idle SMs at the end).
 inline Plan PlanLast(int64_t rows, int64_t channels, int64_t cv, int unroll,
                      bool cap_by_workspace, int resident, int max_tx = kThreads) {
   Plan p;
-  p.tx = Pow2Ceil(cv);
-  if (p.tx > max_tx) p.tx = max_tx;
+  p.tx = PlanTx(cv, max_tx);
   p.ty = kThreads / p.tx;
   p.gx = static_cast<int>(CeilDiv(cv, p.tx));
   int per_sm = GetTuning(cap_by_workspace ? kTuneBnCtasPerSm : kTuneBnApplyCtasPerSm);
@@ -1948,8 +1953,7 @@ constexpr int64_t kApplyFoldSmemMax = 64 * 1024;
 template <typename T>
 inline int64_t ApplyFoldBytes(int64_t cv, int fold_n) {
   constexpr int kVec = VecWidth<T>::value;
-  int tx = Pow2Ceil(cv);
-  if (tx > ApplyMaxTx()) tx = ApplyMaxTx();
+  const int tx = PlanTx(cv, ApplyMaxTx());   // the column block PlanLast will choose
   if (tx * kVec > kThreads) return -1;
   return static_cast<int64_t>(fold_n) * 2 * tx * kVec * static_cast<int64_t>(sizeof(float));
 }
