@@ -36,6 +36,12 @@ def test_every_op_family_on_the_second_device_of_one_process(kernel_lib):
     x, s, o, dy = bn_inputs(41, (6000, 256), "bfloat16", 1.0, 3.0)
     want = np_ref.fused_batch_norm(x, s, o, epsilon=EPS)
     wg = np_ref.fused_batch_norm_grad(dy, x, s, want[3], want[4], EPS)
+    # A wide layer: the element-wise kernel adds the partial rows itself and
+    # takes more dynamic shared memory than a kernel may without the per-device
+    # function attribute.
+    wx, ws_, wo, wdy = bn_inputs(44, (8000, 1024), "bfloat16", 1.0, 3.0)
+    wide = np_ref.fused_batch_norm(wx, ws_, wo, epsilon=EPS)
+    wide_g = np_ref.fused_batch_norm_grad(wdy, wx, ws_, wide[3], wide[4], EPS)
     rows, n = 512, 1024
     rng = np.random.default_rng(42)
     lx = rng.standard_normal((rows, n)).astype(np.float32)
@@ -68,6 +74,21 @@ def test_every_op_family_on_the_second_device_of_one_process(kernel_lib):
             assert_close(to_numpy(grad.x_backprop), wg[0], rt, rt * _rms(wg[0]), dev + " dx")
             assert_close(to_numpy(grad.scale_backprop), wg[1], 1e-4, 1e-4 * _rms(wg[1]),
                          dev + " dscale")
+            twx = to_torch(wx, dev)
+            wf = raw_ops.FusedBatchNormV3(twx, to_torch(ws_, dev), to_torch(wo, dev),
+                                          torch.empty(0, device=dev),
+                                          torch.empty(0, device=dev), epsilon=EPS)
+            wgr = raw_ops.FusedBatchNormGradV3(to_torch(wdy, dev), twx, to_torch(ws_, dev),
+                                               wf.reserve_space_1, wf.reserve_space_2,
+                                               wf.reserve_space_3, epsilon=EPS)
+            torch.cuda.synchronize()
+            assert_close(to_numpy(wf.y), wide[0], rt, rt * _rms(wide[0]), dev + " wide y")
+            assert_close(to_numpy(wf.reserve_space_2), wide[4], 1e-4, 1e-4 * _rms(wide[4]),
+                         dev + " wide var")
+            assert_close(to_numpy(wgr.x_backprop), wide_g[0], rt, rt * _rms(wide_g[0]),
+                         dev + " wide dx")
+            assert_close(to_numpy(wgr.scale_backprop), wide_g[1], 1e-4, 1e-4 * _rms(wide_g[1]),
+                         dev + " wide dscale")
             ly = raw_ops.MusaLayerNorm(to_torch(lx, dev), to_torch(gam, dev),
                                        to_torch(bet, dev), epsilon=1e-5)
             ly = ly[0] if isinstance(ly, (tuple, list)) else ly
