@@ -102,6 +102,11 @@ inline Plan PlanLast(int64_t rows, int64_t channels, int64_t cv, int unroll,
   p.rows_per_cta = CeilDiv(p.rows_per_cta, p.ty) * p.ty;
   p.gy = static_cast<int>(CeilDiv(rows, p.rows_per_cta));
   if (p.gy < 1) p.gy = 1;
+  // Interleaved row tiles do not need whole row ranges per CTA (the kernels
+  // take the number of row splits from the grid): keep the full wave.
+  if (GetTuning(kTuneBnFullWave) != 0 && GetTuning(kTuneBnInterleave) != 0) {
+    p.gy = static_cast<int>(gy);
+  }
   return p;
 }
 

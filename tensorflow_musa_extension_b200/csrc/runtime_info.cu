@@ -23,7 +23,7 @@ void InitTuningOnce() {
         /*BnApplyAddsRows*/ 64, /*BnStatsMaxTx*/ 16, /*BnL2KeepPartial*/ 1,
         /*BnStatsDropRest*/ 1, /*BnApplyDropAll*/ 0, /*BnApplyEarlyLoads*/ 1,
         /*BnFinalizeLanes*/ 128, /*BnApplyCtasPerSm*/ 0, /*BnInterleave*/ 1,
-        /*BnApplyMaxTx*/ 16};
+        /*BnApplyMaxTx*/ 16, /*BnFullWave*/ 1};
     for (int i = 0; i < kTuneCount; ++i) g_tuning[i].store(defaults[i]);
   });
 }

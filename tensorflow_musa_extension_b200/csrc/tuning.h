@@ -31,6 +31,7 @@ enum TuningKey {
   kTuneBnApplyCtasPerSm = 20,  // CTAs per SM of the element-wise grids; 0: what fits
   kTuneBnInterleave = 21,   // 1: CTAs take row tiles round-robin instead of one contiguous range
   kTuneBnApplyMaxTx = 22,   // channel packs per column block of the element-wise kernel; 0: the row
+  kTuneBnFullWave = 23,     // 1: with interleaved row tiles the grid keeps the full wave (no shrink to whole row ranges)
   kTuneCount = 24
 };
 

@@ -264,7 +264,8 @@ def test_dirty_workspace_and_launch_shapes(kernel_lib, dtype, rows, c):
     terms = _rms(dy) * float(np.max(s / np.sqrt(want[4] + EPS)))
     check_grad(grad, wg, dtype, dx_scale=terms)
     for key, value in ((14, 256), (14, 8), (19, 32), (22, 0), (22, 8),
-                       (21, 1 - kernel_lib.MusaKernelsGetTuning(21))):
+                       (21, 1 - kernel_lib.MusaKernelsGetTuning(21)),
+                       (23, 1 - kernel_lib.MusaKernelsGetTuning(23))):
         old = kernel_lib.MusaKernelsSetTuning(key, value)
         try:
             fwd3, grad3 = run_both(x, s, o, dy, "NHWC")
