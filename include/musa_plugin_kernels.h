@@ -453,6 +453,7 @@ size_t BnWorkspaceBytes(int64_t outer, int64_t channels, int64_t inner);
  *   applied when R == 1), blended with est_mean/est_var by exp_avg_factor when
  *   that is not 1 (est_* may be NULL when it is 1);
  *   saved_mean = mean, saved_var = population variance.
+ * y may be x itself (in place); any other overlap of y with x is not allowed.
  * Replaces muDNN BatchNorm::RunComposite plus the copies and the Bessel
  * fix-up after it (musa_ext/kernels/nn/musa_fused_batchnorm_op.cc:106-171). */
 int LaunchBnFwdTrain_F32(const void* x, const float* scale, const float* offset,

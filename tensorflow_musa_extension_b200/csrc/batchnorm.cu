@@ -2139,7 +2139,10 @@ int FwdTrain(const void* x, const float* scale, const float* offset,
   a.mean = saved_mean;
   a.variance = saved_var;
   a.epsilon = epsilon;
-  const bool vector_chain = VectorChain<T>(g, x, y, nullptr);
+  // (An in-place call, y == x, keeps the finalize kernel: the element-wise
+  // kernel would otherwise re-read the first row of x, the shift of the sums,
+  // while other CTAs already overwrite it.)
+  const bool vector_chain = x != y && VectorChain<T>(g, x, y, nullptr);
   int fold = vector_chain ? GetTuning(kTuneBnClusterFold) : 1;
   const int splits = LaunchStats<T, kFwd>(xt, nullptr, nullptr, partial, g, nullptr, stream,
                                           &fold);

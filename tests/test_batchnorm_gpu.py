@@ -573,3 +573,33 @@ def test_tracing_counts_the_kernels_of_a_chain(kernel_lib):
     finally:
         kernel_lib.MusaKernelsTraceEnable(was)
         kernel_lib.MusaKernelsTraceReset()
+
+
+@pytest.mark.parametrize("rows,c", [(5000, 256), (4096, 2048), (300, 64)])
+def test_forward_in_place(kernel_lib, rows, c):
+    """y may be x itself (every element is read and written by one thread):
+    the same bits as the out-of-place call, statistics included - also for the
+    layers whose element-wise kernel would add the partial rows itself."""
+    x, s_, o, _ = bn_inputs(77 + c, (rows, c), "bfloat16", 1.0, 3.0)
+    st = torch.cuda.current_stream().cuda_stream
+    need = kernel_lib.BnWorkspaceBytes(rows, c, 1)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    ts, to_ = to_torch(s_), to_torch(o)
+
+    def run(tx, ty):
+        stats = [torch.empty(c, device="cuda") for _ in range(4)]
+        assert kernel_lib.LaunchBnFwdTrain_BF16(
+            tx.data_ptr(), ts.data_ptr(), to_.data_ptr(), None, None, ty.data_ptr(),
+            *[t.data_ptr() for t in stats], rows, c, 1, EPS, 1.0, ws.data_ptr(), ws.numel(),
+            st) == 0
+        torch.cuda.synchronize()
+        return stats
+
+    tx = to_torch(x)
+    ty = torch.empty_like(tx)
+    want = run(tx, ty)
+    tz = to_torch(x)
+    got = run(tz, tz)
+    assert torch.equal(tz, ty)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
